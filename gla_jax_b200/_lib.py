@@ -1,0 +1,84 @@
+"""ctypes binding of libgla_b200.so (the C ABI in include/gla_b200.h).
+
+There is no fallback: if the shared library is missing or cannot be loaded, every operator
+of this package raises.  Build it with ``python -m gla_jax_b200.build``.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_int, c_int64, c_size_t, c_void_p
+from pathlib import Path
+
+_LIB_PATH = Path(__file__).resolve().parent / "libgla_b200.so"
+_lib = None
+
+GLA_F32, GLA_BF16 = 0, 1
+IMPL_AUTO, IMPL_FP32_SIMT, IMPL_TCGEN05 = 0, 1, 2
+IMPL_BY_NAME = {"auto": IMPL_AUTO, "fp32": IMPL_FP32_SIMT, "simt": IMPL_FP32_SIMT, "tcgen05": IMPL_TCGEN05}
+
+# name -> (restype, argtypes); must list every symbol include/gla_b200.h declares.
+SIGNATURES = {
+    "gla_status_string": (c_char_p, [c_int]),
+    "gla_version": (c_char_p, []),
+    "gla_last_cuda_error": (c_int, []),
+    "gla_cumsum": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int]),
+    "gla_rnn_scan": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
+                             c_void_p, c_void_p, c_int, c_int, c_int]),
+    "gla_recurrent_fwd": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p,
+                                  c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int]),
+    "gla_recurrent_bwd_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int64, c_int]),
+    "gla_recurrent_bwd": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p,
+                                  c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                  c_void_p, c_void_p, c_int, c_void_p, c_size_t]),
+    "gla_chunk_saved_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_int]),
+    "gla_chunk_fwd_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_int]),
+    "gla_chunk_bwd_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_int]),
+    "gla_chunk_fwd": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p,
+                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t]),
+    "gla_chunk_bwd": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p,
+                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                              c_void_p, c_void_p, c_void_p, c_size_t]),
+    "gla_chunk_local_state": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_int, c_void_p,
+                                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t]),
+    "gla_chunk_local_dstate": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_int, c_void_p,
+                                       c_void_p, c_void_p, c_void_p, c_void_p, c_size_t]),
+    "gla_sp_combine": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int,
+                               c_void_p, c_int, c_int]),
+}
+
+
+class GlaError(RuntimeError):
+    """A non-zero status from libgla_b200.so."""
+
+
+def load() -> ctypes.CDLL:
+    """Load the library once and attach the signatures; raises if it is not built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not _LIB_PATH.exists():
+        raise RuntimeError(
+            f"{_LIB_PATH} not found: the CUDA library is not built (run `python -m gla_jax_b200.build`). "
+            "This package has no CPU or PyTorch fallback.")
+    lib = ctypes.CDLL(str(_LIB_PATH))
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)      # AttributeError here means header and library disagree
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def lib_path() -> Path:
+    return _LIB_PATH
+
+
+def check(status: int, what: str) -> None:
+    """Raise GlaError for a non-zero status, with the library's own message."""
+    if status != 0:
+        lib = load()
+        msg = lib.gla_status_string(status).decode()
+        extra = ""
+        if status == 6:
+            extra = f" (cudaError {lib.gla_last_cuda_error()})"
+        raise GlaError(f"{what}: {msg}{extra}")

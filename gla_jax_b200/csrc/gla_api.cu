@@ -1,0 +1,213 @@
+// C ABI of libgla_b200.so: argument validation and dispatch.  See include/gla_b200.h for
+// the contract of every entry point and the reference operator it replaces.
+#include "gla_common.cuh"
+
+namespace gla {
+
+static thread_local int g_last_cuda_error = 0;
+
+int record_cuda_error(cudaError_t e) {
+  if (e == cudaSuccess) return GLA_OK;
+  g_last_cuda_error = (int)e;
+  return GLA_ERR_LAUNCH;
+}
+
+static int check_dtype(int dt) { return (dt == GLA_F32 || dt == GLA_BF16) ? GLA_OK : GLA_ERR_UNSUPPORTED; }
+
+static int check_chunk_dims(int64_t B, int64_t T, int64_t H, int64_t D, int64_t C, int dtype) {
+  if (B <= 0 || T <= 0 || H <= 0 || D <= 0 || C <= 0) return GLA_ERR_BAD_DIMS;
+  if (T % C != 0 || !is_pow2(C)) return GLA_ERR_BAD_DIMS;
+  if (C < 16 || C > 256 || D < 16 || D > 256 || D % 8 != 0) return GLA_ERR_UNSUPPORTED;
+  return check_dtype(dtype);
+}
+
+// Resolve GLA_IMPL_AUTO; returns a negative status (as -status) if the request is invalid.
+static int resolve_impl(int impl, int64_t D, int64_t C, int dtype) {
+  if (impl == GLA_IMPL_AUTO) return tc_supported(D, C, dtype) ? GLA_IMPL_TCGEN05 : GLA_IMPL_FP32_SIMT;
+  if (impl == GLA_IMPL_TCGEN05) return tc_supported(D, C, dtype) ? GLA_IMPL_TCGEN05 : -GLA_ERR_UNSUPPORTED;
+  if (impl == GLA_IMPL_FP32_SIMT) return GLA_IMPL_FP32_SIMT;
+  return -GLA_ERR_UNSUPPORTED;
+}
+
+}  // namespace gla
+
+using namespace gla;
+
+extern "C" {
+
+const char* gla_status_string(int status) {
+  switch (status) {
+    case GLA_OK: return "ok";
+    case GLA_ERR_NULL_POINTER: return "a required pointer is NULL";
+    case GLA_ERR_BAD_DIMS: return "bad dimensions (sizes must be positive, T a multiple of chunk, chunk a power of two)";
+    case GLA_ERR_UNSUPPORTED: return "unsupported dtype or size for this build";
+    case GLA_ERR_ALIGNMENT: return "pointer not 16-byte aligned";
+    case GLA_ERR_WORKSPACE: return "workspace missing or too small";
+    case GLA_ERR_LAUNCH: return "CUDA launch failed (see gla_last_cuda_error)";
+    case GLA_ERR_NO_DEVICE: return "no usable sm_100 device";
+    case GLA_ERR_TOO_LARGE: return "size beyond a fixed maximum";
+    default: return "unknown status";
+  }
+}
+
+const char* gla_version(void) { return "gla_b200 0.1 (sm_100a)"; }
+
+int gla_last_cuda_error(void) { return g_last_cuda_error; }
+
+int gla_cumsum(void* stream, int64_t N, int64_t T, int64_t D, const void* src, const void* init, void* dst,
+               int reverse, int in_dtype, int out_dtype) {
+  if (!src || !dst) return GLA_ERR_NULL_POINTER;
+  if (N <= 0 || T <= 0 || D <= 0) return GLA_ERR_BAD_DIMS;
+  GLA_TRY(check_dtype(in_dtype));
+  GLA_TRY(check_dtype(out_dtype));
+  return launch_cumsum((cudaStream_t)stream, N, T, D, src, init, dst, reverse, in_dtype == GLA_BF16,
+                       out_dtype == GLA_BF16);
+}
+
+int gla_rnn_scan(void* stream, int64_t batch, int64_t T, int64_t K, int64_t V, const float* log_fgate,
+                 const void* kv, const float* init_log_fgate, const void* init_kv, float* out_log,
+                 void* out_state, int reverse, int last_only, int kv_dtype) {
+  if (!log_fgate || !kv || !out_log || !out_state) return GLA_ERR_NULL_POINTER;
+  if ((init_log_fgate == nullptr) != (init_kv == nullptr)) return GLA_ERR_NULL_POINTER;
+  if (batch <= 0 || T <= 0 || K <= 0 || V <= 0) return GLA_ERR_BAD_DIMS;
+  GLA_TRY(check_dtype(kv_dtype));
+  return launch_rnn_scan((cudaStream_t)stream, batch, T, K, V, log_fgate, kv, init_log_fgate, init_kv, out_log,
+                         out_state, reverse, last_only, kv_dtype == GLA_BF16);
+}
+
+int gla_recurrent_fwd(void* stream, int64_t B, int64_t T, int64_t H, int64_t D, int dtype, const void* hidden_init,
+                      const float* log_fgate, const void* value, const void* key, const void* query,
+                      void* hidden_final, void* out, int out_dtype, int reverse) {
+  if (!hidden_init || !log_fgate || !value || !key || !query || !hidden_final || !out) return GLA_ERR_NULL_POINTER;
+  if (B <= 0 || T <= 0 || H <= 0 || D <= 0) return GLA_ERR_BAD_DIMS;
+  GLA_TRY(check_dtype(dtype));
+  GLA_TRY(check_dtype(out_dtype));
+  return recurrent_fwd((cudaStream_t)stream, B, T, H, D, dtype == GLA_BF16, hidden_init, log_fgate, value, key,
+                       query, hidden_final, out, out_dtype == GLA_BF16, reverse);
+}
+
+size_t gla_recurrent_bwd_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int dtype) {
+  (void)dtype;
+  if (B <= 0 || T <= 0 || H <= 0 || D <= 0) return 0;
+  return recurrent_bwd_ws_bytes(B, T, H, D);
+}
+
+int gla_recurrent_bwd(void* stream, int64_t B, int64_t T, int64_t H, int64_t D, int dtype, const void* hidden_init,
+                      const float* log_fgate, const void* value, const void* key, const void* query,
+                      const void* dhidden_final, const void* dout, int dout_dtype, void* dhidden_init,
+                      float* dlog_fgate, void* dvalue, void* dkey, void* dquery, int reverse, void* workspace,
+                      size_t workspace_bytes) {
+  if (!hidden_init || !log_fgate || !value || !key || !query || !dhidden_final || !dout || !dhidden_init ||
+      !dlog_fgate || !dvalue || !dkey || !dquery)
+    return GLA_ERR_NULL_POINTER;
+  if (B <= 0 || T <= 0 || H <= 0 || D <= 0) return GLA_ERR_BAD_DIMS;
+  GLA_TRY(check_dtype(dtype));
+  GLA_TRY(check_dtype(dout_dtype));
+  if (!workspace || workspace_bytes < recurrent_bwd_ws_bytes(B, T, H, D)) return GLA_ERR_WORKSPACE;
+  if (!aligned16(workspace)) return GLA_ERR_ALIGNMENT;
+  return recurrent_bwd((cudaStream_t)stream, B, T, H, D, dtype == GLA_BF16, hidden_init, log_fgate, value, key,
+                       query, dhidden_final, dout, dout_dtype == GLA_BF16, dhidden_init, dlog_fgate, dvalue, dkey,
+                       dquery, reverse, workspace);
+}
+
+size_t gla_chunk_saved_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t chunk, int dtype, int impl) {
+  if (check_chunk_dims(B, T, H, D, chunk, dtype) != GLA_OK) return 0;
+  int r = resolve_impl(impl, D, chunk, dtype);
+  if (r < 0) return 0;
+  return r == GLA_IMPL_TCGEN05 ? tc_saved_bytes(B, T, H, D, chunk) : simt_saved_bytes(B, T, H, D, chunk);
+}
+size_t gla_chunk_fwd_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t chunk, int dtype, int impl) {
+  if (check_chunk_dims(B, T, H, D, chunk, dtype) != GLA_OK) return 0;
+  int r = resolve_impl(impl, D, chunk, dtype);
+  if (r < 0) return 0;
+  return r == GLA_IMPL_TCGEN05 ? tc_fwd_ws_bytes(B, T, H, D, chunk) : simt_fwd_ws_bytes(B, T, H, D, chunk);
+}
+size_t gla_chunk_bwd_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t chunk, int dtype, int impl) {
+  if (check_chunk_dims(B, T, H, D, chunk, dtype) != GLA_OK) return 0;
+  int r = resolve_impl(impl, D, chunk, dtype);
+  if (r < 0) return 0;
+  return r == GLA_IMPL_TCGEN05 ? tc_bwd_ws_bytes(B, T, H, D, chunk) : simt_bwd_ws_bytes(B, T, H, D, chunk);
+}
+
+int gla_chunk_fwd(void* stream, int64_t B, int64_t T, int64_t H, int64_t D, int64_t chunk, int dtype, int impl,
+                  const void* hidden_init, const float* log_fgate, const void* value, const void* key,
+                  const void* query, void* hidden_final, void* out, void* saved, void* workspace,
+                  size_t workspace_bytes) {
+  if (!hidden_init || !log_fgate || !value || !key || !query || !hidden_final || !out) return GLA_ERR_NULL_POINTER;
+  GLA_TRY(check_chunk_dims(B, T, H, D, chunk, dtype));
+  int r = resolve_impl(impl, D, chunk, dtype);
+  if (r < 0) return -r;
+  const size_t need = r == GLA_IMPL_TCGEN05 ? tc_fwd_ws_bytes(B, T, H, D, chunk) : simt_fwd_ws_bytes(B, T, H, D, chunk);
+  if (!workspace || workspace_bytes < need) return GLA_ERR_WORKSPACE;
+  const void* ptrs[] = {hidden_init, log_fgate, value, key, query, hidden_final, out, saved, workspace};
+  for (const void* p : ptrs)
+    if (p && !aligned16(p)) return GLA_ERR_ALIGNMENT;
+  if (r == GLA_IMPL_TCGEN05)
+    return tc_chunk_fwd((cudaStream_t)stream, B, T, H, D, chunk, hidden_init, log_fgate, value, key, query,
+                        hidden_final, out, saved, workspace, 0, nullptr, nullptr);
+  return simt_chunk_fwd((cudaStream_t)stream, B, T, H, D, chunk, dtype == GLA_BF16, hidden_init, log_fgate, value, key,
+                        query, hidden_final, out, saved, workspace, 0, nullptr, nullptr);
+}
+
+int gla_chunk_bwd(void* stream, int64_t B, int64_t T, int64_t H, int64_t D, int64_t chunk, int dtype, int impl,
+                  const float* log_fgate, const void* value, const void* key, const void* query, const void* saved,
+                  const void* dhidden_final, const void* dout, void* dhidden_init, float* dlog_fgate, void* dvalue,
+                  void* dkey, void* dquery, void* workspace, size_t workspace_bytes) {
+  if (!log_fgate || !value || !key || !query || !saved || !dhidden_final || !dout || !dhidden_init || !dlog_fgate ||
+      !dvalue || !dkey || !dquery)
+    return GLA_ERR_NULL_POINTER;
+  GLA_TRY(check_chunk_dims(B, T, H, D, chunk, dtype));
+  int r = resolve_impl(impl, D, chunk, dtype);
+  if (r < 0) return -r;
+  const size_t need = r == GLA_IMPL_TCGEN05 ? tc_bwd_ws_bytes(B, T, H, D, chunk) : simt_bwd_ws_bytes(B, T, H, D, chunk);
+  if (!workspace || workspace_bytes < need) return GLA_ERR_WORKSPACE;
+  const void* ptrs[] = {log_fgate, value, key, query, saved, dhidden_final, dout, dhidden_init, dlog_fgate,
+                        dvalue, dkey, dquery, workspace};
+  for (const void* p : ptrs)
+    if (!aligned16(p)) return GLA_ERR_ALIGNMENT;
+  if (r == GLA_IMPL_TCGEN05)
+    return tc_chunk_bwd((cudaStream_t)stream, B, T, H, D, chunk, log_fgate, value, key, query, saved, dhidden_final,
+                        dout, dhidden_init, dlog_fgate, dvalue, dkey, dquery, workspace);
+  return simt_chunk_bwd((cudaStream_t)stream, B, T, H, D, chunk, dtype == GLA_BF16, log_fgate, value, key, query, saved,
+                        dhidden_final, dout, dhidden_init, dlog_fgate, dvalue, dkey, dquery, workspace);
+}
+
+int gla_chunk_local_state(void* stream, int64_t B, int64_t T, int64_t H, int64_t D, int64_t chunk, int dtype,
+                          int impl, const float* log_fgate, const void* value, const void* key, float* G_total,
+                          float* S_local, void* workspace, size_t workspace_bytes) {
+  if (!log_fgate || !value || !key || !G_total || !S_local) return GLA_ERR_NULL_POINTER;
+  GLA_TRY(check_chunk_dims(B, T, H, D, chunk, dtype));
+  int r = resolve_impl(impl, D, chunk, dtype);
+  if (r < 0) return -r;
+  const size_t need = r == GLA_IMPL_TCGEN05 ? tc_fwd_ws_bytes(B, T, H, D, chunk) : simt_fwd_ws_bytes(B, T, H, D, chunk);
+  if (!workspace || workspace_bytes < need) return GLA_ERR_WORKSPACE;
+  if (r == GLA_IMPL_TCGEN05)
+    return tc_chunk_fwd((cudaStream_t)stream, B, T, H, D, chunk, nullptr, log_fgate, value, key, nullptr, nullptr,
+                        nullptr, nullptr, workspace, 1, G_total, S_local);
+  return simt_chunk_fwd((cudaStream_t)stream, B, T, H, D, chunk, dtype == GLA_BF16, nullptr, log_fgate, value, key,
+                        nullptr, nullptr, nullptr, nullptr, workspace, 1, G_total, S_local);
+}
+
+int gla_chunk_local_dstate(void* stream, int64_t B, int64_t T, int64_t H, int64_t D, int64_t chunk, int dtype,
+                           int impl, const float* log_fgate, const void* query, const void* dout, float* dS_local,
+                           void* workspace, size_t workspace_bytes) {
+  if (!log_fgate || !query || !dout || !dS_local) return GLA_ERR_NULL_POINTER;
+  GLA_TRY(check_chunk_dims(B, T, H, D, chunk, dtype));
+  (void)impl;   // the fp32 kernels serve every implementation here: two small products and a scan
+  if (!workspace || workspace_bytes < simt_bwd_ws_bytes(B, T, H, D, chunk)) return GLA_ERR_WORKSPACE;
+  return simt_chunk_dstate_only((cudaStream_t)stream, B, T, H, D, chunk, dtype == GLA_BF16, log_fgate, query, dout,
+                                dS_local, workspace);
+}
+
+int gla_sp_combine(void* stream, int64_t R, int64_t rank, int64_t BH, int64_t D, const float* all_G,
+                   const float* all_S, const void* init, int init_dtype, void* result, int result_dtype,
+                   int reverse) {
+  if (!all_G || !all_S || !result) return GLA_ERR_NULL_POINTER;
+  if (R <= 0 || rank < 0 || rank >= R || BH <= 0 || D <= 0) return GLA_ERR_BAD_DIMS;
+  GLA_TRY(check_dtype(init_dtype));
+  GLA_TRY(check_dtype(result_dtype));
+  return launch_sp_combine((cudaStream_t)stream, R, rank, BH, D, all_G, all_S, init, init_dtype == GLA_BF16, result,
+                           result_dtype == GLA_BF16, reverse);
+}
+
+}  // extern "C"

@@ -1,0 +1,109 @@
+// Shared helpers for the GLA kernels (sm_100a).
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include "../../include/gla_b200.h"
+
+namespace gla {
+
+typedef __nv_bfloat16 bf16;
+
+// Element (b, t, h, d) of a dense (B, T, H, D) array.
+__host__ __device__ __forceinline__ int64_t idx_bthd(int64_t b, int64_t t, int64_t h, int64_t d,
+                                                     int64_t T, int64_t H, int64_t D) {
+  return ((b * T + t) * H + h) * D + d;
+}
+
+__device__ __forceinline__ float ld_f(const float* p, int64_t i) { return p[i]; }
+__device__ __forceinline__ float ld_f(const bf16* p, int64_t i) { return __bfloat162float(p[i]); }
+__device__ __forceinline__ void st_f(float* p, int64_t i, float v) { p[i] = v; }
+__device__ __forceinline__ void st_f(bf16* p, int64_t i, float v) { p[i] = __float2bfloat16_rn(v); }
+
+// Typed load/store through a void pointer and a runtime dtype flag (used by the generic
+// fp32 kernels whose operands may be either type).
+__device__ __forceinline__ float ld_any(const void* p, int is_bf16, int64_t i) {
+  return is_bf16 ? __bfloat162float(((const bf16*)p)[i]) : ((const float*)p)[i];
+}
+__device__ __forceinline__ void st_any(void* p, int is_bf16, int64_t i, float v) {
+  if (is_bf16) ((bf16*)p)[i] = __float2bfloat16_rn(v); else ((float*)p)[i] = v;
+}
+
+// Host-side: record and translate launch errors.
+int record_cuda_error(cudaError_t e);   // returns GLA_OK or GLA_ERR_LAUNCH
+#define GLA_CHECK_LAUNCH()                                   \
+  do {                                                       \
+    int _s = ::gla::record_cuda_error(cudaGetLastError());   \
+    if (_s != GLA_OK) return _s;                             \
+  } while (0)
+#define GLA_TRY(expr)                                        \
+  do {                                                       \
+    int _s = (expr);                                         \
+    if (_s != GLA_OK) return _s;                             \
+  } while (0)
+
+static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+static inline bool is_pow2(int64_t x) { return x > 0 && (x & (x - 1)) == 0; }
+static inline bool aligned16(const void* p) { return (((uintptr_t)p) & 15) == 0; }
+
+// ---- internal launchers shared between translation units -------------------------------
+
+// Inclusive cumsum along the middle axis of (N, T, D), fp32 math.
+int launch_cumsum(cudaStream_t st, int64_t N, int64_t T, int64_t D, const void* src, const void* init,
+                  void* dst, int reverse, int in_bf16, int out_bf16);
+
+// Exclusive state scan over chunks: for every (bh): S <- init; for n in order:
+// before[n] = S; S = exp(G[n]) (x) S + X[n].  final = S.  X, before: (BH, N, D, D);
+// G: (BH, N, D); init/final: (BH, D, D).  `before` may alias X (in place).
+int launch_state_scan(cudaStream_t st, int64_t BH, int64_t N, int64_t D, const float* G, const void* X,
+                      int x_bf16, const void* init, int init_bf16, void* before, int before_bf16,
+                      void* final_state, int final_bf16, int reverse);
+
+// fp32 CUDA-core chunk path.
+size_t simt_saved_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t C);
+size_t simt_fwd_ws_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t C);
+size_t simt_bwd_ws_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t C);
+int simt_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, int64_t C, int bf,
+                   const void* hidden_init, const float* g, const void* v, const void* k, const void* q,
+                   void* hidden_final, void* out, void* saved, void* ws, int state_only,
+                   float* G_total, float* S_local);
+int simt_chunk_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, int64_t C, int bf,
+                   const float* g, const void* v, const void* k, const void* q, const void* saved,
+                   const void* dhidden_final, const void* dout, void* dhidden_init, float* dg,
+                   void* dv, void* dk, void* dq, void* ws);
+
+int simt_chunk_dstate_only(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, int64_t C, int bf,
+                           const float* g, const void* q, const void* dout, float* dS_local, void* ws);
+
+// tcgen05 tensor-core chunk path (bf16, D = C = 128).
+bool tc_supported(int64_t D, int64_t C, int dtype);
+size_t tc_saved_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t C);
+size_t tc_fwd_ws_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t C);
+size_t tc_bwd_ws_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t C);
+int tc_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, int64_t C,
+                 const void* hidden_init, const float* g, const void* v, const void* k, const void* q,
+                 void* hidden_final, void* out, void* saved, void* ws, int state_only,
+                 float* G_total, float* S_local);
+int tc_chunk_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, int64_t C,
+                 const float* g, const void* v, const void* k, const void* q, const void* saved,
+                 const void* dhidden_final, const void* dout, void* dhidden_init, float* dg,
+                 void* dv, void* dk, void* dq, void* ws);
+
+}  // namespace gla
+
+namespace gla {
+int launch_rnn_scan(cudaStream_t st, int64_t batch, int64_t T, int64_t K, int64_t V, const float* g,
+                    const void* kv, const float* ig, const void* ikv, float* out_log, void* out_state,
+                    int reverse, int last_only, int kv_bf16);
+int launch_sp_combine(cudaStream_t st, int64_t R, int64_t rank, int64_t BH, int64_t D, const float* all_G,
+                      const float* all_S, const void* init, int init_bf16, void* result, int result_bf16,
+                      int reverse);
+int recurrent_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, int bf, const void* hidden_init,
+                  const float* g, const void* v, const void* k, const void* q, void* hidden_final, void* out,
+                  int out_bf, int reverse);
+size_t recurrent_bwd_ws_bytes(int64_t B, int64_t T, int64_t H, int64_t D);
+int recurrent_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, int bf, const void* hidden_init,
+                  const float* g, const void* v, const void* k, const void* q, const void* dhidden_final,
+                  const void* dout, int do_bf, void* dhidden_init, float* dg, void* dv, void* dk, void* dq,
+                  int reverse, void* ws);
+}  // namespace gla

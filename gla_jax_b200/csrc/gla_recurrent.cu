@@ -1,0 +1,298 @@
+// recurrent_gla forward and backward: the exact step recurrence with the state tile held in
+// registers and never written to memory.
+//
+// Reference: gla.py:50-96 (forward kernel), gla.py:271-360 (backward kernel), gla.py:99-170,
+// 172-269 (wrappers).  The reference tiles the state over (head, key block, value block)
+// programs of one warp each and sums per-block partial outputs afterwards (gla.py:140,166,
+// 210-214,257-259).  Here the state is SLICED along one axis only, so that the reduction
+// each pass needs runs over the axis a thread block holds completely, and no partial sums
+// ever reach memory:
+//
+//   pass      slice axis   per step                                         reduction
+//   FWD       value        S = f (.) S + k (x) v_s                          o_s  = sum_k q S
+//   DQ        key          S = f_s S + k_s v            (recompute)         dq_s = sum_v dO S
+//   DV        value        dS = dC + q (x) dO_s ; dC = f (.) dS  (reverse)  dv_s = sum_k k dS
+//   DK        key          dS = dC + q_s dO     ; dC = f_s dS    (reverse)  dk_s = sum_v v dS
+//
+// A block owns a 16-wide slice and all D entries of the other ("long") axis: 128 threads =
+// 16 slice entries x 8 lanes, each lane holding D/8 state elements; the reduction is three
+// warp shuffles.  Time is processed in blocks of 16 steps staged through shared memory in
+// float32 (gate already exponentiated), with the next block's global loads in flight
+// during the current block's arithmetic.  dlog_fgate follows gla.py:263:
+//   dg = cumsum over the remaining tokens of (q dq - k dk) + sum_v(dS_T * S_T).
+#include "gla_common.cuh"
+
+namespace gla {
+
+constexpr int RB = 16;      // time steps per staged block
+constexpr int RS = 16;      // slice width
+constexpr int RTHREADS = 128;
+
+enum RecMode { REC_FWD = 0, REC_DQ = 1, REC_DV = 2, REC_DK = 3 };
+
+struct RecParams {
+  int64_t B, T, H;
+  int bf, do_bf, out_bf;     // element types: inputs/hidden/grads, dout, out
+  const void* hidden_init;
+  const float* g;
+  const void *v, *k, *q;
+  const void* dhidden_final;
+  const void* dout;
+  void* hidden_final;
+  void* out;
+  void *dq, *dk, *dv, *dhidden_init;
+  float* E;                  // (B,T,H,D) float32: q dq - k dk
+  float* boundary;           // (B,H,D) float32: sum_v dS_T * S_T
+  int time_reversed;         // process tokens from last to first
+};
+
+__device__ __forceinline__ float reduce8(float x) {
+  x += __shfl_xor_sync(0xffffffffu, x, 1);
+  x += __shfl_xor_sync(0xffffffffu, x, 2);
+  x += __shfl_xor_sync(0xffffffffu, x, 4);
+  return x;
+}
+
+// A staged tile source: column window [c0, c0 + W) of a (B,T,H,D) array for one (b, h).
+struct TileSrc {
+  const void* p;
+  int bf;
+  int do_exp;
+};
+
+template <int W, int NPT>
+__device__ __forceinline__ void tile_fetch(float (&r)[NPT], const TileSrc& s, int64_t base, int64_t row_stride,
+                                           int64_t step0, int64_t T, int time_reversed, int c0) {
+#pragma unroll
+  for (int i = 0; i < NPT; ++i) {
+    const int e = threadIdx.x + RTHREADS * i;
+    const int row = e / W, col = e % W;
+    const int64_t sidx = step0 + row;
+    float v = 0.f;
+    if (sidx < T) {
+      const int64_t t = time_reversed ? (T - 1 - sidx) : sidx;
+      v = ld_any(s.p, s.bf, base + t * row_stride + c0 + col);
+    }
+    r[i] = v;
+  }
+}
+template <int W, int NPT>
+__device__ __forceinline__ void tile_commit(float* sm, const float (&r)[NPT], int do_exp) {
+#pragma unroll
+  for (int i = 0; i < NPT; ++i) {
+    const int e = threadIdx.x + RTHREADS * i;
+    sm[e] = do_exp ? expf(r[i]) : r[i];
+  }
+}
+
+template <int D, int MODE>
+__global__ void __launch_bounds__(RTHREADS) rec_kernel(RecParams p) {
+  constexpr int KP = D / 8;                       // state elements per thread
+  constexpr int NL = (MODE == REC_FWD || MODE == REC_DV) ? 3 : 2;   // long tiles
+  constexpr int NS = (MODE == REC_FWD || MODE == REC_DV) ? 1 : 3;   // slice tiles
+  constexpr int LPT = RB * D / RTHREADS;          // long-tile elements per thread
+  constexpr int SPT = RB * RS / RTHREADS;         // slice-tile elements per thread (2)
+  extern __shared__ __align__(16) float smem[];
+  float* Ls[3] = {smem, smem + RB * D, smem + 2 * RB * D};
+  float* Ss[3] = {smem + NL * RB * D, smem + NL * RB * D + RB * RS, smem + NL * RB * D + 2 * RB * RS};
+  float* Rs = smem + NL * RB * D + NS * RB * RS;
+
+  const int lp = threadIdx.x % 8, si = threadIdx.x / 8;
+  const int c0 = blockIdx.x * RS;                 // slice window
+  const int64_t h = blockIdx.y, b = blockIdx.z;
+  const int64_t T = p.T, HD = p.H * D;
+  const int64_t base = (b * T * p.H + h) * D;     // element (b, 0, h, 0)
+  const int64_t hbase = (b * p.H + h) * (int64_t)D * D;
+  const bool bwd_pass = (MODE == REC_DV || MODE == REC_DK);
+  const int trev = p.time_reversed ^ (bwd_pass ? 1 : 0);
+  const bool slice_is_value = (MODE == REC_FWD || MODE == REC_DV);
+
+  // long / slice tile sources per mode
+  TileSrc Lsrc[3], Ssrc[3];
+  if (MODE == REC_FWD) {
+    Lsrc[0] = {p.g, 0, 1}; Lsrc[1] = {p.k, p.bf, 0}; Lsrc[2] = {p.q, p.bf, 0};
+    Ssrc[0] = {p.v, p.bf, 0};
+  } else if (MODE == REC_DQ) {
+    Lsrc[0] = {p.v, p.bf, 0}; Lsrc[1] = {p.dout, p.do_bf, 0};
+    Ssrc[0] = {p.g, 0, 1}; Ssrc[1] = {p.k, p.bf, 0}; Ssrc[2] = {p.q, p.bf, 0};
+  } else if (MODE == REC_DV) {
+    Lsrc[0] = {p.g, 0, 1}; Lsrc[1] = {p.k, p.bf, 0}; Lsrc[2] = {p.q, p.bf, 0};
+    Ssrc[0] = {p.dout, p.do_bf, 0};
+  } else {
+    Lsrc[0] = {p.v, p.bf, 0}; Lsrc[1] = {p.dout, p.do_bf, 0};
+    Ssrc[0] = {p.g, 0, 1}; Ssrc[1] = {p.k, p.bf, 0}; Ssrc[2] = {p.q, p.bf, 0};
+  }
+
+  // state: element (long index L(i), slice index c0 + si); memory layout [key][value]
+  auto long_index = [&](int i) { return 4 * lp + 32 * (i / 4) + (i % 4); };
+  auto state_addr = [&](int i) -> int64_t {
+    const int L = long_index(i);
+    return slice_is_value ? hbase + (int64_t)L * D + (c0 + si) : hbase + (int64_t)(c0 + si) * D + L;
+  };
+  float st[KP];
+  {
+    const void* init = bwd_pass ? p.dhidden_final : p.hidden_init;
+#pragma unroll
+    for (int i = 0; i < KP; ++i) st[i] = init ? ld_any(init, p.bf, state_addr(i)) : 0.f;
+  }
+
+  float lreg[NL][LPT];
+  float sreg[NS][SPT];
+  auto fetch = [&](int64_t step0) {
+#pragma unroll
+    for (int a = 0; a < NL; ++a) tile_fetch<D, LPT>(lreg[a], Lsrc[a], base, HD, step0, T, trev, 0);
+#pragma unroll
+    for (int a = 0; a < NS; ++a) tile_fetch<RS, SPT>(sreg[a], Ssrc[a], base, HD, step0, T, trev, c0);
+  };
+  fetch(0);
+  for (int64_t step0 = 0; step0 < T; step0 += RB) {
+    __syncthreads();   // previous block's readers of the tiles and of Rs are done
+#pragma unroll
+    for (int a = 0; a < NL; ++a) tile_commit<D, LPT>(Ls[a], lreg[a], Lsrc[a].do_exp);
+#pragma unroll
+    for (int a = 0; a < NS; ++a) tile_commit<RS, SPT>(Ss[a], sreg[a], Ssrc[a].do_exp);
+    __syncthreads();
+    if (step0 + RB < T) fetch(step0 + RB);
+    const int nt = (int)((T - step0) < RB ? (T - step0) : RB);
+    for (int tt = 0; tt < nt; ++tt) {
+      float red = 0.f;
+      const float s0 = Ss[0][tt * RS + si];
+      float s1 = 0.f, s2 = 0.f;
+      if (NS == 3) { s1 = Ss[1][tt * RS + si]; s2 = Ss[2][tt * RS + si]; }
+#pragma unroll
+      for (int m = 0; m < KP / 4; ++m) {
+        const int off = tt * D + 32 * m + 4 * lp;
+        const float4 a4 = *reinterpret_cast<const float4*>(Ls[0] + off);
+        const float4 b4 = *reinterpret_cast<const float4*>(Ls[1] + off);
+        float4 c4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (NL == 3) c4 = *reinterpret_cast<const float4*>(Ls[2] + off);
+        const float av[4] = {a4.x, a4.y, a4.z, a4.w};
+        const float bv[4] = {b4.x, b4.y, b4.z, b4.w};
+        const float cv[4] = {c4.x, c4.y, c4.z, c4.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float& S = st[4 * m + j];
+          if (MODE == REC_FWD) {          // a = f, b = k, c = q ; s0 = v
+            S = fmaf(av[j], S, bv[j] * s0);
+            red = fmaf(cv[j], S, red);
+          } else if (MODE == REC_DQ) {    // a = v, b = dO ; s0 = f, s1 = k
+            S = fmaf(s0, S, s1 * av[j]);
+            red = fmaf(bv[j], S, red);
+          } else if (MODE == REC_DV) {    // a = f, b = k, c = q ; s0 = dO
+            const float tmp = fmaf(cv[j], s0, S);
+            red = fmaf(bv[j], tmp, red);
+            S = av[j] * tmp;
+          } else {                        // a = v, b = dO ; s0 = f, s1 = k, s2 = q
+            const float tmp = fmaf(s2, bv[j], S);
+            red = fmaf(av[j], tmp, red);
+            S = s0 * tmp;
+          }
+        }
+      }
+      red = reduce8(red);
+      if (lp == 0) Rs[tt * RS + si] = red;
+    }
+    __syncthreads();
+    // write the block's results: RB x RS values, two per thread
+#pragma unroll
+    for (int i = 0; i < SPT; ++i) {
+      const int e = threadIdx.x + RTHREADS * i;
+      const int row = e / RS, col = e % RS;
+      const int64_t sidx = step0 + row;
+      if (sidx < T) {
+        const int64_t t = trev ? (T - 1 - sidx) : sidx;
+        const int64_t addr = base + t * HD + c0 + col;
+        const float r = Rs[e];
+        if (MODE == REC_FWD) {
+          st_any(p.out, p.out_bf, addr, r);
+        } else if (MODE == REC_DQ) {
+          st_any(p.dq, p.bf, addr, r);
+          p.E[addr] = Ss[2][e] * r;
+        } else if (MODE == REC_DV) {
+          st_any(p.dv, p.bf, addr, r);
+        } else {
+          st_any(p.dk, p.bf, addr, r);
+          p.E[addr] -= Ss[1][e] * r;
+        }
+      }
+    }
+  }
+  // final state
+  if (MODE == REC_FWD) {
+    if (p.hidden_final) {
+#pragma unroll
+      for (int i = 0; i < KP; ++i) st_any(p.hidden_final, p.bf, state_addr(i), st[i]);
+    }
+  } else if (MODE == REC_DQ) {
+    float s = 0.f;
+    if (p.dhidden_final) {
+#pragma unroll
+      for (int i = 0; i < KP; ++i) s = fmaf(ld_any(p.dhidden_final, p.bf, state_addr(i)), st[i], s);
+    }
+    s = reduce8(s);
+    if (lp == 0) p.boundary[(b * p.H + h) * D + c0 + si] = s;
+  } else if (MODE == REC_DV) {
+#pragma unroll
+    for (int i = 0; i < KP; ++i) st_any(p.dhidden_init, p.bf, state_addr(i), st[i]);
+  }
+}
+
+template <int D, int MODE>
+static int launch_rec(cudaStream_t st, const RecParams& p) {
+  constexpr int NL = (MODE == REC_FWD || MODE == REC_DV) ? 3 : 2;
+  constexpr int NS = (MODE == REC_FWD || MODE == REC_DV) ? 1 : 3;
+  const size_t smem = (size_t)(NL * RB * D + NS * RB * RS + RB * RS) * sizeof(float);
+  if (p.H > 65535 || p.B > 65535) return GLA_ERR_TOO_LARGE;
+  cudaError_t e = cudaFuncSetAttribute(rec_kernel<D, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return record_cuda_error(e);
+  dim3 grid(D / RS, (unsigned)p.H, (unsigned)p.B);
+  rec_kernel<D, MODE><<<grid, RTHREADS, smem, st>>>(p);
+  GLA_CHECK_LAUNCH();
+  return GLA_OK;
+}
+
+template <int MODE>
+static int launch_rec_d(cudaStream_t st, int D, const RecParams& p) {
+  switch (D) {
+    case 32: return launch_rec<32, MODE>(st, p);
+    case 64: return launch_rec<64, MODE>(st, p);
+    case 128: return launch_rec<128, MODE>(st, p);
+    case 256: return launch_rec<256, MODE>(st, p);
+    default: return GLA_ERR_UNSUPPORTED;
+  }
+}
+
+int recurrent_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, int bf, const void* hidden_init,
+                  const float* g, const void* v, const void* k, const void* q, void* hidden_final, void* out,
+                  int out_bf, int reverse) {
+  RecParams p{};
+  p.B = B; p.T = T; p.H = H; p.bf = bf; p.out_bf = out_bf;
+  p.hidden_init = hidden_init; p.g = g; p.v = v; p.k = k; p.q = q;
+  p.hidden_final = hidden_final; p.out = out; p.time_reversed = reverse;
+  return launch_rec_d<REC_FWD>(st, (int)D, p);
+}
+
+size_t recurrent_bwd_ws_bytes(int64_t B, int64_t T, int64_t H, int64_t D) {
+  return align_up((size_t)B * T * H * D * 4, 256) + align_up((size_t)B * H * D * 4, 256);
+}
+
+int recurrent_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, int bf, const void* hidden_init,
+                  const float* g, const void* v, const void* k, const void* q, const void* dhidden_final,
+                  const void* dout, int do_bf, void* dhidden_init, float* dg, void* dv, void* dk, void* dq,
+                  int reverse, void* ws) {
+  RecParams p{};
+  p.B = B; p.T = T; p.H = H; p.bf = bf; p.do_bf = do_bf;
+  p.hidden_init = hidden_init; p.g = g; p.v = v; p.k = k; p.q = q;
+  p.dhidden_final = dhidden_final; p.dout = dout;
+  p.dq = dq; p.dk = dk; p.dv = dv; p.dhidden_init = dhidden_init;
+  p.E = (float*)ws;
+  p.boundary = (float*)((char*)ws + align_up((size_t)B * T * H * D * 4, 256));
+  p.time_reversed = reverse;
+  GLA_TRY((launch_rec_d<REC_DQ>(st, (int)D, p)));
+  GLA_TRY((launch_rec_d<REC_DV>(st, (int)D, p)));
+  GLA_TRY((launch_rec_d<REC_DK>(st, (int)D, p)));
+  // dg[t] = sum over the tokens processed at or after t of E, plus the boundary term
+  return launch_cumsum(st, B, T, H * D, p.E, p.boundary, dg, reverse ? 0 : 1, 0, 0);
+}
+
+}  // namespace gla

@@ -1,0 +1,244 @@
+// Memory-bound scan kernels: cumsum along time, the log-space linear-RNN scan, the D x D
+// state scan over chunks and the cross-rank state combine.  All math in float32.
+//
+// Reference operators restated here: ops.py:152-284 (cumsum), ops.py:286-456 (linear-RNN
+// scan).  The reference lowers these to a generic Triton `tt.scan` (ops.py:18-104) and
+// needs a host-side hierarchy for long axes; here a thread block walks the time axis in
+// tiles, scanning within a tile in registers and carrying the running total, so any length
+// is one launch with fully coalesced 128-byte row segments.
+#include "gla_common.cuh"
+
+namespace gla {
+
+// ---------------------------------------------------------------------------------------
+// cumsum: src (N, T, D) -> dst (N, T, D), inclusive along T, + init (N, D).
+// Block = 32 column lanes x 8 row lanes; a tile is 64 rows; each thread scans 8
+// consecutive rows of one column in registers, row lanes are combined through shared memory.
+// ---------------------------------------------------------------------------------------
+constexpr int CS_RPT = 8;    // rows per thread
+constexpr int CS_RL = 8;     // row lanes
+
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256) cumsum_kernel(const TI* __restrict__ src, const TI* __restrict__ init,
+                                                     TO* __restrict__ dst, int64_t T, int64_t D, int reverse) {
+  __shared__ float tot[CS_RL][33];
+  const int64_t n = blockIdx.x;
+  const int tx = threadIdx.x, rl = threadIdx.y;
+  const int64_t c = (int64_t)blockIdx.y * 32 + tx;
+  const bool cvalid = c < D;
+  float carry = (init != nullptr && cvalid) ? ld_f(init, n * D + c) : 0.f;
+  const TI* s = src + n * T * D;
+  TO* o = dst + n * T * D;
+  for (int64_t t0 = 0; t0 < T; t0 += CS_RPT * CS_RL) {
+    float x[CS_RPT];
+#pragma unroll
+    for (int r = 0; r < CS_RPT; ++r) {
+      int64_t tt = t0 + rl * CS_RPT + r;
+      int64_t tp = reverse ? (T - 1 - tt) : tt;
+      x[r] = (cvalid && tt < T) ? ld_f(s, tp * D + c) : 0.f;
+    }
+#pragma unroll
+    for (int r = 1; r < CS_RPT; ++r) x[r] += x[r - 1];
+    tot[rl][tx] = x[CS_RPT - 1];
+    __syncthreads();
+    float off = carry, total = 0.f;
+#pragma unroll
+    for (int r2 = 0; r2 < CS_RL; ++r2) {
+      float v = tot[r2][tx];
+      if (r2 < rl) off += v;
+      total += v;
+    }
+#pragma unroll
+    for (int r = 0; r < CS_RPT; ++r) {
+      int64_t tt = t0 + rl * CS_RPT + r;
+      int64_t tp = reverse ? (T - 1 - tt) : tt;
+      if (cvalid && tt < T) st_f(o, tp * D + c, x[r] + off);
+    }
+    carry += total;
+    __syncthreads();
+  }
+}
+
+int launch_cumsum(cudaStream_t st, int64_t N, int64_t T, int64_t D, const void* src, const void* init,
+                  void* dst, int reverse, int in_bf16, int out_bf16) {
+  if (N <= 0 || T <= 0 || D <= 0) return GLA_ERR_BAD_DIMS;
+  int64_t gy = (D + 31) / 32;
+  if (gy > 65535 || N > 2147483647LL) return GLA_ERR_TOO_LARGE;
+  dim3 grid((unsigned)N, (unsigned)gy), block(32, CS_RL);
+  if (!in_bf16 && !out_bf16)
+    cumsum_kernel<float, float><<<grid, block, 0, st>>>((const float*)src, (const float*)init, (float*)dst, T, D, reverse);
+  else if (!in_bf16 && out_bf16)
+    cumsum_kernel<float, bf16><<<grid, block, 0, st>>>((const float*)src, (const float*)init, (bf16*)dst, T, D, reverse);
+  else if (in_bf16 && !out_bf16)
+    cumsum_kernel<bf16, float><<<grid, block, 0, st>>>((const bf16*)src, (const bf16*)init, (float*)dst, T, D, reverse);
+  else
+    cumsum_kernel<bf16, bf16><<<grid, block, 0, st>>>((const bf16*)src, (const bf16*)init, (bf16*)dst, T, D, reverse);
+  GLA_CHECK_LAUNCH();
+  return GLA_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// rnn_scan: one thread per (k, v) element of the state, v fastest (coalesced), sequential
+// over T.  exp() of the gate is recomputed per element: the kernel is bound by the kv
+// stream (4 or 2 bytes in, the same out, per element and step).
+// ---------------------------------------------------------------------------------------
+template <typename TKV>
+__global__ void __launch_bounds__(256) rnn_scan_kernel(int64_t T, int64_t K, int64_t V, int64_t nblk,
+                                                       const float* __restrict__ g, const TKV* __restrict__ kv,
+                                                       const float* __restrict__ ig, const TKV* __restrict__ ikv,
+                                                       float* __restrict__ out_log, TKV* __restrict__ out_state,
+                                                       int reverse, int last_only) {
+  const int64_t prob = blockIdx.x / nblk;
+  const int64_t e = (blockIdx.x % nblk) * 256 + threadIdx.x;
+  const int64_t KV = K * V;
+  if (e >= KV) return;
+  const int64_t kk = e / V, vv = e % V;
+  float A = ig ? ig[prob * K + kk] : 0.f;
+  float b = ikv ? ld_f(ikv, prob * KV + e) : 0.f;
+  const float* gp = g + prob * T * K + kk;
+  const TKV* xp = kv + prob * T * KV + e;
+  TKV* op = out_state + prob * T * KV + e;
+  float* lp = out_log + prob * T * K + kk;
+#pragma unroll 4
+  for (int64_t s = 0; s < T; ++s) {
+    const int64_t t = reverse ? (T - 1 - s) : s;
+    const float gt = gp[t * K];
+    b = expf(gt) * b + ld_f(xp, t * KV);
+    A += gt;
+    if (!last_only || s == T - 1) {
+      st_f(op, t * KV, b);
+      if (vv == 0) lp[t * K] = A;
+    }
+  }
+}
+
+int launch_rnn_scan(cudaStream_t st, int64_t batch, int64_t T, int64_t K, int64_t V, const float* g,
+                    const void* kv, const float* ig, const void* ikv, float* out_log, void* out_state,
+                    int reverse, int last_only, int kv_bf16) {
+  int64_t nblk = (K * V + 255) / 256;
+  if (nblk * batch > 2147483647LL) return GLA_ERR_TOO_LARGE;
+  dim3 grid((unsigned)(nblk * batch)), block(256);
+  if (kv_bf16)
+    rnn_scan_kernel<bf16><<<grid, block, 0, st>>>(T, K, V, nblk, g, (const bf16*)kv, ig, (const bf16*)ikv,
+                                                  out_log, (bf16*)out_state, reverse, last_only);
+  else
+    rnn_scan_kernel<float><<<grid, block, 0, st>>>(T, K, V, nblk, g, (const float*)kv, ig, (const float*)ikv,
+                                                   out_log, (float*)out_state, reverse, last_only);
+  GLA_CHECK_LAUNCH();
+  return GLA_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// State scan over chunks (the D x D recurrence of the chunk algorithm, gla.py:711-723 and
+// its mirror gla.py:759-771).  Four consecutive value-columns per thread; sequential over
+// the N chunks; writes the state BEFORE each update ("exclusive") and the final state.
+// ---------------------------------------------------------------------------------------
+template <typename TX, typename TI, typename TB, typename TF>
+__global__ void __launch_bounds__(256) state_scan_kernel(int64_t N, int64_t D, int64_t nblk,
+                                                         const float* __restrict__ G, const TX* X,
+                                                         const TI* __restrict__ init, TB* before,
+                                                         TF* __restrict__ final_state, int reverse) {
+  const int64_t bh = blockIdx.x / nblk;
+  const int64_t e = ((blockIdx.x % nblk) * 256 + threadIdx.x) * 4;
+  const int64_t DD = D * D;
+  if (e >= DD) return;
+  const int64_t dk = e / D;
+  float s[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) s[i] = init ? ld_f(init, bh * DD + e + i) : 0.f;
+  const float* gp = G + bh * N * D + dk;
+  const TX* xp = X + bh * N * DD + e;
+  TB* bp = before ? before + bh * N * DD + e : nullptr;
+#pragma unroll 2
+  for (int64_t i = 0; i < N; ++i) {
+    const int64_t n = reverse ? (N - 1 - i) : i;
+    const float f = expf(gp[n * D]);
+    float x[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) x[j] = ld_f(xp, n * DD + j);
+    if (bp) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) st_f(bp, n * DD + j, s[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) s[j] = f * s[j] + x[j];
+  }
+  if (final_state) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) st_f(final_state, bh * DD + e + j, s[j]);
+  }
+}
+
+template <typename TX, typename TI, typename TB>
+static int state_scan_dispatch_final(cudaStream_t st, dim3 grid, int64_t N, int64_t D, int64_t nblk, const float* G,
+                                     const void* X, const void* init, void* before, void* fin, int final_bf16,
+                                     int reverse) {
+  if (final_bf16)
+    state_scan_kernel<TX, TI, TB, bf16><<<grid, 256, 0, st>>>(N, D, nblk, G, (const TX*)X, (const TI*)init,
+                                                              (TB*)before, (bf16*)fin, reverse);
+  else
+    state_scan_kernel<TX, TI, TB, float><<<grid, 256, 0, st>>>(N, D, nblk, G, (const TX*)X, (const TI*)init,
+                                                               (TB*)before, (float*)fin, reverse);
+  GLA_CHECK_LAUNCH();
+  return GLA_OK;
+}
+
+int launch_state_scan(cudaStream_t st, int64_t BH, int64_t N, int64_t D, const float* G, const void* X,
+                      int x_bf16, const void* init, int init_bf16, void* before, int before_bf16,
+                      void* final_state, int final_bf16, int reverse) {
+  if (x_bf16) return GLA_ERR_UNSUPPORTED;   // chunk products are always kept in float32
+  int64_t nblk = (D * D / 4 + 255) / 256;
+  dim3 grid((unsigned)(nblk * BH));
+  if (init_bf16) {
+    if (before_bf16)
+      return state_scan_dispatch_final<float, bf16, bf16>(st, grid, N, D, nblk, G, X, init, before, final_state, final_bf16, reverse);
+    return state_scan_dispatch_final<float, bf16, float>(st, grid, N, D, nblk, G, X, init, before, final_state, final_bf16, reverse);
+  }
+  if (before_bf16)
+    return state_scan_dispatch_final<float, float, bf16>(st, grid, N, D, nblk, G, X, init, before, final_state, final_bf16, reverse);
+  return state_scan_dispatch_final<float, float, float>(st, grid, N, D, nblk, G, X, init, before, final_state, final_bf16, reverse);
+}
+
+// ---------------------------------------------------------------------------------------
+// Cross-rank combine for sequence parallelism: an exclusive decayed scan over ranks of the
+// per-rank (total log decay, local state) pairs, evaluated for one rank.
+// ---------------------------------------------------------------------------------------
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256) sp_combine_kernel(int64_t R, int64_t rank, int64_t BH, int64_t D,
+                                                         const float* __restrict__ all_G,
+                                                         const float* __restrict__ all_S,
+                                                         const TI* __restrict__ init, TO* __restrict__ result,
+                                                         int reverse) {
+  const int64_t DD = D * D;
+  const int64_t e = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (e >= BH * DD) return;
+  const int64_t bh = e / DD, dk = (e % DD) / D;
+  float acc = init ? ld_f(init, e) : 0.f;
+  if (!reverse) {
+    for (int64_t s = 0; s < rank; ++s)
+      acc = expf(all_G[(s * BH + bh) * D + dk]) * acc + all_S[s * BH * DD + e];
+  } else {
+    for (int64_t s = R - 1; s > rank; --s)
+      acc = expf(all_G[(s * BH + bh) * D + dk]) * acc + all_S[s * BH * DD + e];
+  }
+  st_f(result, e, acc);
+}
+
+int launch_sp_combine(cudaStream_t st, int64_t R, int64_t rank, int64_t BH, int64_t D, const float* all_G,
+                      const float* all_S, const void* init, int init_bf16, void* result, int result_bf16,
+                      int reverse) {
+  int64_t n = BH * D * D;
+  dim3 grid((unsigned)((n + 255) / 256));
+  if (init_bf16 && result_bf16)
+    sp_combine_kernel<bf16, bf16><<<grid, 256, 0, st>>>(R, rank, BH, D, all_G, all_S, (const bf16*)init, (bf16*)result, reverse);
+  else if (init_bf16 && !result_bf16)
+    sp_combine_kernel<bf16, float><<<grid, 256, 0, st>>>(R, rank, BH, D, all_G, all_S, (const bf16*)init, (float*)result, reverse);
+  else if (!init_bf16 && result_bf16)
+    sp_combine_kernel<float, bf16><<<grid, 256, 0, st>>>(R, rank, BH, D, all_G, all_S, (const float*)init, (bf16*)result, reverse);
+  else
+    sp_combine_kernel<float, float><<<grid, 256, 0, st>>>(R, rank, BH, D, all_G, all_S, (const float*)init, (float*)result, reverse);
+  GLA_CHECK_LAUNCH();
+  return GLA_OK;
+}
+
+}  // namespace gla

@@ -1,0 +1,209 @@
+"""The GLA operators with the reference's signatures (gla.py of zhixuan-lin/gla-jax), backed
+by libgla_b200.so.
+
+    chunk_gla(hidden_init, log_fgate, value, key, query, chunk_size, ...)   gla.py:657
+    recurrent_gla(hidden_init, log_fgate, value, key, query, reverse, ...)  gla.py:405
+    recurrent_gla_naive(hidden, log_fgate, value, key, query, reverse)      gla.py:26
+
+All return ``(hidden_final, out)``.  Shapes are the reference's per-sequence shapes
+``log_fgate, value, key, query : (T, H, D)``, ``hidden : (H, D, D)``; where the reference
+adds a batch axis with ``jax.vmap`` (gla.py:1335), pass arrays with a leading batch axis
+instead (``(B, T, H, D)`` and ``(B, H, D, D)``) — the kernels take the batch natively.
+
+This adapter holds device memory in torch CUDA tensors and differentiates through
+``torch.autograd.Function`` objects that mirror the reference's ``jax.custom_vjp`` pairs
+(gla.py:362/441 and gla.py:628/655).  The JAX adapter (XLA FFI handlers plus
+``jax.custom_vjp``) is ``jax_ffi.py`` / ``csrc/gla_xla_ffi.cc``; both call the same C ABI.
+There is no CPU path: CPU tensors raise.
+"""
+from __future__ import annotations
+
+from typing import Tuple
+
+import torch
+
+from . import _lib
+
+_DT = {torch.float32: _lib.GLA_F32, torch.bfloat16: _lib.GLA_BF16}
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _stream(dev) -> int:
+    return torch.cuda.current_stream(dev).cuda_stream
+
+
+def _prepare(hidden, log_fgate, value, key, query):
+    """Validate like the reference's trace-time asserts (gla.py:118-127, 498-500) and return
+    contiguous batched tensors plus whether a batch axis has to be stripped again."""
+    if not value.is_cuda:
+        raise RuntimeError("gla_jax_b200 operators need CUDA tensors; there is no CPU fallback")
+    if value.dim() not in (3, 4):
+        raise ValueError(f"value must be (T,H,D) or (B,T,H,D), got {tuple(value.shape)}")
+    batched = value.dim() == 4
+    if not (log_fgate.shape == value.shape == key.shape == query.shape):
+        raise ValueError("log_fgate, value, key, query must have the same shape "
+                         f"({tuple(log_fgate.shape)}, {tuple(value.shape)}, {tuple(key.shape)}, {tuple(query.shape)})")
+    if not batched:
+        hidden, log_fgate, value, key, query = (x.unsqueeze(0) for x in (hidden, log_fgate, value, key, query))
+    B, T, H, D = value.shape
+    if tuple(hidden.shape) != (B, H, D, D):
+        raise ValueError(f"hidden must be {'(B,' if batched else '('}H,D,D) = {(B, H, D, D)}, got {tuple(hidden.shape)}")
+    dt = value.dtype
+    if dt not in _DT:
+        raise TypeError(f"unsupported dtype {dt}: float32 and bfloat16 are implemented")
+    if not (key.dtype == query.dtype == hidden.dtype == dt):
+        raise TypeError("value, key, query and hidden must share one dtype")
+    return (hidden.contiguous(), log_fgate.contiguous(), value.contiguous(), key.contiguous(), query.contiguous(),
+            batched)
+
+
+class _ChunkGLA(torch.autograd.Function):
+    """custom-VJP pair of chunk_gla (gla.py:628-655)."""
+
+    @staticmethod
+    def forward(ctx, hidden, g, v, k, q, chunk, impl):
+        lib = _lib.load()
+        B, T, H, D = v.shape
+        dt = _DT[v.dtype]
+        g32 = g if g.dtype == torch.float32 else g.float()
+        need_grad = any(ctx.needs_input_grad[:5])
+        dev = v.device
+        saved_n = lib.gla_chunk_saved_bytes(B, T, H, D, chunk, dt, impl) if need_grad else 0
+        ws_n = lib.gla_chunk_fwd_workspace_bytes(B, T, H, D, chunk, dt, impl)
+        if ws_n == 0:
+            raise _lib.GlaError(f"chunk_gla: unsupported configuration T={T} H={H} D={D} chunk={chunk} dtype={v.dtype}")
+        saved = torch.empty(saved_n, dtype=torch.uint8, device=dev) if need_grad else None
+        ws = torch.empty(ws_n, dtype=torch.uint8, device=dev)
+        hf = torch.empty_like(hidden)
+        out = torch.empty_like(v)
+        st = lib.gla_chunk_fwd(_stream(dev), B, T, H, D, chunk, dt, impl, _ptr(hidden), _ptr(g32), _ptr(v), _ptr(k),
+                               _ptr(q), _ptr(hf), _ptr(out), _ptr(saved), _ptr(ws), ws_n)
+        _lib.check(st, "gla_chunk_fwd")
+        ctx.save_for_backward(g32, v, k, q, saved)
+        ctx.chunk, ctx.impl, ctx.g_dtype = chunk, impl, g.dtype
+        return hf, out
+
+    @staticmethod
+    def backward(ctx, dhf, dout):
+        lib = _lib.load()
+        g32, v, k, q, saved = ctx.saved_tensors
+        B, T, H, D = v.shape
+        dt = _DT[v.dtype]
+        dev = v.device
+        dhf = torch.zeros(B, H, D, D, dtype=v.dtype, device=dev) if dhf is None else dhf.to(v.dtype).contiguous()
+        dout = torch.zeros_like(v) if dout is None else dout.to(v.dtype).contiguous()
+        ws_n = lib.gla_chunk_bwd_workspace_bytes(B, T, H, D, ctx.chunk, dt, ctx.impl)
+        ws = torch.empty(ws_n, dtype=torch.uint8, device=dev)
+        dh = torch.empty(B, H, D, D, dtype=v.dtype, device=dev)
+        dg = torch.empty_like(g32)
+        dv, dk, dq = torch.empty_like(v), torch.empty_like(k), torch.empty_like(q)
+        st = lib.gla_chunk_bwd(_stream(dev), B, T, H, D, ctx.chunk, dt, ctx.impl, _ptr(g32), _ptr(v), _ptr(k), _ptr(q),
+                               _ptr(saved), _ptr(dhf), _ptr(dout), _ptr(dh), _ptr(dg), _ptr(dv), _ptr(dk), _ptr(dq),
+                               _ptr(ws), ws_n)
+        _lib.check(st, "gla_chunk_bwd")
+        return dh, dg.to(ctx.g_dtype), dv, dk, dq, None, None
+
+
+def chunk_gla(hidden_init, log_fgate, value, key, query, chunk_size: int,
+              block_size_t: int = 64, block_size_d: int = 64, interpret: bool = False,
+              num_warps: int = 4, num_stages: int = 2, impl: str = "auto") -> Tuple[torch.Tensor, torch.Tensor]:
+    """Chunk-wise GLA with multi-scale secondary chunking (reference: gla.py:657-692).
+
+    ``block_size_t``, ``block_size_d``, ``num_warps``, ``num_stages`` and ``interpret`` are
+    the reference's Triton tuning knobs; they are accepted for caller compatibility and
+    ignored (the CUDA kernels fix their own tiling).  ``impl`` selects the kernel family:
+    ``"auto"`` (tensor cores when the shape has a kernel), ``"tcgen05"`` or ``"fp32"``.
+    """
+    del block_size_t, block_size_d, interpret, num_warps, num_stages
+    chunk_size = int(chunk_size)
+    T = value.shape[-3]
+    if chunk_size <= 0 or chunk_size & (chunk_size - 1):
+        raise ValueError(f"Chunk length must be power of 2, but got {chunk_size}")   # gla.py:500
+    if T % chunk_size:
+        raise ValueError(f"sequence length {T} is not a multiple of chunk_size {chunk_size}")  # gla.py:674
+    h, g, v, k, q, batched = _prepare(hidden_init, log_fgate, value, key, query)
+    hf, out = _ChunkGLA.apply(h, g, v, k, q, chunk_size, _lib.IMPL_BY_NAME[impl])
+    return (hf, out) if batched else (hf[0], out[0])
+
+
+class _RecurrentGLA(torch.autograd.Function):
+    """custom-VJP pair of recurrent_gla (gla.py:362-388, 441)."""
+
+    @staticmethod
+    def forward(ctx, hidden, g, v, k, q, reverse, out_fp32):
+        lib = _lib.load()
+        B, T, H, D = v.shape
+        dt = _DT[v.dtype]
+        dev = v.device
+        g32 = g if g.dtype == torch.float32 else g.float()
+        hf = torch.empty_like(hidden)
+        out = torch.empty(v.shape, dtype=torch.float32 if out_fp32 else v.dtype, device=dev)
+        st = lib.gla_recurrent_fwd(_stream(dev), B, T, H, D, dt, _ptr(hidden), _ptr(g32), _ptr(v), _ptr(k), _ptr(q),
+                                   _ptr(hf), _ptr(out), _DT[out.dtype], int(reverse))
+        _lib.check(st, "gla_recurrent_fwd")
+        ctx.save_for_backward(hidden, g32, v, k, q)
+        ctx.reverse, ctx.g_dtype = bool(reverse), g.dtype
+        return hf, out
+
+    @staticmethod
+    def backward(ctx, dhf, dout):
+        lib = _lib.load()
+        hidden, g32, v, k, q = ctx.saved_tensors
+        B, T, H, D = v.shape
+        dt = _DT[v.dtype]
+        dev = v.device
+        dhf = torch.zeros_like(hidden) if dhf is None else dhf.to(v.dtype).contiguous()
+        dout = torch.zeros_like(v) if dout is None else dout.contiguous()
+        if dout.dtype not in _DT:
+            dout = dout.float()
+        ws_n = lib.gla_recurrent_bwd_workspace_bytes(B, T, H, D, dt)
+        ws = torch.empty(ws_n, dtype=torch.uint8, device=dev)
+        dh = torch.empty_like(hidden)
+        dg = torch.empty_like(g32)
+        dv, dk, dq = torch.empty_like(v), torch.empty_like(k), torch.empty_like(q)
+        st = lib.gla_recurrent_bwd(_stream(dev), B, T, H, D, dt, _ptr(hidden), _ptr(g32), _ptr(v), _ptr(k), _ptr(q),
+                                   _ptr(dhf), _ptr(dout), _DT[dout.dtype], _ptr(dh), _ptr(dg), _ptr(dv), _ptr(dk),
+                                   _ptr(dq), int(ctx.reverse), _ptr(ws), ws_n)
+        _lib.check(st, "gla_recurrent_bwd")
+        return dh, dg.to(ctx.g_dtype), dv, dk, dq, None, None
+
+
+def recurrent_gla(hidden_init, log_fgate, value, key, query, reverse: bool = False,
+                  max_block_size: int = 64, num_warps: int = 1, num_stages: int = 1,
+                  interpret: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Exact recurrence that never writes hidden states to memory (reference: gla.py:405-439).
+    ``max_block_size``, ``num_warps``, ``num_stages``, ``interpret`` are accepted and ignored."""
+    del max_block_size, num_warps, num_stages, interpret
+    if value.shape[-2] != key.shape[-2]:
+        raise ValueError("value and key must have the same number of heads")   # gla.py:417
+    h, g, v, k, q, batched = _prepare(hidden_init, log_fgate, value, key, query)
+    hf, out = _RecurrentGLA.apply(h, g, v, k, q, bool(reverse), False)
+    return (hf, out) if batched else (hf[0], out[0])
+
+
+def recurrent_gla_naive(hidden, log_fgate, value, key, query, reverse: bool = False):
+    """The definitional recurrence (reference: gla.py:26-47).  On this backend it runs the same
+    on-chip recurrence kernel as ``recurrent_gla``; as in the reference ``out`` is float32
+    and ``hidden_final`` keeps ``hidden``'s dtype (gla.py:43-46)."""
+    h, g, v, k, q, batched = _prepare(hidden, log_fgate, value, key, query)
+    hf, out = _RecurrentGLA.apply(h, g, v, k, q, bool(reverse), True)
+    return (hf, out) if batched else (hf[0], out[0])
+
+
+def auto_block_size(value_dim: int, key_dim: int, num_heads: int, max_block_size: int):
+    """Reference helper (gla.py:390-403) kept for callers that import it: the Triton block
+    sizes it would have chosen.  The CUDA kernels do not use them."""
+    assert value_dim == key_dim, "Not supported yet"
+    vb = min(max_block_size, value_dim)
+    kb = min(max_block_size, key_dim)
+    hb = None
+    for c in sorted(c for c in range(1, num_heads + 1) if num_heads % c == 0):
+        if c * vb <= max_block_size and c * kb <= max_block_size:
+            hb = c
+        else:
+            break
+    assert hb is not None
+    return vb, kb, hb

@@ -1,0 +1,220 @@
+/*
+ * gla_b200.h — C ABI of libgla_b200.so: gated linear attention (GLA) kernels for NVIDIA B200
+ * (sm_100a).  This is the drop-in boundary for the hot path of zhixuan-lin/gla-jax: every
+ * entry point below replaces one Python-level operator of the reference, whose device code
+ * is Pallas/Triton JIT-compiled inside jaxlib (the reference has no C interface of its
+ * own; the cited file:line is the operator each function stands in for).
+ *
+ * Conventions (all entry points)
+ *   - plain pointers and sizes only; every pointer is a DEVICE pointer unless stated;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream); all
+ *     work is enqueued on it, nothing synchronises, nothing allocates, no global state;
+ *   - the caller owns every buffer, including the workspace whose size the matching
+ *     *_workspace_bytes() function reports;
+ *   - arrays are dense row-major with the reference's axis order and an optional leading
+ *     batch axis B (the reference adds it with jax.vmap, gla.py:1335; pass B = 1 for the
+ *     per-sequence API):
+ *         log_fgate, value, key, query, out, and their gradients : (B, T, H, D)
+ *         hidden_init, hidden_final and their gradients          : (B, H, D, D)  [key, value]
+ *   - `dtype` is the element type of value/key/query/hidden/out and their gradients;
+ *     log_fgate and its gradient are always float32 (as in every configuration of the
+ *     reference harness, gla.py:1391);
+ *   - the return value is GLA_OK (0) or a gla_status code; nothing throws across the ABI.
+ *     Dimension and alignment problems are reported before anything is launched (the
+ *     reference raises Python asserts at trace time instead: gla.py:120-127, 499-500,
+ *     975-977; ops.py:195-207, 348-364).
+ *   - every function is thread-safe and reentrant (stream-ordered, no shared host state).
+ */
+#ifndef GLA_B200_H_
+#define GLA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define GLA_API __attribute__((visibility("default")))
+#else
+#define GLA_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum gla_status {
+  GLA_OK = 0,
+  GLA_ERR_NULL_POINTER = 1,   /* a required pointer is NULL */
+  GLA_ERR_BAD_DIMS = 2,       /* non-positive size, T % chunk != 0, chunk not a power of two, ... */
+  GLA_ERR_UNSUPPORTED = 3,    /* dtype / size combination this build has no kernel for */
+  GLA_ERR_ALIGNMENT = 4,      /* a pointer is not 16-byte aligned */
+  GLA_ERR_WORKSPACE = 5,      /* workspace missing or smaller than *_workspace_bytes() */
+  GLA_ERR_LAUNCH = 6,         /* the CUDA runtime rejected a launch (see gla_last_cuda_error) */
+  GLA_ERR_NO_DEVICE = 7,      /* no usable sm_100 device / driver */
+  GLA_ERR_TOO_LARGE = 8       /* size beyond a documented fixed maximum */
+} gla_status;
+
+typedef enum gla_dtype {
+  GLA_F32 = 0,
+  GLA_BF16 = 1
+} gla_dtype;
+
+/* Which implementation gla_chunk_fwd/bwd use. AUTO picks the tcgen05 tensor-core kernels
+ * when the shape has one (bf16, D = chunk = 128) and the fp32 CUDA-core kernels otherwise. */
+typedef enum gla_chunk_impl {
+  GLA_IMPL_AUTO = 0,
+  GLA_IMPL_FP32_SIMT = 1,     /* fp32 math on CUDA cores: every dtype, D <= 256, chunk 16..256 */
+  GLA_IMPL_TCGEN05 = 2        /* bf16 operands, fp32 TMEM accumulators (sm_100a tensor cores) */
+} gla_chunk_impl;
+
+/* Human-readable text for a status code. Never NULL. (Reference: Python assert messages.) */
+GLA_API const char* gla_status_string(int status);
+
+/* Library version string, e.g. "gla_b200 0.1 (sm_100a)". */
+GLA_API const char* gla_version(void);
+
+/* cudaError_t value of the most recent failed launch on the calling thread (0 if none). */
+GLA_API int gla_last_cuda_error(void);
+
+/* ------------------------------------------------------------------------------------
+ * cumsum — replaces ops.py:234 cumsum_recursive / ops.py:166 cumsum_pallas /
+ * ops.py:152 cumsum_kernel.
+ * Inclusive cumulative sum along the middle axis of src (N, T, D); `init` (N, D), if not
+ * NULL, is added to every element (ops.py:91-103); reverse != 0 scans from the end.
+ * Math is float32 (ops.py:159-160).  Any T (the reference's 16384-item and 2048-block
+ * limits, ops.py:195-207,239, do not apply).  `init` has dtype in_dtype.
+ * ---------------------------------------------------------------------------------- */
+GLA_API int gla_cumsum(void* stream, int64_t N, int64_t T, int64_t D,
+               const void* src, const void* init, void* dst,
+               int reverse, int in_dtype, int out_dtype);
+
+/* ------------------------------------------------------------------------------------
+ * rnn_scan — replaces ops.py:396 rnn_recursive / ops.py:338 rnn_pallas / ops.py:299
+ * rnn_kernel with ops.py:286 binary_operator.
+ * For each of `batch` independent problems: inclusive scan over the leading axis of
+ * (log_fgate (T, K) float32, kv (T, K, V)) under
+ *     (A_i, b_i) o (A_j, b_j) = (A_i + A_j, exp(A_j) * b_i + b_j),
+ * with the optional pair (init_log_fgate (K) float32, init_kv (K, V)) combined in front
+ * (both NULL or both set, ops.py:351).  Outputs: out_log (T, K) float32 cumulative log
+ * decay, out_state (T, K, V) in kv_dtype.  reverse != 0 scans from the end.  With
+ * last_only != 0 only the final row (row 0 when reversed) of both outputs is written
+ * (ops.py:330-334); the other rows are left untouched.  Any T (no 8192-item limit).
+ * ---------------------------------------------------------------------------------- */
+GLA_API int gla_rnn_scan(void* stream, int64_t batch, int64_t T, int64_t K, int64_t V,
+                 const float* log_fgate, const void* kv,
+                 const float* init_log_fgate, const void* init_kv,
+                 float* out_log, void* out_state,
+                 int reverse, int last_only, int kv_dtype);
+
+/* ------------------------------------------------------------------------------------
+ * recurrent_gla — replaces gla.py:405 recurrent_gla (forward: gla.py:99, kernel gla.py:50)
+ * and, with out_dtype = GLA_F32, gla.py:26 recurrent_gla_naive.
+ * Exact step recurrence S_t = exp(g_t) * S_{t-1} + k_t (x) v_t, o_t = q_t S_t with the
+ * state held on chip in float32 and never written to memory.  reverse != 0 runs the
+ * recurrence from the last token to the first (gla.py:421-423,437-438).
+ * `out` has dtype out_dtype (the reference's recurrent_gla returns value's dtype,
+ * recurrent_gla_naive returns float32).
+ * ---------------------------------------------------------------------------------- */
+GLA_API int gla_recurrent_fwd(void* stream, int64_t B, int64_t T, int64_t H, int64_t D, int dtype,
+                      const void* hidden_init, const float* log_fgate,
+                      const void* value, const void* key, const void* query,
+                      void* hidden_final, void* out, int out_dtype, int reverse);
+
+/* Bytes of workspace gla_recurrent_bwd needs for these sizes. */
+GLA_API size_t gla_recurrent_bwd_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int dtype);
+
+/* Backward of recurrent_gla — replaces gla.py:172 recurrent_gla_backward (kernel
+ * gla.py:271): a recompute pass for dquery, a reverse pass for dvalue, dkey and
+ * dhidden_init, and dlog_fgate = reverse_cumsum_T(q*dq - k*dk) + sum_v(dS_T * S_T)
+ * (gla.py:263).  `dout` has dtype dout_dtype.  Gradients have dtype `dtype`
+ * (dlog_fgate float32).
+ */
+GLA_API int gla_recurrent_bwd(void* stream, int64_t B, int64_t T, int64_t H, int64_t D, int dtype,
+                      const void* hidden_init, const float* log_fgate,
+                      const void* value, const void* key, const void* query,
+                      const void* dhidden_final, const void* dout, int dout_dtype,
+                      void* dhidden_init, float* dlog_fgate,
+                      void* dvalue, void* dkey, void* dquery,
+                      int reverse, void* workspace, size_t workspace_bytes);
+
+/* ------------------------------------------------------------------------------------
+ * chunk_gla — replaces gla.py:657 chunk_gla, gla.py:483 chunk_gla_forward (with
+ * gla.py:695 compute_inter_contrib, gla.py:792 compute_intra_contrib, gla.py:1242
+ * compute_score) and gla.py:552 chunk_gla_backward (with gla.py:731, 857, 1191).
+ *
+ * Requirements: T % chunk == 0; chunk a power of two, 16 <= chunk <= 256; 16 <= D <= 256
+ * and D % 8 == 0.  `impl` is a gla_chunk_impl.
+ *
+ * The forward writes the residuals the backward needs into `saved` (size
+ * gla_chunk_saved_bytes): the state entering every chunk, the per-chunk total log decay
+ * and the intra-chunk score matrices (the reference keeps `state` and `score_list`,
+ * gla.py:542-549).  Pass saved = NULL for a forward that will not be differentiated.
+ * ---------------------------------------------------------------------------------- */
+GLA_API size_t gla_chunk_saved_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t chunk,
+                             int dtype, int impl);
+GLA_API size_t gla_chunk_fwd_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t chunk,
+                                     int dtype, int impl);
+GLA_API size_t gla_chunk_bwd_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t chunk,
+                                     int dtype, int impl);
+
+GLA_API int gla_chunk_fwd(void* stream, int64_t B, int64_t T, int64_t H, int64_t D, int64_t chunk,
+                  int dtype, int impl,
+                  const void* hidden_init, const float* log_fgate,
+                  const void* value, const void* key, const void* query,
+                  void* hidden_final, void* out,
+                  void* saved, void* workspace, size_t workspace_bytes);
+
+GLA_API int gla_chunk_bwd(void* stream, int64_t B, int64_t T, int64_t H, int64_t D, int64_t chunk,
+                  int dtype, int impl,
+                  const float* log_fgate,
+                  const void* value, const void* key, const void* query,
+                  const void* saved,
+                  const void* dhidden_final, const void* dout,
+                  void* dhidden_init, float* dlog_fgate,
+                  void* dvalue, void* dkey, void* dquery,
+                  void* workspace, size_t workspace_bytes);
+
+/* ------------------------------------------------------------------------------------
+ * Sequence-parallel support (no counterpart in the reference, which is single-device; the
+ * algebra is ops.py:286 binary_operator applied across ranks and the exact chaining of
+ * hidden_init -> hidden_final, gla.py:720-723).
+ *
+ * gla_chunk_local_state: for a slice of the sequence, the total log decay
+ * G (B, H, D) float32 = sum_t log_fgate and the state S (B, H, D, D) float32 reached from
+ * a ZERO initial state (only the K^T V products and the state scan run).
+ * Workspace: gla_chunk_fwd_workspace_bytes.
+ *
+ * gla_sp_combine: given every rank's (G_r, S_r) gathered as all_G (R, B, H, D) and
+ * all_S (R, B, H, D, D) float32, computes for rank `rank`
+ *   forward  (reverse == 0): H_in = sum_{p<rank} exp(sum_{p<s<rank} G_s) * S_p
+ *                                   + exp(sum_{s<rank} G_s) * init
+ *   backward (reverse != 0): the mirror image over ranks p > rank, used for dhidden_final,
+ * where `init` (B, H, D, D) has dtype init_dtype (hidden_init on the forward pass,
+ * dhidden_final of the whole sequence on the backward pass) and `result` has dtype
+ * result_dtype.  The decay multiplies along the key axis.
+ * ---------------------------------------------------------------------------------- */
+GLA_API int gla_chunk_local_state(void* stream, int64_t B, int64_t T, int64_t H, int64_t D, int64_t chunk,
+                          int dtype, int impl,
+                          const float* log_fgate, const void* value, const void* key,
+                          float* G_total, float* S_local,
+                          void* workspace, size_t workspace_bytes);
+
+/* gla_chunk_local_dstate: the backward counterpart of gla_chunk_local_state.  For a slice of
+ * the sequence, A (B, H, D, D) float32 = the gradient reaching the slice's initial state
+ * when the gradient of its final state is ZERO: sum_n exp(sum_{m<n} G_m) * (q_hat_n^T dO_n).
+ * The slice's dhidden_init for a non-zero dhidden_final is A + exp(G_total) * dhidden_final
+ * (the scan is linear), which is what gla_sp_combine evaluates across ranks with
+ * reverse != 0.  Workspace: gla_chunk_bwd_workspace_bytes. */
+GLA_API int gla_chunk_local_dstate(void* stream, int64_t B, int64_t T, int64_t H, int64_t D, int64_t chunk,
+                           int dtype, int impl,
+                           const float* log_fgate, const void* query, const void* dout,
+                           float* dS_local, void* workspace, size_t workspace_bytes);
+
+GLA_API int gla_sp_combine(void* stream, int64_t R, int64_t rank, int64_t BH, int64_t D,
+                   const float* all_G, const float* all_S,
+                   const void* init, int init_dtype,
+                   void* result, int result_dtype, int reverse);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GLA_B200_H_ */

@@ -1,0 +1,197 @@
+"""GPU parity tests (pytest -m gpu): the CUDA kernels, called through the C ABI via the
+Python operators, against the CPU oracle on the same seeded inputs.
+
+Tolerances are the ones the project states (relative L2, |a-b|/|a|, gla.py:1462):
+  float32: out, hidden_final and gradients <= 1e-4
+  bfloat16: out, hidden_final <= 1e-2, gradients <= 2e-2
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import gla_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+TOL = {torch.float32: (1e-4, 1e-4), torch.bfloat16: (1e-2, 2e-2)}
+NAMES = ("dhidden_init", "dlog_fgate", "dvalue", "dkey", "dquery")
+
+
+def _case(B, T, H, D, dtype, seed, shift, zero_init=False):
+    h, g, v, k, q = O.make_inputs(B, T, H, D, dtype, seed=seed, shift=shift, zero_init=zero_init)
+    gen = torch.Generator().manual_seed(seed + 100)
+    dhf = torch.randn(B, H, D, D, generator=gen).to(dtype)
+    do = torch.randn(B, T, H, D, generator=gen).to(dtype)
+    return h, g, v, k, q, dhf, do
+
+
+def _oracle(h, g, v, k, q, dhf, do, reverse=False):
+    outs = []
+    for b in range(v.shape[0]):
+        outs.append(O.value_and_grads(O.recurrent_gla_naive, h[b], g[b], v[b], k[b], q[b], dhf[b], do[b],
+                                      reverse=reverse))
+    hf = torch.stack([o[0] for o in outs])
+    out = torch.stack([o[1] for o in outs])
+    grads = [torch.stack([o[2][i] for o in outs]) for i in range(5)]
+    return hf, out, grads
+
+
+def _run_gpu(fn, dev, h, g, v, k, q, dhf, do, **kw):
+    leaves = [x.to(dev).requires_grad_(True) for x in (h, g, v, k, q)]
+    hf, out = fn(*leaves, **kw)
+    loss = (hf.float() * dhf.to(dev).float()).sum() + (out.float() * do.to(dev).float()).sum()
+    grads = torch.autograd.grad(loss, leaves)
+    torch.cuda.synchronize()
+    return hf.cpu(), out.cpu(), [x.cpu() for x in grads]
+
+
+def _compare(ref, got, dtype, what):
+    tol_f, tol_g = TOL[dtype]
+    hf0, o0, g0 = ref
+    hf1, o1, g1 = got
+    errs = {"hidden_final": O.rel_l2(hf0, hf1), "out": O.rel_l2(o0, o1)}
+    for n, a, b in zip(NAMES, g0, g1):
+        errs[n] = O.rel_l2(a, b)
+    bad = {n: e for n, e in errs.items() if not (e < (tol_f if n in ("hidden_final", "out") else tol_g))}
+    assert not bad, f"{what}: relative L2 over tolerance: {bad} (all: {errs})"
+
+
+CHUNK_CASES = [
+    # B, T, H, D, C, dtype, shift, zero_init
+    (1, 256, 2, 64, 64, torch.float32, 5.0, False),      # BASELINE config 1
+    (2, 128, 2, 32, 32, torch.float32, 0.0, False),      # sharp gates
+    (1, 64, 1, 64, 64, torch.float32, 5.0, False),       # a single chunk
+    (1, 128, 3, 16, 16, torch.float32, 5.0, True),       # smallest sizes, zero initial state
+    (1, 256, 2, 128, 128, torch.float32, 5.0, False),
+    (1, 512, 1, 256, 256, torch.float32, 0.0, False),    # config 5 head size, sharp gates
+    (2, 256, 2, 64, 64, torch.bfloat16, 5.0, False),
+    (1, 512, 2, 128, 128, torch.bfloat16, 5.0, False),   # config 2 tile shape
+    (1, 256, 2, 128, 128, torch.bfloat16, 0.0, False),   # config 2 tile shape, sharp gates
+]
+
+
+@pytest.mark.parametrize("B,T,H,D,C,dtype,shift,zero_init", CHUNK_CASES)
+def test_chunk_gla_fp32_kernels_vs_oracle(cuda_device, B, T, H, D, C, dtype, shift, zero_init):
+    from gla_jax_b200 import chunk_gla
+    case = _case(B, T, H, D, dtype, 0, shift, zero_init)
+    ref = _oracle(*case)
+    got = _run_gpu(chunk_gla, cuda_device, *case, chunk_size=C, impl="fp32")
+    _compare(ref, got, dtype, f"chunk_gla fp32 kernels {B,T,H,D,C,dtype}")
+
+
+@pytest.mark.parametrize("B,T,H,D,dtype,shift,reverse", [
+    (1, 256, 2, 64, torch.float32, 5.0, False),
+    (2, 100, 3, 32, torch.float32, 0.0, False),          # T not a multiple of the time block
+    (1, 128, 2, 128, torch.float32, 5.0, True),
+    (1, 64, 1, 256, torch.float32, 0.0, False),
+    (2, 256, 2, 128, torch.bfloat16, 5.0, False),
+    (1, 128, 2, 64, torch.bfloat16, 0.0, True),
+])
+def test_recurrent_gla_vs_oracle(cuda_device, B, T, H, D, dtype, shift, reverse):
+    from gla_jax_b200 import recurrent_gla
+    case = _case(B, T, H, D, dtype, 1, shift)
+    ref = _oracle(*case, reverse=reverse)
+    got = _run_gpu(recurrent_gla, cuda_device, *case, reverse=reverse)
+    _compare(ref, got, dtype, f"recurrent_gla {B,T,H,D,dtype,reverse}")
+
+
+def test_recurrent_gla_naive_returns_fp32_out(cuda_device):
+    from gla_jax_b200 import recurrent_gla_naive
+    case = _case(1, 128, 2, 64, torch.bfloat16, 2, 5.0)
+    ref = _oracle(*case)
+    got = _run_gpu(recurrent_gla_naive, cuda_device, *case, reverse=False)
+    assert got[1].dtype == torch.float32 and got[0].dtype == torch.bfloat16   # gla.py:43-46
+    _compare(ref, got, torch.bfloat16, "recurrent_gla_naive")
+
+
+def test_per_sequence_signature(cuda_device):
+    """The reference's unbatched shapes (T,H,D)/(H,D,D) work unchanged."""
+    from gla_jax_b200 import chunk_gla, recurrent_gla
+    h, g, v, k, q = O.make_inputs(1, 128, 2, 64, torch.float32, seed=5, batch_axis=False)
+    hf0, o0 = O.recurrent_gla_naive(h, g, v, k, q)
+    dev = cuda_device
+    hf1, o1 = chunk_gla(h.to(dev), g.to(dev), v.to(dev), k.to(dev), q.to(dev), chunk_size=64)
+    hf2, o2 = recurrent_gla(h.to(dev), g.to(dev), v.to(dev), k.to(dev), q.to(dev))
+    assert tuple(o1.shape) == (128, 2, 64) and tuple(hf1.shape) == (2, 64, 64)
+    for hf, o in ((hf1, o1), (hf2, o2)):
+        assert O.rel_l2(hf0, hf.cpu()) < 1e-4 and O.rel_l2(o0, o.cpu()) < 1e-4
+
+
+def test_golden_fixtures_on_gpu(cuda_device):
+    """Committed fixtures (float64 oracle, stored float32) vs the GPU kernels."""
+    from pathlib import Path
+    from gla_jax_b200 import chunk_gla, recurrent_gla
+    for f in sorted((Path(__file__).parent / "golden").glob("*.npz")):
+        z = np.load(f)
+        T, H, D, C = (int(z[n]) for n in ("T", "H", "D", "C"))
+        h, g, v, k, q = O.make_inputs(1, T, H, D, torch.float32, seed=int(z["seed"]), shift=float(z["shift"]))
+        dhf, do = torch.from_numpy(z["dhf"])[None], torch.from_numpy(z["dout"])[None]
+        ref = (torch.from_numpy(z["hidden_final"])[None], torch.from_numpy(z["out"])[None],
+               [torch.from_numpy(z[n])[None] for n in NAMES])
+        got = _run_gpu(chunk_gla, cuda_device, h, g, v, k, q, dhf, do, chunk_size=C)
+        _compare(ref, got, torch.float32, f"golden {f.name} chunk_gla")
+        got = _run_gpu(recurrent_gla, cuda_device, h, g, v, k, q, dhf, do)
+        _compare(ref, got, torch.float32, f"golden {f.name} recurrent_gla")
+
+
+@pytest.mark.parametrize("N,T,D,reverse,with_init,dtype", [
+    (3, 50, 7, False, True, torch.float32), (2, 4096, 96, True, True, torch.float32),
+    (1, 1, 33, False, False, torch.float32), (4, 300, 64, True, False, torch.bfloat16),
+])
+def test_cumsum_vs_oracle(cuda_device, N, T, D, reverse, with_init, dtype):
+    from gla_jax_b200 import cumsum_recursive, cumsum_pallas
+    gen = torch.Generator().manual_seed(3)
+    x = torch.randn(N, T, D, generator=gen).to(dtype)
+    init = torch.randn(N, D, generator=gen).to(dtype) if with_init else None
+    ref = O.cumsum(x, 1, init=init, reverse=reverse, out_dtype=torch.float32, compute_dtype=torch.float64)
+    dev = cuda_device
+    y = cumsum_recursive(x.to(dev), axis=1, init=None if init is None else init.to(dev), reverse=reverse)
+    assert y.dtype == dtype
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    assert O.rel_l2(ref, y.cpu().float()) < tol
+    y2 = cumsum_pallas(x.to(dev), axis=-2, init=None if init is None else init.to(dev), reverse=reverse,
+                       out_dtype=torch.float32)
+    assert y2.dtype == torch.float32 and O.rel_l2(ref, y2.cpu()) < (1e-5 if dtype == torch.float32 else 1e-2)
+
+
+def test_cumsum_inner_axis_layout(cuda_device):
+    """Scan along a middle axis of a 4-d array, the layout chunk_gla uses (N, C, D) -> axis -2."""
+    from gla_jax_b200 import cumsum_recursive
+    x = torch.randn(2, 5, 64, 24)
+    y = cumsum_recursive(x.to(cuda_device), axis=-2)
+    assert O.rel_l2(torch.cumsum(x.double(), -2), y.cpu()) < 1e-5
+
+
+@pytest.mark.parametrize("T,K,V,reverse,with_init,dtype", [
+    (20, 5, 4, False, True, torch.float32), (32, 128, 128, True, True, torch.float32),
+    (300, 16, 24, False, False, torch.float32), (64, 64, 64, False, True, torch.bfloat16),
+])
+def test_rnn_scan_vs_oracle(cuda_device, T, K, V, reverse, with_init, dtype):
+    from gla_jax_b200 import rnn_recursive, rnn_pallas
+    gen = torch.Generator().manual_seed(4)
+    g = -torch.rand(T, K, generator=gen)
+    kv = torch.randn(T, K, V, generator=gen).to(dtype)
+    ig = -torch.rand(K, generator=gen) if with_init else None
+    ikv = torch.randn(K, V, generator=gen).to(dtype) if with_init else None
+    A0, S0 = O.rnn_scan(g.double(), kv.double(), None if ig is None else ig.double(),
+                        None if ikv is None else ikv.double(), reverse=reverse, compute_dtype=torch.float64)
+    dev = cuda_device
+    mv = lambda x: None if x is None else x.to(dev)
+    A1, S1 = rnn_recursive(mv(g), mv(kv), mv(ig), mv(ikv), reverse=reverse)
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    assert S1.dtype == dtype
+    assert O.rel_l2(A0, A1.cpu()) < 1e-5 and O.rel_l2(S0, S1.cpu().float()) < tol
+    # last_only: only the final row is defined (ops.py:330-334)
+    A2, S2 = rnn_pallas(mv(g), mv(kv), mv(ig), mv(ikv), reverse=reverse, last_only=True)
+    last = 0 if reverse else T - 1
+    assert O.rel_l2(A0[last], A2[last].cpu()) < 1e-5 and O.rel_l2(S0[last], S2[last].cpu().float()) < tol
+
+
+def test_chunk_equals_recurrent_on_gpu_full_size_slice(cuda_device):
+    """Cross-check of the two GPU implementations at the README tile shape (D = C = 128) on
+    a longer sequence than the oracle can afford: chunk_gla vs recurrent_gla, fp32."""
+    from gla_jax_b200 import chunk_gla, recurrent_gla
+    h, g, v, k, q = (x.to(cuda_device) for x in O.make_inputs(2, 2048, 2, 128, torch.float32, seed=9))
+    hf1, o1 = chunk_gla(h, g, v, k, q, chunk_size=128, impl="fp32")
+    hf2, o2 = recurrent_gla(h, g, v, k, q)
+    assert O.rel_l2(hf2.cpu(), hf1.cpu()) < 1e-4 and O.rel_l2(o2.cpu(), o1.cpu()) < 1e-4
