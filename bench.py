@@ -1,0 +1,376 @@
+"""Benchmark of the GLA hot path: chunk_gla forward+backward tokens/s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--chunk-impl auto|fp32|tcgen05]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+
+A step is one forward+backward of ``chunk_gla`` with the reference harness loss
+``hidden_final.sum() + out.sum()`` (gla.py:1336-1340) on the README shape (BASELINE config 2:
+B=4, H=6, D=128, T=4096, bf16, chunk 128, log_fgate = log_sigmoid(5 + N(0,1)) in float32), with
+seeded synthetic inputs.  With N GPUs every rank runs that shape on its own batch shard
+(batch x heads sharding needs no collective), so scaling is weak and ``value`` is the whole-job
+tokens/s.  Rank 0 prints ONE JSON line.
+
+Timed quantities:
+  value      device-resident inputs, the C ABI called directly, CUDA events around each step,
+             two rotating input/output sets so that no step finds its operands in L2.
+  e2e        the public Python operator (gla_jax_b200.chunk_gla + autograd) with HOST pinned
+             inputs: host->device copies of all five inputs and a device->host read of the
+             scalar loss inside every timed step.
+  roofline   the dominant kernel's time, from CUDA events the library records around each of
+             its launches during the timed steps.
+  cpu_baseline  the oracle's chunk path (torch CPU, float32) on a bounded sample.
+``--impl reference`` times that CPU path alone (the reference itself needs jax 0.4.29 with
+Pallas/Triton, which cannot be installed here; its CPU-runnable restatement is the oracle).
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+# README shape (BASELINE config 2), per GPU
+CFG = dict(B=4, T=4096, H=6, D=128, C=128)
+METRIC = "chunk_gla fwd+bwd tokens/sec"
+
+
+def flops_per_token_head(C, D):
+    """Algorithmic matmul flops of chunk_gla fwd+bwd per token and head: 6CD + 12D^2."""
+    return 6 * C * D + 12 * D * D
+
+
+def bytes_per_token_head(D):
+    """Compulsory HBM bytes per token and head, bf16 tensors + float32 gate: 34 D."""
+    return 34 * D
+
+
+def load_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return dict(hbm=float(d["hbm_gbs"]), tf_burst=float(d["bf16_tflops"]),
+                    tf_sustained=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), source="measured")
+    return dict(hbm=6650.0, tf_burst=1590.0, tf_sustained=1400.0, source="fallback")
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.stop_flag, self.max_mhz = index, [], set(), False, None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        if self.nv is None:
+            return
+        nv = self.nv
+        names = {
+            nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+            nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap",
+        }
+        while not self.stop_flag:
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.02)
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+def cpu_baseline(seconds_budget=20.0, threads=None):
+    """Oracle chunk path, forward + autograd backward, float32 torch-CPU, on single sequences of
+    the benchmark shape (T=4096, H=6, D=128, chunk 128) until the budget is spent."""
+    import torch
+    from oracle import gla_oracle as O
+    threads = threads or len(os.sched_getaffinity(0))
+    torch.set_num_threads(threads)
+    T, H, D, C = CFG["T"], CFG["H"], CFG["D"], CFG["C"]
+    h, g, v, k, q = O.make_inputs(1, T, H, D, torch.float32, seed=0)
+    n, t0 = 0, time.perf_counter()
+    while True:
+        O.chunk_gla_cpu_fwd_bwd(h, g, v, k, q, C)
+        n += 1
+        el = time.perf_counter() - t0
+        if el > seconds_budget or n >= 64:
+            break
+    return {"value": n * T / el, "unit": "tokens/s", "cores": threads, "kind": "port",
+            "sample": f"{n} sequence(s) of T={T}, H={H}, D={D}, chunk={C}, float32, fwd+bwd, {el:.1f} s"}
+
+
+def run_reference(args, rank, world):
+    """The reference arm: the reference's CPU-runnable path (its jnp chunk algorithm restated in
+    the oracle) on the host cores; rank 0 only."""
+    if rank != 0:
+        return
+    import torch
+    from oracle import gla_oracle as O
+    threads = len(os.sched_getaffinity(0))
+    torch.set_num_threads(threads)
+    T, H, D, C = CFG["T"], CFG["H"], CFG["D"], CFG["C"]
+    h, g, v, k, q = O.make_inputs(1, T, H, D, torch.float32, seed=0)
+    for _ in range(min(args.warmup, 1)):
+        O.chunk_gla_cpu_fwd_bwd(h, g, v, k, q, C)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        O.chunk_gla_cpu_fwd_bwd(h, g, v, k, q, C)
+    el = time.perf_counter() - t0
+    val = args.steps * T / el
+    sample = f"each step = one sequence (B=1 of the B={CFG['B']} workload): T={T}, H={H}, D={D}, chunk={C}, float32"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * el / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "README shape B=4,H=6,D=128,T=4096,chunk=128 (BASELINE config 2); CPU sample B=1"},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "reference needs jax==0.4.29 + Pallas/Triton (not installable here); this is its chunk "
+                "algorithm restated with plain tensor ops (oracle/gla_oracle.py) on the host cores",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--chunk-impl", default="auto", choices=["auto", "fp32", "tcgen05"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=15.0)
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from gla_jax_b200 import _lib, chunk_gla
+    from oracle import gla_oracle as O   # input generator and the cpu_baseline leg only
+
+    lib = _lib.load()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (no CPU fallback exists); use --impl reference for the CPU arm")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    W = max(args.warmup, 3)
+    K = args.steps
+    B, T, H, D, C = (CFG[x] for x in "BTHDC")
+    impl = _lib.IMPL_BY_NAME[args.chunk_impl]
+    dt = _lib.GLA_BF16
+
+    # two rotating sets of inputs and outputs (each step touches > 400 MB, L2 is 126 MB)
+    NSETS = 2
+    sets = []
+    for s in range(NSETS):
+        h, g, v, k, q = O.make_inputs(B, T, H, D, torch.bfloat16, seed=1000 * rank + 10 * s)
+        ins = [x.to(dev) for x in (h, g, v, k, q)]
+        outs = dict(hf=torch.empty_like(ins[0]), out=torch.empty_like(ins[2]), dh=torch.empty_like(ins[0]),
+                    dg=torch.empty_like(ins[1]), dv=torch.empty_like(ins[2]), dk=torch.empty_like(ins[2]),
+                    dq=torch.empty_like(ins[2]), dhf=torch.ones_like(ins[0]), dout=torch.ones_like(ins[2]))
+        sets.append((ins, outs))
+    saved_n = lib.gla_chunk_saved_bytes(B, T, H, D, C, dt, impl)
+    wsf_n = lib.gla_chunk_fwd_workspace_bytes(B, T, H, D, C, dt, impl)
+    wsb_n = lib.gla_chunk_bwd_workspace_bytes(B, T, H, D, C, dt, impl)
+    saved = torch.empty(saved_n, dtype=torch.uint8, device=dev)
+    ws = torch.empty(max(wsf_n, wsb_n), dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+
+    def step(i):
+        (h, g, v, k, q), o = sets[i % NSETS]
+        st = lib.gla_chunk_fwd(stream, B, T, H, D, C, dt, impl, h.data_ptr(), g.data_ptr(), v.data_ptr(), k.data_ptr(),
+                               q.data_ptr(), o["hf"].data_ptr(), o["out"].data_ptr(), saved.data_ptr(),
+                               ws.data_ptr(), ws.numel())
+        _lib.check(st, "gla_chunk_fwd")
+        st = lib.gla_chunk_bwd(stream, B, T, H, D, C, dt, impl, g.data_ptr(), v.data_ptr(), k.data_ptr(), q.data_ptr(),
+                               saved.data_ptr(), o["dhf"].data_ptr(), o["dout"].data_ptr(), o["dh"].data_ptr(),
+                               o["dg"].data_ptr(), o["dv"].data_ptr(), o["dk"].data_ptr(), o["dq"].data_ptr(),
+                               ws.data_ptr(), ws.numel())
+        _lib.check(st, "gla_chunk_bwd")
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(W):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    launches0 = lib.gla_launch_count()
+    lib.gla_profile_enable(1)
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+    barrier()
+    for i in range(K):
+        evs[i][0].record()
+        step(i)
+        evs[i][1].record()
+    barrier()
+    lib.gla_profile_enable(0)
+    launches = lib.gla_launch_count() - launches0
+    ms_total = sum(a.elapsed_time(b) for a, b in evs)
+    buf = ctypes.create_string_buffer(1 << 16)
+    lib.gla_profile_report(buf, len(buf))
+    kern = {}
+    for ln in buf.value.decode().strip().splitlines():
+        name, n, ms = ln.split()
+        kern[name] = (int(n), float(ms))
+
+    # ---- end to end through the public operator, host buffers in and a host read out -------
+    host = [x.pin_memory() for x in O.make_inputs(B, T, H, D, torch.bfloat16, seed=1000 * rank + 77)]
+    h2d = sum(x.numel() * x.element_size() for x in host)
+
+    def e2e_step():
+        leaves = [x.to(dev, non_blocking=True).requires_grad_(True) for x in host]
+        hf, out = chunk_gla(*leaves, chunk_size=C, impl=args.chunk_impl)
+        loss = hf.float().sum() + out.float().sum()
+        loss.backward()
+        return float(loss.item())       # 4-byte device->host read; also orders the step
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e_evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+    for i in range(K):
+        e_evs[i][0].record()
+        e2e_step()
+        e_evs[i][1].record()
+    barrier()
+    e2e_ms = sum(a.elapsed_time(b) for a, b in e_evs)
+    sampler.stop_flag = True
+    sampler.join(timeout=1.0)
+
+    # ---- reduce over ranks: max time ---------------------------------------------------------
+    t = torch.tensor([ms_total, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total, e2e_ms = float(t[0]), float(t[1])
+    tokens_per_step = B * T * world
+    value = tokens_per_step * K / (ms_total * 1e-3)
+    e2e_val = tokens_per_step * K / (e2e_ms * 1e-3)
+
+    if rank == 0:
+        peaks = load_peaks()
+        th = B * T * H                                   # token-heads per step per GPU
+        step_s = ms_total * 1e-3 / K
+        # whole-step fractions (both rooflines of the path)
+        tensor_frac = flops_per_token_head(C, D) * th / step_s / (peaks["tf_burst"] * 1e12)
+        hbm_frac = bytes_per_token_head(D) * th / step_s / (peaks["hbm"] * 1e9)
+        # dominant kernel: largest share of the recorded kernel time
+        total_k = sum(ms for _, ms in kern.values()) or 1.0
+        dom = max(kern, key=lambda n: kern[n][1]) if kern else None
+        roof = None
+        if dom:
+            n_l, ms_l = kern[dom]
+            per_launch_s = ms_l * 1e-3 / n_l
+            alg = KERNEL_ALGORITHMIC.get(dom, KERNEL_ALGORITHMIC["_default"])(B, T, H, D, C)
+            if alg["bound"] == "hbm":
+                ach = alg["bytes"] / per_launch_s / 1e9
+                roof = {"bound": "hbm", "kernel": dom, "achieved": ach, "peak": peaks["hbm"], "unit": "GB/s",
+                        "frac": ach / peaks["hbm"], "traffic": None}
+            else:
+                ach = alg["flops"] / per_launch_s / 1e12
+                roof = {"bound": "tensor", "kernel": dom, "achieved": ach, "peak": peaks["tf_burst"],
+                        "unit": "TFLOP/s", "frac": ach / peaks["tf_burst"], "traffic": None}
+            roof.update({"peak_source": peaks["source"], "launches": n_l, "ms_per_launch": 1e3 * per_launch_s,
+                         "share_of_kernel_time": ms_l / total_k, "algorithmic": alg["what"]})
+        line = {
+            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms_total / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "README shape per GPU: B=4,H=6,D=128,T=4096,chunk=128,bf16 q/k/v/hidden, f32 "
+                                   "log_fgate=log_sigmoid(5+N(0,1)) (BASELINE config 2); loss=hidden_final.sum()+out.sum()",
+                       "global_batch": B * world, "seq_len": T, "parallelism": f"batch-shard x{world}, no collectives",
+                       "l2": f"{NSETS} rotating input/output sets; one step touches > 400 MB (L2 = 126 MB)",
+                       "chunk_impl": args.chunk_impl},
+            "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
+                    "ms_per_step": e2e_ms / K},
+            "gpu_launches": int(launches),
+            "clocks": sampler.summary(),
+            "roofline": roof,
+            "step_fractions": {"tensor_frac_of_burst_peak": tensor_frac, "hbm_frac_of_measured_copy": hbm_frac,
+                               "flops_per_step": flops_per_token_head(C, D) * th,
+                               "compulsory_bytes_per_step": bytes_per_token_head(D) * th},
+            "kernels": {n: {"launches": c, "ms_total": ms, "share": ms / total_k} for n, (c, ms) in
+                        sorted(kern.items(), key=lambda kv: -kv[1][1])},
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(args.cpu_seconds)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def _alg_simt_intra_bwd(B, T, H, D, C):
+    th = B * T * H
+    return {"bound": "hbm", "bytes": th * D * (2 + 2 + 4 + 4 + 4 + 2 + 2 + 4) + th * C * 4,
+            "what": "q,k (bf16), lam, dqh, dkh (f32) in; dq, dk (bf16), dlam (f32) out; dP (f32 CxC per chunk) in"}
+
+
+def _alg_simt_score(B, T, H, D, C):
+    th = B * T * H
+    return {"bound": "hbm", "bytes": th * D * (2 + 2 + 4) + th * C * 4,
+            "what": "q,k (bf16), lam (f32) in; P (f32, C per token) out"}
+
+
+def _alg_whole_step(B, T, H, D, C):
+    th = B * T * H
+    return {"bound": "hbm", "bytes": th * bytes_per_token_head(D), "what": "34*D bytes per token-head (whole step)"}
+
+
+def _alg_tc_fwd(B, T, H, D, C):
+    th = B * T * H
+    return {"bound": "hbm", "bytes": th * 12 * D, "what": "forward: q,k,v (bf16) + log_fgate (f32) in, out (bf16): 12*D B per token-head"}
+
+
+def _alg_tc_bwd(B, T, H, D, C):
+    th = B * T * H
+    return {"bound": "hbm", "bytes": th * 22 * D,
+            "what": "backward: q,k,v,dout (bf16) + log_fgate (f32) in, dq,dk,dv (bf16) + dlog_fgate (f32) out: 22*D B per token-head"}
+
+
+KERNEL_ALGORITHMIC = {
+    "simt_intra_bwd_kernel": _alg_simt_intra_bwd,
+    "simt_score_kernel": _alg_simt_score,
+    "tc_chunk_fwd_kernel": _alg_tc_fwd,
+    "tc_chunk_bwd_kernel": _alg_tc_bwd,
+    "_default": _alg_whole_step,
+}
+
+
+if __name__ == "__main__":
+    main()

@@ -1,6 +1,7 @@
 // C ABI of libgla_b200.so: argument validation and dispatch.  See include/gla_b200.h for
 // the contract of every entry point and the reference operator it replaces.
 #include "gla_common.cuh"
+#include <cstdio>
 
 namespace gla {
 
@@ -10,6 +11,30 @@ int record_cuda_error(cudaError_t e) {
   if (e == cudaSuccess) return GLA_OK;
   g_last_cuda_error = (int)e;
   return GLA_ERR_LAUNCH;
+}
+
+// ---- launch counter and optional per-kernel event timing (thread-local) -----------------
+static thread_local long long g_launches = 0;
+void count_launch() { ++g_launches; }
+
+struct ProfRec { const char* name; cudaEvent_t a, b; };
+static thread_local bool g_prof_on = false;
+static thread_local ProfRec g_prof[4096];
+static thread_local int g_prof_n = 0, g_prof_created = 0;
+
+ProfScope::ProfScope(const char* name, cudaStream_t stream) : slot(-1), st(stream) {
+  if (!g_prof_on || g_prof_n >= 4096) return;
+  slot = g_prof_n++;
+  if (slot >= g_prof_created) {
+    cudaEventCreate(&g_prof[slot].a);
+    cudaEventCreate(&g_prof[slot].b);
+    g_prof_created = slot + 1;
+  }
+  g_prof[slot].name = name;
+  cudaEventRecord(g_prof[slot].a, st);
+}
+ProfScope::~ProfScope() {
+  if (slot >= 0) cudaEventRecord(g_prof[slot].b, st);
 }
 
 static int check_dtype(int dt) { return (dt == GLA_F32 || dt == GLA_BF16) ? GLA_OK : GLA_ERR_UNSUPPORTED; }
@@ -53,6 +78,35 @@ const char* gla_status_string(int status) {
 const char* gla_version(void) { return "gla_b200 0.1 (sm_100a)"; }
 
 int gla_last_cuda_error(void) { return g_last_cuda_error; }
+
+long long gla_launch_count(void) { return g_launches; }
+
+void gla_profile_enable(int on) {
+  g_prof_on = on != 0;
+  if (on) g_prof_n = 0;
+}
+
+// Writes "name launches total_ms\n" per kernel for the launches recorded since
+// gla_profile_enable(1); synchronises on the recorded events.  Returns bytes written.
+size_t gla_profile_report(char* buf, size_t cap) {
+  struct Agg { const char* name; int n; double ms; } agg[64];
+  int na = 0;
+  for (int i = 0; i < g_prof_n; ++i) {
+    float ms = 0.f;
+    cudaEventSynchronize(g_prof[i].b);
+    cudaEventElapsedTime(&ms, g_prof[i].a, g_prof[i].b);
+    int j = 0;
+    for (; j < na; ++j) if (agg[j].name == g_prof[i].name) break;
+    if (j == na) { if (na == 64) continue; agg[na++] = {g_prof[i].name, 0, 0.0}; }
+    agg[j].n += 1; agg[j].ms += ms;
+  }
+  size_t off = 0;
+  for (int j = 0; j < na && off + 128 < cap; ++j)
+    off += (size_t)snprintf(buf + off, cap - off, "%s %d %.6f\n", agg[j].name, agg[j].n, agg[j].ms);
+  g_prof_n = 0;
+  if (off < cap) buf[off] = 0;
+  return off;
+}
 
 int gla_cumsum(void* stream, int64_t N, int64_t T, int64_t D, const void* src, const void* init, void* dst,
                int reverse, int in_dtype, int out_dtype) {

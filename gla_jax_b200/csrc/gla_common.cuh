@@ -31,8 +31,10 @@ __device__ __forceinline__ void st_any(void* p, int is_bf16, int64_t i, float v)
 
 // Host-side: record and translate launch errors.
 int record_cuda_error(cudaError_t e);   // returns GLA_OK or GLA_ERR_LAUNCH
+void count_launch();
 #define GLA_CHECK_LAUNCH()                                   \
   do {                                                       \
+    ::gla::count_launch();                                   \
     int _s = ::gla::record_cuda_error(cudaGetLastError());   \
     if (_s != GLA_OK) return _s;                             \
   } while (0)
@@ -41,6 +43,15 @@ int record_cuda_error(cudaError_t e);   // returns GLA_OK or GLA_ERR_LAUNCH
     int _s = (expr);                                         \
     if (_s != GLA_OK) return _s;                             \
   } while (0)
+
+// Optional per-kernel timing (off by default): while enabled on the calling thread, every
+// kernel launch site is bracketed by a pair of CUDA events on its stream.
+struct ProfScope {
+  int slot;
+  cudaStream_t st;
+  ProfScope(const char* name, cudaStream_t stream);
+  ~ProfScope();
+};
 
 static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 static inline bool is_pow2(int64_t x) { return x > 0 && (x & (x - 1)) == 0; }

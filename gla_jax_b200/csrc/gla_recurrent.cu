@@ -246,6 +246,8 @@ static int launch_rec(cudaStream_t st, const RecParams& p) {
   cudaError_t e = cudaFuncSetAttribute(rec_kernel<D, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return record_cuda_error(e);
   dim3 grid(D / RS, (unsigned)p.H, (unsigned)p.B);
+  static const char* names[4] = {"rec_kernel_fwd", "rec_kernel_dq", "rec_kernel_dv", "rec_kernel_dk"};
+  ProfScope ps(names[MODE], st);
   rec_kernel<D, MODE><<<grid, RTHREADS, smem, st>>>(p);
   GLA_CHECK_LAUNCH();
   return GLA_OK;

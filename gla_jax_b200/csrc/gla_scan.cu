@@ -65,6 +65,7 @@ int launch_cumsum(cudaStream_t st, int64_t N, int64_t T, int64_t D, const void* 
   int64_t gy = (D + 31) / 32;
   if (gy > 65535 || N > 2147483647LL) return GLA_ERR_TOO_LARGE;
   dim3 grid((unsigned)N, (unsigned)gy), block(32, CS_RL);
+  ProfScope ps("cumsum_kernel", st);
   if (!in_bf16 && !out_bf16)
     cumsum_kernel<float, float><<<grid, block, 0, st>>>((const float*)src, (const float*)init, (float*)dst, T, D, reverse);
   else if (!in_bf16 && out_bf16)
@@ -118,6 +119,7 @@ int launch_rnn_scan(cudaStream_t st, int64_t batch, int64_t T, int64_t K, int64_
   int64_t nblk = (K * V + 255) / 256;
   if (nblk * batch > 2147483647LL) return GLA_ERR_TOO_LARGE;
   dim3 grid((unsigned)(nblk * batch)), block(256);
+  ProfScope ps("rnn_scan_kernel", st);
   if (kv_bf16)
     rnn_scan_kernel<bf16><<<grid, block, 0, st>>>(T, K, V, nblk, g, (const bf16*)kv, ig, (const bf16*)ikv,
                                                   out_log, (bf16*)out_state, reverse, last_only);
@@ -189,6 +191,7 @@ int launch_state_scan(cudaStream_t st, int64_t BH, int64_t N, int64_t D, const f
   if (x_bf16) return GLA_ERR_UNSUPPORTED;   // chunk products are always kept in float32
   int64_t nblk = (D * D / 4 + 255) / 256;
   dim3 grid((unsigned)(nblk * BH));
+  ProfScope ps("state_scan_kernel", st);
   if (init_bf16) {
     if (before_bf16)
       return state_scan_dispatch_final<float, bf16, bf16>(st, grid, N, D, nblk, G, X, init, before, final_state, final_bf16, reverse);
@@ -229,6 +232,7 @@ int launch_sp_combine(cudaStream_t st, int64_t R, int64_t rank, int64_t BH, int6
                       int reverse) {
   int64_t n = BH * D * D;
   dim3 grid((unsigned)((n + 255) / 256));
+  ProfScope ps("sp_combine_kernel", st);
   if (init_bf16 && result_bf16)
     sp_combine_kernel<bf16, bf16><<<grid, 256, 0, st>>>(R, rank, BH, D, all_G, all_S, (const bf16*)init, (bf16*)result, reverse);
   else if (init_bf16 && !result_bf16)

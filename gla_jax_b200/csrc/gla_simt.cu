@@ -111,6 +111,7 @@ __global__ void __launch_bounds__(256) gemm_kernel(GemmArgs a) {
 }
 
 static int launch_gemm(cudaStream_t st, const GemmArgs& a, int64_t batches) {
+  ProfScope ps("simt_gemm_kernel", st);
   dim3 grid((a.N + GT - 1) / GT, (a.M + GT - 1) / GT, (unsigned)batches);
   if (batches > 65535) return GLA_ERR_TOO_LARGE;
   gemm_kernel<<<grid, 256, 0, st>>>(a);
@@ -312,7 +313,10 @@ int simt_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, 
   }
   // lam: within-chunk cumsum, viewing g as (B*N, C, H*D)
   GLA_TRY(launch_cumsum(st, B * N, C, H * D, g, nullptr, lam, 0, 0, 0));
-  prep_kernel<<<(unsigned)((E + 255) / 256), 256, 0, st>>>(d, lam, k, q, bf, khat, state_only ? nullptr : qhat, Gc);
+  {
+    ProfScope ps_prep_kernel("simt_prep_kernel", st);
+    prep_kernel<<<(unsigned)((E + 255) / 256), 256, 0, st>>>(d, lam, k, q, bf, khat, state_only ? nullptr : qhat, Gc);
+  }
   GLA_CHECK_LAUNCH();
   {  // kv = k_hat^T v
     GemmArgs a{};
@@ -323,6 +327,7 @@ int simt_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, 
   }
   if (state_only) {
     GLA_TRY(launch_state_scan(st, BH, N, D, Gc, kv, 0, nullptr, 0, nullptr, 0, S_local, 0, 0));
+    ProfScope ps_gsum_kernel("simt_gsum_kernel", st);
     gsum_kernel<<<(unsigned)((BH * D + 255) / 256), 256, 0, st>>>(BH, N, D, Gc, G_total);
     GLA_CHECK_LAUNCH();
     return GLA_OK;
@@ -339,6 +344,7 @@ int simt_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, 
   {
     dim3 grid((unsigned)(C / 8), (unsigned)N, (unsigned)BH);
     if (N > 65535 || BH > 65535) return GLA_ERR_TOO_LARGE;
+    ProfScope ps_score_kernel("simt_score_kernel", st);
     score_kernel<<<grid, 256, 0, st>>>(d, lam, k, q, bf, Pbuf);
     GLA_CHECK_LAUNCH();
   }
@@ -363,6 +369,7 @@ __global__ void __launch_bounds__(256) dG_transpose_kernel(int64_t B, int64_t H,
 }
 static int launch_dG_transpose(cudaStream_t st, int64_t B, int64_t H, int64_t N, int64_t D, const float* in, float* out) {
   const int64_t n = B * H * N * D;
+  ProfScope ps_dG_transpose_kernel("simt_dG_transpose_kernel", st);
   dG_transpose_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(B, H, N, D, in, out);
   GLA_CHECK_LAUNCH();
   return GLA_OK;
@@ -390,7 +397,10 @@ int simt_chunk_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, 
   const float* P = (const float*)s;
 
   GLA_TRY(launch_cumsum(st, B * N, C, H * D, g, nullptr, lam, 0, 0, 0));
-  prep_kernel<<<(unsigned)((E + 255) / 256), 256, 0, st>>>(d, lam, k, q, bf, khat, qhat, nullptr);
+  {
+    ProfScope ps_prep_kernel("simt_prep_kernel", st);
+    prep_kernel<<<(unsigned)((E + 255) / 256), 256, 0, st>>>(d, lam, k, q, bf, khat, qhat, nullptr);
+  }
   GLA_CHECK_LAUNCH();
   auto sq_out = [&](GemmArgs& a, float* C_, int64_t R) {
     a.C = C_; a.c_bf = 0; a.csb = H * N * R * R; a.csh = N * R * R; a.csn = R * R; a.cm = R; a.cn = 1;
@@ -436,12 +446,14 @@ int simt_chunk_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, 
   }
   {
     const int64_t nw = BH * N * D;
+    ProfScope ps_dG_kernel("simt_dG_kernel", st);
     dG_kernel<<<(unsigned)((nw + 7) / 8), 256, 0, st>>>(d, dkh, khat, Gc, S_prev, dS, dG);
     GLA_CHECK_LAUNCH();
   }
   float* dlam = qhat;   // q_hat is dead from here on
   {
     dim3 grid((unsigned)C, (unsigned)N, (unsigned)BH);
+    ProfScope ps_intra_bwd_kernel("simt_intra_bwd_kernel", st);
     intra_bwd_kernel<<<grid, 256, 0, st>>>(d, lam, k, q, bf, dP, dqh, dkh, dq, dk, dlam);
     GLA_CHECK_LAUNCH();
   }
@@ -473,7 +485,10 @@ int simt_chunk_dstate_only(cudaStream_t st, int64_t B, int64_t T, int64_t H, int
   w += f32b(BH * N * C * C);
   float* Gc = (float*)w;
   GLA_TRY(launch_cumsum(st, B * N, C, H * D, g, nullptr, lam, 0, 0, 0));
-  prep_kernel<<<(unsigned)((E + 255) / 256), 256, 0, st>>>(d, lam, nullptr, q, bf, nullptr, qhat, Gc);
+  {
+    ProfScope ps_prep_kernel("simt_prep_kernel", st);
+    prep_kernel<<<(unsigned)((E + 255) / 256), 256, 0, st>>>(d, lam, nullptr, q, bf, nullptr, qhat, Gc);
+  }
   GLA_CHECK_LAUNCH();
   GemmArgs a{};
   a.nprod = 1; a.A[0] = mat_bthd(qhat, 0, d, true); a.B[0] = mat_bthd(dout, bf, d, false); a.K[0] = (int)C;

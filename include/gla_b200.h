@@ -75,6 +75,19 @@ GLA_API const char* gla_version(void);
 /* cudaError_t value of the most recent failed launch on the calling thread (0 if none). */
 GLA_API int gla_last_cuda_error(void);
 
+/* Number of kernels this library has launched from the calling thread since load
+ * (monotonic).  Diagnostic; the reference has no counterpart. */
+GLA_API long long gla_launch_count(void);
+
+/* Per-kernel device timing for benchmarks (diagnostic; no counterpart in the reference, whose
+ * harness times whole calls with timeit, gla.py:1430-1434).  While enabled on the calling
+ * thread, each internal kernel launch is bracketed by CUDA events on its stream;
+ * gla_profile_report waits for them and writes one line "kernel_name launches total_ms" per
+ * kernel into buf (NUL-terminated), returning the bytes written.  At most 4096 launches are
+ * recorded between enable(1) and report. */
+GLA_API void gla_profile_enable(int on);
+GLA_API size_t gla_profile_report(char* buf, size_t capacity);
+
 /* ------------------------------------------------------------------------------------
  * cumsum — replaces ops.py:234 cumsum_recursive / ops.py:166 cumsum_pallas /
  * ops.py:152 cumsum_kernel.
