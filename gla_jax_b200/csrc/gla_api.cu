@@ -48,7 +48,7 @@ static int check_chunk_dims(int64_t B, int64_t T, int64_t H, int64_t D, int64_t 
 
 // Resolve GLA_IMPL_AUTO; returns a negative status (as -status) if the request is invalid.
 static int resolve_impl(int impl, int64_t D, int64_t C, int dtype) {
-  if (impl == GLA_IMPL_AUTO) return tc_supported(D, C, dtype) ? GLA_IMPL_TCGEN05 : GLA_IMPL_FP32_SIMT;
+  if (impl == GLA_IMPL_AUTO) return (tc_auto_default() && tc_supported(D, C, dtype)) ? GLA_IMPL_TCGEN05 : GLA_IMPL_FP32_SIMT;
   if (impl == GLA_IMPL_TCGEN05) return tc_supported(D, C, dtype) ? GLA_IMPL_TCGEN05 : -GLA_ERR_UNSUPPORTED;
   if (impl == GLA_IMPL_FP32_SIMT) return GLA_IMPL_FP32_SIMT;
   return -GLA_ERR_UNSUPPORTED;
@@ -80,6 +80,8 @@ const char* gla_version(void) { return "gla_b200 0.1 (sm_100a)"; }
 int gla_last_cuda_error(void) { return g_last_cuda_error; }
 
 long long gla_launch_count(void) { return g_launches; }
+
+unsigned int gla_device_wait_timeouts(void) { return tc_read_wait_timeouts(); }
 
 void gla_profile_enable(int on) {
   g_prof_on = on != 0;

@@ -79,6 +79,12 @@ GLA_API int gla_last_cuda_error(void);
  * (monotonic).  Diagnostic; the reference has no counterpart. */
 GLA_API long long gla_launch_count(void);
 
+/* Every device-side wait in this library (on an mbarrier that a tensor-core operation
+ * completes) is bounded: a wait that runs out makes its thread block skip its output and
+ * increments a device counter instead of spinning forever.  This reads that counter
+ * (synchronises the device; diagnostic).  0 means no wait has ever given up. */
+GLA_API unsigned int gla_device_wait_timeouts(void);
+
 /* Per-kernel device timing for benchmarks (diagnostic; no counterpart in the reference, whose
  * harness times whole calls with timeit, gla.py:1430-1434).  While enabled on the calling
  * thread, each internal kernel launch is bracketed by CUDA events on its stream;
