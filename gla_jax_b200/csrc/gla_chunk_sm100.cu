@@ -17,6 +17,7 @@
 // so only C*D exponentials are evaluated per chunk and no exponent is ever positive.
 #include "gla_common.cuh"
 #include "tc_ptx.cuh"
+#include <type_traits>
 
 namespace gla {
 
@@ -517,6 +518,464 @@ tc_chunk_fwd_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g
   if (warp == 0) tmem_dealloc(tmem, 512);
 }
 
+// ---------------------------------------------------------------------------------------
+// Backward chunk kernel (gla.py:552-625, 731-790, 857-960, 1036-1189).
+//
+//   dP = dO V^T                      dV = P^T dO + k_hat dS_next
+//   dq = (dO S_prev^T) exp(lam) + sum_levels (dP_l k~_l) wq_l + diag
+//   dk = (V dS_next^T) exp(G-lam) + sum_levels (dP_l^T q~_l) wk_l + diag
+//   dlam = q dq - k dk ;  dG = sum_c dk_hat k_hat + e^G sum_v S_prev dS_next
+//   dg = reverse cumsum of dlam within the chunk + dG
+//
+// Everything that must be multiplied by a (row, feature)-dependent decay weight AFTER its
+// contraction (the two inter-chunk terms and all level terms) is computed TRANSPOSED, with
+// the feature index d on the TMEM lanes and the chunk rows on the TMEM columns.  A thread
+// then owns one feature d and a run of rows ("column layout"): the accumulator it reads back
+// with tcgen05.ld is exactly the slice whose weights it can form from its own gates by
+// running products, and the final reverse cumsum over rows is a serial loop in registers.
+//
+// Register budget forces two passes over the rows (first rows 64..127, then 0..63): in a
+// pass thread (d, rq) owns rows 64 p + 16 rq + [0, 16).  For half sizes h <= 32 a row's dyadic
+// partners lie in the same 64-row half, so a level is M = 128 (d) x N = 64 (rows of the half)
+// x K = 64 (partner rows): A = W_l (row r' holds q~ or k~ of that row, whichever side it is
+// on), B = the 64 x 64 block of dP masked to the level, once as (n = i, k = j) and once as
+// (n = j, k = i), both accumulating into one tile.  For h = 64 the partners are the other
+// half; W_64 for all 128 rows is built before the passes.
+// ---------------------------------------------------------------------------------------
+struct BwdSmem {
+  static constexpr uint32_t DO = 0;                        // dO   (rows i, cols dv)     -> later W64
+  static constexpr uint32_t V = DO + 2 * TILE_BYTES;       // v    (rows j, cols dv)     -> later W_l x2
+  static constexpr uint32_t SP = V + 2 * TILE_BYTES;       // S_prev (rows dk, cols dv)  -> later dP_l x2
+  static constexpr uint32_t DS = SP + 2 * TILE_BYTES;      // dS_next (rows dk, cols dv)
+  static constexpr uint32_t P = DS + 2 * TILE_BYTES;       // P    (rows i, cols j)
+  static constexpr uint32_t KH = P + 2 * TILE_BYTES;       // k_hat (rows j, cols dk)
+  static constexpr uint32_t TOT = KH + 2 * TILE_BYTES;     // [8][128] float: gate products per 16 rows
+  static constexpr uint32_t GRP = TOT + 8 * TD * 4;        // [8][128] float: dlam totals per 16 rows
+  static constexpr uint32_t DIAG = GRP + 8 * TD * 4;       // [128] float: dP[i][i]
+  static constexpr uint32_t DG1 = DIAG + TC * 4;           // [128] float
+  static constexpr uint32_t DG2 = DG1 + TD * 4;            // [128] float
+  static constexpr uint32_t BAR = DG2 + TD * 4;            // 3 mbarriers + tmem slot
+  static constexpr uint32_t END = BAR + 64;
+  static constexpr uint32_t W64 = DO;
+  static constexpr uint32_t WL = V;                        // 2 x 16 KB
+  static constexpr uint32_t DPL = SP;                      // 2 x 8 KB
+};
+constexpr uint32_t TM_DP = 0, TM_DQH = 128, TM_DKH = 256, TM_DV = 384, TM_T = 384;
+
+// Decay weights of the thread's 16 rows at level slot S (half size 2^S), column layout.
+// f[i] = gate of row i of the thread's run; rq = which 16-row run of the 64-row half; p = which half.
+// right(i) tells which side row i is on; w[i] is wq (right side) or wk (left side).
+template <int S>
+__device__ __forceinline__ void level_weights(const float (&f)[16], int rq, int p, const float* tot, int d,
+                                              float (&w)[16]) {
+  if (S < 4) {
+    constexpr int HH = 1 << S;
+    float run = 1.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {          // inclusive prefix within aligned HH-blocks
+      run = (i % HH == 0) ? f[i] : run * f[i];
+      if (i & HH) w[i] = run;
+    }
+#pragma unroll
+    for (int i = 15; i >= 0; --i) {         // exclusive suffix within aligned HH-blocks
+      if (i % HH == HH - 1) run = 1.f;
+      if (!(i & HH)) w[i] = run;
+      run *= f[i];
+    }
+  } else {
+    const int g = 4 * p + rq;
+    bool right;
+    float cross = 1.f;
+    if (S == 4) {
+      right = rq & 1;
+    } else if (S == 5) {
+      right = rq >= 2;
+      if (rq == 3) cross = tot[(g - 1) * TD + d];
+      if (rq == 0) cross = tot[(g + 1) * TD + d];
+    } else {
+      right = p == 1;
+      if (right) { for (int b2 = 4; b2 < g; ++b2) cross *= tot[b2 * TD + d]; }
+      else       { for (int b2 = g + 1; b2 < 4; ++b2) cross *= tot[b2 * TD + d]; }
+    }
+    if (right) {
+      float run = cross;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) { run *= f[i]; w[i] = run; }
+    } else {
+      float run = cross;
+#pragma unroll
+      for (int i = 15; i >= 0; --i) { w[i] = run; run *= f[i]; }
+    }
+  }
+}
+template <int S>
+__device__ __forceinline__ bool row_is_right(int i, int rq, int p) {
+  return S < 4 ? ((i >> S) & 1) : S == 4 ? (rq & 1) : S == 5 ? (rq >= 2) : (p == 1);
+}
+
+__device__ __forceinline__ float bf16_lo(uint32_t u) { return __uint_as_float(u << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t u) { return __uint_as_float(u & 0xffff0000u); }
+__device__ __forceinline__ void st_bf16(uint8_t* p, float v) { *reinterpret_cast<bf16*>(p) = __float2bfloat16_rn(v); }
+
+__global__ void __launch_bounds__(TTHREADS, 1)
+tc_chunk_bwd_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g, const bf16* __restrict__ v,
+                    const bf16* __restrict__ k, const bf16* __restrict__ q, const bf16* __restrict__ dO,
+                    const bf16* __restrict__ S_prev, const bf16* __restrict__ dS_next, const bf16* __restrict__ P_saved,
+                    bf16* __restrict__ dq_out, bf16* __restrict__ dk_out, bf16* __restrict__ dv_out,
+                    float* __restrict__ dg_out) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* sm = align1024(smem_raw);
+  float* tot = reinterpret_cast<float*>(sm + BwdSmem::TOT);
+  float* grp = reinterpret_cast<float*>(sm + BwdSmem::GRP);
+  float* diag = reinterpret_cast<float*>(sm + BwdSmem::DIAG);
+  float* dG1 = reinterpret_cast<float*>(sm + BwdSmem::DG1);
+  float* dG2 = reinterpret_cast<float*>(sm + BwdSmem::DG2);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + BwdSmem::BAR);   // [0]: phase 1, [1],[2]: level buffers
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int q4 = warp & 3, wq_ = warp >> 2;        // TMEM lane quadrant, and which quarter of the columns
+  const int d = 32 * q4 + lane;                     // column layout: feature index
+  const int64_t n = blockIdx.x % N, bh = blockIdx.x / N, b = bh / H, h_ = bh % H;
+  const int64_t HD = H * TD;
+  const int64_t row0 = ((b * T + n * TC) * H + h_) * TD;
+  const int64_t chunk_id = bh * N + n;
+
+  if (warp == 0) {
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  if (tid == 0) {
+    mbar_init(smem_u32(bars + 0), 1);
+    mbar_init(smem_u32(bars + 1), 1);
+    mbar_init(smem_u32(bars + 2), 1);
+    mbar_fence_init();
+  }
+  if (tid < TD) { dG1[tid] = 0.f; dG2[tid] = 0.f; }
+
+  // ---- phase 0: operand tiles; gate products per 16 rows; k_hat -------------------------------
+  copy_tile_128x128(sm + BwdSmem::DO, dO + row0, HD);
+  copy_tile_128x128(sm + BwdSmem::V, v + row0, HD);
+  copy_tile_128x128(sm + BwdSmem::SP, S_prev + chunk_id * TD * TD, TD);
+  copy_tile_128x128(sm + BwdSmem::DS, dS_next + chunk_id * TD * TD, TD);
+  copy_tile_128x128(sm + BwdSmem::P, P_saved + chunk_id * TC * TC, TC);
+  float f32r[32];                                   // gates of rows 32 wq_ + [0, 32), feature d
+  {
+    float p0 = 1.f, p1 = 1.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      f32r[i] = __expf(g[row0 + (int64_t)(32 * wq_ + i) * HD + d]);
+      if (i < 16) p0 *= f32r[i]; else p1 *= f32r[i];
+    }
+    tot[(2 * wq_) * TD + d] = p0;
+    tot[(2 * wq_ + 1) * TD + d] = p1;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  {
+    // k_hat[r][d] = k[r][d] * prod_{t > r} f_t   (rows of this thread: 32 wq_ + i)
+    float run = 1.f;
+    for (int b2 = 2 * wq_ + 2; b2 < 8; ++b2) run *= tot[b2 * TD + d];
+    uint8_t* tile = sm + BwdSmem::KH + (d >> 6) * TILE_BYTES;
+#pragma unroll
+    for (int i = 31; i >= 0; --i) {
+      const int r = 32 * wq_ + i;
+      const float kk = __bfloat162float(k[row0 + (int64_t)r * HD + d]);
+      st_bf16(tile + sw128_off(r, d & 63), kk * run);
+      run *= f32r[i];
+    }
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+
+  // ---- phase 1: the four dense products --------------------------------------------------------------
+  if (tid == 0) {
+    tc_fence_after();
+    const uint32_t aDO = smem_u32(sm + BwdSmem::DO), aV = smem_u32(sm + BwdSmem::V), aSP = smem_u32(sm + BwdSmem::SP),
+                   aDS = smem_u32(sm + BwdSmem::DS), aP = smem_u32(sm + BwdSmem::P), aKH = smem_u32(sm + BwdSmem::KH);
+    constexpr uint32_t iKK = idesc_bf16(128, 128, 0, 0), iMM = idesc_bf16(128, 128, 1, 1), iKM = idesc_bf16(128, 128, 0, 1);
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks)   // dP[i][j] = sum_dv dO[i][dv] v[j][dv]
+      umma_bf16(tmem + TM_DP, desc_kmajor(aDO, TILE_BYTES, ks), desc_kmajor(aV, TILE_BYTES, ks), iKK, ks > 0);
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks)   // dQh^T[dk][i] = sum_dv S_prev[dk][dv] dO[i][dv]
+      umma_bf16(tmem + TM_DQH, desc_kmajor(aSP, TILE_BYTES, ks), desc_kmajor(aDO, TILE_BYTES, ks), iKK, ks > 0);
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks)   // dKh^T[dk][j] = sum_dv dS_next[dk][dv] v[j][dv]
+      umma_bf16(tmem + TM_DKH, desc_kmajor(aDS, TILE_BYTES, ks), desc_kmajor(aV, TILE_BYTES, ks), iKK, ks > 0);
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks)   // dV[j][dv] = sum_i P[i][j] dO[i][dv]
+      umma_bf16(tmem + TM_DV, desc_mnmajor(aP, TILE_BYTES, ks), desc_mnmajor(aDO, TILE_BYTES, ks), iMM, ks > 0);
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks)   //          + sum_dk k_hat[j][dk] dS_next[dk][dv]
+      umma_bf16(tmem + TM_DV, desc_kmajor(aKH, TILE_BYTES, ks), desc_mnmajor(aDS, TILE_BYTES, ks), iKM, 1);
+    umma_commit(smem_u32(bars + 0));
+  }
+  bool ok = mbar_wait(smem_u32(bars + 0), 0);
+  tc_fence_after();
+
+  // ---- phase 1.5: dV out, dP diagonal, the two dG sums ---------------------------------------------------
+  {
+    uint32_t r[32];
+    tmem_ld32(tmem + ((uint32_t)(q4 * 32) << 16) + TM_DV + 32 * wq_, r);     // row j = d here (row layout)
+    tmem_ld_wait();
+    if (ok) {
+      bf16* o = dv_out + row0 + (int64_t)d * HD + 32 * wq_;
+#pragma unroll
+      for (int c4 = 0; c4 < 4; ++c4) {
+        uint4 u;
+        u.x = pack_bf16x2(__uint_as_float(r[8 * c4 + 0]), __uint_as_float(r[8 * c4 + 1]));
+        u.y = pack_bf16x2(__uint_as_float(r[8 * c4 + 2]), __uint_as_float(r[8 * c4 + 3]));
+        u.z = pack_bf16x2(__uint_as_float(r[8 * c4 + 4]), __uint_as_float(r[8 * c4 + 5]));
+        u.w = pack_bf16x2(__uint_as_float(r[8 * c4 + 6]), __uint_as_float(r[8 * c4 + 7]));
+        *reinterpret_cast<uint4*>(o + 8 * c4) = u;
+      }
+    }
+    if (wq_ == q4) {          // the 32 x 32 diagonal block of dP: pick dP[i][i]
+      tmem_ld32(tmem + ((uint32_t)(q4 * 32) << 16) + TM_DP + 32 * q4, r);
+      tmem_ld_wait();
+      float dv_ = 0.f;
+#pragma unroll
+      for (int m = 0; m < 32; ++m)
+        if (m == lane) dv_ = __uint_as_float(r[m]);
+      diag[d] = dv_;
+    }
+    // dG1[d] = sum_r dKh^T[d][r] k_hat[r][d]   (this thread: rows 32 wq_ + m)
+    tmem_ld32(tmem + ((uint32_t)(q4 * 32) << 16) + TM_DKH + 32 * wq_, r);
+    tmem_ld_wait();
+    float s1 = 0.f;
+    const uint8_t* tile = sm + BwdSmem::KH + (d >> 6) * TILE_BYTES;
+#pragma unroll
+    for (int m = 0; m < 32; ++m)
+      s1 = fmaf(__uint_as_float(r[m]), __bfloat162float(*reinterpret_cast<const bf16*>(tile + sw128_off(32 * wq_ + m, d & 63))), s1);
+    atomicAdd(dG1 + d, s1);
+    // dG2[d] = sum_v S_prev[d][v] dS_next[d][v]    (this thread: v in 32 wq_ + [0, 32))
+    float s2 = 0.f;
+    const uint8_t* ts = sm + BwdSmem::SP + (wq_ >> 1) * TILE_BYTES;
+    const uint8_t* td = sm + BwdSmem::DS + (wq_ >> 1) * TILE_BYTES;
+#pragma unroll
+    for (int c4 = 0; c4 < 4; ++c4) {
+      const uint4 a = *reinterpret_cast<const uint4*>(ts + sw128_chunk(d, (wq_ & 1) * 4 + c4));
+      const uint4 c = *reinterpret_cast<const uint4*>(td + sw128_chunk(d, (wq_ & 1) * 4 + c4));
+      s2 += bf16_lo(a.x) * bf16_lo(c.x) + bf16_hi(a.x) * bf16_hi(c.x) + bf16_lo(a.y) * bf16_lo(c.y) + bf16_hi(a.y) * bf16_hi(c.y) +
+            bf16_lo(a.z) * bf16_lo(c.z) + bf16_hi(a.z) * bf16_hi(c.z) + bf16_lo(a.w) * bf16_lo(c.w) + bf16_hi(a.w) * bf16_hi(c.w);
+    }
+    atomicAdd(dG2 + d, s2);
+  }
+  tc_fence_before();
+  __syncthreads();      // all readers of the phase-1 tiles are done: the regions can be reused
+  tc_fence_after();
+
+  // ---- phase 1.9: W64 for all 128 rows (rows < 64: k~, rows >= 64: q~, anchor row 63) ----------------------
+  {
+    uint8_t* tile = sm + BwdSmem::W64 + (d >> 6) * TILE_BYTES;
+    if (wq_ < 2) {
+      float run = (wq_ == 0) ? tot[2 * TD + d] * tot[3 * TD + d] : 1.f;
+#pragma unroll
+      for (int i = 31; i >= 0; --i) {
+        const int r = 32 * wq_ + i;
+        st_bf16(tile + sw128_off(r, d & 63), __bfloat162float(k[row0 + (int64_t)r * HD + d]) * run);
+        run *= f32r[i];
+      }
+    } else {
+      float run = (wq_ == 3) ? tot[4 * TD + d] * tot[5 * TD + d] : 1.f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const int r = 32 * wq_ + i;
+        run *= f32r[i];
+        st_bf16(tile + sw128_off(r, d & 63), __bfloat162float(q[row0 + (int64_t)r * HD + d]) * run);
+      }
+    }
+  }
+  float eG = 1.f;
+#pragma unroll
+  for (int b2 = 0; b2 < 8; ++b2) eG *= tot[b2 * TD + d];
+  const float dG = dG1[d] + eG * dG2[d];
+
+  // ---- phase 2: two passes over the rows ----------------------------------------------------------------------
+  uint32_t ph1 = 0, ph2 = 0;      // completed-phase counters of bars[1], bars[2]
+  const uint32_t aW64 = smem_u32(sm + BwdSmem::W64), aWL = smem_u32(sm + BwdSmem::WL), aDPL = smem_u32(sm + BwdSmem::DPL);
+  const int rq = wq_;
+  float later = 0.f;              // sum of dlam over all rows after this thread's run (filled per pass)
+#pragma unroll 1
+  for (int p = 1; p >= 0; --p) {
+    const int rbase = 64 * p + 16 * rq;
+    const int gi = 4 * p + rq;
+    float f[16], dq[16], dk[16];
+    uint32_t qk[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int64_t e = row0 + (int64_t)(rbase + i) * HD + d;
+      f[i] = __expf(g[e]);
+      qk[i] = (uint32_t)__bfloat16_as_ushort(q[e]) | ((uint32_t)__bfloat16_as_ushort(k[e]) << 16);
+    }
+    // inter-chunk terms and the diagonal
+    {
+      float crossq = 1.f, crossk = 1.f;
+      for (int b2 = 0; b2 < gi; ++b2) crossq *= tot[b2 * TD + d];
+      for (int b2 = gi + 1; b2 < 8; ++b2) crossk *= tot[b2 * TD + d];
+      uint32_t r[16];
+      tmem_ld16(tmem + ((uint32_t)(q4 * 32) << 16) + TM_DQH + rbase, r);
+      tmem_ld_wait();
+      float run = crossq;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        run *= f[i];
+        dq[i] = __uint_as_float(r[i]) * run + diag[rbase + i] * bf16_hi(qk[i]);
+      }
+      tmem_ld16(tmem + ((uint32_t)(q4 * 32) << 16) + TM_DKH + rbase, r);
+      tmem_ld_wait();
+      run = crossk;
+#pragma unroll
+      for (int i = 15; i >= 0; --i) {
+        dk[i] = __uint_as_float(r[i]) * run + diag[rbase + i] * bf16_lo(qk[i]);
+        run *= f[i];
+      }
+    }
+
+    // one level: build operands, issue; the accumulate of the previous level overlaps the MMA
+    auto build_and_issue = [&](auto SC) {
+      constexpr int S = decltype(SC)::value;
+      constexpr int HHv = 1 << S;
+      const int bsel = S & 1;
+      if (S < 6) {
+        float w[16];
+        level_weights<S>(f, rq, p, tot, d, w);
+        uint8_t* tile = sm + BwdSmem::WL + bsel * TILE_BYTES + (d >> 6) * KC_TILE;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float x = row_is_right<S>(i, rq, p) ? bf16_lo(qk[i]) : bf16_hi(qk[i]);
+          st_bf16(tile + sw128_off(16 * rq + i, d & 63), x * w[i]);
+        }
+      }
+      // masked 64 x 64 block of dP (row layout): rows i, columns j
+      {
+        const int ibase = (S == 6) ? 64 : 64 * p;
+        const int jbase = (S == 6) ? 0 : 64 * p;
+        if ((q4 >> 1) == (ibase >> 6)) {
+          const int i = 32 * q4 + lane;
+          uint32_t r[16];
+          tmem_ld16(tmem + ((uint32_t)(q4 * 32) << 16) + TM_DP + jbase + 16 * wq_, r);
+          tmem_ld_wait();
+          float x[16];
+#pragma unroll
+          for (int m = 0; m < 16; ++m) {
+            const int j = jbase + 16 * wq_ + m;
+            const bool keep = (S == 6) ? true : ((((i ^ j) >> S) == 1) && ((j & HHv) == 0));
+            x[m] = keep ? __uint_as_float(r[m]) : 0.f;
+          }
+          uint8_t* tile = sm + BwdSmem::DPL + bsel * (KC_TILE);
+#pragma unroll
+          for (int c2 = 0; c2 < 2; ++c2) {
+            uint4 u;
+            u.x = pack_bf16x2(x[8 * c2 + 0], x[8 * c2 + 1]);
+            u.y = pack_bf16x2(x[8 * c2 + 2], x[8 * c2 + 3]);
+            u.z = pack_bf16x2(x[8 * c2 + 4], x[8 * c2 + 5]);
+            u.w = pack_bf16x2(x[8 * c2 + 6], x[8 * c2 + 7]);
+            *reinterpret_cast<uint4*>(tile + sw128_chunk(i - ibase, 2 * wq_ + c2)) = u;
+          }
+        }
+      }
+      fence_async_smem();
+      tc_fence_before();
+      __syncthreads();
+      if (tid == 0) {
+        tc_fence_after();
+        const uint32_t tacc = tmem + TM_T + 64 * bsel;
+        const uint32_t bD = aDPL + bsel * KC_TILE;
+        constexpr uint32_t iK = idesc_bf16(128, 64, 1, 0), iM = idesc_bf16(128, 64, 1, 1);
+        if (S < 6) {
+          const uint32_t aW = aWL + bsel * TILE_BYTES;
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)    // rows i of the half on the columns: dq side
+            umma_bf16(tacc, desc_mnmajor(aW, KC_TILE, ks), desc_kmajor(bD, KC_TILE, ks), iK, ks > 0);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)    // rows j on the columns: dk side
+            umma_bf16(tacc, desc_mnmajor(aW, KC_TILE, ks), desc_mnmajor(bD, KC_TILE, ks), iM, 1);
+        } else if (p == 1) {
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)    // T[d][i-64] = sum_{j<64} k~64[j][d] dP[i][j]
+            umma_bf16(tacc, desc_mnmajor(aW64, TILE_BYTES, ks), desc_kmajor(bD, KC_TILE, ks), iK, ks > 0);
+        } else {
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)    // T[d][j] = sum_{i>=64} q~64[i][d] dP[i][j]
+            umma_bf16(tacc, desc_mnmajor(aW64 + 64 * 128, TILE_BYTES, ks), desc_mnmajor(bD, KC_TILE, ks), iM, ks > 0);
+        }
+        umma_commit(smem_u32(bars + 1 + bsel));
+      }
+    };
+    auto accumulate = [&](auto SC) {
+      constexpr int S = decltype(SC)::value;
+      const int bsel = S & 1;
+      if (bsel == 0) { ok = mbar_wait(smem_u32(bars + 1), ph1 & 1) && ok; ++ph1; }
+      else           { ok = mbar_wait(smem_u32(bars + 2), ph2 & 1) && ok; ++ph2; }
+      tc_fence_after();
+      uint32_t r[16];
+      tmem_ld16(tmem + ((uint32_t)(q4 * 32) << 16) + TM_T + 64 * bsel + 16 * rq, r);
+      tmem_ld_wait();
+      float w[16];
+      level_weights<S>(f, rq, p, tot, d, w);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float t = __uint_as_float(r[i]) * w[i];
+        if (row_is_right<S>(i, rq, p)) dq[i] += t; else dk[i] += t;
+      }
+    };
+    using I0 = std::integral_constant<int, 0>; using I1 = std::integral_constant<int, 1>;
+    using I2 = std::integral_constant<int, 2>; using I3 = std::integral_constant<int, 3>;
+    using I4 = std::integral_constant<int, 4>; using I5 = std::integral_constant<int, 5>;
+    using I6 = std::integral_constant<int, 6>;
+    build_and_issue(I0{});
+    build_and_issue(I1{});
+    accumulate(I0{});
+    build_and_issue(I2{});
+    accumulate(I1{});
+    build_and_issue(I3{});
+    accumulate(I2{});
+    build_and_issue(I4{});
+    accumulate(I3{});
+    build_and_issue(I5{});
+    accumulate(I4{});
+    build_and_issue(I6{});
+    accumulate(I5{});
+    accumulate(I6{});
+
+    // ---- outputs of this pass ---------------------------------------------------------------------------
+    float dl[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int64_t e = row0 + (int64_t)(rbase + i) * HD + d;
+      dl[i] = bf16_lo(qk[i]) * dq[i] - bf16_hi(qk[i]) * dk[i];
+      if (ok) {
+        dq_out[e] = __float2bfloat16_rn(dq[i]);
+        dk_out[e] = __float2bfloat16_rn(dk[i]);
+      }
+    }
+#pragma unroll
+    for (int i = 14; i >= 0; --i) dl[i] += dl[i + 1];      // inclusive suffix sums within the run
+    grp[gi * TD + d] = dl[0];
+    tc_fence_before();
+    __syncthreads();
+    float off = dG + later;
+    for (int g2 = gi + 1; g2 < 4 * p + 4; ++g2) off += grp[g2 * TD + d];
+    if (ok) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) dg_out[row0 + (int64_t)(rbase + i) * HD + d] = dl[i] + off;
+    }
+    if (p == 1) {
+      later = 0.f;
+      for (int g2 = 4; g2 < 8; ++g2) later += grp[g2 * TD + d];
+    }
+  }
+  if (!ok && tid == 0) atomicAdd(&g_tc_wait_timeouts, 1u);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
 // Sum of G over the chunks of a slice: G_total (B*H, D) = sum_n Gc[bh, n, d].
 __global__ void __launch_bounds__(256) tc_gsum_kernel(int64_t BH, int64_t N, const float* __restrict__ Gc,
                                                       float* __restrict__ Gt) {
@@ -532,7 +991,7 @@ __global__ void __launch_bounds__(256) tc_gsum_kernel(int64_t BH, int64_t N, con
 // Host side
 // ---------------------------------------------------------------------------------------
 bool tc_supported(int64_t D, int64_t C, int dtype) { return D == TD && C == TC && dtype == GLA_BF16; }
-bool tc_auto_default() { return false; }
+bool tc_auto_default() { return true; }
 
 static size_t f32b(int64_t n) { return align_up((size_t)n * 4, 256); }
 
@@ -548,7 +1007,11 @@ size_t tc_fwd_ws_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t C) {
   const int64_t N = T / C, BH = B * H;
   return f32b(BH * N * D * D) + f32b(BH * N * D) + b16b(BH * N * D * D);
 }
-size_t tc_bwd_ws_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t C) { return simt_bwd_ws_bytes(B, T, H, D, C); }
+// bwd workspace: dstate f32 (BH,N,D,D) | dS_next bf16 (BH,N,D,D)
+size_t tc_bwd_ws_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t C) {
+  const int64_t N = T / C, BH = B * H;
+  return f32b(BH * N * D * D) + b16b(BH * N * D * D);
+}
 
 constexpr size_t FWD_SMEM = 1024 + FwdSmem::END;
 
@@ -587,9 +1050,31 @@ int tc_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
   return GLA_OK;
 }
 
-int tc_chunk_bwd(cudaStream_t, int64_t, int64_t, int64_t, int64_t, int64_t, const float*, const void*, const void*,
-                 const void*, const void*, const void*, const void*, void*, float*, void*, void*, void*, void*) {
-  return GLA_ERR_UNSUPPORTED;
+constexpr size_t BWD_SMEM = 1024 + BwdSmem::END;
+
+int tc_chunk_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, int64_t C, const float* g,
+                 const void* v, const void* k, const void* q, const void* saved, const void* dhidden_final,
+                 const void* dout, void* dhidden_init, float* dg, void* dv, void* dk, void* dq, void* ws) {
+  const int64_t N = T / C, BH = B * H;
+  char* w = (char*)ws;
+  float* dstate = (float*)w; w += f32b(BH * N * D * D);
+  bf16* dS_next = (bf16*)w;
+  const char* s = (const char*)saved;
+  const bf16* S_prev = (const bf16*)s; s += b16b(BH * N * D * D);
+  const float* Gc = (const float*)s;   s += f32b(BH * N * D);
+  const bf16* P = (const bf16*)s;
+  GLA_TRY((launch_tc_kv<1>(st, B, T, H, g, q, dout, dstate, nullptr)));
+  GLA_TRY(launch_state_scan(st, BH, N, D, Gc, dstate, 0, dhidden_final, 1, dS_next, 1, dhidden_init, 1, 1));
+  cudaError_t e = cudaFuncSetAttribute(tc_chunk_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)BWD_SMEM);
+  if (e != cudaSuccess) return record_cuda_error(e);
+  {
+    ProfScope ps("tc_chunk_bwd_kernel", st);
+    tc_chunk_bwd_kernel<<<(unsigned)(BH * N), TTHREADS, BWD_SMEM, st>>>(
+        T, H, N, g, (const bf16*)v, (const bf16*)k, (const bf16*)q, (const bf16*)dout, S_prev, dS_next, P, (bf16*)dq,
+        (bf16*)dk, (bf16*)dv, dg);
+  }
+  GLA_CHECK_LAUNCH();
+  return GLA_OK;
 }
 
 unsigned int tc_read_wait_timeouts() {

@@ -79,6 +79,60 @@ def test_chunk_gla_fp32_kernels_vs_oracle(cuda_device, B, T, H, D, C, dtype, shi
     _compare(ref, got, dtype, f"chunk_gla fp32 kernels {B,T,H,D,C,dtype}")
 
 
+TC_CASES = [
+    # B, T, H, shift, zero_init   (bf16, D = chunk = 128: the shapes the tcgen05 kernels serve)
+    (1, 128, 1, 5.0, False),       # one chunk
+    (1, 512, 2, 5.0, False),
+    (2, 512, 3, 0.0, False),       # sharp gates (BASELINE config 5's gate distribution)
+    (1, 256, 2, -3.0, False),      # very sharp gates: every level's weights underflow gracefully
+    (2, 384, 2, 5.0, True),        # zero initial state, three chunks
+]
+
+
+@pytest.mark.parametrize("B,T,H,shift,zero_init", TC_CASES)
+def test_chunk_gla_tcgen05_vs_oracle(cuda_device, B, T, H, shift, zero_init):
+    from gla_jax_b200 import chunk_gla, _lib
+    case = _case(B, T, H, 128, torch.bfloat16, 21, shift, zero_init)
+    ref = _oracle(*case)
+    got = _run_gpu(chunk_gla, cuda_device, *case, chunk_size=128, impl="tcgen05")
+    assert _lib.load().gla_device_wait_timeouts() == 0
+    _compare(ref, got, torch.bfloat16, f"chunk_gla tcgen05 {B,T,H,shift}")
+
+
+def test_auto_picks_tcgen05_for_readme_shape(cuda_device):
+    """impl='auto' must run the tensor-core kernels at D = chunk = 128 in bf16 (checked through
+    the library's own launch profile) and the fp32 kernels elsewhere."""
+    import ctypes
+    from gla_jax_b200 import chunk_gla, _lib
+    lib = _lib.load()
+    for dtype, D, C, want in ((torch.bfloat16, 128, 128, b"tc_chunk_fwd_kernel"), (torch.float32, 64, 64, b"simt_score_kernel")):
+        h, g, v, k, q = (x.to(cuda_device) for x in O.make_inputs(1, 2 * C, 2, D, dtype, seed=3))
+        lib.gla_profile_enable(1)
+        chunk_gla(h, g, v, k, q, chunk_size=C)
+        lib.gla_profile_enable(0)
+        buf = ctypes.create_string_buffer(1 << 14)
+        lib.gla_profile_report(buf, len(buf))
+        assert want in buf.value, buf.value
+
+
+def test_tcgen05_matches_recurrent_at_readme_shape(cuda_device):
+    """Full BASELINE config 2 shape (B=4, H=6, D=128, T=4096, bf16), forward and backward: the
+    tensor-core chunk path against recurrent_gla (exact fp32 recurrence) on the GPU, since the
+    CPU oracle cannot afford this size.  Same tolerances as against the oracle."""
+    from gla_jax_b200 import chunk_gla, recurrent_gla
+    case = _case(4, 4096, 6, 128, torch.bfloat16, 31, 5.0)
+    a = _run_gpu(recurrent_gla, cuda_device, *case)
+    b = _run_gpu(chunk_gla, cuda_device, *case, chunk_size=128, impl="tcgen05")
+    _compare(a, b, torch.bfloat16, "tcgen05 vs recurrent at config 2")
+    # size-independent property: chaining two half-length calls equals one call (gla.py:720-723)
+    h, g, v, k, q = (x.to(cuda_device) for x in case[:5])
+    with torch.no_grad():
+        hf, out = chunk_gla(h, g, v, k, q, chunk_size=128)
+        h1, o1 = chunk_gla(h, g[:, :2048], v[:, :2048], k[:, :2048], q[:, :2048], chunk_size=128)
+        h2, o2 = chunk_gla(h1, g[:, 2048:], v[:, 2048:], k[:, 2048:], q[:, 2048:], chunk_size=128)
+    assert O.rel_l2(hf.cpu(), h2.cpu()) < 1e-2 and O.rel_l2(out.cpu(), torch.cat([o1, o2], 1).cpu()) < 1e-2
+
+
 @pytest.mark.parametrize("B,T,H,D,dtype,shift,reverse", [
     (1, 256, 2, 64, torch.float32, 5.0, False),
     (2, 100, 3, 32, torch.float32, 0.0, False),          # T not a multiple of the time block
