@@ -192,6 +192,34 @@ GLA_API int gla_chunk_bwd(void* stream, int64_t B, int64_t T, int64_t H, int64_t
                   void* dvalue, void* dkey, void* dquery,
                   void* workspace, size_t workspace_bytes);
 
+/* gla_chunk_fwd_static: the forward of gla_chunk_fwd (no residuals, so not differentiable)
+ * for callers that cannot give the library a workspace.  (No counterpart in the reference,
+ * where XLA owns all memory.)
+ *
+ * Who needs it: code that runs where device allocation is not available to it - a custom
+ * call inside a runtime that owns the allocator and exposes no scratch to the callee, a
+ * plugin in a serving process whose memory pool is closed, a callback in a region where
+ * cudaMalloc would fail or stall the device.  Such a caller still passes inputs and outputs,
+ * but the scratch comes from a fixed array inside the library image:
+ *   - the array is gla_chunk_fwd_static_max_bytes() = 32 MiB of device memory PER GPU, held
+ *     from the first use of the library on that GPU until the process exits;
+ *   - a problem whose gla_chunk_fwd_workspace_bytes() exceeds it returns GLA_ERR_TOO_LARGE
+ *     and launches nothing (32 MiB covers, e.g., one sequence of T=4096, H=6, D=128);
+ *   - the function allocates nothing and frees nothing, on host or device.  The first call
+ *     on each device looks up the array's device address (a symbol query, with that device
+ *     current); make that first call outside any stream capture;
+ *   - every call on a device uses the SAME array, and it keeps whatever the previous call
+ *     left there.  Nothing in it has to start at zero (each launch sequence writes every
+ *     word before reading it), but two calls whose kernels overlap on the GPU - different
+ *     streams, or different host threads - race on it: serialise them on one stream.
+ * Arguments, layouts, validation and status codes otherwise match gla_chunk_fwd. */
+GLA_API size_t gla_chunk_fwd_static_max_bytes(void);
+GLA_API int gla_chunk_fwd_static(void* stream, int64_t B, int64_t T, int64_t H, int64_t D, int64_t chunk,
+                         int dtype, int impl,
+                         const void* hidden_init, const float* log_fgate,
+                         const void* value, const void* key, const void* query,
+                         void* hidden_final, void* out);
+
 /* ------------------------------------------------------------------------------------
  * Sequence-parallel support (no counterpart in the reference, which is single-device; the
  * algebra is ops.py:286 binary_operator applied across ranks and the exact chaining of
