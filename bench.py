@@ -165,6 +165,7 @@ def main():
     ap.add_argument("--chunk-impl", default="auto", choices=["auto", "fp32", "tcgen05"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (for profiler runs)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -261,16 +262,18 @@ def main():
         loss.backward()
         return float(loss.item())       # 4-byte device->host read; also orders the step
 
-    for _ in range(3):
-        e2e_step()
-    barrier()
-    e_evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
-    for i in range(K):
-        e_evs[i][0].record()
-        e2e_step()
-        e_evs[i][1].record()
-    barrier()
-    e2e_ms = sum(a.elapsed_time(b) for a, b in e_evs)
+    e2e_ms = float("nan")
+    if not args.no_e2e:
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        e_evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+        for i in range(K):
+            e_evs[i][0].record()
+            e2e_step()
+            e_evs[i][1].record()
+        barrier()
+        e2e_ms = sum(a.elapsed_time(b) for a, b in e_evs)
     sampler.stop_flag = True
     sampler.join(timeout=1.0)
 
