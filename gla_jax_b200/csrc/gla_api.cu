@@ -259,7 +259,7 @@ int gla_sp_combine(void* stream, int64_t R, int64_t rank, int64_t BH, int64_t D,
                    const float* all_S, const void* init, int init_dtype, void* result, int result_dtype,
                    int reverse) {
   if (!all_G || !all_S || !result) return GLA_ERR_NULL_POINTER;
-  if (R <= 0 || rank < 0 || rank >= R || BH <= 0 || D <= 0) return GLA_ERR_BAD_DIMS;
+  if (R <= 0 || rank < -1 || rank > R || BH <= 0 || D <= 0) return GLA_ERR_BAD_DIMS;
   GLA_TRY(check_dtype(init_dtype));
   GLA_TRY(check_dtype(result_dtype));
   return launch_sp_combine((cudaStream_t)stream, R, rank, BH, D, all_G, all_S, init, init_dtype == GLA_BF16, result,

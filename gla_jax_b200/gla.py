@@ -60,50 +60,65 @@ def _prepare(hidden, log_fgate, value, key, query):
             batched)
 
 
+def _chunk_fwd_raw(hidden, g32, v, k, q, chunk, impl, need_grad):
+    """gla_chunk_fwd on batched contiguous tensors -> (hidden_final, out, (saved,) or ())."""
+    lib = _lib.load()
+    B, T, H, D = v.shape
+    dt = _DT[v.dtype]
+    dev = v.device
+    ws_n = lib.gla_chunk_fwd_workspace_bytes(B, T, H, D, chunk, dt, impl)
+    if ws_n == 0:
+        raise _lib.GlaError(f"chunk_gla: unsupported configuration T={T} H={H} D={D} chunk={chunk} dtype={v.dtype}")
+    saved = None
+    if need_grad:
+        saved = torch.empty(lib.gla_chunk_saved_bytes(B, T, H, D, chunk, dt, impl), dtype=torch.uint8, device=dev)
+    ws = torch.empty(ws_n, dtype=torch.uint8, device=dev)
+    hf = torch.empty_like(hidden)
+    out = torch.empty_like(v)
+    st = lib.gla_chunk_fwd(_stream(dev), B, T, H, D, chunk, dt, impl, _ptr(hidden), _ptr(g32), _ptr(v), _ptr(k),
+                           _ptr(q), _ptr(hf), _ptr(out), _ptr(saved), _ptr(ws), ws_n)
+    _lib.check(st, "gla_chunk_fwd")
+    return hf, out, ((saved,) if need_grad else ())
+
+
+def _chunk_bwd_raw(g32, v, k, q, residuals, dhf, dout, chunk, impl):
+    """gla_chunk_bwd -> (dhidden_init, dlog_fgate (float32), dvalue, dkey, dquery)."""
+    lib = _lib.load()
+    (saved,) = residuals
+    B, T, H, D = v.shape
+    dt = _DT[v.dtype]
+    dev = v.device
+    ws_n = lib.gla_chunk_bwd_workspace_bytes(B, T, H, D, chunk, dt, impl)
+    ws = torch.empty(ws_n, dtype=torch.uint8, device=dev)
+    dh = torch.empty(B, H, D, D, dtype=v.dtype, device=dev)
+    dg = torch.empty_like(g32)
+    dv, dk, dq = torch.empty_like(v), torch.empty_like(k), torch.empty_like(q)
+    st = lib.gla_chunk_bwd(_stream(dev), B, T, H, D, chunk, dt, impl, _ptr(g32), _ptr(v), _ptr(k), _ptr(q),
+                           _ptr(saved), _ptr(dhf), _ptr(dout), _ptr(dh), _ptr(dg), _ptr(dv), _ptr(dk), _ptr(dq),
+                           _ptr(ws), ws_n)
+    _lib.check(st, "gla_chunk_bwd")
+    return dh, dg, dv, dk, dq
+
+
 class _ChunkGLA(torch.autograd.Function):
     """custom-VJP pair of chunk_gla (gla.py:628-655)."""
 
     @staticmethod
     def forward(ctx, hidden, g, v, k, q, chunk, impl):
-        lib = _lib.load()
-        B, T, H, D = v.shape
-        dt = _DT[v.dtype]
         g32 = g if g.dtype == torch.float32 else g.float()
         need_grad = any(ctx.needs_input_grad[:5])
-        dev = v.device
-        saved_n = lib.gla_chunk_saved_bytes(B, T, H, D, chunk, dt, impl) if need_grad else 0
-        ws_n = lib.gla_chunk_fwd_workspace_bytes(B, T, H, D, chunk, dt, impl)
-        if ws_n == 0:
-            raise _lib.GlaError(f"chunk_gla: unsupported configuration T={T} H={H} D={D} chunk={chunk} dtype={v.dtype}")
-        saved = torch.empty(saved_n, dtype=torch.uint8, device=dev) if need_grad else None
-        ws = torch.empty(ws_n, dtype=torch.uint8, device=dev)
-        hf = torch.empty_like(hidden)
-        out = torch.empty_like(v)
-        st = lib.gla_chunk_fwd(_stream(dev), B, T, H, D, chunk, dt, impl, _ptr(hidden), _ptr(g32), _ptr(v), _ptr(k),
-                               _ptr(q), _ptr(hf), _ptr(out), _ptr(saved), _ptr(ws), ws_n)
-        _lib.check(st, "gla_chunk_fwd")
-        ctx.save_for_backward(g32, v, k, q, saved)
+        hf, out, res = _chunk_fwd_raw(hidden, g32, v, k, q, chunk, impl, need_grad)
+        ctx.save_for_backward(g32, v, k, q, *res)
         ctx.chunk, ctx.impl, ctx.g_dtype = chunk, impl, g.dtype
         return hf, out
 
     @staticmethod
     def backward(ctx, dhf, dout):
-        lib = _lib.load()
-        g32, v, k, q, saved = ctx.saved_tensors
+        g32, v, k, q, *res = ctx.saved_tensors
         B, T, H, D = v.shape
-        dt = _DT[v.dtype]
-        dev = v.device
-        dhf = torch.zeros(B, H, D, D, dtype=v.dtype, device=dev) if dhf is None else dhf.to(v.dtype).contiguous()
+        dhf = torch.zeros(B, H, D, D, dtype=v.dtype, device=v.device) if dhf is None else dhf.to(v.dtype).contiguous()
         dout = torch.zeros_like(v) if dout is None else dout.to(v.dtype).contiguous()
-        ws_n = lib.gla_chunk_bwd_workspace_bytes(B, T, H, D, ctx.chunk, dt, ctx.impl)
-        ws = torch.empty(ws_n, dtype=torch.uint8, device=dev)
-        dh = torch.empty(B, H, D, D, dtype=v.dtype, device=dev)
-        dg = torch.empty_like(g32)
-        dv, dk, dq = torch.empty_like(v), torch.empty_like(k), torch.empty_like(q)
-        st = lib.gla_chunk_bwd(_stream(dev), B, T, H, D, ctx.chunk, dt, ctx.impl, _ptr(g32), _ptr(v), _ptr(k), _ptr(q),
-                               _ptr(saved), _ptr(dhf), _ptr(dout), _ptr(dh), _ptr(dg), _ptr(dv), _ptr(dk), _ptr(dq),
-                               _ptr(ws), ws_n)
-        _lib.check(st, "gla_chunk_bwd")
+        dh, dg, dv, dk, dq = _chunk_bwd_raw(g32, v, k, q, tuple(res), dhf, dout, ctx.chunk, ctx.impl)
         return dh, dg.to(ctx.g_dtype), dv, dk, dq, None, None
 
 

@@ -237,7 +237,9 @@ GLA_API int gla_chunk_fwd_static(void* stream, int64_t B, int64_t T, int64_t H, 
  *   backward (reverse != 0): the mirror image over ranks p > rank, used for dhidden_final,
  * where `init` (B, H, D, D) has dtype init_dtype (hidden_init on the forward pass,
  * dhidden_final of the whole sequence on the backward pass) and `result` has dtype
- * result_dtype.  The decay multiplies along the key axis.
+ * result_dtype.  The decay multiplies along the key axis.  rank may also be R (forward: the
+ * state after the last rank = hidden_final of the whole sequence) or -1 (backward: the
+ * gradient reaching hidden_init of the whole sequence).
  * ---------------------------------------------------------------------------------- */
 GLA_API int gla_chunk_local_state(void* stream, int64_t B, int64_t T, int64_t H, int64_t D, int64_t chunk,
                           int dtype, int impl,
