@@ -67,9 +67,27 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB
 
 
+def build_xla_ffi() -> Path:
+    """Compile csrc/gla_xla_ffi.cc into libgla_b200_xla.so against jaxlib's XLA FFI headers.
+    Needs an importable jax (jax.ffi.include_dir()); raises otherwise."""
+    import jax  # noqa: F401  (ImportError here means: no jax in this environment)
+    inc = jax.ffi.include_dir()
+    out = PKG / "libgla_b200_xla.so"
+    cmd = [NVCC, "-std=c++17", "-O2", "-shared", "-Xcompiler", "-fPIC", "-I", inc, str(CSRC / "gla_xla_ffi.cc"),
+           "-o", str(out), "-L", str(PKG), "-lgla_b200", "-Xlinker", "-rpath,$ORIGIN"]
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if r.returncode != 0:
+        sys.stderr.write(r.stdout)
+        raise RuntimeError("building the XLA FFI handlers failed")
+    return out
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--with-jax", action="store_true", help="also build the XLA FFI handler library")
     a = ap.parse_args()
     print(build(a.force, a.verbose))
+    if a.with_jax:
+        print(build_xla_ffi())

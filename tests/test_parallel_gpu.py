@@ -65,7 +65,7 @@ def _nccl_worker(rank, world, port, q_out):
         hf, out = P.sequence_parallel_chunk_gla(*leaves, chunk_size=C)
         grads = torch.autograd.grad((hf.float() * dhf.to(dev).float()).sum() + (out.float() * do[:, sl].to(dev).float()).sum(), leaves)
         torch.cuda.synchronize()
-        q_out.put((rank, hf.cpu(), out.cpu(), [x.cpu() for x in grads]))
+        q_out.put((rank, hf.detach().cpu(), out.detach().cpu(), [x.detach().cpu() for x in grads]))
     finally:
         dist.destroy_process_group()
 
@@ -81,7 +81,7 @@ def test_sequence_parallel_nccl_two_gpus(cuda_device):
     procs = [ctx.Process(target=_nccl_worker, args=(r, world, port, q_out)) for r in range(world)]
     for p in procs:
         p.start()
-    res = sorted([q_out.get(timeout=300) for _ in range(world)], key=lambda x: x[0])
+    res = sorted([q_out.get(timeout=120) for _ in range(world)], key=lambda x: x[0])
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
