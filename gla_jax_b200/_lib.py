@@ -23,6 +23,7 @@ SIGNATURES = {
     "gla_last_cuda_error": (c_int, []),
     "gla_launch_count": (ctypes.c_longlong, []),
     "gla_device_wait_timeouts": (ctypes.c_uint, []),
+    "gla_debug_phase_clocks": (None, [c_void_p]),
     "gla_profile_enable": (None, [c_int]),
     "gla_profile_report": (c_size_t, [c_char_p, c_size_t]),
     "gla_cumsum": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int]),

@@ -83,6 +83,9 @@ long long gla_launch_count(void) { return g_launches; }
 
 unsigned int gla_device_wait_timeouts(void) { return tc_read_wait_timeouts(); }
 
+void gla_debug_phase_clocks(long long* out64) { tc_read_trace(out64); }
+__attribute__((visibility("default"))) void gla_debug_wtrace(long long* o) { tc_read_wtrace(o); }
+
 void gla_profile_enable(int on) {
   g_prof_on = on != 0;
   if (on) g_prof_n = 0;

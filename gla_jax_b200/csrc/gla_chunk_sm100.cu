@@ -18,6 +18,7 @@
 #include "gla_common.cuh"
 #include "tc_ptx.cuh"
 #include <type_traits>
+#include <cuda.h>
 
 namespace gla {
 
@@ -29,6 +30,13 @@ constexpr int TTHREADS = 512;
 constexpr uint32_t TILE_BYTES = 128 * 128;     // one SW128 tile of 128 rows
 
 __device__ unsigned int g_tc_wait_timeouts = 0;   // incremented when a bounded wait gives up
+
+// Phase clock stamps of one thread block (block 100, thread 0) of the last forward / backward
+// chunk kernel: a cheap always-on diagnostic read back by gla_debug_phase_clocks().
+__device__ long long g_tc_trace[2][32];
+__device__ long long g_tc_wtrace[16][32];
+#define TC_WSTAMP(idx) do { if (blockIdx.x == 500 && (threadIdx.x & 31) == 0) g_tc_wtrace[threadIdx.x >> 5][idx] = clock64(); } while (0)
+#define TC_STAMP(which, idx) do { if (blockIdx.x == 500 && threadIdx.x == 0) g_tc_trace[which][idx] = clock64(); } while (0)
 
 // smem carve-up helper: dynamic shared memory aligned to 1024 bytes
 __device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
@@ -207,81 +215,98 @@ static int launch_tc_kv(cudaStream_t st, int64_t B, int64_t T, int64_t H, const 
 // P tile, columns [0, 128) are reused for the output accumulator.
 // ---------------------------------------------------------------------------------------
 struct FwdSmem {
-  static constexpr uint32_t Q = 0;                         // 2 buffers x 32 KB   (q~ / q_hat)
-  static constexpr uint32_t K = Q + 2 * 2 * TILE_BYTES;    // 2 buffers x 16 KB   (compact k~)
+  static constexpr uint32_t Q = 0;                         // 2 buffers x 32 KB   (q~ / q_hat); TMA lands g here first
+  static constexpr uint32_t K = Q + 2 * 2 * TILE_BYTES;    // 2 buffers x 16 KB   (compact k~);  TMA lands raw q here first
   static constexpr uint32_t V = K + 2 * TILE_BYTES;        // 32 KB
   static constexpr uint32_t S = V + 2 * TILE_BYTES;        // 32 KB
-  static constexpr uint32_t P = S + 2 * TILE_BYTES;        // 32 KB
+  static constexpr uint32_t P = S + 2 * TILE_BYTES;        // 32 KB;               TMA lands raw k here first
   static constexpr uint32_t TOT = P + 2 * TILE_BYTES;      // 8 x 128 float
   static constexpr uint32_t DIAG = TOT + 8 * TD * 4;       // 2 x 128 float
-  static constexpr uint32_t BAR = DIAG + 2 * TC * 4;       // 3 mbarriers + tmem slot
+  static constexpr uint32_t BAR = DIAG + 2 * TC * 4;       // 4 mbarriers + tmem slot
   static constexpr uint32_t END = BAR + 64;
 };
 constexpr uint32_t KC_TILE = 64 * 128;    // one SW128 tile of 64 rows
 
-template <int HH>
-__device__ __forceinline__ void emit_level_local(const float2 (&pre)[16], const float2 (&suf)[16],
-                                                 const uint32_t (&qv)[16], const uint32_t (&kv)[16], uint8_t* sQb,
-                                                 uint8_t* sKb, int rg, int cp) {
-  constexpr int LG = HH == 1 ? 0 : HH == 2 ? 1 : HH == 4 ? 2 : 3;
+// TMA descriptors of one launch (built on the host per call, passed by value).
+struct FwdMaps { CUtensorMap g, q, k, v, s; };
+
+// Operands of level slot S (half size 2^S) for the thread's 16 rows x 2 columns, with the decay
+// weights formed on the fly as running products of the gates f (no weight arrays are kept):
+// rows in a right half write q~ (inclusive prefix from the half's first row), rows in a left
+// half write k~ at their compact index (exclusive suffix to the half's last row).
+template <int S>
+__device__ __forceinline__ void fwd_emit(const float2 (&f)[16], const uint32_t (&qv)[16], const uint32_t (&kv)[16],
+                                         uint8_t* sQb, uint8_t* sKb, int rg, int cp, const float* tot) {
+  constexpr int HH = 1 << S;
   const int tile = cp >> 5, col = (2 * cp) & 63;
+  uint8_t* qb = sQb + tile * TILE_BYTES;
+  uint8_t* kb = sKb + tile * KC_TILE;
+  if (S < 4) {
+    float2 run = make_float2(1.f, 1.f);
 #pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const int r = rg * 16 + i;
-    if (i & HH) {
-      const float2 x = unpack_bf16x2(qv[i]);
-      *reinterpret_cast<uint32_t*>(sQb + tile * TILE_BYTES + sw128_off(r, col)) = pack_bf16x2(x.x * pre[i].x, x.y * pre[i].y);
+    for (int i = 0; i < 16; ++i) {
+      if (i % HH == 0) run = f[i]; else { run.x *= f[i].x; run.y *= f[i].y; }
+      if (i & HH) {
+        const float2 x = unpack_bf16x2(qv[i]);
+        *reinterpret_cast<uint32_t*>(qb + sw128_off(rg * 16 + i, col)) = pack_bf16x2(x.x * run.x, x.y * run.y);
+      }
+    }
+#pragma unroll
+    for (int i = 15; i >= 0; --i) {
+      if (i % HH == HH - 1) run = make_float2(1.f, 1.f);
+      if (!(i & HH)) {
+        const float2 x = unpack_bf16x2(kv[i]);
+        const int r = rg * 16 + i;
+        const int c = ((r >> (S + 1)) << S) + (r & (HH - 1));
+        *reinterpret_cast<uint32_t*>(kb + sw128_off(c, col)) = pack_bf16x2(x.x * run.x, x.y * run.y);
+      }
+      run.x *= f[i].x; run.y *= f[i].y;
+    }
+  } else {
+    auto tot_at = [&](int r2) { return *reinterpret_cast<const float2*>(tot + r2 * TD + 2 * cp); };
+    bool right;
+    float2 run = make_float2(1.f, 1.f);
+    if (S == 4) {
+      right = (rg & 1) != 0;
+    } else if (S == 5) {
+      const int m = rg & 3;
+      right = m >= 2;
+      if (m == 3) run = tot_at(rg - 1);
+      if (m == 0) run = tot_at(rg + 1);
     } else {
-      const float2 x = unpack_bf16x2(kv[i]);
-      const int c = ((r >> (LG + 1)) << LG) + (r & (HH - 1));
-      *reinterpret_cast<uint32_t*>(sKb + tile * KC_TILE + sw128_off(c, col)) = pack_bf16x2(x.x * suf[i].x, x.y * suf[i].y);
+      right = rg >= 4;
+      if (right) { for (int r2 = 4; r2 < rg; ++r2) { const float2 t = tot_at(r2); run.x *= t.x; run.y *= t.y; } }
+      else       { for (int r2 = rg + 1; r2 < 4; ++r2) { const float2 t = tot_at(r2); run.x *= t.x; run.y *= t.y; } }
     }
-  }
-}
-// pre/suf for half size HH -> half size 2 HH (in place)
-template <int HH>
-__device__ __forceinline__ void widen_products(float2 (&pre)[16], float2 (&suf)[16]) {
-#pragma unroll
-  for (int s0 = 0; s0 < 16; s0 += 2 * HH) {
-    const float2 tf = pre[s0 + HH - 1], ts = pre[s0 + 2 * HH - 1];
-#pragma unroll
-    for (int i = 0; i < HH; ++i) {
-      suf[s0 + i].x *= ts.x; suf[s0 + i].y *= ts.y;
-      pre[s0 + HH + i].x *= tf.x; pre[s0 + HH + i].y *= tf.y;
-    }
-  }
-}
-// Level with half size >= 16: every row of the thread is on the same side.
-__device__ __forceinline__ void emit_level_wide(int h, int lg, bool right, float2 cross, const float2 (&pre)[16],
-                                                const float2 (&suf)[16], const uint32_t (&qv)[16],
-                                                const uint32_t (&kv)[16], uint8_t* sQb, uint8_t* sKb, int rg, int cp) {
-  const int tile = cp >> 5, col = (2 * cp) & 63;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const int r = rg * 16 + i;
     if (right) {
-      const float2 x = unpack_bf16x2(qv[i]);
-      *reinterpret_cast<uint32_t*>(sQb + tile * TILE_BYTES + sw128_off(r, col)) =
-          pack_bf16x2(x.x * pre[i].x * cross.x, x.y * pre[i].y * cross.y);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        run.x *= f[i].x; run.y *= f[i].y;
+        const float2 x = unpack_bf16x2(qv[i]);
+        *reinterpret_cast<uint32_t*>(qb + sw128_off(rg * 16 + i, col)) = pack_bf16x2(x.x * run.x, x.y * run.y);
+      }
     } else {
-      const float2 x = unpack_bf16x2(kv[i]);
-      const int c = ((r >> (lg + 1)) << lg) + (r & (h - 1));
-      *reinterpret_cast<uint32_t*>(sKb + tile * KC_TILE + sw128_off(c, col)) =
-          pack_bf16x2(x.x * suf[i].x * cross.x, x.y * suf[i].y * cross.y);
+#pragma unroll
+      for (int i = 15; i >= 0; --i) {
+        const float2 x = unpack_bf16x2(kv[i]);
+        const int r = rg * 16 + i;
+        const int c = ((r >> (S + 1)) << S) + (r & (HH - 1));
+        *reinterpret_cast<uint32_t*>(kb + sw128_off(c, col)) = pack_bf16x2(x.x * run.x, x.y * run.y);
+        run.x *= f[i].x; run.y *= f[i].y;
+      }
     }
   }
 }
 
 __global__ void __launch_bounds__(TTHREADS, 1)
-tc_chunk_fwd_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g, const bf16* __restrict__ v,
-                    const bf16* __restrict__ k, const bf16* __restrict__ q, const bf16* __restrict__ S_prev,
-                    bf16* __restrict__ out, bf16* __restrict__ P_saved) {
+tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, int64_t N, bf16* __restrict__ out,
+                    bf16* __restrict__ P_saved) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = align1024(smem_raw);
   float* tot = reinterpret_cast<float*>(sm + FwdSmem::TOT);
   float* diag = reinterpret_cast<float*>(sm + FwdSmem::DIAG);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + FwdSmem::BAR);   // [0],[1]: level buffers, [2]: output
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + FwdSmem::BAR);   // [0],[1]: level buffers, [2]: output, [3]: loads
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int rg = tid >> 6, cp = tid & 63;
@@ -289,32 +314,58 @@ tc_chunk_fwd_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g
   const int64_t HD = H * TD;
   const int64_t row0 = ((b * T + n * TC) * H + h_) * TD;
   const int64_t chunk_id = bh * N + n;
+  TC_STAMP(0, 0);
 
-  if (warp == 0) {
-    tmem_alloc(smem_u32(tmem_slot), 512);
-    tmem_relinquish();
-  }
   if (tid == 0) {
     mbar_init(smem_u32(bars + 0), 1);
     mbar_init(smem_u32(bars + 1), 1);
     mbar_init(smem_u32(bars + 2), 1);
+    mbar_init(smem_u32(bars + 3), 1);
     mbar_fence_init();
-  }
-
-  // ---- loads -----------------------------------------------------------------------------------
-  float2 pre[16], suf[16];
-  uint32_t qv[16], kv[16];
+    // ---- all global inputs of the chunk through TMA: 192 KB in flight on one barrier ----------
+    const uint32_t lb = smem_u32(bars + 3);
+    const int z = (int)(b * T + n * TC), y = (int)h_;
+    mbar_arrive_expect_tx(lb, 6 * 2 * TILE_BYTES);
+    tma_load_3d(smem_u32(sm + FwdSmem::Q), &maps.g, 0, y, z, lb);                       // 128 x 128 float, row pitch 512 B
 #pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const int64_t e = row0 + (int64_t)(rg * 16 + i) * HD + 2 * cp;
-    const float2 gg = *reinterpret_cast<const float2*>(g + e);
-    qv[i] = *reinterpret_cast<const uint32_t*>(q + e);
-    kv[i] = *reinterpret_cast<const uint32_t*>(k + e);
-    pre[i] = make_float2(__expf(gg.x), __expf(gg.y));
-    suf[i] = make_float2(1.f, 1.f);
+    for (int half = 0; half < 2; ++half) {
+      tma_load_3d(smem_u32(sm + FwdSmem::K + half * TILE_BYTES), &maps.q, 64 * half, y, z, lb);
+      tma_load_3d(smem_u32(sm + FwdSmem::P + half * TILE_BYTES), &maps.k, 64 * half, y, z, lb);
+      tma_load_3d(smem_u32(sm + FwdSmem::V + half * TILE_BYTES), &maps.v, 64 * half, y, z, lb);
+      tma_load_2d(smem_u32(sm + FwdSmem::S + half * TILE_BYTES), &maps.s, 64 * half, (int)(chunk_id * TD), lb);
+    }
   }
-  copy_tile_128x128(sm + FwdSmem::V, v + row0, HD);
-  copy_tile_128x128(sm + FwdSmem::S, S_prev + chunk_id * TD * TD, TD);
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();          // barrier inits and the TMEM address are visible
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  bool ok = mbar_wait(smem_u32(bars + 3), 0);
+  TC_STAMP(0, 1);
+
+  // ---- gates, q, k of the thread's 16 rows x 2 columns from the landed tiles ---------------------
+  float2 f[16];
+  uint32_t qv[16], kv[16];
+  {
+    const uint8_t* gq = sm + FwdSmem::Q;
+    const uint8_t* qt = sm + FwdSmem::K + (cp >> 5) * TILE_BYTES;
+    const uint8_t* kt = sm + FwdSmem::P + (cp >> 5) * TILE_BYTES;
+    const int col = (2 * cp) & 63;
+    float2 prod = make_float2(1.f, 1.f);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int r = rg * 16 + i;
+      const float2 gg = *reinterpret_cast<const float2*>(gq + r * 512 + cp * 8);
+      qv[i] = *reinterpret_cast<const uint32_t*>(qt + sw128_off(r, col));
+      kv[i] = *reinterpret_cast<const uint32_t*>(kt + sw128_off(r, col));
+      f[i] = make_float2(__expf(gg.x), __expf(gg.y));
+      prod.x *= f[i].x; prod.y *= f[i].y;
+    }
+    *reinterpret_cast<float2*>(tot + rg * TD + 2 * cp) = prod;
+  }
   // diagonal: sum_d q k, reduced over the 64 column-pair threads of a row group (two warps)
   {
     float part[16];
@@ -332,14 +383,11 @@ tc_chunk_fwd_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g
       for (int i = 0; i < 16; ++i) diag[(warp & 1) * TC + rg * 16 + i] = part[i];
     }
   }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *tmem_slot;
+  __syncthreads();          // raw g and q have been consumed: their regions become the level buffers
+  TC_STAMP(0, 2);
   const uint32_t sQ0 = smem_u32(sm + FwdSmem::Q), sK0 = smem_u32(sm + FwdSmem::K);
 
   auto issue_level = [&](int slot) {
-    // executed by thread 0 after the block-wide barrier that follows the operand build
     const int bsel = slot & 1;
     constexpr uint32_t idesc = idesc_bf16(128, 64, 0, 0);
     const uint32_t a0 = sQ0 + bsel * 2 * TILE_BYTES, b0 = sK0 + bsel * 2 * KC_TILE;
@@ -348,7 +396,6 @@ tc_chunk_fwd_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g
       umma_bf16(tmem + 64 * slot, desc_kmajor(a0, TILE_BYTES, ks), desc_kmajor(b0, KC_TILE, ks), idesc, ks > 0);
     umma_commit(smem_u32(bars + bsel));
   };
-  bool ok = true;
   auto level_sync_and_issue = [&](int slot) {
     fence_async_smem();
     tc_fence_before();
@@ -357,62 +404,50 @@ tc_chunk_fwd_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g
       tc_fence_after();
       issue_level(slot);
     }
+    TC_STAMP(0, 3 + slot);
   };
   auto wait_buffer_free = [&](int slot) {
     // before rebuilding buffer (slot & 1): the MMA of level slot-2 must have consumed it
     if (slot >= 2) ok = mbar_wait(smem_u32(bars + (slot & 1)), (uint32_t)(((slot - 2) >> 1) & 1)) && ok;
   };
+  uint8_t* sQb[2] = {sm + FwdSmem::Q, sm + FwdSmem::Q + 2 * TILE_BYTES};
+  uint8_t* sKb[2] = {sm + FwdSmem::K, sm + FwdSmem::K + 2 * KC_TILE};
 
-  // ---- levels h = 1, 2, 4, 8: rows of one block all belong to this thread -----------------------
-  emit_level_local<1>(pre, suf, qv, kv, sm + FwdSmem::Q, sm + FwdSmem::K, rg, cp);
-  level_sync_and_issue(0);
-  widen_products<1>(pre, suf);
-  emit_level_local<2>(pre, suf, qv, kv, sm + FwdSmem::Q + 2 * TILE_BYTES, sm + FwdSmem::K + 2 * KC_TILE, rg, cp);
-  level_sync_and_issue(1);
-  widen_products<2>(pre, suf);
+  fwd_emit<0>(f, qv, kv, sQb[0], sKb[0], rg, cp, tot); level_sync_and_issue(0);
+  fwd_emit<1>(f, qv, kv, sQb[1], sKb[1], rg, cp, tot); level_sync_and_issue(1);
   wait_buffer_free(2);
-  emit_level_local<4>(pre, suf, qv, kv, sm + FwdSmem::Q, sm + FwdSmem::K, rg, cp);
-  level_sync_and_issue(2);
-  widen_products<4>(pre, suf);
+  fwd_emit<2>(f, qv, kv, sQb[0], sKb[0], rg, cp, tot); level_sync_and_issue(2);
   wait_buffer_free(3);
-  emit_level_local<8>(pre, suf, qv, kv, sm + FwdSmem::Q + 2 * TILE_BYTES, sm + FwdSmem::K + 2 * KC_TILE, rg, cp);
-  widen_products<8>(pre, suf);     // now pre/suf span the thread's 16 rows
-  *reinterpret_cast<float2*>(tot + rg * TD + 2 * cp) = pre[15];
-  level_sync_and_issue(3);         // the barrier inside also publishes tot
+  fwd_emit<3>(f, qv, kv, sQb[1], sKb[1], rg, cp, tot); level_sync_and_issue(3);
+  wait_buffer_free(4);
+  fwd_emit<4>(f, qv, kv, sQb[0], sKb[0], rg, cp, tot); level_sync_and_issue(4);
+  wait_buffer_free(5);
+  fwd_emit<5>(f, qv, kv, sQb[1], sKb[1], rg, cp, tot); level_sync_and_issue(5);
+  wait_buffer_free(6);
+  fwd_emit<6>(f, qv, kv, sQb[0], sKb[0], rg, cp, tot); level_sync_and_issue(6);
 
-  // ---- levels h = 16, 32, 64 ------------------------------------------------------------------------
-  auto tot_at = [&](int r2) { return *reinterpret_cast<const float2*>(tot + r2 * TD + 2 * cp); };
+  // ---- q_hat into Q buffer 1 (free once the MMA of level slot 5 has completed); overlaps slot 6's MMA
+  ok = mbar_wait(smem_u32(bars + 1), 0) && ok;     // buffer 1, third use (level slot 5)
   {
-    wait_buffer_free(4);
-    emit_level_wide(16, 4, (rg & 1) != 0, make_float2(1.f, 1.f), pre, suf, qv, kv, sm + FwdSmem::Q, sm + FwdSmem::K, rg, cp);
-    level_sync_and_issue(4);
-  }
-  {
-    const int m = rg & 3;
-    float2 cross = make_float2(1.f, 1.f);
-    if (m == 3) cross = tot_at(rg - 1);
-    if (m == 0) cross = tot_at(rg + 1);
-    wait_buffer_free(5);
-    emit_level_wide(32, 5, m >= 2, cross, pre, suf, qv, kv, sm + FwdSmem::Q + 2 * TILE_BYTES, sm + FwdSmem::K + 2 * KC_TILE, rg, cp);
-    level_sync_and_issue(5);
-  }
-  float2 cross_q = make_float2(1.f, 1.f);      // prod of tot over row groups before rg (for q_hat)
-  {
-    float2 cross = make_float2(1.f, 1.f);
-    if (rg >= 4) {
-      for (int r2 = 4; r2 < rg; ++r2) { const float2 t = tot_at(r2); cross.x *= t.x; cross.y *= t.y; }
-    } else {
-      for (int r2 = rg + 1; r2 < 4; ++r2) { const float2 t = tot_at(r2); cross.x *= t.x; cross.y *= t.y; }
+    float2 run = make_float2(1.f, 1.f);
+    for (int r2 = 0; r2 < rg; ++r2) {
+      const float2 t = *reinterpret_cast<const float2*>(tot + r2 * TD + 2 * cp);
+      run.x *= t.x; run.y *= t.y;
     }
-    for (int r2 = 0; r2 < rg; ++r2) { const float2 t = tot_at(r2); cross_q.x *= t.x; cross_q.y *= t.y; }
-    wait_buffer_free(6);
-    emit_level_wide(64, 6, rg >= 4, cross, pre, suf, qv, kv, sm + FwdSmem::Q, sm + FwdSmem::K, rg, cp);
-    level_sync_and_issue(6);
+    uint8_t* tile = sQb[1] + (cp >> 5) * TILE_BYTES;
+    const int col = (2 * cp) & 63;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      run.x *= f[i].x; run.y *= f[i].y;
+      const float2 x = unpack_bf16x2(qv[i]);
+      *reinterpret_cast<uint32_t*>(tile + sw128_off(rg * 16 + i, col)) = pack_bf16x2(x.x * run.x, x.y * run.y);
+    }
   }
+  TC_STAMP(0, 10);
   // all seven level MMAs done when the last commit (buffer 0, fourth use) completes
   ok = mbar_wait(smem_u32(bars + 0), 1) && ok;
-  ok = mbar_wait(smem_u32(bars + 1), 0) && ok;     // buffer 1, third use (level slot 5)
   tc_fence_after();
+  TC_STAMP(0, 11);
 
   // ---- read the scores back into the bf16 P tile -----------------------------------------------------
   {
@@ -467,24 +502,13 @@ tc_chunk_fwd_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g
         *reinterpret_cast<uint4*>(P_saved + (chunk_id * TC + i) * TC + 32 * cj + 8 * c4) = u;
     }
   }
-  // ---- q_hat into Q buffer 0 (all level MMAs have completed) ------------------------------------------
-  {
-    uint8_t* tile = sm + FwdSmem::Q + (cp >> 5) * TILE_BYTES;
-    const int col = (2 * cp) & 63;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const float2 x = unpack_bf16x2(qv[i]);
-      *reinterpret_cast<uint32_t*>(tile + sw128_off(rg * 16 + i, col)) =
-          pack_bf16x2(x.x * pre[i].x * cross_q.x, x.y * pre[i].y * cross_q.y);
-    }
-  }
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
   if (tid == 0) {
     tc_fence_after();
     constexpr uint32_t idesc = idesc_bf16(128, 128, 0, 1);
-    const uint32_t aq = sQ0, bs = smem_u32(sm + FwdSmem::S), ap = smem_u32(sm + FwdSmem::P), bv = smem_u32(sm + FwdSmem::V);
+    const uint32_t aq = sQ0 + 2 * TILE_BYTES, bs = smem_u32(sm + FwdSmem::S), ap = smem_u32(sm + FwdSmem::P), bv = smem_u32(sm + FwdSmem::V);
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks)
       umma_bf16(tmem, desc_kmajor(aq, TILE_BYTES, ks), desc_mnmajor(bs, TILE_BYTES, ks), idesc, ks > 0);
@@ -493,8 +517,10 @@ tc_chunk_fwd_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g
       umma_bf16(tmem, desc_kmajor(ap, TILE_BYTES, ks), desc_mnmajor(bv, TILE_BYTES, ks), idesc, 1);
     umma_commit(smem_u32(bars + 2));
   }
+  TC_STAMP(0, 12);
   ok = mbar_wait(smem_u32(bars + 2), 0) && ok;
   tc_fence_after();
+  TC_STAMP(0, 13);
   if (ok) {
     const int q4 = warp & 3, cg = warp >> 2;
     uint32_t r[32];
@@ -513,9 +539,10 @@ tc_chunk_fwd_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g
   } else if (tid == 0) {
     atomicAdd(&g_tc_wait_timeouts, 1u);
   }
+  TC_STAMP(0, 14);
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, 512);
+  if (warp == 1) tmem_dealloc(tmem, 512);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -652,6 +679,7 @@ tc_chunk_bwd_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g
     mbar_fence_init();
   }
   if (tid < TD) { dG1[tid] = 0.f; dG2[tid] = 0.f; }
+  TC_STAMP(1, 0);
 
   // ---- phase 0: operand tiles; gate products per 16 rows; k_hat -------------------------------
   copy_tile_128x128(sm + BwdSmem::DO, dO + row0, HD);
@@ -674,6 +702,7 @@ tc_chunk_bwd_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  TC_STAMP(1, 1);
   {
     // k_hat[r][d] = k[r][d] * prod_{t > r} f_t   (rows of this thread: 32 wq_ + i)
     float run = 1.f;
@@ -691,6 +720,7 @@ tc_chunk_bwd_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g
   tc_fence_before();
   __syncthreads();
 
+  TC_STAMP(1, 2);
   // ---- phase 1: the four dense products --------------------------------------------------------------
   if (tid == 0) {
     tc_fence_after();
@@ -716,6 +746,7 @@ tc_chunk_bwd_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g
   }
   bool ok = mbar_wait(smem_u32(bars + 0), 0);
   tc_fence_after();
+  TC_STAMP(1, 3);
 
   // ---- phase 1.5: dV out, dP diagonal, the two dG sums ---------------------------------------------------
   {
@@ -769,6 +800,7 @@ tc_chunk_bwd_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g
   __syncthreads();      // all readers of the phase-1 tiles are done: the regions can be reused
   tc_fence_after();
 
+  TC_STAMP(1, 4);
   // ---- phase 1.9: W64 for all 128 rows (rows < 64: k~, rows >= 64: q~, anchor row 63) ----------------------
   {
     uint8_t* tile = sm + BwdSmem::W64 + (d >> 6) * TILE_BYTES;
@@ -795,6 +827,7 @@ tc_chunk_bwd_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g
   for (int b2 = 0; b2 < 8; ++b2) eG *= tot[b2 * TD + d];
   const float dG = dG1[d] + eG * dG2[d];
 
+  TC_STAMP(1, 5);
   // ---- phase 2: two passes over the rows ----------------------------------------------------------------------
   uint32_t ph1 = 0, ph2 = 0;      // completed-phase counters of bars[1], bars[2]
   const uint32_t aW64 = smem_u32(sm + BwdSmem::W64), aWL = smem_u32(sm + BwdSmem::WL), aDPL = smem_u32(sm + BwdSmem::DPL);
@@ -836,6 +869,7 @@ tc_chunk_bwd_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g
       }
     }
 
+    TC_STAMP(1, 6 + 10 * (1 - p));
     // one level: build operands, issue; the accumulate of the previous level overlaps the MMA
     auto build_and_issue = [&](auto SC) {
       constexpr int S = decltype(SC)::value;
@@ -931,17 +965,21 @@ tc_chunk_bwd_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g
     build_and_issue(I0{});
     build_and_issue(I1{});
     accumulate(I0{});
+    TC_STAMP(1, 7 + 10 * (1 - p));
     build_and_issue(I2{});
     accumulate(I1{});
     build_and_issue(I3{});
     accumulate(I2{});
+    TC_STAMP(1, 8 + 10 * (1 - p));
     build_and_issue(I4{});
     accumulate(I3{});
     build_and_issue(I5{});
     accumulate(I4{});
+    TC_STAMP(1, 9 + 10 * (1 - p));
     build_and_issue(I6{});
     accumulate(I5{});
     accumulate(I6{});
+    TC_STAMP(1, 10 + 10 * (1 - p));
 
     // ---- outputs of this pass ---------------------------------------------------------------------------
     float dl[16];
@@ -965,6 +1003,7 @@ tc_chunk_bwd_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g
 #pragma unroll
       for (int i = 0; i < 16; ++i) dg_out[row0 + (int64_t)(rbase + i) * HD + d] = dl[i] + off;
     }
+    TC_STAMP(1, 11 + 10 * (1 - p));
     if (p == 1) {
       later = 0.f;
       for (int g2 = 4; g2 < 8; ++g2) later += grp[g2 * TD + d];
@@ -994,6 +1033,53 @@ bool tc_supported(int64_t D, int64_t C, int dtype) { return D == TD && C == TC &
 bool tc_auto_default() { return true; }
 
 static size_t f32b(int64_t n) { return align_up((size_t)n * 4, 256); }
+
+// ---- TMA descriptors -------------------------------------------------------------------------
+// cuTensorMapEncodeTiled is fetched through the runtime so that the library has no link-time
+// dependency on libcuda (it must load on machines without a driver).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+// (B,T,H,128) array seen as 3-d (d, h, b*T + t); box = (box_cols, 1, 128 rows); float32 or bf16.
+static int make_map_bthd(CUtensorMap* m, const void* ptr, int is_f32, int64_t B, int64_t T, int64_t H, int box_cols,
+                         int swizzle128) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return GLA_ERR_NO_DEVICE;
+  const cuuint64_t es = is_f32 ? 4 : 2;
+  cuuint64_t dims[3] = {(cuuint64_t)TD, (cuuint64_t)H, (cuuint64_t)(B * T)};
+  cuuint64_t strides[2] = {(cuuint64_t)TD * es, (cuuint64_t)H * TD * es};
+  cuuint32_t box[3] = {(cuuint32_t)box_cols, 1, 128};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(m, is_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, (void*)ptr, dims,
+                  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? GLA_OK : GLA_ERR_LAUNCH;
+}
+// dense bf16 matrix of `rows` rows x 128 columns; box = (box_cols, box_rows), 128-byte swizzle.
+static int make_map_rows(CUtensorMap* m, const void* ptr, int64_t rows, int box_cols, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return GLA_ERR_NO_DEVICE;
+  cuuint64_t dims[2] = {(cuuint64_t)TD, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)TD * 2};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)ptr, dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? GLA_OK : GLA_ERR_LAUNCH;
+}
 
 static size_t b16b(int64_t n) { return align_up((size_t)n * 2, 256); }
 
@@ -1041,10 +1127,15 @@ int tc_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
   GLA_TRY(launch_state_scan(st, BH, N, D, Gc, kv, 0, hidden_init, 1, S_prev, 1, hidden_final, 1, 0));
   cudaError_t e = cudaFuncSetAttribute(tc_chunk_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FWD_SMEM);
   if (e != cudaSuccess) return record_cuda_error(e);
+  FwdMaps maps;
+  GLA_TRY(make_map_bthd(&maps.g, g, 1, B, T, H, 128, 0));
+  GLA_TRY(make_map_bthd(&maps.q, q, 0, B, T, H, 64, 1));
+  GLA_TRY(make_map_bthd(&maps.k, k, 0, B, T, H, 64, 1));
+  GLA_TRY(make_map_bthd(&maps.v, v, 0, B, T, H, 64, 1));
+  GLA_TRY(make_map_rows(&maps.s, S_prev, BH * N * D, 64, 128));
   {
     ProfScope ps("tc_chunk_fwd_kernel", st);
-    tc_chunk_fwd_kernel<<<(unsigned)(BH * N), TTHREADS, FWD_SMEM, st>>>(T, H, N, g, (const bf16*)v, (const bf16*)k,
-                                                                       (const bf16*)q, S_prev, (bf16*)out, P);
+    tc_chunk_fwd_kernel<<<(unsigned)(BH * N), TTHREADS, FWD_SMEM, st>>>(maps, T, H, N, (bf16*)out, P);
   }
   GLA_CHECK_LAUNCH();
   return GLA_OK;
@@ -1075,6 +1166,13 @@ int tc_chunk_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
   }
   GLA_CHECK_LAUNCH();
   return GLA_OK;
+}
+
+void tc_read_trace(long long* out64) {
+  cudaMemcpyFromSymbol(out64, g_tc_trace, sizeof(long long) * 64);
+}
+void tc_read_wtrace(long long* out512) {
+  cudaMemcpyFromSymbol(out512, g_tc_wtrace, sizeof(long long) * 512);
 }
 
 unsigned int tc_read_wait_timeouts() {

@@ -90,6 +90,8 @@ int simt_chunk_dstate_only(cudaStream_t st, int64_t B, int64_t T, int64_t H, int
 bool tc_supported(int64_t D, int64_t C, int dtype);
 bool tc_auto_default();
 unsigned int tc_read_wait_timeouts();
+void tc_read_trace(long long* out64);
+void tc_read_wtrace(long long* out512);
 size_t tc_saved_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t C);
 size_t tc_fwd_ws_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t C);
 size_t tc_bwd_ws_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t C);

@@ -85,6 +85,11 @@ GLA_API long long gla_launch_count(void);
  * (synchronises the device; diagnostic).  0 means no wait has ever given up. */
 GLA_API unsigned int gla_device_wait_timeouts(void);
 
+/* SM clock stamps taken at the phase boundaries of one thread block (block 100) of the most
+ * recent tensor-core forward ([0..31]) and backward ([32..63]) chunk kernels; diagnostic for
+ * tuning, synchronises the device.  No counterpart in the reference. */
+GLA_API void gla_debug_phase_clocks(long long* out64);
+
 /* Per-kernel device timing for benchmarks (diagnostic; no counterpart in the reference, whose
  * harness times whole calls with timeit, gla.py:1430-1434).  While enabled on the calling
  * thread, each internal kernel launch is bracketed by CUDA events on its stream;
