@@ -9,7 +9,10 @@ import ctypes
 from ctypes import c_char_p, c_int, c_int64, c_size_t, c_void_p
 from pathlib import Path
 
-_LIB_PATH = Path(__file__).resolve().parent / "libgla_b200.so"
+import os
+
+# GLA_B200_LIB may point at another build of the library (used to compare kernel variants).
+_LIB_PATH = Path(os.environ.get("GLA_B200_LIB") or (Path(__file__).resolve().parent / "libgla_b200.so"))
 _lib = None
 
 GLA_F32, GLA_BF16 = 0, 1

@@ -19,6 +19,7 @@
 #include "tc_ptx.cuh"
 #include <type_traits>
 #include <cuda.h>
+#include <cstdlib>
 
 namespace gla {
 
@@ -298,6 +299,7 @@ __device__ __forceinline__ void fwd_emit(const float2 (&f)[16], const uint32_t (
   }
 }
 
+
 __global__ void __launch_bounds__(TTHREADS, 1)
 tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, int64_t N, bf16* __restrict__ out,
                     bf16* __restrict__ P_saved) {
@@ -450,56 +452,81 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, 
   TC_STAMP(0, 11);
 
   // ---- read the scores back into the bf16 P tile -----------------------------------------------------
+  // Rows 32 q4 + lane belong to the four warps of TMEM quadrant q4; each of them (cj = 0..3) writes
+  // 32 of the row's 128 columns in 16-byte chunks of 8: q4 chunks below the diagonal block (copied
+  // from level slot 5 or 6), one chunk of the 32 x 32 diagonal block (assembled from slots 0..4 and
+  // the q.k diagonal) and 3 - q4 chunks of zeros above it, so that the four warps are balanced.
   {
     const int q4 = warp & 3, cj = warp >> 2;
-    const int li = lane;
+    const int li = lane, i = 32 * q4 + li;
     const uint32_t lane_base = tmem + ((uint32_t)(q4 * 32) << 16);
-    float pr[32];
-    if (cj > q4) {
-#pragma unroll
-      for (int m = 0; m < 32; ++m) pr[m] = 0.f;
-    } else if (cj < q4) {
-      const int slot = ((q4 ^ cj) >= 2) ? 6 : 5;
-      const int col = (slot == 6) ? 32 * cj : 16 * cj;
-      uint32_t r[32];
-      tmem_ld32(lane_base + 64 * slot + col, r);
+    auto put_chunk = [&](int col0, const float (&x)[8]) {
+      uint4 u;
+      u.x = pack_bf16x2(x[0], x[1]); u.y = pack_bf16x2(x[2], x[3]);
+      u.z = pack_bf16x2(x[4], x[5]); u.w = pack_bf16x2(x[6], x[7]);
+      *reinterpret_cast<uint4*>(sm + FwdSmem::P + (col0 >> 6) * TILE_BYTES + sw128_chunk(i, (col0 & 63) >> 3)) = u;
+      if (P_saved) *reinterpret_cast<uint4*>(P_saved + (chunk_id * TC + i) * TC + col0) = u;
+    };
+    // below the diagonal block
+    for (int ch = 0; ch < q4; ++ch) {
+      const int col0 = 8 * (q4 * cj + ch), cb = col0 >> 5;
+      const int tcol = ((q4 ^ cb) >= 2) ? (64 * 6 + col0) : (64 * 5 + (cb >> 1) * 32 + (col0 & 31));
+      uint32_t r[8];
+      tmem_ld8(lane_base + tcol, r);
       tmem_ld_wait();
+      float x[8];
 #pragma unroll
-      for (int m = 0; m < 32; ++m) pr[m] = __uint_as_float(r[m]);
-    } else {
+      for (int m = 0; m < 8; ++m) x[m] = __uint_as_float(r[m]);
+      put_chunk(col0, x);
+    }
+    // the diagonal block: local columns lj = 8 cj + m
+    {
+      float x[8];
 #pragma unroll
-      for (int m = 0; m < 32; ++m) pr[m] = 0.f;
+      for (int m = 0; m < 8; ++m) x[m] = 0.f;
+      const int lj0 = 8 * cj;
 #pragma unroll
-      for (int s = 0; s < 5; ++s) {
-        const int hh = 1 << s;
-        uint32_t r[16];
-        tmem_ld16(lane_base + 64 * s + 16 * q4, r);
+      for (int s2 = 0; s2 < 3; ++s2) {
+        const int hh = 1 << s2;
+        uint32_t r[4];
+        tmem_ld4(lane_base + 64 * s2 + 16 * q4 + 4 * cj, r);
         tmem_ld_wait();
 #pragma unroll
-        for (int lj = 0; lj < 32; ++lj) {
-          if ((lj & hh) == 0) {
-            const int c = ((lj >> (s + 1)) << s) + (lj & (hh - 1));
-            if (((li ^ lj) >> s) == 1) pr[lj] = __uint_as_float(r[c]);
+        for (int m = 0; m < 8; ++m) {
+          if ((m & hh) == 0) {
+            const int c = ((m >> (s2 + 1)) << s2) + (m & (hh - 1));
+            if (((li ^ (lj0 + m)) >> s2) == 1) x[m] = __uint_as_float(r[c]);
           }
         }
       }
-      const float dg = diag[32 * q4 + li] + diag[TC + 32 * q4 + li];
+      if ((cj & 1) == 0) {            // half size 8: columns with bit 3 clear
+        uint32_t r[8];
+        tmem_ld8(lane_base + 64 * 3 + 16 * q4 + 8 * (cj >> 1), r);
+        tmem_ld_wait();
 #pragma unroll
-      for (int lj = 0; lj < 32; ++lj)
-        if (lj == li) pr[lj] = dg;
+        for (int m = 0; m < 8; ++m)
+          if (((li ^ (lj0 + m)) >> 3) == 1) x[m] = __uint_as_float(r[m]);
+      }
+      if (cj < 2) {                   // half size 16: columns with bit 4 clear
+        uint32_t r[8];
+        tmem_ld8(lane_base + 64 * 4 + 16 * q4 + 8 * cj, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int m = 0; m < 8; ++m)
+          if (((li ^ (lj0 + m)) >> 4) == 1) x[m] = __uint_as_float(r[m]);
+      }
+      const float dgv = diag[i] + diag[TC + i];
+#pragma unroll
+      for (int m = 0; m < 8; ++m)
+        if (lj0 + m == li) x[m] = dgv;
+      put_chunk(32 * q4 + lj0, x);
     }
-    const int i = 32 * q4 + li;
-    uint8_t* tile = sm + FwdSmem::P + (cj >> 1) * TILE_BYTES;
+    // above the diagonal block
+    {
+      float z[8];
 #pragma unroll
-    for (int c4 = 0; c4 < 4; ++c4) {
-      uint4 u;
-      u.x = pack_bf16x2(pr[8 * c4 + 0], pr[8 * c4 + 1]);
-      u.y = pack_bf16x2(pr[8 * c4 + 2], pr[8 * c4 + 3]);
-      u.z = pack_bf16x2(pr[8 * c4 + 4], pr[8 * c4 + 5]);
-      u.w = pack_bf16x2(pr[8 * c4 + 6], pr[8 * c4 + 7]);
-      *reinterpret_cast<uint4*>(tile + sw128_chunk(i, (cj & 1) * 4 + c4)) = u;
-      if (P_saved)
-        *reinterpret_cast<uint4*>(P_saved + (chunk_id * TC + i) * TC + 32 * cj + 8 * c4) = u;
+      for (int m = 0; m < 8; ++m) z[m] = 0.f;
+      for (int ch = 0; ch < 3 - q4; ++ch) put_chunk(32 * (q4 + 1) + 8 * ((3 - q4) * cj + ch), z);
     }
   }
   fence_async_smem();
