@@ -98,7 +98,8 @@ def _worker(rank, world, port, q_out):
         loss = (hf * dhf).sum() / world + (out * do[:, sl]).sum()      # hidden_final term shared by the ranks
         # each rank holds the same hidden_final; its cotangent must be the full dhf on every rank
         grads = torch.autograd.grad((hf * dhf).sum() + (out * do[:, sl]).sum(), leaves)
-        q_out.put((rank, hf.detach(), out.detach(), [x.detach() for x in grads], float(loss)))
+        # numpy arrays are pickled by value: no shared-memory handles that die with the child process
+        q_out.put((rank, hf.detach().numpy(), out.detach().numpy(), [x.detach().numpy() for x in grads], float(loss.detach())))
     finally:
         dist.destroy_process_group()
 
@@ -112,6 +113,7 @@ def test_sequence_parallel_gloo_world2():
     for p in procs:
         p.start()
     res = sorted([q_out.get(timeout=60) for _ in range(world)], key=lambda x: x[0])
+    res = [(r[0], torch.from_numpy(r[1]), torch.from_numpy(r[2]), [torch.from_numpy(x) for x in r[3]]) for r in res]
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0

@@ -65,7 +65,9 @@ def _nccl_worker(rank, world, port, q_out):
         hf, out = P.sequence_parallel_chunk_gla(*leaves, chunk_size=C)
         grads = torch.autograd.grad((hf.float() * dhf.to(dev).float()).sum() + (out.float() * do[:, sl].to(dev).float()).sum(), leaves)
         torch.cuda.synchronize()
-        q_out.put((rank, hf.detach().cpu(), out.detach().cpu(), [x.detach().cpu() for x in grads]))
+        # numpy arrays are pickled by value: no shared-memory handles that die with the child process
+        q_out.put((rank, hf.detach().float().cpu().numpy(), out.detach().float().cpu().numpy(),
+                   [x.detach().float().cpu().numpy() for x in grads]))
     finally:
         dist.destroy_process_group()
 
@@ -82,6 +84,7 @@ def test_sequence_parallel_nccl_two_gpus(cuda_device):
     for p in procs:
         p.start()
     res = sorted([q_out.get(timeout=120) for _ in range(world)], key=lambda x: x[0])
+    res = [(r[0], torch.from_numpy(r[1]), torch.from_numpy(r[2]), [torch.from_numpy(x) for x in r[3]]) for r in res]
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
