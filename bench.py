@@ -167,6 +167,8 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (for profiler runs)")
     ap.add_argument("--no-graph", action="store_true", help="time plain launches instead of CUDA-graph replays")
+    ap.add_argument("--op", default="chunk_gla", choices=["chunk_gla", "recurrent_gla"],
+                    help="chunk_gla is the headline metric; recurrent_gla times the exact recurrence on the same shape")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -211,7 +213,23 @@ def main():
     ws = torch.empty(max(wsf_n, wsb_n), dtype=torch.uint8, device=dev)
     stream = torch.cuda.current_stream(dev).cuda_stream
 
+    rws_n = lib.gla_recurrent_bwd_workspace_bytes(B, T, H, D, dt)
+    rws = torch.empty(rws_n if args.op == "recurrent_gla" else 16, dtype=torch.uint8, device=dev)
+
+    def step_recurrent(i):
+        (h, g, v, k, q), o = sets[i % NSETS]
+        st = lib.gla_recurrent_fwd(stream, B, T, H, D, dt, h.data_ptr(), g.data_ptr(), v.data_ptr(), k.data_ptr(),
+                                   q.data_ptr(), o["hf"].data_ptr(), o["out"].data_ptr(), dt, 0)
+        _lib.check(st, "gla_recurrent_fwd")
+        st = lib.gla_recurrent_bwd(stream, B, T, H, D, dt, h.data_ptr(), g.data_ptr(), v.data_ptr(), k.data_ptr(),
+                                   q.data_ptr(), o["dhf"].data_ptr(), o["dout"].data_ptr(), dt, o["dh"].data_ptr(),
+                                   o["dg"].data_ptr(), o["dv"].data_ptr(), o["dk"].data_ptr(), o["dq"].data_ptr(), 0,
+                                   rws.data_ptr(), rws.numel())
+        _lib.check(st, "gla_recurrent_bwd")
+
     def step(i):
+        if args.op == "recurrent_gla":
+            return step_recurrent(i)
         (h, g, v, k, q), o = sets[i % NSETS]
         st = lib.gla_chunk_fwd(stream, B, T, H, D, C, dt, impl, h.data_ptr(), g.data_ptr(), v.data_ptr(), k.data_ptr(),
                                q.data_ptr(), o["hf"].data_ptr(), o["out"].data_ptr(), saved.data_ptr(),
@@ -285,7 +303,11 @@ def main():
 
     def e2e_step():
         leaves = [x.to(dev, non_blocking=True).requires_grad_(True) for x in host]
-        hf, out = chunk_gla(*leaves, chunk_size=C, impl=args.chunk_impl)
+        if args.op == "recurrent_gla":
+            from gla_jax_b200 import recurrent_gla
+            hf, out = recurrent_gla(*leaves)
+        else:
+            hf, out = chunk_gla(*leaves, chunk_size=C, impl=args.chunk_impl)
         loss = hf.float().sum() + out.float().sum()
         loss.backward()
         return float(loss.item())       # 4-byte device->host read; also orders the step
@@ -340,7 +362,8 @@ def main():
             roof.update({"peak_source": peaks["source"], "launches": n_l, "ms_per_launch": 1e3 * per_launch_s,
                          "share_of_kernel_time": ms_l / total_k, "algorithmic": alg["what"]})
         line = {
-            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+            "metric": METRIC if args.op == "chunk_gla" else "recurrent_gla fwd+bwd tokens/sec", "value": value,
+            "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": ms_total / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "README shape per GPU: B=4,H=6,D=128,T=4096,chunk=128,bf16 q/k/v/hidden, f32 "

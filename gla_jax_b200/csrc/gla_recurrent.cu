@@ -60,28 +60,52 @@ struct TileSrc {
   int do_exp;
 };
 
-template <int W, int NPT>
-__device__ __forceinline__ void tile_fetch(float (&r)[NPT], const TileSrc& s, int64_t base, int64_t row_stride,
+// A staged tile of RB rows x W columns is fetched in groups of four consecutive elements (one 8- or
+// 16-byte load per group; group index = threadIdx.x + RTHREADS * i).  The fetch only issues the
+// loads and parks the RAW bits in registers: nothing in it consumes a loaded value, so all of a
+// thread's loads are in flight together (a conversion right behind each load would stall the
+// in-order warp for a full memory latency per load).  tile_commit converts and stores to smem.
+template <int W, int NG>
+__device__ __forceinline__ void tile_fetch(uint4 (&raw)[NG], const TileSrc& s, int64_t base, int64_t row_stride,
                                            int64_t step0, int64_t T, int time_reversed, int c0) {
 #pragma unroll
-  for (int i = 0; i < NPT; ++i) {
-    const int e = threadIdx.x + RTHREADS * i;
+  for (int i = 0; i < NG; ++i) {
+    const int e = (threadIdx.x + RTHREADS * i) * 4;
     const int row = e / W, col = e % W;
     const int64_t sidx = step0 + row;
-    float v = 0.f;
-    if (sidx < T) {
+    uint4 u = make_uint4(0u, 0u, 0u, 0u);
+    if (e < RB * W && sidx < T) {
       const int64_t t = time_reversed ? (T - 1 - sidx) : sidx;
-      v = ld_any(s.p, s.bf, base + t * row_stride + c0 + col);
+      const int64_t off = base + t * row_stride + c0 + col;
+#ifndef REC_NO_LOAD
+      if (s.bf) {
+        const uint2 w = __ldg(reinterpret_cast<const uint2*>((const bf16*)s.p + off));
+        u.x = w.x; u.y = w.y;
+      } else {
+        u = __ldg(reinterpret_cast<const uint4*>((const float*)s.p + off));
+      }
+#endif
     }
-    r[i] = v;
+    raw[i] = u;
   }
 }
-template <int W, int NPT>
-__device__ __forceinline__ void tile_commit(float* sm, const float (&r)[NPT], int do_exp) {
+template <int W, int NG>
+__device__ __forceinline__ void tile_commit(float* sm, const uint4 (&raw)[NG], int is_bf16, int do_exp) {
 #pragma unroll
-  for (int i = 0; i < NPT; ++i) {
-    const int e = threadIdx.x + RTHREADS * i;
-    sm[e] = do_exp ? expf(r[i]) : r[i];
+  for (int i = 0; i < NG; ++i) {
+    const int e = (threadIdx.x + RTHREADS * i) * 4;
+    if (e < RB * W) {
+      const uint4 u = raw[i];
+      float4 o;
+      if (is_bf16) {
+        o.x = __uint_as_float(u.x << 16); o.y = __uint_as_float(u.x & 0xffff0000u);
+        o.z = __uint_as_float(u.y << 16); o.w = __uint_as_float(u.y & 0xffff0000u);
+      } else {
+        o.x = __uint_as_float(u.x); o.y = __uint_as_float(u.y); o.z = __uint_as_float(u.z); o.w = __uint_as_float(u.w);
+      }
+      if (do_exp) { o.x = expf(o.x); o.y = expf(o.y); o.z = expf(o.z); o.w = expf(o.w); }
+      *reinterpret_cast<float4*>(sm + e) = o;
+    }
   }
 }
 
@@ -90,12 +114,12 @@ __global__ void __launch_bounds__(RTHREADS) rec_kernel(RecParams p) {
   constexpr int KP = D / 8;                       // state elements per thread
   constexpr int NL = (MODE == REC_FWD || MODE == REC_DV) ? 3 : 2;   // long tiles
   constexpr int NS = (MODE == REC_FWD || MODE == REC_DV) ? 1 : 3;   // slice tiles
-  constexpr int LPT = RB * D / RTHREADS;          // long-tile elements per thread
-  constexpr int SPT = RB * RS / RTHREADS;         // slice-tile elements per thread (2)
+  constexpr int LG = RB * D / RTHREADS / 4;       // long-tile groups of four elements per thread
+  constexpr int SG = 1;                           // slice tile: 64 groups of four elements, threads 0..63
   extern __shared__ __align__(16) float smem[];
-  float* Ls[3] = {smem, smem + RB * D, smem + 2 * RB * D};
-  float* Ss[3] = {smem + NL * RB * D, smem + NL * RB * D + RB * RS, smem + NL * RB * D + 2 * RB * RS};
-  float* Rs = smem + NL * RB * D + NS * RB * RS;
+  // tile offsets inside the one shared array (plain offsets, not pointer tables, so that every
+  // access is compiled as a shared-memory access)
+  constexpr int L_OFF = RB * D, S_BASE = NL * RB * D, S_OFF = RB * RS, R_BASE = NL * RB * D + NS * RB * RS;
 
   const int lp = threadIdx.x % 8, si = threadIdx.x / 8;
   const int c0 = blockIdx.x * RS;                 // slice window
@@ -136,36 +160,40 @@ __global__ void __launch_bounds__(RTHREADS) rec_kernel(RecParams p) {
     for (int i = 0; i < KP; ++i) st[i] = init ? ld_any(init, p.bf, state_addr(i)) : 0.f;
   }
 
-  float lreg[NL][LPT];
-  float sreg[NS][SPT];
+  uint4 lreg[NL][LG];
+  uint4 sreg[NS][SG];
   auto fetch = [&](int64_t step0) {
 #pragma unroll
-    for (int a = 0; a < NL; ++a) tile_fetch<D, LPT>(lreg[a], Lsrc[a], base, HD, step0, T, trev, 0);
+    for (int a = 0; a < NL; ++a) tile_fetch<D, LG>(lreg[a], Lsrc[a], base, HD, step0, T, trev, 0);
 #pragma unroll
-    for (int a = 0; a < NS; ++a) tile_fetch<RS, SPT>(sreg[a], Ssrc[a], base, HD, step0, T, trev, c0);
+    for (int a = 0; a < NS; ++a) tile_fetch<RS, SG>(sreg[a], Ssrc[a], base, HD, step0, T, trev, c0);
   };
   fetch(0);
   for (int64_t step0 = 0; step0 < T; step0 += RB) {
     __syncthreads();   // previous block's readers of the tiles and of Rs are done
 #pragma unroll
-    for (int a = 0; a < NL; ++a) tile_commit<D, LPT>(Ls[a], lreg[a], Lsrc[a].do_exp);
+    for (int a = 0; a < NL; ++a) tile_commit<D, LG>(smem + a * L_OFF, lreg[a], Lsrc[a].bf, Lsrc[a].do_exp);
 #pragma unroll
-    for (int a = 0; a < NS; ++a) tile_commit<RS, SPT>(Ss[a], sreg[a], Ssrc[a].do_exp);
+    for (int a = 0; a < NS; ++a) tile_commit<RS, SG>(smem + S_BASE + a * S_OFF, sreg[a], Ssrc[a].bf, Ssrc[a].do_exp);
     __syncthreads();
     if (step0 + RB < T) fetch(step0 + RB);
     const int nt = (int)((T - step0) < RB ? (T - step0) : RB);
+#ifdef REC_NO_COMPUTE
+    for (int tt = 0; tt < 0; ++tt) {
+#else
     for (int tt = 0; tt < nt; ++tt) {
+#endif
       float red = 0.f;
-      const float s0 = Ss[0][tt * RS + si];
+      const float s0 = smem[S_BASE + tt * RS + si];
       float s1 = 0.f, s2 = 0.f;
-      if (NS == 3) { s1 = Ss[1][tt * RS + si]; s2 = Ss[2][tt * RS + si]; }
+      if (NS == 3) { s1 = smem[S_BASE + S_OFF + tt * RS + si]; s2 = smem[S_BASE + 2 * S_OFF + tt * RS + si]; }
 #pragma unroll
       for (int m = 0; m < KP / 4; ++m) {
         const int off = tt * D + 32 * m + 4 * lp;
-        const float4 a4 = *reinterpret_cast<const float4*>(Ls[0] + off);
-        const float4 b4 = *reinterpret_cast<const float4*>(Ls[1] + off);
+        const float4 a4 = *reinterpret_cast<const float4*>(smem + off);
+        const float4 b4 = *reinterpret_cast<const float4*>(smem + L_OFF + off);
         float4 c4 = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (NL == 3) c4 = *reinterpret_cast<const float4*>(Ls[2] + off);
+        if (NL == 3) c4 = *reinterpret_cast<const float4*>(smem + 2 * L_OFF + off);
         const float av[4] = {a4.x, a4.y, a4.z, a4.w};
         const float bv[4] = {b4.x, b4.y, b4.z, b4.w};
         const float cv[4] = {c4.x, c4.y, c4.z, c4.w};
@@ -190,29 +218,29 @@ __global__ void __launch_bounds__(RTHREADS) rec_kernel(RecParams p) {
         }
       }
       red = reduce8(red);
-      if (lp == 0) Rs[tt * RS + si] = red;
+      if (lp == 0) smem[R_BASE + tt * RS + si] = red;
     }
     __syncthreads();
     // write the block's results: RB x RS values, two per thread
 #pragma unroll
-    for (int i = 0; i < SPT; ++i) {
+    for (int i = 0; i < RB * RS / RTHREADS; ++i) {
       const int e = threadIdx.x + RTHREADS * i;
       const int row = e / RS, col = e % RS;
       const int64_t sidx = step0 + row;
       if (sidx < T) {
         const int64_t t = trev ? (T - 1 - sidx) : sidx;
         const int64_t addr = base + t * HD + c0 + col;
-        const float r = Rs[e];
+        const float r = smem[R_BASE + e];
         if (MODE == REC_FWD) {
           st_any(p.out, p.out_bf, addr, r);
         } else if (MODE == REC_DQ) {
           st_any(p.dq, p.bf, addr, r);
-          p.E[addr] = Ss[2][e] * r;
+          p.E[addr] = smem[S_BASE + 2 * S_OFF + e] * r;
         } else if (MODE == REC_DV) {
           st_any(p.dv, p.bf, addr, r);
         } else {
           st_any(p.dk, p.bf, addr, r);
-          p.E[addr] -= Ss[1][e] * r;
+          p.E[addr] -= smem[S_BASE + S_OFF + e] * r;
         }
       }
     }
