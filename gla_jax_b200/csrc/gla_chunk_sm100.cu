@@ -37,6 +37,16 @@ __device__ unsigned int g_tc_wait_timeouts = 0;   // incremented when a bounded 
 __device__ long long g_tc_trace[2][32];
 __device__ long long g_tc_wtrace[16][32];
 #define TC_WSTAMP(idx) do { if (blockIdx.x == 500 && (threadIdx.x & 31) == 0) g_tc_wtrace[threadIdx.x >> 5][idx] = clock64(); } while (0)
+#ifdef GLA_TIMELINE
+__device__ long long g_tl[3 * 1024];
+__device__ __forceinline__ long long gtimer() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+__device__ __forceinline__ int smid() { int t; asm volatile("mov.u32 %0, %smid;" : "=r"(t)); return t; }
+#define TL_BEGIN() do { if (threadIdx.x == 0 && blockIdx.x < 1024) { g_tl[3 * blockIdx.x] = gtimer(); g_tl[3 * blockIdx.x + 2] = smid(); } } while (0)
+#define TL_END() do { if (threadIdx.x == 0 && blockIdx.x < 1024) { g_tl[3 * blockIdx.x + 1] = gtimer(); } } while (0)
+#else
+#define TL_BEGIN()
+#define TL_END()
+#endif
 #define TC_STAMP(which, idx) do { if (blockIdx.x == 500 && threadIdx.x == 0) g_tc_trace[which][idx] = clock64(); } while (0)
 
 // smem carve-up helper: dynamic shared memory aligned to 1024 bytes
@@ -62,8 +72,11 @@ __device__ __forceinline__ void copy_tile_128x128(uint8_t* dst, const bf16* __re
 // Also writes the chunk's total log decay G[d] (MODE 0).  One CTA per chunk.
 // MMA: M = dk (128), N = dv (128), K = c (128); both operands MN-major.
 // ---------------------------------------------------------------------------------------
+#ifndef KV_MINB
+#define KV_MINB 1
+#endif
 template <int MODE>
-__global__ void __launch_bounds__(TTHREADS, 1)
+__global__ void __launch_bounds__(TTHREADS, KV_MINB)
 tc_kv_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g, const bf16* __restrict__ x,
              const bf16* __restrict__ y, float* __restrict__ out, float* __restrict__ Gc) {
   extern __shared__ uint8_t smem_raw[];
@@ -80,6 +93,7 @@ tc_kv_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g, const
   const int64_t n = blockIdx.x % N, bh = blockIdx.x / N, b = bh / H, h = bh % H;
   const int64_t HD = H * TD;
   const int64_t row0 = ((b * T + n * TC) * H + h) * TD;     // element (b, n*C, h, 0)
+  if (MODE == 0) TL_BEGIN();
 
   if (warp == 0) {
     tmem_alloc(smem_u32(tmem_slot), 128);
@@ -91,23 +105,29 @@ tc_kv_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g, const
   }
 
   // ---- element-wise stage ------------------------------------------------------------------
+  // All loads of the stage are issued before anything consumes one; the weights overwrite the gates.
   float2 f[16];
   uint32_t xv[16];
+  {
+    const int64_t e0 = row0 + (int64_t)(rg * 16) * HD + 2 * cp;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      f[i] = __ldg(reinterpret_cast<const float2*>(g + e0 + (int64_t)i * HD));
+      xv[i] = __ldg(reinterpret_cast<const unsigned int*>(x + e0 + (int64_t)i * HD));
+    }
+  }
   float2 gs = make_float2(0.f, 0.f);
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
-    const int64_t e = row0 + (int64_t)(rg * 16 + i) * HD + 2 * cp;
-    const float2 gg = *reinterpret_cast<const float2*>(g + e);
-    xv[i] = *reinterpret_cast<const uint32_t*>(x + e);
-    gs.x += gg.x; gs.y += gg.y;
-    f[i] = make_float2(__expf(gg.x), __expf(gg.y));
+    gs.x += f[i].x; gs.y += f[i].y;
+    f[i] = make_float2(__expf(f[i].x), __expf(f[i].y));
   }
-  // w[i]: MODE 0 exclusive suffix product, MODE 1 inclusive prefix product, within the 16 rows
-  float2 w[16];
+  // f[i] becomes w[i]: MODE 0 exclusive suffix product, MODE 1 inclusive prefix product, within the 16 rows
+  float2 (&w)[16] = f;
   if (MODE == 0) {
     float2 run = make_float2(1.f, 1.f);
 #pragma unroll
-    for (int i = 15; i >= 0; --i) { w[i] = run; run.x *= f[i].x; run.y *= f[i].y; }
+    for (int i = 15; i >= 0; --i) { const float2 t = f[i]; w[i] = run; run.x *= t.x; run.y *= t.y; }
     *reinterpret_cast<float2*>(tot + rg * TD + 2 * cp) = run;
   } else {
     float2 run = make_float2(1.f, 1.f);
@@ -185,6 +205,24 @@ tc_kv_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g, const
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, 128);
+  if (MODE == 0) TL_END();
+}
+
+// Number of thread blocks resident at a time (SMs x blocks per SM) = how far ahead in block index the
+// block that follows on the same SM lies; 0 disables the L2 prefetch.  GLA_B200_PREFETCH=0 turns it off.
+static int prefetch_distance(int blocks_per_sm) {
+  static int sms[64] = {0};
+  static int enabled = -1;
+  if (enabled < 0) { const char* e = getenv("GLA_B200_PREFETCH"); enabled = (e && e[0] == '0') ? 0 : 1; }
+  if (!enabled) return 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (sms[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 0;
+    sms[dev] = n;
+  }
+  return sms[dev] * blocks_per_sm;
 }
 
 constexpr size_t KV_SMEM = 1024 + 4 * TILE_BYTES + 2 * 8 * TD * sizeof(float) + 64;
@@ -667,12 +705,17 @@ __device__ __forceinline__ bool row_is_right(int i, int rq, int p) {
   return S < 4 ? ((i >> S) & 1) : S == 4 ? (rq & 1) : S == 5 ? (rq >= 2) : (p == 1);
 }
 
+// Raw 16-bit global load (bf16 bits).  Loops below first issue ALL their loads into raw registers and
+// only then convert / use them: an instruction consuming a loaded value right behind the load stalls
+// the in-order warp for a full memory latency per load, which serialises the loads.
+__device__ __forceinline__ uint32_t ldg_u16(const bf16* p) { return (uint32_t)__ldg(reinterpret_cast<const unsigned short*>(p)); }
+__device__ __forceinline__ float bf16_bits_to_float(uint32_t u) { return __uint_as_float(u << 16); }
 __device__ __forceinline__ float bf16_lo(uint32_t u) { return __uint_as_float(u << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t u) { return __uint_as_float(u & 0xffff0000u); }
 __device__ __forceinline__ void st_bf16(uint8_t* p, float v) { *reinterpret_cast<bf16*>(p) = __float2bfloat16_rn(v); }
 
 __global__ void __launch_bounds__(TTHREADS, 1)
-tc_chunk_bwd_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g, const bf16* __restrict__ v,
+tc_chunk_bwd_kernel(int64_t T, int64_t H, int64_t N, int pf_dist, const float* __restrict__ g, const bf16* __restrict__ v,
                     const bf16* __restrict__ k, const bf16* __restrict__ q, const bf16* __restrict__ dO,
                     const bf16* __restrict__ S_prev, const bf16* __restrict__ dS_next, const bf16* __restrict__ P_saved,
                     bf16* __restrict__ dq_out, bf16* __restrict__ dk_out, bf16* __restrict__ dv_out,
@@ -709,17 +752,34 @@ tc_chunk_bwd_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g
   TC_STAMP(1, 0);
 
   // ---- phase 0: operand tiles; gate products per 16 rows; k_hat -------------------------------
-  copy_tile_128x128(sm + BwdSmem::DO, dO + row0, HD);
-  copy_tile_128x128(sm + BwdSmem::V, v + row0, HD);
-  copy_tile_128x128(sm + BwdSmem::SP, S_prev + chunk_id * TD * TD, TD);
-  copy_tile_128x128(sm + BwdSmem::DS, dS_next + chunk_id * TD * TD, TD);
-  copy_tile_128x128(sm + BwdSmem::P, P_saved + chunk_id * TC * TC, TC);
+  {
+    // all 20 vector loads of the five operand tiles are issued before the first store consumes one
+    const int crow = tid >> 4, cch = tid & 15;       // this thread's 16-byte chunk in rows crow + 32 j
+    const bf16* src[5] = {dO + row0, v + row0, S_prev + chunk_id * TD * TD, dS_next + chunk_id * TD * TD,
+                          P_saved + chunk_id * TC * TC};
+    const int64_t ld[5] = {HD, HD, TD, TD, TC};
+    uint4 t[20];
+#pragma unroll
+    for (int m = 0; m < 5; ++m)
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        t[4 * m + j] = __ldg(reinterpret_cast<const uint4*>(src[m] + (int64_t)(crow + 32 * j) * ld[m] + cch * 8));
+#pragma unroll
+    for (int m = 0; m < 5; ++m)
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        *reinterpret_cast<uint4*>(sm + BwdSmem::DO + m * 2 * TILE_BYTES + (cch >> 3) * TILE_BYTES +
+                                  sw128_chunk(crow + 32 * j, cch & 7)) = t[4 * m + j];
+  }
   float f32r[32];                                   // gates of rows 32 wq_ + [0, 32), feature d
   {
     float p0 = 1.f, p1 = 1.f;
+    const float* gp = g + row0 + (int64_t)(32 * wq_) * HD + d;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) f32r[i] = __ldg(gp + (int64_t)i * HD);       // all 32 loads in flight
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
-      f32r[i] = __expf(g[row0 + (int64_t)(32 * wq_ + i) * HD + d]);
+      f32r[i] = __expf(f32r[i]);
       if (i < 16) p0 *= f32r[i]; else p1 *= f32r[i];
     }
     tot[(2 * wq_) * TD + d] = p0;
@@ -734,14 +794,26 @@ tc_chunk_bwd_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g
     // k_hat[r][d] = k[r][d] * prod_{t > r} f_t   (rows of this thread: 32 wq_ + i)
     float run = 1.f;
     for (int b2 = 2 * wq_ + 2; b2 < 8; ++b2) run *= tot[b2 * TD + d];
-    uint8_t* tile = sm + BwdSmem::KH + (d >> 6) * TILE_BYTES;
+    // stored TRANSPOSED: row = feature dk, columns = chunk rows j, so the thread's 32 values are 64
+    // contiguous bytes (four 16-byte stores instead of 32 two-byte ones)
+    uint8_t* tile = sm + BwdSmem::KH + (wq_ >> 1) * TILE_BYTES;
+    const bf16* kp = k + row0 + (int64_t)(32 * wq_) * HD + d;
+    uint32_t kraw[32];
 #pragma unroll
-    for (int i = 31; i >= 0; --i) {
-      const int r = 32 * wq_ + i;
-      const float kk = __bfloat162float(k[row0 + (int64_t)r * HD + d]);
-      st_bf16(tile + sw128_off(r, d & 63), kk * run);
+    for (int i = 0; i < 32; ++i) kraw[i] = ldg_u16(kp + (int64_t)i * HD);
+    uint32_t pk[16];
+#pragma unroll
+    for (int i = 31; i >= 1; i -= 2) {
+      const float hi = bf16_bits_to_float(kraw[i]) * run;
       run *= f32r[i];
+      const float lo = bf16_bits_to_float(kraw[i - 1]) * run;
+      run *= f32r[i - 1];
+      pk[i >> 1] = pack_bf16x2(lo, hi);
     }
+#pragma unroll
+    for (int c4 = 0; c4 < 4; ++c4)
+      *reinterpret_cast<uint4*>(tile + sw128_chunk(d, (wq_ & 1) * 4 + c4)) =
+          make_uint4(pk[4 * c4], pk[4 * c4 + 1], pk[4 * c4 + 2], pk[4 * c4 + 3]);
   }
   fence_async_smem();
   tc_fence_before();
@@ -753,7 +825,7 @@ tc_chunk_bwd_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g
     tc_fence_after();
     const uint32_t aDO = smem_u32(sm + BwdSmem::DO), aV = smem_u32(sm + BwdSmem::V), aSP = smem_u32(sm + BwdSmem::SP),
                    aDS = smem_u32(sm + BwdSmem::DS), aP = smem_u32(sm + BwdSmem::P), aKH = smem_u32(sm + BwdSmem::KH);
-    constexpr uint32_t iKK = idesc_bf16(128, 128, 0, 0), iMM = idesc_bf16(128, 128, 1, 1), iKM = idesc_bf16(128, 128, 0, 1);
+    constexpr uint32_t iKK = idesc_bf16(128, 128, 0, 0), iMM = idesc_bf16(128, 128, 1, 1);
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks)   // dP[i][j] = sum_dv dO[i][dv] v[j][dv]
       umma_bf16(tmem + TM_DP, desc_kmajor(aDO, TILE_BYTES, ks), desc_kmajor(aV, TILE_BYTES, ks), iKK, ks > 0);
@@ -768,8 +840,28 @@ tc_chunk_bwd_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g
       umma_bf16(tmem + TM_DV, desc_mnmajor(aP, TILE_BYTES, ks), desc_mnmajor(aDO, TILE_BYTES, ks), iMM, ks > 0);
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks)   //          + sum_dk k_hat[j][dk] dS_next[dk][dv]
-      umma_bf16(tmem + TM_DV, desc_kmajor(aKH, TILE_BYTES, ks), desc_mnmajor(aDS, TILE_BYTES, ks), iKM, 1);
+      umma_bf16(tmem + TM_DV, desc_mnmajor(aKH, TILE_BYTES, ks), desc_mnmajor(aDS, TILE_BYTES, ks), iMM, 1);
     umma_commit(smem_u32(bars + 0));
+  }
+  // This chunk's operands have landed: ask L2 for those of the chunk that the block scheduler will
+  // start on this SM when this block retires (pf_dist blocks ahead), so that its load phase streams
+  // from L2 while DRAM is busy during everybody's compute phases instead of everybody's load phases.
+  {
+    const int64_t nb = (int64_t)blockIdx.x + pf_dist;
+    if (pf_dist > 0 && nb < (int64_t)gridDim.x) {
+      const int64_t n2 = nb % N, bh2 = nb / N;
+      const int64_t r2 = (((bh2 / H) * T + n2 * TC) * H + (bh2 % H)) * TD;
+      const int64_t c2 = (bh2 * N + n2) * TD * TD;
+      // strided rows: one 128-byte line per request (256-byte rows of dO, v, k, q; 512-byte rows of g)
+      const int64_t e2 = r2 + (int64_t)((tid >> 1) & (TC - 1)) * HD + (tid & 1) * 64;
+      l2_prefetch_line(tid < 256 ? dO + e2 : v + e2);
+      l2_prefetch_line(tid < 256 ? k + e2 : q + e2);
+      l2_prefetch_line(g + r2 + (int64_t)(tid >> 2) * HD + (tid & 3) * 32);
+      // contiguous 32 KB tiles: one bulk request each
+      if (tid == 0) l2_prefetch_bulk(S_prev + c2, 2 * TD * TD);
+      else if (tid == 32) l2_prefetch_bulk(dS_next + c2, 2 * TD * TD);
+      else if (tid == 64) l2_prefetch_bulk(P_saved + (bh2 * N + n2) * TC * TC, 2 * TC * TC);
+    }
   }
   bool ok = mbar_wait(smem_u32(bars + 0), 0);
   tc_fence_after();
@@ -805,10 +897,15 @@ tc_chunk_bwd_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g
     tmem_ld32(tmem + ((uint32_t)(q4 * 32) << 16) + TM_DKH + 32 * wq_, r);
     tmem_ld_wait();
     float s1 = 0.f;
-    const uint8_t* tile = sm + BwdSmem::KH + (d >> 6) * TILE_BYTES;
+    const uint8_t* tile = sm + BwdSmem::KH + (wq_ >> 1) * TILE_BYTES;
 #pragma unroll
-    for (int m = 0; m < 32; ++m)
-      s1 = fmaf(__uint_as_float(r[m]), __bfloat162float(*reinterpret_cast<const bf16*>(tile + sw128_off(32 * wq_ + m, d & 63))), s1);
+    for (int c4 = 0; c4 < 4; ++c4) {
+      const uint4 a = *reinterpret_cast<const uint4*>(tile + sw128_chunk(d, (wq_ & 1) * 4 + c4));
+      s1 = fmaf(__uint_as_float(r[8 * c4 + 0]), bf16_lo(a.x), s1); s1 = fmaf(__uint_as_float(r[8 * c4 + 1]), bf16_hi(a.x), s1);
+      s1 = fmaf(__uint_as_float(r[8 * c4 + 2]), bf16_lo(a.y), s1); s1 = fmaf(__uint_as_float(r[8 * c4 + 3]), bf16_hi(a.y), s1);
+      s1 = fmaf(__uint_as_float(r[8 * c4 + 4]), bf16_lo(a.z), s1); s1 = fmaf(__uint_as_float(r[8 * c4 + 5]), bf16_hi(a.z), s1);
+      s1 = fmaf(__uint_as_float(r[8 * c4 + 6]), bf16_lo(a.w), s1); s1 = fmaf(__uint_as_float(r[8 * c4 + 7]), bf16_hi(a.w), s1);
+    }
     atomicAdd(dG1 + d, s1);
     // dG2[d] = sum_v S_prev[d][v] dS_next[d][v]    (this thread: v in 32 wq_ + [0, 32))
     float s2 = 0.f;
@@ -830,24 +927,37 @@ tc_chunk_bwd_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g
   TC_STAMP(1, 4);
   // ---- phase 1.9: W64 for all 128 rows (rows < 64: k~, rows >= 64: q~, anchor row 63) ----------------------
   {
-    uint8_t* tile = sm + BwdSmem::W64 + (d >> 6) * TILE_BYTES;
+    uint8_t* tile = sm + BwdSmem::W64 + (wq_ >> 1) * TILE_BYTES;       // transposed like k_hat: row = feature
+    const bf16* xp = (wq_ < 2 ? k : q) + row0 + (int64_t)(32 * wq_) * HD + d;
+    uint32_t xraw[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) xraw[i] = ldg_u16(xp + (int64_t)i * HD);
+    uint32_t pk[16];
     if (wq_ < 2) {
       float run = (wq_ == 0) ? tot[2 * TD + d] * tot[3 * TD + d] : 1.f;
 #pragma unroll
-      for (int i = 31; i >= 0; --i) {
-        const int r = 32 * wq_ + i;
-        st_bf16(tile + sw128_off(r, d & 63), __bfloat162float(k[row0 + (int64_t)r * HD + d]) * run);
+      for (int i = 31; i >= 1; i -= 2) {
+        const float hi = bf16_bits_to_float(xraw[i]) * run;
         run *= f32r[i];
+        const float lo = bf16_bits_to_float(xraw[i - 1]) * run;
+        run *= f32r[i - 1];
+        pk[i >> 1] = pack_bf16x2(lo, hi);
       }
     } else {
       float run = (wq_ == 3) ? tot[4 * TD + d] * tot[5 * TD + d] : 1.f;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const int r = 32 * wq_ + i;
+      for (int i = 0; i < 32; i += 2) {
         run *= f32r[i];
-        st_bf16(tile + sw128_off(r, d & 63), __bfloat162float(q[row0 + (int64_t)r * HD + d]) * run);
+        const float lo = bf16_bits_to_float(xraw[i]) * run;
+        run *= f32r[i + 1];
+        const float hi = bf16_bits_to_float(xraw[i + 1]) * run;
+        pk[i >> 1] = pack_bf16x2(lo, hi);
       }
     }
+#pragma unroll
+    for (int c4 = 0; c4 < 4; ++c4)
+      *reinterpret_cast<uint4*>(tile + sw128_chunk(d, (wq_ & 1) * 4 + c4)) =
+          make_uint4(pk[4 * c4], pk[4 * c4 + 1], pk[4 * c4 + 2], pk[4 * c4 + 3]);
   }
   float eG = 1.f;
 #pragma unroll
@@ -866,11 +976,20 @@ tc_chunk_bwd_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g
     const int gi = 4 * p + rq;
     float f[16], dq[16], dk[16];
     uint32_t qk[16];
+    {
+      const int64_t e1 = row0 + (int64_t)rbase * HD + d;
+      uint32_t kr[16];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const int64_t e = row0 + (int64_t)(rbase + i) * HD + d;
-      f[i] = __expf(g[e]);
-      qk[i] = (uint32_t)__bfloat16_as_ushort(q[e]) | ((uint32_t)__bfloat16_as_ushort(k[e]) << 16);
+      for (int i = 0; i < 16; ++i) {          // 48 loads in flight before anything uses one
+        f[i] = __ldg(g + e1 + (int64_t)i * HD);
+        qk[i] = ldg_u16(q + e1 + (int64_t)i * HD);
+        kr[i] = ldg_u16(k + e1 + (int64_t)i * HD);
+      }
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        f[i] = __expf(f[i]);
+        qk[i] |= kr[i] << 16;
+      }
     }
     // inter-chunk terms and the diagonal
     {
@@ -903,41 +1022,60 @@ tc_chunk_bwd_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g
       constexpr int HHv = 1 << S;
       const int bsel = S & 1;
       if (S < 6) {
+        // W_l stored transposed (row = feature d, columns = the 64 rows of the half): this thread's 16
+        // values are 32 contiguous bytes
         float w[16];
         level_weights<S>(f, rq, p, tot, d, w);
-        uint8_t* tile = sm + BwdSmem::WL + bsel * TILE_BYTES + (d >> 6) * KC_TILE;
+        uint8_t* tile = sm + BwdSmem::WL + bsel * TILE_BYTES;
+        const uint32_t sh = (S < 4) ? 0u : (row_is_right<S>(0, rq, p) ? 16u : 0u);
+        uint32_t pk[8];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float x = row_is_right<S>(i, rq, p) ? bf16_lo(qk[i]) : bf16_hi(qk[i]);
-          st_bf16(tile + sw128_off(16 * rq + i, d & 63), x * w[i]);
+        for (int i = 0; i < 16; i += 2) {
+          float x0, x1;
+          if (S < 4) {
+            x0 = row_is_right<S>(i, rq, p) ? bf16_lo(qk[i]) : bf16_hi(qk[i]);
+            x1 = row_is_right<S>(i + 1, rq, p) ? bf16_lo(qk[i + 1]) : bf16_hi(qk[i + 1]);
+          } else {
+            x0 = __uint_as_float((qk[i] << sh) & 0xffff0000u);
+            x1 = __uint_as_float((qk[i + 1] << sh) & 0xffff0000u);
+          }
+          pk[i >> 1] = pack_bf16x2(x0 * w[i], x1 * w[i + 1]);
         }
+        *reinterpret_cast<uint4*>(tile + sw128_chunk(d, 2 * rq)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        *reinterpret_cast<uint4*>(tile + sw128_chunk(d, 2 * rq + 1)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
       }
-      // masked 64 x 64 block of dP (row layout): rows i, columns j
+      // masked 64 x 64 block of dP (row layout): rows i, columns j = jbase + 16 wq_ + m
       {
         const int ibase = (S == 6) ? 64 : 64 * p;
         const int jbase = (S == 6) ? 0 : 64 * p;
         if ((q4 >> 1) == (ibase >> 6)) {
           const int i = 32 * q4 + lane;
+          // Level membership: i and j in the same block of 2^(S+1) rows, i in its right half, j in its
+          // left half.  The 16 columns of this thread start at a multiple of 16, so for S < 4 the test
+          // splits into a per-thread part (sel) and a compile-time part (m); for S >= 4 it is per-thread.
+          int sel;          // S < 4: the value (m >> (S+1)) must have, or -1; S >= 4: 0 keep all, -1 none
+          if (S < 4)       sel = (((i >> 4) == ((jbase >> 4) + wq_)) && ((i >> S) & 1)) ? ((i & 15) >> (S + 1)) : -1;
+          else if (S == 4) sel = (((i >> 5) == ((jbase >> 5) + (wq_ >> 1))) && ((i >> 4) & 1) && !(wq_ & 1)) ? 0 : -1;
+          else if (S == 5) sel = (((i >> 5) & 1) && (wq_ < 2)) ? 0 : -1;
+          else             sel = 0;
           uint32_t r[16];
           tmem_ld16(tmem + ((uint32_t)(q4 * 32) << 16) + TM_DP + jbase + 16 * wq_, r);
           tmem_ld_wait();
-          float x[16];
+          uint32_t pk[8];
 #pragma unroll
-          for (int m = 0; m < 16; ++m) {
-            const int j = jbase + 16 * wq_ + m;
-            const bool keep = (S == 6) ? true : ((((i ^ j) >> S) == 1) && ((j & HHv) == 0));
-            x[m] = keep ? __uint_as_float(r[m]) : 0.f;
+          for (int m = 0; m < 16; m += 2) {
+            bool k0, k1;
+            if (S < 4) {
+              k0 = !((m >> S) & 1) && (sel == (m >> (S + 1)));
+              k1 = !(((m + 1) >> S) & 1) && (sel == ((m + 1) >> (S + 1)));
+            } else {
+              k0 = k1 = (sel == 0);
+            }
+            pk[m >> 1] = pack_bf16x2(k0 ? __uint_as_float(r[m]) : 0.f, k1 ? __uint_as_float(r[m + 1]) : 0.f);
           }
           uint8_t* tile = sm + BwdSmem::DPL + bsel * (KC_TILE);
-#pragma unroll
-          for (int c2 = 0; c2 < 2; ++c2) {
-            uint4 u;
-            u.x = pack_bf16x2(x[8 * c2 + 0], x[8 * c2 + 1]);
-            u.y = pack_bf16x2(x[8 * c2 + 2], x[8 * c2 + 3]);
-            u.z = pack_bf16x2(x[8 * c2 + 4], x[8 * c2 + 5]);
-            u.w = pack_bf16x2(x[8 * c2 + 6], x[8 * c2 + 7]);
-            *reinterpret_cast<uint4*>(tile + sw128_chunk(i - ibase, 2 * wq_ + c2)) = u;
-          }
+          *reinterpret_cast<uint4*>(tile + sw128_chunk(i - ibase, 2 * wq_)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          *reinterpret_cast<uint4*>(tile + sw128_chunk(i - ibase, 2 * wq_ + 1)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
         }
       }
       fence_async_smem();
@@ -947,23 +1085,23 @@ tc_chunk_bwd_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g
         tc_fence_after();
         const uint32_t tacc = tmem + TM_T + 64 * bsel;
         const uint32_t bD = aDPL + bsel * KC_TILE;
-        constexpr uint32_t iK = idesc_bf16(128, 64, 1, 0), iM = idesc_bf16(128, 64, 1, 1);
+        constexpr uint32_t iK = idesc_bf16(128, 64, 0, 0), iM = idesc_bf16(128, 64, 0, 1);
         if (S < 6) {
           const uint32_t aW = aWL + bsel * TILE_BYTES;
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks)    // rows i of the half on the columns: dq side
-            umma_bf16(tacc, desc_mnmajor(aW, KC_TILE, ks), desc_kmajor(bD, KC_TILE, ks), iK, ks > 0);
+            umma_bf16(tacc, desc_kmajor(aW, TILE_BYTES, ks), desc_kmajor(bD, KC_TILE, ks), iK, ks > 0);
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks)    // rows j on the columns: dk side
-            umma_bf16(tacc, desc_mnmajor(aW, KC_TILE, ks), desc_mnmajor(bD, KC_TILE, ks), iM, 1);
+            umma_bf16(tacc, desc_kmajor(aW, TILE_BYTES, ks), desc_mnmajor(bD, KC_TILE, ks), iM, 1);
         } else if (p == 1) {
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks)    // T[d][i-64] = sum_{j<64} k~64[j][d] dP[i][j]
-            umma_bf16(tacc, desc_mnmajor(aW64, TILE_BYTES, ks), desc_kmajor(bD, KC_TILE, ks), iK, ks > 0);
+            umma_bf16(tacc, desc_kmajor(aW64, TILE_BYTES, ks), desc_kmajor(bD, KC_TILE, ks), iK, ks > 0);
         } else {
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks)    // T[d][j] = sum_{i>=64} q~64[i][d] dP[i][j]
-            umma_bf16(tacc, desc_mnmajor(aW64 + 64 * 128, TILE_BYTES, ks), desc_mnmajor(bD, KC_TILE, ks), iM, ks > 0);
+            umma_bf16(tacc, desc_kmajor(aW64 + TILE_BYTES, TILE_BYTES, ks), desc_mnmajor(bD, KC_TILE, ks), iM, ks > 0);
         }
         umma_commit(smem_u32(bars + 1 + bsel));
       }
@@ -1188,7 +1326,7 @@ int tc_chunk_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
   {
     ProfScope ps("tc_chunk_bwd_kernel", st);
     tc_chunk_bwd_kernel<<<(unsigned)(BH * N), TTHREADS, BWD_SMEM, st>>>(
-        T, H, N, g, (const bf16*)v, (const bf16*)k, (const bf16*)q, (const bf16*)dout, S_prev, dS_next, P, (bf16*)dq,
+        T, H, N, prefetch_distance(1), g, (const bf16*)v, (const bf16*)k, (const bf16*)q, (const bf16*)dout, S_prev, dS_next, P, (bf16*)dq,
         (bf16*)dk, (bf16*)dv, dg);
   }
   GLA_CHECK_LAUNCH();
@@ -1198,9 +1336,13 @@ int tc_chunk_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
 void tc_read_trace(long long* out64) {
   cudaMemcpyFromSymbol(out64, g_tc_trace, sizeof(long long) * 64);
 }
+#ifdef GLA_TIMELINE
+void tc_read_wtrace(long long* o) { cudaMemcpyFromSymbol(o, g_tl, sizeof(g_tl)); }
+#else
 void tc_read_wtrace(long long* out512) {
   cudaMemcpyFromSymbol(out512, g_tc_wtrace, sizeof(long long) * 512);
 }
+#endif
 
 unsigned int tc_read_wait_timeouts() {
   unsigned int v = 0;
