@@ -17,6 +17,7 @@
 // so only C*D exponentials are evaluated per chunk and no exponent is ever positive.
 #include "gla_common.cuh"
 #include "tc_ptx.cuh"
+#include "tma_maps.cuh"
 #include <type_traits>
 #include <cuda.h>
 #include <cstdlib>
@@ -1199,53 +1200,6 @@ bool tc_auto_default() { return true; }
 
 static size_t f32b(int64_t n) { return align_up((size_t)n * 4, 256); }
 
-// ---- TMA descriptors -------------------------------------------------------------------------
-// cuTensorMapEncodeTiled is fetched through the runtime so that the library has no link-time
-// dependency on libcuda (it must load on machines without a driver).
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)p;
-  }
-  return fn;
-}
-// (B,T,H,128) array seen as 3-d (d, h, b*T + t); box = (box_cols, 1, 128 rows); float32 or bf16.
-static int make_map_bthd(CUtensorMap* m, const void* ptr, int is_f32, int64_t B, int64_t T, int64_t H, int box_cols,
-                         int swizzle128) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return GLA_ERR_NO_DEVICE;
-  const cuuint64_t es = is_f32 ? 4 : 2;
-  cuuint64_t dims[3] = {(cuuint64_t)TD, (cuuint64_t)H, (cuuint64_t)(B * T)};
-  cuuint64_t strides[2] = {(cuuint64_t)TD * es, (cuuint64_t)H * TD * es};
-  cuuint32_t box[3] = {(cuuint32_t)box_cols, 1, 128};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = fn(m, is_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, (void*)ptr, dims,
-                  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? GLA_OK : GLA_ERR_LAUNCH;
-}
-// dense bf16 matrix of `rows` rows x 128 columns; box = (box_cols, box_rows), 128-byte swizzle.
-static int make_map_rows(CUtensorMap* m, const void* ptr, int64_t rows, int box_cols, int box_rows) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return GLA_ERR_NO_DEVICE;
-  cuuint64_t dims[2] = {(cuuint64_t)TD, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)TD * 2};
-  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)ptr, dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? GLA_OK : GLA_ERR_LAUNCH;
-}
-
 static size_t b16b(int64_t n) { return align_up((size_t)n * 2, 256); }
 
 // saved: S_prev bf16 (BH,N,D,D) | Gc f32 (BH,N,D) | P bf16 (BH,N,C,C)
@@ -1281,7 +1235,9 @@ int tc_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
     Gc = (float*)s;    s += f32b(BH * N * D);
     P = (bf16*)s;
   }
-  GLA_TRY((launch_tc_kv<0>(st, B, T, H, g, k, v, kv, Gc)));
+  const bool fused_states = !state_only && tc_state_fused_preferred(BH, N);
+  if (fused_states) GLA_TRY(tc_state_fused(st, 0, B, T, H, g, k, v, hidden_init, S_prev, hidden_final, Gc));
+  else GLA_TRY((launch_tc_kv<0>(st, B, T, H, g, k, v, kv, Gc)));
   if (state_only) {
     GLA_TRY(launch_state_scan(st, BH, N, D, Gc, kv, 0, nullptr, 0, nullptr, 0, S_local, 0, 0));
     ProfScope ps("tc_gsum_kernel", st);
@@ -1289,7 +1245,7 @@ int tc_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
     GLA_CHECK_LAUNCH();
     return GLA_OK;
   }
-  GLA_TRY(launch_state_scan(st, BH, N, D, Gc, kv, 0, hidden_init, 1, S_prev, 1, hidden_final, 1, 0));
+  if (!fused_states) GLA_TRY(launch_state_scan(st, BH, N, D, Gc, kv, 0, hidden_init, 1, S_prev, 1, hidden_final, 1, 0));
   cudaError_t e = cudaFuncSetAttribute(tc_chunk_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FWD_SMEM);
   if (e != cudaSuccess) return record_cuda_error(e);
   FwdMaps maps;
@@ -1319,8 +1275,12 @@ int tc_chunk_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
   const bf16* S_prev = (const bf16*)s; s += b16b(BH * N * D * D);
   const float* Gc = (const float*)s;   s += f32b(BH * N * D);
   const bf16* P = (const bf16*)s;
-  GLA_TRY((launch_tc_kv<1>(st, B, T, H, g, q, dout, dstate, nullptr)));
-  GLA_TRY(launch_state_scan(st, BH, N, D, Gc, dstate, 0, dhidden_final, 1, dS_next, 1, dhidden_init, 1, 1));
+  if (tc_state_fused_preferred(BH, N)) {
+    GLA_TRY(tc_state_fused(st, 1, B, T, H, g, q, dout, dhidden_final, dS_next, dhidden_init, nullptr));
+  } else {
+    GLA_TRY((launch_tc_kv<1>(st, B, T, H, g, q, dout, dstate, nullptr)));
+    GLA_TRY(launch_state_scan(st, BH, N, D, Gc, dstate, 0, dhidden_final, 1, dS_next, 1, dhidden_init, 1, 1));
+  }
   cudaError_t e = cudaFuncSetAttribute(tc_chunk_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)BWD_SMEM);
   if (e != cudaSuccess) return record_cuda_error(e);
   {

@@ -99,6 +99,14 @@ int tc_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
                  const void* hidden_init, const float* g, const void* v, const void* k, const void* q,
                  void* hidden_final, void* out, void* saved, void* ws, int state_only,
                  float* G_total, float* S_local);
+// One-pass chunk states (product and recurrence fused); mode 0 forward states, mode 1 gradient states.
+bool tc_state_fused_preferred(int64_t BH, int64_t N);
+int tc_state_fused(cudaStream_t st, int mode, int64_t B, int64_t T, int64_t H, const float* g, const void* x,
+                   const void* y, const void* init, void* states, void* fin, float* Gc);
+unsigned int tc_state_read_wait_timeouts();
+#ifdef ST_TRACE
+void tc_state_read_trace(long long* o);
+#endif
 int tc_chunk_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, int64_t C,
                  const float* g, const void* v, const void* k, const void* q, const void* saved,
                  const void* dhidden_final, const void* dout, void* dhidden_init, float* dg,

@@ -45,6 +45,15 @@ __device__ __forceinline__ uint64_t desc_kmajor(uint32_t base, uint32_t tile_str
 __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t base, uint32_t tile_stride, int ks) {
   return smem_desc(base + (uint32_t)ks * 2048u, tile_stride, 1024u);
 }
+// A descriptor whose start address is `bytes` further on (bytes a multiple of 16, the sum staying below the
+// 256 KB the 14-bit field covers): only the low word changes, so stepping through the K slices of an
+// operand costs one 32-bit add per MMA instead of rebuilding the descriptor.
+__device__ __forceinline__ uint64_t desc_advance(uint64_t d, uint32_t bytes) {
+  uint32_t lo = (uint32_t)d + (bytes >> 4), hi = (uint32_t)(d >> 32);
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
 // 32-bit instruction descriptor for kind::f16 with bf16 inputs and fp32 accumulation.
 __host__ __device__ constexpr uint32_t idesc_bf16(int M, int N, int a_mn_major, int b_mn_major) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) |
