@@ -50,6 +50,14 @@ __device__ __forceinline__ int smid() { int t; asm volatile("mov.u32 %0, %smid;"
 #endif
 #define TC_STAMP(which, idx) do { if (blockIdx.x == 500 && threadIdx.x == 0) g_tc_trace[which][idx] = clock64(); } while (0)
 
+// K slice ks of an operand whose slice-0 descriptor is d0 (K-major: 32 bytes per slice, next 64-column
+// block after four; MN-major: 2048 bytes per slice).  One 32-bit add instead of a descriptor rebuild, which
+// matters because the issuing thread's instruction stream is serial and on the critical path.
+__device__ __forceinline__ uint64_t kslice_kmajor(uint64_t d0, uint32_t tile_stride, int ks) {
+  return desc_advance(d0, (uint32_t)(ks >> 2) * tile_stride + (uint32_t)(ks & 3) * 32u);
+}
+__device__ __forceinline__ uint64_t kslice_mnmajor(uint64_t d0, int ks) { return desc_advance(d0, (uint32_t)ks * 2048u); }
+
 // smem carve-up helper: dynamic shared memory aligned to 1024 bytes
 __device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
   return (uint8_t*)(((uintptr_t)p + 1023) & ~(uintptr_t)1023);
@@ -431,10 +439,11 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, 
   auto issue_level = [&](int slot) {
     const int bsel = slot & 1;
     constexpr uint32_t idesc = idesc_bf16(128, 64, 0, 0);
-    const uint32_t a0 = sQ0 + bsel * 2 * TILE_BYTES, b0 = sK0 + bsel * 2 * KC_TILE;
+    const uint64_t a0 = desc_kmajor(sQ0 + bsel * 2 * TILE_BYTES, TILE_BYTES, 0), b0 = desc_kmajor(sK0 + bsel * 2 * KC_TILE, KC_TILE, 0);
+    const uint32_t acc = tmem + 64 * slot;
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks)
-      umma_bf16(tmem + 64 * slot, desc_kmajor(a0, TILE_BYTES, ks), desc_kmajor(b0, KC_TILE, ks), idesc, ks > 0);
+      umma_bf16(acc, kslice_kmajor(a0, TILE_BYTES, ks), kslice_kmajor(b0, KC_TILE, ks), idesc, ks > 0);
     umma_commit(smem_u32(bars + bsel));
   };
   auto level_sync_and_issue = [&](int slot) {
@@ -574,13 +583,14 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, 
   if (tid == 0) {
     tc_fence_after();
     constexpr uint32_t idesc = idesc_bf16(128, 128, 0, 1);
-    const uint32_t aq = sQ0 + 2 * TILE_BYTES, bs = smem_u32(sm + FwdSmem::S), ap = smem_u32(sm + FwdSmem::P), bv = smem_u32(sm + FwdSmem::V);
+    const uint64_t aq = desc_kmajor(sQ0 + 2 * TILE_BYTES, TILE_BYTES, 0), bs = desc_mnmajor(smem_u32(sm + FwdSmem::S), TILE_BYTES, 0);
+    const uint64_t ap = desc_kmajor(smem_u32(sm + FwdSmem::P), TILE_BYTES, 0), bv = desc_mnmajor(smem_u32(sm + FwdSmem::V), TILE_BYTES, 0);
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks)
-      umma_bf16(tmem, desc_kmajor(aq, TILE_BYTES, ks), desc_mnmajor(bs, TILE_BYTES, ks), idesc, ks > 0);
+      umma_bf16(tmem, kslice_kmajor(aq, TILE_BYTES, ks), kslice_mnmajor(bs, ks), idesc, ks > 0);
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks)
-      umma_bf16(tmem, desc_kmajor(ap, TILE_BYTES, ks), desc_mnmajor(bv, TILE_BYTES, ks), idesc, 1);
+      umma_bf16(tmem, kslice_kmajor(ap, TILE_BYTES, ks), kslice_mnmajor(bv, ks), idesc, 1);
     umma_commit(smem_u32(bars + 2));
   }
   TC_STAMP(0, 12);
@@ -824,24 +834,28 @@ tc_chunk_bwd_kernel(int64_t T, int64_t H, int64_t N, int pf_dist, const float* _
   // ---- phase 1: the four dense products --------------------------------------------------------------
   if (tid == 0) {
     tc_fence_after();
+    constexpr uint32_t iKK = idesc_bf16(128, 128, 0, 0), iMM = idesc_bf16(128, 128, 1, 1);
     const uint32_t aDO = smem_u32(sm + BwdSmem::DO), aV = smem_u32(sm + BwdSmem::V), aSP = smem_u32(sm + BwdSmem::SP),
                    aDS = smem_u32(sm + BwdSmem::DS), aP = smem_u32(sm + BwdSmem::P), aKH = smem_u32(sm + BwdSmem::KH);
-    constexpr uint32_t iKK = idesc_bf16(128, 128, 0, 0), iMM = idesc_bf16(128, 128, 1, 1);
+    const uint64_t kDO = desc_kmajor(aDO, TILE_BYTES, 0), kV = desc_kmajor(aV, TILE_BYTES, 0), kSP = desc_kmajor(aSP, TILE_BYTES, 0),
+                   kDS = desc_kmajor(aDS, TILE_BYTES, 0);
+    const uint64_t mP = desc_mnmajor(aP, TILE_BYTES, 0), mDO = desc_mnmajor(aDO, TILE_BYTES, 0), mKH = desc_mnmajor(aKH, TILE_BYTES, 0),
+                   mDS = desc_mnmajor(aDS, TILE_BYTES, 0);
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks)   // dP[i][j] = sum_dv dO[i][dv] v[j][dv]
-      umma_bf16(tmem + TM_DP, desc_kmajor(aDO, TILE_BYTES, ks), desc_kmajor(aV, TILE_BYTES, ks), iKK, ks > 0);
+      umma_bf16(tmem + TM_DP, kslice_kmajor(kDO, TILE_BYTES, ks), kslice_kmajor(kV, TILE_BYTES, ks), iKK, ks > 0);
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks)   // dQh^T[dk][i] = sum_dv S_prev[dk][dv] dO[i][dv]
-      umma_bf16(tmem + TM_DQH, desc_kmajor(aSP, TILE_BYTES, ks), desc_kmajor(aDO, TILE_BYTES, ks), iKK, ks > 0);
+      umma_bf16(tmem + TM_DQH, kslice_kmajor(kSP, TILE_BYTES, ks), kslice_kmajor(kDO, TILE_BYTES, ks), iKK, ks > 0);
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks)   // dKh^T[dk][j] = sum_dv dS_next[dk][dv] v[j][dv]
-      umma_bf16(tmem + TM_DKH, desc_kmajor(aDS, TILE_BYTES, ks), desc_kmajor(aV, TILE_BYTES, ks), iKK, ks > 0);
+      umma_bf16(tmem + TM_DKH, kslice_kmajor(kDS, TILE_BYTES, ks), kslice_kmajor(kV, TILE_BYTES, ks), iKK, ks > 0);
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks)   // dV[j][dv] = sum_i P[i][j] dO[i][dv]
-      umma_bf16(tmem + TM_DV, desc_mnmajor(aP, TILE_BYTES, ks), desc_mnmajor(aDO, TILE_BYTES, ks), iMM, ks > 0);
+      umma_bf16(tmem + TM_DV, kslice_mnmajor(mP, ks), kslice_mnmajor(mDO, ks), iMM, ks > 0);
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks)   //          + sum_dk k_hat[j][dk] dS_next[dk][dv]
-      umma_bf16(tmem + TM_DV, desc_mnmajor(aKH, TILE_BYTES, ks), desc_mnmajor(aDS, TILE_BYTES, ks), iMM, 1);
+      umma_bf16(tmem + TM_DV, kslice_mnmajor(mKH, ks), kslice_mnmajor(mDS, ks), iMM, 1);
     umma_commit(smem_u32(bars + 0));
   }
   // This chunk's operands have landed: ask L2 for those of the chunk that the block scheduler will
@@ -1085,24 +1099,26 @@ tc_chunk_bwd_kernel(int64_t T, int64_t H, int64_t N, int pf_dist, const float* _
       if (tid == 0) {
         tc_fence_after();
         const uint32_t tacc = tmem + TM_T + 64 * bsel;
-        const uint32_t bD = aDPL + bsel * KC_TILE;
+        const uint64_t kD = desc_kmajor(aDPL + bsel * KC_TILE, KC_TILE, 0), mD = desc_mnmajor(aDPL + bsel * KC_TILE, KC_TILE, 0);
         constexpr uint32_t iK = idesc_bf16(128, 64, 0, 0), iM = idesc_bf16(128, 64, 0, 1);
         if (S < 6) {
-          const uint32_t aW = aWL + bsel * TILE_BYTES;
+          const uint64_t kW = desc_kmajor(aWL + bsel * TILE_BYTES, TILE_BYTES, 0);
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks)    // rows i of the half on the columns: dq side
-            umma_bf16(tacc, desc_kmajor(aW, TILE_BYTES, ks), desc_kmajor(bD, KC_TILE, ks), iK, ks > 0);
+            umma_bf16(tacc, kslice_kmajor(kW, TILE_BYTES, ks), kslice_kmajor(kD, KC_TILE, ks), iK, ks > 0);
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks)    // rows j on the columns: dk side
-            umma_bf16(tacc, desc_kmajor(aW, TILE_BYTES, ks), desc_mnmajor(bD, KC_TILE, ks), iM, 1);
+            umma_bf16(tacc, kslice_kmajor(kW, TILE_BYTES, ks), kslice_mnmajor(mD, ks), iM, 1);
         } else if (p == 1) {
+          const uint64_t kW = desc_kmajor(aW64, TILE_BYTES, 0);
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks)    // T[d][i-64] = sum_{j<64} k~64[j][d] dP[i][j]
-            umma_bf16(tacc, desc_kmajor(aW64, TILE_BYTES, ks), desc_kmajor(bD, KC_TILE, ks), iK, ks > 0);
+            umma_bf16(tacc, kslice_kmajor(kW, TILE_BYTES, ks), kslice_kmajor(kD, KC_TILE, ks), iK, ks > 0);
         } else {
+          const uint64_t kW = desc_kmajor(aW64 + TILE_BYTES, TILE_BYTES, 0);
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks)    // T[d][j] = sum_{i>=64} q~64[i][d] dP[i][j]
-            umma_bf16(tacc, desc_kmajor(aW64 + TILE_BYTES, TILE_BYTES, ks), desc_mnmajor(bD, KC_TILE, ks), iM, ks > 0);
+            umma_bf16(tacc, kslice_kmajor(kW, TILE_BYTES, ks), kslice_mnmajor(mD, ks), iM, ks > 0);
         }
         umma_commit(smem_u32(bars + 1 + bsel));
       }
