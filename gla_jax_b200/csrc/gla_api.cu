@@ -84,11 +84,6 @@ long long gla_launch_count(void) { return g_launches; }
 unsigned int gla_device_wait_timeouts(void) { return tc_read_wait_timeouts() + tc_state_read_wait_timeouts(); }
 
 void gla_debug_phase_clocks(long long* out64) { tc_read_trace(out64); }
-#ifdef ST_TRACE
-__attribute__((visibility("default"))) void gla_debug_wtrace(long long* o) { tc_state_read_trace(o); }
-#else
-__attribute__((visibility("default"))) void gla_debug_wtrace(long long* o) { tc_read_wtrace(o); }
-#endif
 
 void gla_profile_enable(int on) {
   g_prof_on = on != 0;

@@ -36,18 +36,6 @@ __device__ unsigned int g_tc_wait_timeouts = 0;   // incremented when a bounded 
 // Phase clock stamps of one thread block (block 100, thread 0) of the last forward / backward
 // chunk kernel: a cheap always-on diagnostic read back by gla_debug_phase_clocks().
 __device__ long long g_tc_trace[2][32];
-__device__ long long g_tc_wtrace[16][32];
-#define TC_WSTAMP(idx) do { if (blockIdx.x == 500 && (threadIdx.x & 31) == 0) g_tc_wtrace[threadIdx.x >> 5][idx] = clock64(); } while (0)
-#ifdef GLA_TIMELINE
-__device__ long long g_tl[3 * 1024];
-__device__ __forceinline__ long long gtimer() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-__device__ __forceinline__ int smid() { int t; asm volatile("mov.u32 %0, %smid;" : "=r"(t)); return t; }
-#define TL_BEGIN() do { if (threadIdx.x == 0 && blockIdx.x < 1024) { g_tl[3 * blockIdx.x] = gtimer(); g_tl[3 * blockIdx.x + 2] = smid(); } } while (0)
-#define TL_END() do { if (threadIdx.x == 0 && blockIdx.x < 1024) { g_tl[3 * blockIdx.x + 1] = gtimer(); } } while (0)
-#else
-#define TL_BEGIN()
-#define TL_END()
-#endif
 #define TC_STAMP(which, idx) do { if (blockIdx.x == 500 && threadIdx.x == 0) g_tc_trace[which][idx] = clock64(); } while (0)
 
 // K slice ks of an operand whose slice-0 descriptor is d0 (K-major: 32 bytes per slice, next 64-column
@@ -102,7 +90,6 @@ tc_kv_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g, const
   const int64_t n = blockIdx.x % N, bh = blockIdx.x / N, b = bh / H, h = bh % H;
   const int64_t HD = H * TD;
   const int64_t row0 = ((b * T + n * TC) * H + h) * TD;     // element (b, n*C, h, 0)
-  if (MODE == 0) TL_BEGIN();
 
   if (warp == 0) {
     tmem_alloc(smem_u32(tmem_slot), 128);
@@ -214,7 +201,6 @@ tc_kv_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g, const
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, 128);
-  if (MODE == 0) TL_END();
 }
 
 // Number of thread blocks resident at a time (SMs x blocks per SM) = how far ahead in block index the
@@ -1312,13 +1298,6 @@ int tc_chunk_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
 void tc_read_trace(long long* out64) {
   cudaMemcpyFromSymbol(out64, g_tc_trace, sizeof(long long) * 64);
 }
-#ifdef GLA_TIMELINE
-void tc_read_wtrace(long long* o) { cudaMemcpyFromSymbol(o, g_tl, sizeof(g_tl)); }
-#else
-void tc_read_wtrace(long long* out512) {
-  cudaMemcpyFromSymbol(out512, g_tc_wtrace, sizeof(long long) * 512);
-}
-#endif
 
 unsigned int tc_read_wait_timeouts() {
   unsigned int v = 0;

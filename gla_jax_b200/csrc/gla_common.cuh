@@ -91,7 +91,6 @@ bool tc_supported(int64_t D, int64_t C, int dtype);
 bool tc_auto_default();
 unsigned int tc_read_wait_timeouts();
 void tc_read_trace(long long* out64);
-void tc_read_wtrace(long long* out512);
 size_t tc_saved_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t C);
 size_t tc_fwd_ws_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t C);
 size_t tc_bwd_ws_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t C);
@@ -104,9 +103,6 @@ bool tc_state_fused_preferred(int64_t BH, int64_t N);
 int tc_state_fused(cudaStream_t st, int mode, int64_t B, int64_t T, int64_t H, const float* g, const void* x,
                    const void* y, const void* init, void* states, void* fin, float* Gc);
 unsigned int tc_state_read_wait_timeouts();
-#ifdef ST_TRACE
-void tc_state_read_trace(long long* o);
-#endif
 int tc_chunk_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, int64_t C,
                  const float* g, const void* v, const void* k, const void* q, const void* saved,
                  const void* dhidden_final, const void* dout, void* dhidden_init, float* dg,

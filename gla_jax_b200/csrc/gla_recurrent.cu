@@ -77,14 +77,12 @@ __device__ __forceinline__ void tile_fetch(uint4 (&raw)[NG], const TileSrc& s, i
     if (e < RB * W && sidx < T) {
       const int64_t t = time_reversed ? (T - 1 - sidx) : sidx;
       const int64_t off = base + t * row_stride + c0 + col;
-#ifndef REC_NO_LOAD
       if (s.bf) {
         const uint2 w = __ldg(reinterpret_cast<const uint2*>((const bf16*)s.p + off));
         u.x = w.x; u.y = w.y;
       } else {
         u = __ldg(reinterpret_cast<const uint4*>((const float*)s.p + off));
       }
-#endif
     }
     raw[i] = u;
   }
@@ -178,11 +176,7 @@ __global__ void __launch_bounds__(RTHREADS) rec_kernel(RecParams p) {
     __syncthreads();
     if (step0 + RB < T) fetch(step0 + RB);
     const int nt = (int)((T - step0) < RB ? (T - step0) : RB);
-#ifdef REC_NO_COMPUTE
-    for (int tt = 0; tt < 0; ++tt) {
-#else
     for (int tt = 0; tt < nt; ++tt) {
-#endif
       float red = 0.f;
       const float s0 = smem[S_BASE + tt * RS + si];
       float s1 = 0.f, s2 = 0.f;

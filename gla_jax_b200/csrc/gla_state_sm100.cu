@@ -10,12 +10,22 @@
 //     thread block owns one (batch, head) and a SLICE of 32 key features dk, and walks the chunks in
 //     order with its 32 x 128 piece of S in float32 registers;
 //   * per chunk it needs g and k (or q) for its 32 features only (24 KB) plus the whole v (or dO)
-//     tile (32 KB); all of it arrives by TMA through a 3-stage ring, two chunks ahead of use;
+//     tile (32 KB); both arrive by TMA through rings (3 and 4 deep), three chunks ahead of use;
 //   * per chunk: decay weights as running products of f = exp(g) <= 1 down the rows, k_hat^T stored
 //     K-major, ONE tcgen05 product D[dv][dk] = sum_c v[c][dv] k_hat[c][dk] (M 128, N 32, K 128) into
-//     one of two TMEM accumulators, then S_prev[n] = S (stored bf16), S = e^G S + D;
-//   * the product of chunk n+1 is built and issued before the state update of chunk n is done, so
-//     the tensor core, the TMA engine and the update overlap.
+//     one of two TMEM accumulators, then S_prev[n] = S (stored bf16), S = e^G S + D.
+//
+// The block is a pipeline of warp roles, each a step ahead of the next, so that a step costs the
+// slowest role instead of their sum:
+//   builders   2 groups x 8 warps; group (i & 1) writes k_hat^T of step i (thread = one feature, 16 rows)
+//   issuer     1 warp: the eight MMAs of a step and their completion barrier
+//   updaters   8 warps: own the state registers (thread = one dv row of TMEM, 16 features); read the
+//              product, store S_prev, apply the decay
+//   producer   1 warp: TMA loads into the rings as their stages come free
+// Hand-offs: named barriers 3/4 (operand of an even/odd step written: builders arrive, issuer and
+// producer wait), mbarriers for TMA arrival, MMA completion, accumulator release and the chunk's e^G.
+// The issuer's serial path is kept to the eight MMAs: every wait it would need is taken by the builders
+// before they arrive.
 //
 // MODE 0 walks chunks forward with k_hat = k prod_{t>r} f_t; MODE 1 walks them backward with
 // q_hat = q prod_{t<=r} f_t and dO in place of v (the gradient recurrence is the same scan reversed).
@@ -35,39 +45,34 @@ namespace {
 constexpr int SD = 128;          // head dim
 constexpr int SC = 128;          // chunk length
 constexpr int SL = 32;           // key features per block
-constexpr int SWORKERS = 512;    // 16 warps: operand build and state update
-constexpr int STHREADS = SWORKERS + 32;   // + 1 warp: TMA producer and MMA issuer
-constexpr int NSTAGE = 3;
+constexpr int NBUILD = 512;      // 2 groups x 8 warps
+constexpr int NUPD = 256;        // 8 warps
+constexpr int STHREADS = NBUILD + NUPD + 64;     // + MMA issuer warp + TMA producer warp
+constexpr int READY_COUNT = 256 + 64;            // one builder group + issuer + producer
+constexpr int NY = 4, NGX = 3;   // ring depths
 
-// Named barriers: 1 = among the worker warps; 2 = workers arrive (operand written), issuer waits.
+// Named barriers: 1/2 = inside builder group 0/1; 3/4 = operand of an even/odd step written.
 __device__ __forceinline__ void bar_sync(int id, int n) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory"); }
 __device__ __forceinline__ void bar_arrive(int id, int n) { asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(n) : "memory"); }
 
 struct StSmem {
-  static constexpr uint32_t Y = 0;                       // v / dO tile: two SW128 halves of 128 rows x 64 cols
-  static constexpr uint32_t G = 2 * 16384;               // g slice  [128][32] float
-  static constexpr uint32_t X = G + 16384;               // k / q slice [128][32] bf16
-  static constexpr uint32_t STAGE = X + 8192;            // 56 KB, a multiple of 1024
-  static constexpr uint32_t BOP = NSTAGE * STAGE;        // 2 x 8 KB: k_hat^T, K-major, two 64-row K blocks
-  static constexpr uint32_t TOT = BOP + 2 * 8192;        // [2][16][32] float: gate products per 8 rows
-  static constexpr uint32_t GSUM = TOT + 2 * 16 * SL * 4;  // [2][16][32] float: gate sums per 8 rows
-  static constexpr uint32_t EG = GSUM + 2 * 16 * SL * 4;   // [2][32] float: e^G of the chunk
-  static constexpr uint32_t BAR = EG + 2 * SL * 4;       // full[3], mma[2], tmem slot
-  static constexpr uint32_t END = BAR + 64;
+  static constexpr uint32_t Y = 0;                          // NY x 32 KB: v / dO tile, two SW128 halves of 128 rows x 64 cols
+  static constexpr uint32_t GX = NY * 32768;                // NGX x (16 KB g slice [128][32] float + 8 KB k/q slice [128][32] bf16)
+  static constexpr uint32_t GXS = 16384 + 8192;
+  static constexpr uint32_t BOP = GX + NGX * GXS;           // 2 x 8 KB: k_hat^T, K-major, two 64-row K blocks (1024-aligned)
+  static constexpr uint32_t TOT = BOP + 2 * 8192;           // [2 groups][2][8][32] float: gate products per 16 rows
+  static constexpr uint32_t GSUM = TOT + 4 * 8 * SL * 4;    // [2 groups][2][8][32] float: gate sums per 16 rows
+  static constexpr uint32_t EG = GSUM + 4 * 8 * SL * 4;     // [4][32] float: e^G of the chunk, by step & 3
+  static constexpr uint32_t BAR = EG + 4 * SL * 4;          // fully[NY], fullgx[NGX], mma[2], accfree[2], egbar[4], tmem slot
+  static constexpr uint32_t END = BAR + 128;
 };
+static_assert(StSmem::BOP % 1024 == 0, "operand buffers need 1024-byte alignment");
 constexpr size_t ST_SMEM = 1024 + StSmem::END;
+static_assert(ST_SMEM <= 232448, "shared memory budget");
 
 __device__ unsigned int g_state_wait_timeouts = 0;
 
 struct StMaps { CUtensorMap g, x, y; };
-#ifdef ST_TRACE
-__device__ long long g_st_trace[4][16];
-#define ST_STAMP(k) do { if (blockIdx.x == 40 && i == 10 && lane == 0 && (warp == 0 || warp == 7 || warp == 15)) g_st_trace[warp == 0 ? 0 : warp == 7 ? 1 : 2][k] = clock64(); } while (0)
-#define ST_STAMP_I(k) do { if (blockIdx.x == 40 && j == 10 && lane == 0) g_st_trace[3][k] = clock64(); } while (0)
-#else
-#define ST_STAMP(k)
-#define ST_STAMP_I(k)
-#endif
 
 template <int MODE>
 __global__ void __launch_bounds__(STHREADS, 1)
@@ -78,34 +83,27 @@ tc_state_kernel(const __grid_constant__ StMaps maps, int64_t T, int64_t H, int N
   float* tot = reinterpret_cast<float*>(sm + StSmem::TOT);
   float* gsum = reinterpret_cast<float*>(sm + StSmem::GSUM);
   float* eG = reinterpret_cast<float*>(sm + StSmem::EG);
-  uint64_t* full = reinterpret_cast<uint64_t*>(sm + StSmem::BAR);
-  uint64_t* mma = full + NSTAGE;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mma + 2);
+  uint64_t* fully = reinterpret_cast<uint64_t*>(sm + StSmem::BAR);
+  uint64_t* fullgx = fully + NY;
+  uint64_t* mma = fullgx + NGX;
+  uint64_t* accfree = mma + 2;
+  uint64_t* egbar = accfree + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(egbar + 4);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int slice = blockIdx.x & 3;
   const int64_t bh = blockIdx.x >> 2, b = bh / H, h = bh % H;
-
   auto chunk_of = [&](int i) { return MODE == 0 ? i : N - 1 - i; };
-  const int z0 = (int)(b * T), y = (int)h;
-  const uint32_t sm_base = smem_u32(sm), full_base = smem_u32(full);
-  auto issue_loads = [&](int i) {           // one thread: chunk of step i into ring stage i % NSTAGE
-    const int sidx = i % NSTAGE;
-    const uint32_t st = sm_base + sidx * StSmem::STAGE, fb = full_base + sidx * 8;
-    const int z = z0 + chunk_of(i) * SC;
-    mbar_arrive_expect_tx(fb, StSmem::STAGE);
-    tma_load_3d(st + StSmem::Y, &maps.y, 0, y, z, fb);
-    tma_load_3d(st + StSmem::Y + 16384, &maps.y, 64, y, z, fb);
-    tma_load_3d(st + StSmem::G, &maps.g, SL * slice, y, z, fb);
-    tma_load_3d(st + StSmem::X, &maps.x, SL * slice, y, z, fb);
-  };
 
-  if (tid == SWORKERS) {
-    for (int s = 0; s < NSTAGE; ++s) mbar_init(smem_u32(full + s), 1);
+  if (tid == NBUILD + NUPD) {
+    for (int s = 0; s < NY; ++s) mbar_init(smem_u32(fully + s), 1);
+    for (int s = 0; s < NGX; ++s) mbar_init(smem_u32(fullgx + s), 1);
     mbar_init(smem_u32(mma + 0), 1);
     mbar_init(smem_u32(mma + 1), 1);
+    mbar_init(smem_u32(accfree + 0), NUPD);
+    mbar_init(smem_u32(accfree + 1), NUPD);
+    for (int s = 0; s < 4; ++s) mbar_init(smem_u32(egbar + s), 32);
     mbar_fence_init();
-    for (int i = 0; i < NSTAGE && i < N; ++i) issue_loads(i);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), 64);
@@ -117,141 +115,174 @@ tc_state_kernel(const __grid_constant__ StMaps maps, int64_t T, int64_t H, int N
   const uint32_t tmem = *tmem_slot;
   bool ok = true;
 
-  if (warp == SWORKERS / 32) {
-    // ---- issuer warp: product of step j as soon as its operand is written ------------------------------
-    // descriptors of the two operands at K slice 0, per ring stage / operand buffer; later slices by desc_advance
-    uint64_t dY[NSTAGE], dB[2];
-#pragma unroll
-    for (int s = 0; s < NSTAGE; ++s) dY[s] = desc_mnmajor(smem_u32(sm + s * StSmem::STAGE + StSmem::Y), 16384, 0);
-    dB[0] = desc_kmajor(smem_u32(sm + StSmem::BOP), 4096, 0);
-    dB[1] = desc_kmajor(smem_u32(sm + StSmem::BOP + 8192), 4096, 0);
-    int stage = 0;
+  if (warp == (NBUILD + NUPD) / 32 + 1) {
+    // ================= TMA producer warp =================
+    const int z0 = (int)(b * T), y = (int)h;
+    const int zstep = MODE == 0 ? SC : -SC;
+    const uint32_t sm_base = smem_u32(sm), fully0 = smem_u32(fully), fullgx0 = smem_u32(fullgx);
+    auto load_y = [&](int z, int s) {
+      const uint32_t dst = sm_base + StSmem::Y + s * 32768, fb = fully0 + 8 * s;
+      mbar_arrive_expect_tx(fb, 32768);
+      tma_load_3d(dst, &maps.y, 0, y, z, fb);
+      tma_load_3d(dst + 16384, &maps.y, 64, y, z, fb);
+    };
+    auto load_gx = [&](int z, int s) {
+      const uint32_t dst = sm_base + StSmem::GX + s * StSmem::GXS, fb = fullgx0 + 8 * s;
+      mbar_arrive_expect_tx(fb, StSmem::GXS);
+      tma_load_3d(dst, &maps.g, SL * slice, y, z, fb);
+      tma_load_3d(dst + 16384, &maps.x, SL * slice, y, z, fb);
+    };
+    const int zfirst = z0 + chunk_of(0) * SC;
+    if (lane == 0) {
+      for (int i = 0; i < NGX && i < N; ++i) load_gx(zfirst + i * zstep, i);
+      for (int i = 0; i < NY && i < N; ++i) load_y(zfirst + i * zstep, i);
+    }
+    int zgx = zfirst + NGX * zstep, sgx = 0;      // next g / k slice load: step j + NGX into ring stage j % NGX
+    int zy = zfirst + NY * zstep, sy = 0;         // next tile load: step j - 1 + NY into ring stage (j - 1) % NY
     for (int j = 0; j < N; ++j) {
-      ST_STAMP_I(0);
-      bar_sync(2, STHREADS);
-      ST_STAMP_I(1);
+      const int g = j & 1;
+      bar_sync(3 + g, READY_COUNT);          // operand of step j written: its g / k slices are consumed
       if (lane == 0) {
-        tc_fence_after();
-        constexpr uint32_t idesc = idesc_bf16(128, SL, 1, 0);
-        const uint64_t a0 = stage == 0 ? dY[0] : stage == 1 ? dY[1] : dY[2];
-        const uint64_t b0 = (j & 1) ? dB[1] : dB[0];
-        const uint32_t acc = tmem + SL * (j & 1);
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)      // D[dv][dk] = sum_c y[c][dv] x_hat[c][dk]
-          umma_bf16(acc, desc_advance(a0, ks * 2048), desc_advance(b0, (ks >> 2) * 4096 + (ks & 3) * 32), idesc, ks > 0);
-        umma_commit(smem_u32(mma + (j & 1)));
-        // When this product has completed its ring stage is free: refill it at once with the loads of
-        // step j + NSTAGE, so that they have almost NSTAGE steps to land.
-        if (j + NSTAGE < N) {
-          if (ok) ok = mbar_wait(smem_u32(mma + (j & 1)), (uint32_t)((j >> 1) & 1));
-          issue_loads(j + NSTAGE);
+        if (j + NGX < N) load_gx(zgx, sgx);
+        // the product of step j-1 has completed (or is about to): its tile stage takes step j-1+NY
+        if (j >= 1 && j - 1 + NY < N) {
+          if (ok) ok = mbar_wait(smem_u32(mma + (g ^ 1)), (uint32_t)(((j - 1) >> 1) & 1));
+          load_y(zy, sy);
         }
       }
-      stage = stage == NSTAGE - 1 ? 0 : stage + 1;
+      zgx += zstep; sgx = sgx == NGX - 1 ? 0 : sgx + 1;
+      if (j >= 1) { zy += zstep; sy = sy == NY - 1 ? 0 : sy + 1; }
       __syncwarp();
     }
     if (!ok && lane == 0) atomicAdd(&g_state_wait_timeouts, 1u);
-  } else {
-    // ---- worker warps ---------------------------------------------------------------------------------------
-    // state registers: TMEM lane = dv, this thread's 8 columns = key features 8 cg + [0, 8) of the slice
-    const int q4 = warp & 3, cg = warp >> 2;
-    const int dv = 32 * q4 + lane;
-    const int64_t el0 = ((bh * SD) + SL * slice + 8 * cg) * SD + dv;     // element (bh, dk0, dv); dk stride SD
-    float S[8];
+  } else if (warp == (NBUILD + NUPD) / 32) {
+    // ================= MMA issuer warp =================
+    const uint32_t sm_base = smem_u32(sm);
+    const uint64_t dB0 = desc_kmajor(sm_base + StSmem::BOP, 4096, 0), dB1 = desc_kmajor(sm_base + StSmem::BOP + 8192, 4096, 0);
+    const uint64_t dY0 = desc_mnmajor(sm_base + StSmem::Y, 16384, 0);
+    int ys = 0;                              // j % NY
+    for (int j = 0; j < N; ++j) {
+      const int g = j & 1;
+      bar_sync(3 + g, READY_COUNT);          // operand of step j written
+      if (lane == 0) {
+        // No waits here: the builders held back their arrival until the v / dO tile of this step had landed
+        // and the updaters had read accumulator g out, so this warp's serial path is the eight MMAs.
+        tc_fence_after();
+        constexpr uint32_t idesc = idesc_bf16(128, SL, 1, 0);
+        const uint64_t a0 = desc_advance(dY0, (uint32_t)ys * 32768u), b0 = g ? dB1 : dB0;
+        const uint32_t acc = tmem + SL * g;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) S[j] = init ? __bfloat162float(init[el0 + (int64_t)j * SD]) : 0.f;
-
-    // Build k_hat^T (or q_hat^T) of step i into operand buffer i & 1 and hand it to the issuer.
-    auto build = [&](int i) {
-      const int s = i % NSTAGE;
-      ST_STAMP(0);
-      if (ok) ok = mbar_wait(smem_u32(full + s), (uint32_t)((i / NSTAGE) & 1));
-      ST_STAMP(1);
-      const float* gt = reinterpret_cast<const float*>(sm + s * StSmem::STAGE + StSmem::G);
-      const unsigned short* xt = reinterpret_cast<const unsigned short*>(sm + s * StSmem::STAGE + StSmem::X);
-      float* tt = tot + (i & 1) * 16 * SL;
-      float* gg = gsum + (i & 1) * 16 * SL;
-      const int r0 = 8 * warp;                 // this thread: feature `lane` of the slice, rows r0 + [0, 8)
-      float f[8];
-      uint32_t xr[8];
-      float gs = 0.f;
+        for (int ks = 0; ks < 8; ++ks)       // D[dv][dk] = sum_c y[c][dv] x_hat[c][dk]
+          umma_bf16(acc, desc_advance(a0, ks * 2048), desc_advance(b0, (ks >> 2) * 4096 + (ks & 3) * 32), idesc, ks > 0);
+        umma_commit(smem_u32(mma + g));
+      }
+      ys = ys == NY - 1 ? 0 : ys + 1;
+      __syncwarp();
+    }
+    if (!ok && lane == 0) atomicAdd(&g_state_wait_timeouts, 1u);
+  } else if (warp < NBUILD / 32) {
+    // ================= builders: group g writes the operand of steps i = g, g+2, ... =================
+    const int g = warp >> 3, w = warp & 7;           // thread: feature `lane` of the slice, rows 16 w + [0, 16)
+    for (int i = g; i < N; i += 2) {
+      const int s = i % NGX;
+      // The product of step i-2 has completed: operand buffer g is free, and (through the accumulator
+      // release the issuer waited for before step i-2) the updaters are done with the e^G slot of step i-4.
+      if (i >= 2 && ok) ok = mbar_wait(smem_u32(mma + g), (uint32_t)(((i - 2) >> 1) & 1));
+      float* tt = tot + (2 * g + ((i >> 1) & 1)) * 8 * SL;      // double-buffered: a warp a step ahead never
+      float* gg = gsum + (2 * g + ((i >> 1) & 1)) * 8 * SL;     // overwrites what a slower warp still reads
+      if (ok) ok = mbar_wait(smem_u32(fullgx + s), (uint32_t)((i / NGX) & 1));
+      const float* gt = reinterpret_cast<const float*>(sm + StSmem::GX + s * StSmem::GXS);
+      const unsigned short* xt = reinterpret_cast<const unsigned short*>(sm + StSmem::GX + s * StSmem::GXS + 16384);
+      const int r0 = 16 * w;
+      float f[16];
+      uint32_t xr[16];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
+      for (int j = 0; j < 16; ++j) {
         f[j] = gt[(r0 + j) * SL + lane];
         xr[j] = xt[(r0 + j) * SL + lane];
       }
+      // The product of the 16 gates first (as the exponential of their sum), so that the groups can exchange
+      // totals early and the running products below start from the cross-group factor.
+      float gs = 0.f;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) { gs += f[j]; f[j] = __expf(f[j]); }
+      for (int j = 0; j < 16; ++j) gs += f[j];
+      tt[w * SL + lane] = __expf(gs);
+      if (MODE == 0) gg[w * SL + lane] = gs;
+      bar_sync(1 + g, 256);
+      float tw[8];
+#pragma unroll
+      for (int w2 = 0; w2 < 8; ++w2) tw[w2] = tt[w2 * SL + lane];
       float run = 1.f;
-      if (MODE == 0) {
 #pragma unroll
-        for (int j = 7; j >= 0; --j) { const float t = f[j]; f[j] = run; run *= t; }      // exclusive suffix
-      } else {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) { run *= f[j]; f[j] = run; }                          // inclusive prefix
+      for (int w2 = 0; w2 < 8; ++w2) {
+        const bool use = (MODE == 0) ? (w2 > w) : (w2 < w);
+        run *= use ? tw[w2] : 1.f;
       }
-      tt[warp * SL + lane] = run;
-      if (MODE == 0) gg[warp * SL + lane] = gs;
-      ST_STAMP(2);
-      bar_sync(1, SWORKERS);
-      ST_STAMP(3);
-      float tw[16];
-#pragma unroll
-      for (int w2 = 0; w2 < 16; ++w2) tw[w2] = tt[w2 * SL + lane];
-      float cross = 1.f;
-#pragma unroll
-      for (int w2 = 0; w2 < 16; ++w2) {
-        const bool use = (MODE == 0) ? (w2 > warp) : (w2 < warp);
-        cross *= use ? tw[w2] : 1.f;
-      }
-      if (warp == (MODE == 0 ? 15 : 0)) {       // chunk totals of the slice's features
+      if (w == (MODE == 0 ? 7 : 0)) {           // chunk totals of the slice's features
         float e = 1.f, sg = 0.f;
 #pragma unroll
-        for (int w2 = 0; w2 < 16; ++w2) { e *= tw[w2]; if (MODE == 0) sg += gg[w2 * SL + lane]; }
-        eG[(i & 1) * SL + lane] = e;
+        for (int w2 = 0; w2 < 8; ++w2) { e *= tw[w2]; if (MODE == 0) sg += gg[w2 * SL + lane]; }
+        eG[(i & 3) * SL + lane] = e;
+        mbar_arrive(smem_u32(egbar + (i & 3)));       // release: the updaters acquire it before reading e^G
         if (MODE == 0 && Gc != nullptr) Gc[(bh * N + chunk_of(i)) * SD + SL * slice + lane] = sg;
       }
-      uint4 pk;
-      pk.x = pack_bf16x2(__uint_as_float(xr[0] << 16) * (f[0] * cross), __uint_as_float(xr[1] << 16) * (f[1] * cross));
-      pk.y = pack_bf16x2(__uint_as_float(xr[2] << 16) * (f[2] * cross), __uint_as_float(xr[3] << 16) * (f[3] * cross));
-      pk.z = pack_bf16x2(__uint_as_float(xr[4] << 16) * (f[4] * cross), __uint_as_float(xr[5] << 16) * (f[5] * cross));
-      pk.w = pack_bf16x2(__uint_as_float(xr[6] << 16) * (f[6] * cross), __uint_as_float(xr[7] << 16) * (f[7] * cross));
-      // row = feature (the N index), 64 chunk rows per 128-byte line, this thread's 8 rows = one 16-byte piece
-      uint8_t* bop = sm + StSmem::BOP + (i & 1) * 8192 + (warp >> 3) * 4096;
-      *reinterpret_cast<uint4*>(bop + sw128_chunk(lane, warp & 7)) = pk;
-      ST_STAMP(4);
+      // weights by running product from the cross-group factor, applied on the fly
+      float v[16];
+      if (MODE == 0) {
+#pragma unroll
+        for (int j = 15; j >= 0; --j) { v[j] = __uint_as_float(xr[j] << 16) * run; run *= __expf(f[j]); }   // exclusive suffix
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) { run *= __expf(f[j]); v[j] = __uint_as_float(xr[j] << 16) * run; }    // inclusive prefix
+      }
+      uint32_t pk[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) pk[j] = pack_bf16x2(v[2 * j], v[2 * j + 1]);
+      // row = feature (the N index); 64 chunk rows per 128-byte line; this thread's 16 rows = two 16-byte pieces
+      uint8_t* bop = sm + StSmem::BOP + g * 8192 + (w >> 2) * 4096;
+      *reinterpret_cast<uint4*>(bop + sw128_chunk(lane, 2 * (w & 3))) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      *reinterpret_cast<uint4*>(bop + sw128_chunk(lane, 2 * (w & 3) + 1)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
       fence_async_smem();
-      tc_fence_before();
-      bar_arrive(2, STHREADS);
-      ST_STAMP(5);
-    };
-
-    if (N > 0) build(0);
+      // on behalf of the issuer (these have long completed as a rule; the builders have the slack to check):
+      // accumulator g read out by the updaters (step i-2), and the v / dO tile of step i landed
+      if (i >= 2 && ok) ok = mbar_wait(smem_u32(accfree + g), (uint32_t)(((i - 2) >> 1) & 1));
+      if (ok) ok = mbar_wait(smem_u32(fully + (i % NY)), (uint32_t)((i / NY) & 1));
+      bar_arrive(3 + g, READY_COUNT);
+    }
+    if (!ok && lane == 0) atomicAdd(&g_state_wait_timeouts, 1u);
+  } else {
+    // ================= updaters: the state registers =================
+    // TMEM lane = dv; this thread's 16 columns = key features 16 cg + [0, 16) of the slice
+    const int e8 = warp - NBUILD / 32;
+    const int q4 = e8 & 3, cg = e8 >> 2;            // (warp % 4) == q4: the TMEM lanes this warp may read
+    const int dv = 32 * q4 + lane;
+    const int64_t el0 = ((bh * SD) + SL * slice + 16 * cg) * SD + dv;     // element (bh, dk0, dv); dk stride SD
+    float S[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) S[j] = init ? __bfloat162float(init[el0 + (int64_t)j * SD]) : 0.f;
     for (int i = 0; i < N; ++i) {
-      if (i + 1 < N) build(i + 1);
-      else bar_sync(1, SWORKERS);          // the totals written while building step i are visible to all
-      // state update of step i
-      ST_STAMP(6);
-      if (ok) ok = mbar_wait(smem_u32(mma + (i & 1)), (uint32_t)((i >> 1) & 1));
-      ST_STAMP(7);
+      const int g = i & 1;
+      if (ok) ok = mbar_wait(smem_u32(egbar + (i & 3)), (uint32_t)((i >> 2) & 1));     // e^G of step i written
+      float e[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) e[j] = eG[(i & 3) * SL + 16 * cg + j];
+      if (ok) ok = mbar_wait(smem_u32(mma + g), (uint32_t)((i >> 1) & 1));
       tc_fence_after();
-      uint32_t r[8];
-      tmem_ld8(tmem + ((uint32_t)(q4 * 32) << 16) + SL * (i & 1) + 8 * cg, r);
+      uint32_t r[16];
+      tmem_ld16(tmem + ((uint32_t)(q4 * 32) << 16) + SL * g + 16 * cg, r);
       tmem_ld_wait();
       tc_fence_before();
-      ST_STAMP(8);
+      mbar_arrive(smem_u32(accfree + g));    // accumulator g may be overwritten by step i + 2
       bf16* so = states + (int64_t)(bh * N + chunk_of(i)) * SD * SD + (el0 - bh * SD * SD);
-      const float* e = eG + (i & 1) * SL + 8 * cg;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
+      for (int j = 0; j < 16; ++j) {
         so[(int64_t)j * SD] = __float2bfloat16_rn(S[j]);
         S[j] = fmaf(e[j], S[j], __uint_as_float(r[j]));
       }
-      ST_STAMP(9);
     }
     if (fin != nullptr) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) fin[el0 + (int64_t)j * SD] = __float2bfloat16_rn(S[j]);
+      for (int j = 0; j < 16; ++j) fin[el0 + (int64_t)j * SD] = __float2bfloat16_rn(S[j]);
     }
     if (!ok && lane == 0) atomicAdd(&g_state_wait_timeouts, 1u);
   }
@@ -262,9 +293,6 @@ tc_state_kernel(const __grid_constant__ StMaps maps, int64_t T, int64_t H, int N
 
 }  // namespace
 
-#ifdef ST_TRACE
-void tc_state_read_trace(long long* o) { cudaMemcpyFromSymbol(o, g_st_trace, sizeof(g_st_trace)); }
-#endif
 unsigned int tc_state_read_wait_timeouts() {
   unsigned int v = 0;
   cudaMemcpyFromSymbol(&v, g_state_wait_timeouts, sizeof(v));

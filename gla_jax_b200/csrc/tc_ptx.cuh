@@ -95,16 +95,23 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 // Bounded wait: returns false if the phase did not complete within the iteration limit, so a
-// kernel can never spin forever on a completion that is not coming.
+// kernel can never spin forever on a completion that is not coming.  The suspend-time hint lets the
+// hardware park the thread until the phase completes instead of re-issuing the test every few cycles:
+// spinning waiters would otherwise take issue slots from the warps doing the work.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (int it = 0; it < (1 << 22); ++it) {
+  for (int it = 0; it < (1 << 18); ++it) {
     uint32_t ok;
     asm volatile(
-        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"(10000u) : "memory");
     if (ok) return true;
   }
   return false;
+}
+
+// Plain arrival (counts one towards the barrier's expected arrivals).
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(bar) : "memory");
 }
 
 // Arrive on the barrier and add `bytes` to its pending transaction count (one thread).
