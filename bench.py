@@ -16,7 +16,8 @@ Timed quantities:
              two rotating input/output sets so that no step finds its operands in L2.
   e2e        the public Python operator (gla_jax_b200.chunk_gla + autograd) with HOST pinned
              inputs: host->device copies of all five inputs and a device->host read of the
-             scalar loss inside every timed step.
+             scalar loss inside every timed step; the copies of step i+1 are issued on a copy
+             stream while step i computes (a double-buffered input feed).
   roofline   the dominant kernel's time, from CUDA events the library records around each of
              its launches during the timed steps.
   cpu_baseline  the oracle's chunk path (torch CPU, float32) on a bounded sample.
@@ -301,8 +302,26 @@ def main():
     host = [x.pin_memory() for x in O.make_inputs(B, T, H, D, torch.bfloat16, seed=1000 * rank + 77)]
     h2d = sum(x.numel() * x.element_size() for x in host)
 
-    def e2e_step():
-        leaves = [x.to(dev, non_blocking=True).requires_grad_(True) for x in host]
+    # The input feed is double-buffered the way a training loop's loader is: while step i computes, the
+    # host->device copies of step i+1 run on a copy stream.  Every timed step still contains one full set of
+    # copies (those of the next step; the last step's are issued and waited for too) and one host read.
+    copy_stream = torch.cuda.Stream(device=dev)
+    staged = [None, None]
+    staged_ev = [torch.cuda.Event(), torch.cuda.Event()]
+
+    def stage(slot):
+        with torch.cuda.stream(copy_stream):
+            staged[slot] = [x.to(dev, non_blocking=True) for x in host]
+            staged_ev[slot].record(copy_stream)
+
+    def e2e_step(i):
+        cur = torch.cuda.current_stream(dev)
+        copy_stream.wait_stream(cur)            # the buffers being replaced are no longer in use
+        stage((i + 1) % 2)
+        cur.wait_event(staged_ev[i % 2])
+        leaves = [x.requires_grad_(True) for x in staged[i % 2]]
+        for x in leaves:
+            x.record_stream(cur)
         if args.op == "recurrent_gla":
             from gla_jax_b200 import recurrent_gla
             hf, out = recurrent_gla(*leaves)
@@ -314,13 +333,15 @@ def main():
 
     e2e_ms = float("nan")
     if not args.no_e2e:
-        for _ in range(3):
-            e2e_step()
+        stage(0)
+        for i in range(3):
+            e2e_step(i)
         barrier()
         e_evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
         for i in range(K):
             e_evs[i][0].record()
-            e2e_step()
+            e2e_step(i + 3)
+            copy_stream.synchronize() if i == K - 1 else None    # the last step's copies end inside the region
             e_evs[i][1].record()
         barrier()
         e2e_ms = sum(a.elapsed_time(b) for a, b in e_evs)
