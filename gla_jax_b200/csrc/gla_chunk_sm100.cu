@@ -648,6 +648,7 @@ struct BwdSmem {
   static constexpr uint32_t W64 = DO;
   static constexpr uint32_t WL = V;                        // 2 x 16 KB
   static constexpr uint32_t DPL = SP;                      // 2 x 8 KB
+  static constexpr uint32_t DPD = P;                       // [128][16] float: each row's 16 x 16 diagonal block of dP
 };
 constexpr uint32_t TM_DP = 0, TM_DQH = 128, TM_DKH = 256, TM_DV = 384, TM_T = 384;
 
@@ -893,6 +894,14 @@ tc_chunk_bwd_kernel(int64_t T, int64_t H, int64_t N, int pf_dist, const float* _
       for (int m = 0; m < 32; ++m)
         if (m == lane) dv_ = __uint_as_float(r[m]);
       diag[d] = dv_;
+      // this row's 16 x 16 diagonal block of dP in float32, for the small levels done on the CUDA cores
+      // (the P tile this overwrites was last read by the dV product, which has completed)
+      float4* dpd = reinterpret_cast<float4*>(sm + BwdSmem::DPD + d * 64);
+      const bool hi = (lane & 16) != 0;
+#pragma unroll
+      for (int c4 = 0; c4 < 4; ++c4)
+        dpd[c4] = make_float4(__uint_as_float(hi ? r[16 + 4 * c4 + 0] : r[4 * c4 + 0]), __uint_as_float(hi ? r[16 + 4 * c4 + 1] : r[4 * c4 + 1]),
+                              __uint_as_float(hi ? r[16 + 4 * c4 + 2] : r[4 * c4 + 2]), __uint_as_float(hi ? r[16 + 4 * c4 + 3] : r[4 * c4 + 3]));
     }
     // dG1[d] = sum_r dKh^T[d][r] k_hat[r][d]   (this thread: rows 32 wq_ + m)
     tmem_ld32(tmem + ((uint32_t)(q4 * 32) << 16) + TM_DKH + 32 * wq_, r);
@@ -1126,21 +1135,46 @@ tc_chunk_bwd_kernel(int64_t T, int64_t H, int64_t N, int pf_dist, const float* _
         if (row_is_right<S>(i, rq, p)) dq[i] += t; else dk[i] += t;
       }
     };
-    using I0 = std::integral_constant<int, 0>; using I1 = std::integral_constant<int, 1>;
-    using I2 = std::integral_constant<int, 2>; using I3 = std::integral_constant<int, 3>;
+    using I3 = std::integral_constant<int, 3>;
     using I4 = std::integral_constant<int, 4>; using I5 = std::integral_constant<int, 5>;
     using I6 = std::integral_constant<int, 6>;
-    build_and_issue(I0{});
-    build_and_issue(I1{});
-    accumulate(I0{});
-    TC_STAMP(1, 7 + 10 * (1 - p));
-    build_and_issue(I2{});
-    accumulate(I1{});
     build_and_issue(I3{});
-    accumulate(I2{});
-    TC_STAMP(1, 8 + 10 * (1 - p));
     build_and_issue(I4{});
+    // Half sizes 1, 2, 4 together are all pairs i > j inside each block of 8 rows.  Their partners are this
+    // thread's own rows, so they need no contraction across threads: float32 FMAs with the exact pairwise decay
+    // prod_{t in (j, i]} f_t, run while the tensor core works on the two products just issued.
+    {
+      const float* dpd = reinterpret_cast<const float*>(sm + BwdSmem::DPD) + rbase * 16;
+#pragma unroll
+      for (int blk = 0; blk < 2; ++blk) {
+#pragma unroll
+        for (int i = 1; i < 8; ++i) {
+          const int ri = 8 * blk + i;
+          float pv[8];
+          {
+            const float4 a = *reinterpret_cast<const float4*>(dpd + ri * 16 + 8 * blk);
+            pv[0] = a.x; pv[1] = a.y; pv[2] = a.z; pv[3] = a.w;
+            if (i > 4) {
+              const float4 b4 = *reinterpret_cast<const float4*>(dpd + ri * 16 + 8 * blk + 4);
+              pv[4] = b4.x; pv[5] = b4.y; pv[6] = b4.z; pv[7] = b4.w;
+            }
+          }
+          const float qi = bf16_lo(qk[ri]);
+          float D = 1.f;
+#pragma unroll
+          for (int j = i - 1; j >= 0; --j) {
+            const int rj = 8 * blk + j;
+            D *= f[rj + 1];
+            const float t = pv[j] * D;
+            dq[ri] = fmaf(t, bf16_hi(qk[rj]), dq[ri]);
+            dk[rj] = fmaf(t, qi, dk[rj]);
+          }
+        }
+      }
+    }
+    TC_STAMP(1, 7 + 10 * (1 - p));
     accumulate(I3{});
+    TC_STAMP(1, 8 + 10 * (1 - p));
     build_and_issue(I5{});
     accumulate(I4{});
     TC_STAMP(1, 9 + 10 * (1 - p));
