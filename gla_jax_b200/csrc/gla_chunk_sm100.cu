@@ -643,13 +643,20 @@ struct BwdSmem {
   static constexpr uint32_t DIAG = GRP + 8 * TD * 4;       // [128] float: dP[i][i]
   static constexpr uint32_t DG1 = DIAG + TC * 4;           // [128] float
   static constexpr uint32_t DG2 = DG1 + TD * 4;            // [128] float
-  static constexpr uint32_t BAR = DG2 + TD * 4;            // 3 mbarriers + tmem slot
+  static constexpr uint32_t BAR = DG2 + TD * 4;            // 5 mbarriers + tmem slot
   static constexpr uint32_t END = BAR + 64;
-  static constexpr uint32_t W64 = DO;
-  static constexpr uint32_t WL = V;                        // 2 x 16 KB
-  static constexpr uint32_t DPL = SP;                      // 2 x 8 KB
-  static constexpr uint32_t DPD = P;                       // [128][16] float: each row's 16 x 16 diagonal block of dP
+  // After the phase-1 products have completed, dO, v and P are dead; after phase 1.5 the rest is.  Reuse:
+  static constexpr uint32_t W64 = KH;                      // 32 KB: k~ / q~ at the h = 64 anchor, all 128 rows
+  static constexpr uint32_t WL = DS;                       // 2 x 16 KB: per-level W_l
+  static constexpr uint32_t DPL = SP;                      // 2 x 8 KB: per-level masked dP block
+  static constexpr uint32_t DPD = V + 24576;               // [128][16] float: each row's 16 x 16 diagonal block of dP
+  // TMA landing zones of g, q, k for the row passes (plain row-major, 64 rows each)
+  static constexpr uint32_t GH = DO;                       // [64][128] float: gates of the pass's rows
+  static constexpr uint32_t QH = P;                        // [64][128] bf16: q of the pass's rows
+  static constexpr uint32_t K1 = P + 16384;                // [64][128] bf16: k of rows 64..127
+  static constexpr uint32_t K0 = V;                        // [64][128] bf16: k of rows 0..63
 };
+struct BwdMaps { CUtensorMap g, q, k; };                   // boxes of 128 features x 64 rows, unswizzled
 constexpr uint32_t TM_DP = 0, TM_DQH = 128, TM_DKH = 256, TM_DV = 384, TM_T = 384;
 
 // Decay weights of the thread's 16 rows at level slot S (half size 2^S), column layout.
@@ -713,7 +720,7 @@ __device__ __forceinline__ float bf16_hi(uint32_t u) { return __uint_as_float(u 
 __device__ __forceinline__ void st_bf16(uint8_t* p, float v) { *reinterpret_cast<bf16*>(p) = __float2bfloat16_rn(v); }
 
 __global__ void __launch_bounds__(TTHREADS, 1)
-tc_chunk_bwd_kernel(int64_t T, int64_t H, int64_t N, int pf_dist, const float* __restrict__ g, const bf16* __restrict__ v,
+tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, int64_t N, int pf_dist, const float* __restrict__ g, const bf16* __restrict__ v,
                     const bf16* __restrict__ k, const bf16* __restrict__ q, const bf16* __restrict__ dO,
                     const bf16* __restrict__ S_prev, const bf16* __restrict__ dS_next, const bf16* __restrict__ P_saved,
                     bf16* __restrict__ dq_out, bf16* __restrict__ dk_out, bf16* __restrict__ dv_out,
@@ -725,8 +732,8 @@ tc_chunk_bwd_kernel(int64_t T, int64_t H, int64_t N, int pf_dist, const float* _
   float* diag = reinterpret_cast<float*>(sm + BwdSmem::DIAG);
   float* dG1 = reinterpret_cast<float*>(sm + BwdSmem::DG1);
   float* dG2 = reinterpret_cast<float*>(sm + BwdSmem::DG2);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + BwdSmem::BAR);   // [0]: phase 1, [1],[2]: level buffers
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + BwdSmem::BAR);   // [0]: phase 1, [1],[2]: level buffers, [3],[4]: pass loads
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int q4 = warp & 3, wq_ = warp >> 2;        // TMEM lane quadrant, and which quarter of the columns
@@ -744,6 +751,8 @@ tc_chunk_bwd_kernel(int64_t T, int64_t H, int64_t N, int pf_dist, const float* _
     mbar_init(smem_u32(bars + 0), 1);
     mbar_init(smem_u32(bars + 1), 1);
     mbar_init(smem_u32(bars + 2), 1);
+    mbar_init(smem_u32(bars + 3), 1);
+    mbar_init(smem_u32(bars + 4), 1);
     mbar_fence_init();
   }
   if (tid < TD) { dG1[tid] = 0.f; dG2[tid] = 0.f; }
@@ -868,6 +877,17 @@ tc_chunk_bwd_kernel(int64_t T, int64_t H, int64_t N, int pf_dist, const float* _
   bool ok = mbar_wait(smem_u32(bars + 0), 0);
   tc_fence_after();
   TC_STAMP(1, 3);
+  // dO, v and P have been consumed by the products: their regions take g, q, k of rows 64..127 and k of rows
+  // 0..63 by TMA while phase 1.5 runs, so that the W64 build and the first pass read them from shared memory.
+  const int zrow = (int)(b * T + n * TC), yh = (int)h_;
+  if (tid == 0) {
+    const uint32_t lb = smem_u32(bars + 3);
+    mbar_arrive_expect_tx(lb, 32768 + 3 * 16384);
+    tma_load_3d(smem_u32(sm + BwdSmem::GH), &maps.g, 0, yh, zrow + 64, lb);
+    tma_load_3d(smem_u32(sm + BwdSmem::QH), &maps.q, 0, yh, zrow + 64, lb);
+    tma_load_3d(smem_u32(sm + BwdSmem::K1), &maps.k, 0, yh, zrow + 64, lb);
+    tma_load_3d(smem_u32(sm + BwdSmem::K0), &maps.k, 0, yh, zrow, lb);
+  }
 
   // ---- phase 1.5: dV out, dP diagonal, the two dG sums ---------------------------------------------------
   {
@@ -938,10 +958,13 @@ tc_chunk_bwd_kernel(int64_t T, int64_t H, int64_t N, int pf_dist, const float* _
   // ---- phase 1.9: W64 for all 128 rows (rows < 64: k~, rows >= 64: q~, anchor row 63) ----------------------
   {
     uint8_t* tile = sm + BwdSmem::W64 + (wq_ >> 1) * TILE_BYTES;       // transposed like k_hat: row = feature
-    const bf16* xp = (wq_ < 2 ? k : q) + row0 + (int64_t)(32 * wq_) * HD + d;
+    ok = mbar_wait(smem_u32(bars + 3), 0) && ok;
+    // rows 32 wq_ + i: k of rows 0..63 (K0) for wq_ < 2, q of rows 64..127 (QH) otherwise; 256-byte rows
+    const unsigned short* xp = reinterpret_cast<const unsigned short*>(sm + (wq_ < 2 ? BwdSmem::K0 : BwdSmem::QH)) +
+                               (32 * (wq_ & 1)) * TD + d;
     uint32_t xraw[32];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) xraw[i] = ldg_u16(xp + (int64_t)i * HD);
+    for (int i = 0; i < 32; ++i) xraw[i] = xp[i * TD];
     uint32_t pk[16];
     if (wq_ < 2) {
       float run = (wq_ == 0) ? tot[2 * TD + d] * tot[3 * TD + d] : 1.f;
@@ -987,19 +1010,17 @@ tc_chunk_bwd_kernel(int64_t T, int64_t H, int64_t N, int pf_dist, const float* _
     float f[16], dq[16], dk[16];
     uint32_t qk[16];
     {
-      const int64_t e1 = row0 + (int64_t)rbase * HD + d;
-      uint32_t kr[16];
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {          // 48 loads in flight before anything uses one
-        f[i] = __ldg(g + e1 + (int64_t)i * HD);
-        qk[i] = ldg_u16(q + e1 + (int64_t)i * HD);
-        kr[i] = ldg_u16(k + e1 + (int64_t)i * HD);
-      }
+      if (p == 0) ok = mbar_wait(smem_u32(bars + 4), 0) && ok;      // pass 0's g and q have landed (pass 1: waited above)
+      const float* gs_ = reinterpret_cast<const float*>(sm + BwdSmem::GH) + (16 * rq) * TD + d;
+      const unsigned short* qs_ = reinterpret_cast<const unsigned short*>(sm + BwdSmem::QH) + (16 * rq) * TD + d;
+      const unsigned short* ks_ = reinterpret_cast<const unsigned short*>(sm + (p ? BwdSmem::K1 : BwdSmem::K0)) + (16 * rq) * TD + d;
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
-        f[i] = __expf(f[i]);
-        qk[i] |= kr[i] << 16;
+        f[i] = gs_[i * TD];
+        qk[i] = (uint32_t)qs_[i * TD] | ((uint32_t)ks_[i * TD] << 16);
       }
+#pragma unroll
+      for (int i = 0; i < 16; ++i) f[i] = __expf(f[i]);
     }
     // inter-chunk terms and the diagonal
     {
@@ -1092,6 +1113,14 @@ tc_chunk_bwd_kernel(int64_t T, int64_t H, int64_t N, int pf_dist, const float* _
       tc_fence_before();
       __syncthreads();
       if (tid == 0) {
+        if (S == 3 && p == 1) {
+          // every thread has read its pass-1 gates and q (they are past the barrier above): the landing zones
+          // take g and q of rows 0..63, which arrive while this pass runs
+          const uint32_t lb = smem_u32(bars + 4);
+          mbar_arrive_expect_tx(lb, 32768 + 16384);
+          tma_load_3d(smem_u32(sm + BwdSmem::GH), &maps.g, 0, yh, zrow, lb);
+          tma_load_3d(smem_u32(sm + BwdSmem::QH), &maps.q, 0, yh, zrow, lb);
+        }
         tc_fence_after();
         const uint32_t tacc = tmem + TM_T + 64 * bsel;
         const uint64_t kD = desc_kmajor(aDPL + bsel * KC_TILE, KC_TILE, 0), mD = desc_mnmajor(aDPL + bsel * KC_TILE, KC_TILE, 0);
@@ -1319,10 +1348,14 @@ int tc_chunk_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
   }
   cudaError_t e = cudaFuncSetAttribute(tc_chunk_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)BWD_SMEM);
   if (e != cudaSuccess) return record_cuda_error(e);
+  BwdMaps bmaps;
+  GLA_TRY(make_map_bthd(&bmaps.g, g, 1, B, T, H, 128, 0, 64));
+  GLA_TRY(make_map_bthd(&bmaps.q, q, 0, B, T, H, 128, 0, 64));
+  GLA_TRY(make_map_bthd(&bmaps.k, k, 0, B, T, H, 128, 0, 64));
   {
     ProfScope ps("tc_chunk_bwd_kernel", st);
     tc_chunk_bwd_kernel<<<(unsigned)(BH * N), TTHREADS, BWD_SMEM, st>>>(
-        T, H, N, prefetch_distance(1), g, (const bf16*)v, (const bf16*)k, (const bf16*)q, (const bf16*)dout, S_prev, dS_next, P, (bf16*)dq,
+        bmaps, T, H, N, prefetch_distance(1), g, (const bf16*)v, (const bf16*)k, (const bf16*)q, (const bf16*)dout, S_prev, dS_next, P, (bf16*)dq,
         (bf16*)dk, (bf16*)dv, dg);
   }
   GLA_CHECK_LAUNCH();

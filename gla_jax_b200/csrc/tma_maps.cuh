@@ -22,15 +22,15 @@ inline EncodeTiledFn encode_fn() {
   }
   return fn;
 }
-// (B,T,H,128) array seen as 3-d (d, h, b*T + t); box = (box_cols, 1, 128 rows); float32 or bf16.
+// (B,T,H,128) array seen as 3-d (d, h, b*T + t); box = (box_cols, 1, box_rows); float32 or bf16.
 inline int make_map_bthd(CUtensorMap* m, const void* ptr, int is_f32, int64_t B, int64_t T, int64_t H, int box_cols,
-                         int swizzle128) {
+                         int swizzle128, int box_rows = 128) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return GLA_ERR_NO_DEVICE;
   const cuuint64_t es = is_f32 ? 4 : 2;
   cuuint64_t dims[3] = {(cuuint64_t)128, (cuuint64_t)H, (cuuint64_t)(B * T)};
   cuuint64_t strides[2] = {(cuuint64_t)128 * es, (cuuint64_t)H * 128 * es};
-  cuuint32_t box[3] = {(cuuint32_t)box_cols, 1, 128};
+  cuuint32_t box[3] = {(cuuint32_t)box_cols, 1, (cuuint32_t)box_rows};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = fn(m, is_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, (void*)ptr, dims,
                   strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
