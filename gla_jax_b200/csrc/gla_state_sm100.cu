@@ -301,17 +301,17 @@ unsigned int tc_state_read_wait_timeouts() {
 
 // Whether the one-pass kernel is expected to beat the product + scan pair for this shape.
 // Its time is (waves of (B*H*4) blocks over the SMs) x N sequential steps; the pair's time grows with
-// the total number of chunks.  Step and per-chunk costs measured on B200; GLA_B200_STATE_FUSED=0/1
+// the total number of chunks.  Step and per-chunk costs measured on B200; the environment variable
+// GLA_B200_STATE_FUSED=0/1
 // overrides the estimate.
 bool tc_state_fused_preferred(int64_t BH, int64_t N) {
-  static int forced = -2;
-  if (forced == -2) { const char* e = getenv("GLA_B200_STATE_FUSED"); forced = e ? (e[0] == '0' ? 0 : 1) : -1; }
-  if (forced >= 0) return forced == 1;
+  const char* e = getenv("GLA_B200_STATE_FUSED");      // read per call: tests switch it within one process
+  if (e != nullptr && e[0] != 0) return e[0] != '0';
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (sms <= 0) sms = 148;
   const double waves = (double)((4 * BH + sms - 1) / sms);
-  const double t_fused = waves * (double)N * 1.0 + 5.0;          // us
+  const double t_fused = waves * (double)N * 1.0 + 8.0;          // us
   const double t_pair = (double)(BH * N) * 0.1 + 10.0;           // us
   return t_fused < t_pair;
 }

@@ -99,6 +99,33 @@ def test_chunk_gla_tcgen05_vs_oracle(cuda_device, B, T, H, shift, zero_init):
     _compare(ref, got, torch.bfloat16, f"chunk_gla tcgen05 {B,T,H,shift}")
 
 
+STATE_PATH_CASES = [
+    # B, T, H    (bf16, D = chunk = 128); the ring depths are 3 and 4, so 1..5 chunks cover every wrap case
+    (1, 128, 1), (1, 256, 1), (1, 384, 2), (1, 512, 1), (1, 640, 1), (2, 1024, 3),
+    (5, 256, 8),        # 160 blocks of the one-pass kernel: more than one wave of SMs
+]
+
+
+@pytest.mark.parametrize("B,T,H", STATE_PATH_CASES)
+def test_chunk_states_one_pass_vs_product_and_scan(cuda_device, B, T, H, monkeypatch):
+    """The two ways of producing the chunk states (one-pass kernel; batched product + scan) are chosen by a
+    cost estimate: force each in turn and require the same results, and parity with the oracle."""
+    from gla_jax_b200 import chunk_gla, _lib
+    case = _case(B, T, H, 128, torch.bfloat16, 33, 2.0, False)
+    got = {}
+    for mode in ("1", "0"):
+        monkeypatch.setenv("GLA_B200_STATE_FUSED", mode)
+        got[mode] = _run_gpu(chunk_gla, cuda_device, *case, chunk_size=128, impl="tcgen05")
+    monkeypatch.delenv("GLA_B200_STATE_FUSED")
+    assert _lib.load().gla_device_wait_timeouts() == 0
+    flat = {m: [got[m][0], got[m][1], *got[m][2]] for m in got}
+    for name, a, b in zip(["hidden_final", "out", *NAMES], flat["1"], flat["0"]):
+        err = O.rel_l2(b, a)
+        assert err <= 4e-3, f"{name}: one-pass vs product+scan {err:.3e}"     # same bf16 operands, different summation order
+    if B * T * H <= 4096:
+        _compare(_oracle(*case), got["1"], torch.bfloat16, f"chunk_gla one-pass states {B,T,H}")
+
+
 def test_auto_picks_tcgen05_for_readme_shape(cuda_device):
     """impl='auto' must run the tensor-core kernels at D = chunk = 128 in bf16 (checked through
     the library's own launch profile) and the fp32 kernels elsewhere."""
