@@ -14,9 +14,13 @@
 //   DV        value        dS = dC + q (x) dO_s ; dC = f (.) dS  (reverse)  dv_s = sum_k k dS
 //   DK        key          dS = dC + q_s dO     ; dC = f_s dS    (reverse)  dk_s = sum_v v dS
 //
-// A block owns a 16-wide slice and all D entries of the other ("long") axis: 128 threads =
-// 16 slice entries x 8 lanes, each lane holding D/8 state elements; the reduction is three
-// warp shuffles.  Time is processed in blocks of 16 steps staged through shared memory in
+// A block owns a 16-wide slice and all D entries of the other ("long") axis.  The kernel is bound by
+// the shared-memory / shuffle pipe, not by FMAs, so the thread layout is chosen to reuse what a thread
+// reads: LP = min(32, D/4) lanes span the long axis (a warp's 16-byte loads cover a whole row of a
+// staged tile), and each thread carries the state of its D/LP long entries for FOUR slice entries, so
+// every tile value it loads feeds four recurrences.  The four per-step sums are reduced over the
+// lanes by a transposing butterfly (2 + 1 + log2(LP/4) shuffles instead of 4 log2(LP)).
+// Time is processed in blocks of 32 steps staged through shared memory in
 // float32 (gate already exponentiated), with the next block's global loads in flight
 // during the current block's arithmetic.  dlog_fgate follows gla.py:263:
 //   dg = cumsum over the remaining tokens of (q dq - k dk) + sum_v(dS_T * S_T).
@@ -24,9 +28,11 @@
 
 namespace gla {
 
-constexpr int RB = 16;      // time steps per staged block
+constexpr int RB = 32;      // time steps per staged block
 constexpr int RS = 16;      // slice width
-constexpr int RTHREADS = 128;
+constexpr int NSI = 4;      // slice entries per thread
+constexpr int rec_lanes(int D) { return D / 4 < 32 ? D / 4 : 32; }     // lanes along the long axis
+constexpr int rec_threads(int D) { return (RS / NSI) * rec_lanes(D); }
 
 enum RecMode { REC_FWD = 0, REC_DQ = 1, REC_DV = 2, REC_DK = 3 };
 
@@ -46,12 +52,29 @@ struct RecParams {
   int time_reversed;         // process tokens from last to first
 };
 
-__device__ __forceinline__ float reduce8(float x) {
-  x += __shfl_xor_sync(0xffffffffu, x, 1);
-  x += __shfl_xor_sync(0xffffffffu, x, 2);
-  x += __shfl_xor_sync(0xffffffffu, x, 4);
+// Sum over the LP consecutive lanes of a lane group.
+template <int LP>
+__device__ __forceinline__ float reduce_lanes(float x) {
+#pragma unroll
+  for (int o = 1; o < LP; o <<= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
   return x;
 }
+// Four sums at once: after two exchange stages each lane holds one of the four values summed over its
+// group of four lanes, the remaining stages sum that value over the other lanes.  On return lane lp
+// (lp < 4) of the group holds the total of v[rec_which(lp)].
+template <int LP>
+__device__ __forceinline__ float reduce4_lanes(const float (&v)[4], int lp) {
+  const bool o1 = (lp & 1) != 0, o2 = (lp & 2) != 0;
+  float a0 = o1 ? v[2] : v[0], a1 = o1 ? v[3] : v[1];
+  a0 += __shfl_xor_sync(0xffffffffu, o1 ? v[0] : v[2], 1);
+  a1 += __shfl_xor_sync(0xffffffffu, o1 ? v[1] : v[3], 1);
+  float b = o2 ? a1 : a0;
+  b += __shfl_xor_sync(0xffffffffu, o2 ? a0 : a1, 2);
+#pragma unroll
+  for (int o = 4; o < LP; o <<= 1) b += __shfl_xor_sync(0xffffffffu, b, o);
+  return b;
+}
+__device__ __forceinline__ int rec_which(int lp) { return 2 * (lp & 1) + ((lp >> 1) & 1); }
 
 // A staged tile source: column window [c0, c0 + W) of a (B,T,H,D) array for one (b, h).
 struct TileSrc {
@@ -65,7 +88,7 @@ struct TileSrc {
 // loads and parks the RAW bits in registers: nothing in it consumes a loaded value, so all of a
 // thread's loads are in flight together (a conversion right behind each load would stall the
 // in-order warp for a full memory latency per load).  tile_commit converts and stores to smem.
-template <int W, int NG>
+template <int W, int NG, int RTHREADS>
 __device__ __forceinline__ void tile_fetch(uint4 (&raw)[NG], const TileSrc& s, int64_t base, int64_t row_stride,
                                            int64_t step0, int64_t T, int time_reversed, int c0) {
 #pragma unroll
@@ -87,7 +110,7 @@ __device__ __forceinline__ void tile_fetch(uint4 (&raw)[NG], const TileSrc& s, i
     raw[i] = u;
   }
 }
-template <int W, int NG>
+template <int W, int NG, int RTHREADS>
 __device__ __forceinline__ void tile_commit(float* sm, const uint4 (&raw)[NG], int is_bf16, int do_exp) {
 #pragma unroll
   for (int i = 0; i < NG; ++i) {
@@ -108,18 +131,19 @@ __device__ __forceinline__ void tile_commit(float* sm, const uint4 (&raw)[NG], i
 }
 
 template <int D, int MODE>
-__global__ void __launch_bounds__(RTHREADS) rec_kernel(RecParams p) {
-  constexpr int KP = D / 8;                       // state elements per thread
+__global__ void __launch_bounds__(rec_threads(D)) rec_kernel(RecParams p) {
+  constexpr int LP = rec_lanes(D), RTHREADS = rec_threads(D);
+  constexpr int KP = D / LP;                      // long entries per thread (x NSI slice entries of state)
   constexpr int NL = (MODE == REC_FWD || MODE == REC_DV) ? 3 : 2;   // long tiles
   constexpr int NS = (MODE == REC_FWD || MODE == REC_DV) ? 1 : 3;   // slice tiles
   constexpr int LG = RB * D / RTHREADS / 4;       // long-tile groups of four elements per thread
-  constexpr int SG = 1;                           // slice tile: 64 groups of four elements, threads 0..63
+  constexpr int SG = (RB * RS / 4 + RTHREADS - 1) / RTHREADS;       // slice-tile groups per thread
   extern __shared__ __align__(16) float smem[];
   // tile offsets inside the one shared array (plain offsets, not pointer tables, so that every
   // access is compiled as a shared-memory access)
   constexpr int L_OFF = RB * D, S_BASE = NL * RB * D, S_OFF = RB * RS, R_BASE = NL * RB * D + NS * RB * RS;
 
-  const int lp = threadIdx.x % 8, si = threadIdx.x / 8;
+  const int lp = threadIdx.x % LP, sg = threadIdx.x / LP;     // lane on the long axis, group of NSI slice entries
   const int c0 = blockIdx.x * RS;                 // slice window
   const int64_t h = blockIdx.y, b = blockIdx.z;
   const int64_t T = p.T, HD = p.H * D;
@@ -145,45 +169,56 @@ __global__ void __launch_bounds__(RTHREADS) rec_kernel(RecParams p) {
     Ssrc[0] = {p.g, 0, 1}; Ssrc[1] = {p.k, p.bf, 0}; Ssrc[2] = {p.q, p.bf, 0};
   }
 
-  // state: element (long index L(i), slice index c0 + si); memory layout [key][value]
-  auto long_index = [&](int i) { return 4 * lp + 32 * (i / 4) + (i % 4); };
-  auto state_addr = [&](int i) -> int64_t {
-    const int L = long_index(i);
-    return slice_is_value ? hbase + (int64_t)L * D + (c0 + si) : hbase + (int64_t)(c0 + si) * D + L;
+  // state: element (long index L(i), slice index c0 + NSI sg + j); memory layout [key][value]
+  auto long_index = [&](int i) { return 4 * lp + 4 * LP * (i / 4) + (i % 4); };
+  auto state_addr = [&](int i, int j) -> int64_t {
+    const int L = long_index(i), c = c0 + NSI * sg + j;
+    return slice_is_value ? hbase + (int64_t)L * D + c : hbase + (int64_t)c * D + L;
   };
-  float st[KP];
+  float st[KP][NSI];
   {
     const void* init = bwd_pass ? p.dhidden_final : p.hidden_init;
 #pragma unroll
-    for (int i = 0; i < KP; ++i) st[i] = init ? ld_any(init, p.bf, state_addr(i)) : 0.f;
+    for (int i = 0; i < KP; ++i)
+#pragma unroll
+      for (int j = 0; j < NSI; ++j) st[i][j] = init ? ld_any(init, p.bf, state_addr(i, j)) : 0.f;
   }
 
   uint4 lreg[NL][LG];
   uint4 sreg[NS][SG];
   auto fetch = [&](int64_t step0) {
 #pragma unroll
-    for (int a = 0; a < NL; ++a) tile_fetch<D, LG>(lreg[a], Lsrc[a], base, HD, step0, T, trev, 0);
+    for (int a = 0; a < NL; ++a) tile_fetch<D, LG, RTHREADS>(lreg[a], Lsrc[a], base, HD, step0, T, trev, 0);
 #pragma unroll
-    for (int a = 0; a < NS; ++a) tile_fetch<RS, SG>(sreg[a], Ssrc[a], base, HD, step0, T, trev, c0);
+    for (int a = 0; a < NS; ++a) tile_fetch<RS, SG, RTHREADS>(sreg[a], Ssrc[a], base, HD, step0, T, trev, c0);
   };
   fetch(0);
   for (int64_t step0 = 0; step0 < T; step0 += RB) {
     __syncthreads();   // previous block's readers of the tiles and of Rs are done
 #pragma unroll
-    for (int a = 0; a < NL; ++a) tile_commit<D, LG>(smem + a * L_OFF, lreg[a], Lsrc[a].bf, Lsrc[a].do_exp);
+    for (int a = 0; a < NL; ++a) tile_commit<D, LG, RTHREADS>(smem + a * L_OFF, lreg[a], Lsrc[a].bf, Lsrc[a].do_exp);
 #pragma unroll
-    for (int a = 0; a < NS; ++a) tile_commit<RS, SG>(smem + S_BASE + a * S_OFF, sreg[a], Ssrc[a].bf, Ssrc[a].do_exp);
+    for (int a = 0; a < NS; ++a) tile_commit<RS, SG, RTHREADS>(smem + S_BASE + a * S_OFF, sreg[a], Ssrc[a].bf, Ssrc[a].do_exp);
     __syncthreads();
     if (step0 + RB < T) fetch(step0 + RB);
     const int nt = (int)((T - step0) < RB ? (T - step0) : RB);
-    for (int tt = 0; tt < nt; ++tt) {
-      float red = 0.f;
-      const float s0 = smem[S_BASE + tt * RS + si];
-      float s1 = 0.f, s2 = 0.f;
-      if (NS == 3) { s1 = smem[S_BASE + S_OFF + tt * RS + si]; s2 = smem[S_BASE + 2 * S_OFF + tt * RS + si]; }
+    // One step of the recurrence for this thread's state; returns the four per-step sums (not yet reduced).
+    auto step = [&](int tt, float (&red)[NSI]) {
+#pragma unroll
+      for (int j = 0; j < NSI; ++j) red[j] = 0.f;
+      // the step's slice-axis scalars for this thread's four slice entries (one broadcast 16-byte load each)
+      const float4 s0q = *reinterpret_cast<const float4*>(smem + S_BASE + tt * RS + NSI * sg);
+      float4 s1q = make_float4(0.f, 0.f, 0.f, 0.f), s2q = s1q;
+      if (NS == 3) {
+        s1q = *reinterpret_cast<const float4*>(smem + S_BASE + S_OFF + tt * RS + NSI * sg);
+        s2q = *reinterpret_cast<const float4*>(smem + S_BASE + 2 * S_OFF + tt * RS + NSI * sg);
+      }
+      const float s0v[4] = {s0q.x, s0q.y, s0q.z, s0q.w};
+      const float s1v[4] = {s1q.x, s1q.y, s1q.z, s1q.w};
+      const float s2v[4] = {s2q.x, s2q.y, s2q.z, s2q.w};
 #pragma unroll
       for (int m = 0; m < KP / 4; ++m) {
-        const int off = tt * D + 32 * m + 4 * lp;
+        const int off = tt * D + 4 * LP * m + 4 * lp;
         const float4 a4 = *reinterpret_cast<const float4*>(smem + off);
         const float4 b4 = *reinterpret_cast<const float4*>(smem + L_OFF + off);
         float4 c4 = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -192,33 +227,58 @@ __global__ void __launch_bounds__(RTHREADS) rec_kernel(RecParams p) {
         const float bv[4] = {b4.x, b4.y, b4.z, b4.w};
         const float cv[4] = {c4.x, c4.y, c4.z, c4.w};
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          float& S = st[4 * m + j];
-          if (MODE == REC_FWD) {          // a = f, b = k, c = q ; s0 = v
-            S = fmaf(av[j], S, bv[j] * s0);
-            red = fmaf(cv[j], S, red);
-          } else if (MODE == REC_DQ) {    // a = v, b = dO ; s0 = f, s1 = k
-            S = fmaf(s0, S, s1 * av[j]);
-            red = fmaf(bv[j], S, red);
-          } else if (MODE == REC_DV) {    // a = f, b = k, c = q ; s0 = dO
-            const float tmp = fmaf(cv[j], s0, S);
-            red = fmaf(bv[j], tmp, red);
-            S = av[j] * tmp;
-          } else {                        // a = v, b = dO ; s0 = f, s1 = k, s2 = q
-            const float tmp = fmaf(s2, bv[j], S);
-            red = fmaf(av[j], tmp, red);
-            S = s0 * tmp;
+        for (int e = 0; e < 4; ++e) {
+#pragma unroll
+          for (int j = 0; j < NSI; ++j) {
+            float& S = st[4 * m + e][j];
+            if (MODE == REC_FWD) {          // a = f, b = k, c = q ; s0 = v
+              S = fmaf(av[e], S, bv[e] * s0v[j]);
+              red[j] = fmaf(cv[e], S, red[j]);
+            } else if (MODE == REC_DQ) {    // a = v, b = dO ; s0 = f, s1 = k
+              S = fmaf(s0v[j], S, s1v[j] * av[e]);
+              red[j] = fmaf(bv[e], S, red[j]);
+            } else if (MODE == REC_DV) {    // a = f, b = k, c = q ; s0 = dO
+              const float tmp = fmaf(cv[e], s0v[j], S);
+              red[j] = fmaf(bv[e], tmp, red[j]);
+              S = av[e] * tmp;
+            } else {                        // a = v, b = dO ; s0 = f, s1 = k, s2 = q
+              const float tmp = fmaf(s2v[j], bv[e], S);
+              red[j] = fmaf(av[e], tmp, red[j]);
+              S = s0v[j] * tmp;
+            }
           }
         }
       }
-      red = reduce8(red);
-      if (lp == 0) smem[R_BASE + tt * RS + si] = red;
+    };
+    // The block's steps are fully unrolled with the reduced sums kept in registers until the end: with no
+    // shared-memory store between the steps the compiler is free to issue a step's loads and FMAs while the
+    // previous step's shuffle chain is still in flight (an in-order warp otherwise waits out every chain).
+    float res[RB];
+    if (nt == RB) {
+#pragma unroll
+      for (int tt = 0; tt < RB; ++tt) {
+        float red[NSI];
+        step(tt, red);
+        res[tt] = reduce4_lanes<LP>(red, lp);
+      }
+    } else {
+#pragma unroll
+      for (int tt = 0; tt < RB; ++tt) res[tt] = 0.f;
+      for (int tt = 0; tt < nt; ++tt) {
+        float red[NSI];
+        step(tt, red);
+        const float tot = reduce4_lanes<LP>(red, lp);
+#pragma unroll
+        for (int u = 0; u < RB; ++u) if (u == tt) res[u] = tot;
+      }
+    }
+    if (lp < 4) {
+#pragma unroll
+      for (int tt = 0; tt < RB; ++tt) smem[R_BASE + tt * RS + NSI * sg + rec_which(lp)] = res[tt];
     }
     __syncthreads();
-    // write the block's results: RB x RS values, two per thread
-#pragma unroll
-    for (int i = 0; i < RB * RS / RTHREADS; ++i) {
-      const int e = threadIdx.x + RTHREADS * i;
+    // write the block's results: RB x RS values
+    for (int e = threadIdx.x; e < RB * RS; e += RTHREADS) {
       const int row = e / RS, col = e % RS;
       const int64_t sidx = step0 + row;
       if (sidx < T) {
@@ -243,19 +303,28 @@ __global__ void __launch_bounds__(RTHREADS) rec_kernel(RecParams p) {
   if (MODE == REC_FWD) {
     if (p.hidden_final) {
 #pragma unroll
-      for (int i = 0; i < KP; ++i) st_any(p.hidden_final, p.bf, state_addr(i), st[i]);
+      for (int i = 0; i < KP; ++i)
+#pragma unroll
+        for (int j = 0; j < NSI; ++j) st_any(p.hidden_final, p.bf, state_addr(i, j), st[i][j]);
     }
   } else if (MODE == REC_DQ) {
-    float s = 0.f;
+    float s[NSI] = {0.f, 0.f, 0.f, 0.f};
     if (p.dhidden_final) {
 #pragma unroll
-      for (int i = 0; i < KP; ++i) s = fmaf(ld_any(p.dhidden_final, p.bf, state_addr(i)), st[i], s);
+      for (int i = 0; i < KP; ++i)
+#pragma unroll
+        for (int j = 0; j < NSI; ++j) s[j] = fmaf(ld_any(p.dhidden_final, p.bf, state_addr(i, j)), st[i][j], s[j]);
     }
-    s = reduce8(s);
-    if (lp == 0) p.boundary[(b * p.H + h) * D + c0 + si] = s;
+#pragma unroll
+    for (int j = 0; j < NSI; ++j) {
+      const float t = reduce_lanes<LP>(s[j]);
+      if (lp == 0) p.boundary[(b * p.H + h) * D + c0 + NSI * sg + j] = t;
+    }
   } else if (MODE == REC_DV) {
 #pragma unroll
-    for (int i = 0; i < KP; ++i) st_any(p.dhidden_init, p.bf, state_addr(i), st[i]);
+    for (int i = 0; i < KP; ++i)
+#pragma unroll
+      for (int j = 0; j < NSI; ++j) st_any(p.dhidden_init, p.bf, state_addr(i, j), st[i][j]);
   }
 }
 
@@ -270,7 +339,7 @@ static int launch_rec(cudaStream_t st, const RecParams& p) {
   dim3 grid(D / RS, (unsigned)p.H, (unsigned)p.B);
   static const char* names[4] = {"rec_kernel_fwd", "rec_kernel_dq", "rec_kernel_dv", "rec_kernel_dk"};
   ProfScope ps(names[MODE], st);
-  rec_kernel<D, MODE><<<grid, RTHREADS, smem, st>>>(p);
+  rec_kernel<D, MODE><<<grid, rec_threads(D), smem, st>>>(p);
   GLA_CHECK_LAUNCH();
   return GLA_OK;
 }
