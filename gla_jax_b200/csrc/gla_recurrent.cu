@@ -30,7 +30,7 @@ namespace gla {
 
 constexpr int RB = 32;      // time steps per staged block
 constexpr int RS = 16;      // slice width
-constexpr int NSI = 4;      // slice entries per thread
+constexpr int NSI = 4;      // slice entries per thread (4 or 2)
 constexpr int rec_lanes(int D) { return D / 4 < 32 ? D / 4 : 32; }     // lanes along the long axis
 constexpr int rec_threads(int D) { return (RS / NSI) * rec_lanes(D); }
 
@@ -74,7 +74,20 @@ __device__ __forceinline__ float reduce4_lanes(const float (&v)[4], int lp) {
   for (int o = 4; o < LP; o <<= 1) b += __shfl_xor_sync(0xffffffffu, b, o);
   return b;
 }
-__device__ __forceinline__ int rec_which(int lp) { return 2 * (lp & 1) + ((lp >> 1) & 1); }
+__device__ __forceinline__ int rec_which(int lp) { return NSI == 4 ? 2 * (lp & 1) + ((lp >> 1) & 1) : (lp & 1); }
+template <int LP>
+__device__ __forceinline__ float reduce2_lanes(const float (&v)[2], int lp) {
+  const bool o1 = (lp & 1) != 0;
+  float b = o1 ? v[1] : v[0];
+  b += __shfl_xor_sync(0xffffffffu, o1 ? v[0] : v[1], 1);
+#pragma unroll
+  for (int o = 2; o < LP; o <<= 1) b += __shfl_xor_sync(0xffffffffu, b, o);
+  return b;
+}
+template <int LP, int N>
+__device__ __forceinline__ float reduceN_lanes(const float (&v)[N], int lp) {
+  if constexpr (N == 4) return reduce4_lanes<LP>(v, lp); else return reduce2_lanes<LP>(v, lp);
+}
 
 // A staged tile source: column window [c0, c0 + W) of a (B,T,H,D) array for one (b, h).
 struct TileSrc {
@@ -207,15 +220,13 @@ __global__ void __launch_bounds__(rec_threads(D)) rec_kernel(RecParams p) {
 #pragma unroll
       for (int j = 0; j < NSI; ++j) red[j] = 0.f;
       // the step's slice-axis scalars for this thread's four slice entries (one broadcast 16-byte load each)
-      const float4 s0q = *reinterpret_cast<const float4*>(smem + S_BASE + tt * RS + NSI * sg);
-      float4 s1q = make_float4(0.f, 0.f, 0.f, 0.f), s2q = s1q;
-      if (NS == 3) {
-        s1q = *reinterpret_cast<const float4*>(smem + S_BASE + S_OFF + tt * RS + NSI * sg);
-        s2q = *reinterpret_cast<const float4*>(smem + S_BASE + 2 * S_OFF + tt * RS + NSI * sg);
+      float s0v[NSI], s1v[NSI], s2v[NSI];
+#pragma unroll
+      for (int j = 0; j < NSI; ++j) {
+        s0v[j] = smem[S_BASE + tt * RS + NSI * sg + j];
+        s1v[j] = NS == 3 ? smem[S_BASE + S_OFF + tt * RS + NSI * sg + j] : 0.f;
+        s2v[j] = NS == 3 ? smem[S_BASE + 2 * S_OFF + tt * RS + NSI * sg + j] : 0.f;
       }
-      const float s0v[4] = {s0q.x, s0q.y, s0q.z, s0q.w};
-      const float s1v[4] = {s1q.x, s1q.y, s1q.z, s1q.w};
-      const float s2v[4] = {s2q.x, s2q.y, s2q.z, s2q.w};
 #pragma unroll
       for (int m = 0; m < KP / 4; ++m) {
         const int off = tt * D + 4 * LP * m + 4 * lp;
@@ -259,7 +270,7 @@ __global__ void __launch_bounds__(rec_threads(D)) rec_kernel(RecParams p) {
       for (int tt = 0; tt < RB; ++tt) {
         float red[NSI];
         step(tt, red);
-        res[tt] = reduce4_lanes<LP>(red, lp);
+        res[tt] = reduceN_lanes<LP, NSI>(red, lp);
       }
     } else {
 #pragma unroll
@@ -267,12 +278,12 @@ __global__ void __launch_bounds__(rec_threads(D)) rec_kernel(RecParams p) {
       for (int tt = 0; tt < nt; ++tt) {
         float red[NSI];
         step(tt, red);
-        const float tot = reduce4_lanes<LP>(red, lp);
+        const float tot = reduceN_lanes<LP, NSI>(red, lp);
 #pragma unroll
         for (int u = 0; u < RB; ++u) if (u == tt) res[u] = tot;
       }
     }
-    if (lp < 4) {
+    if (lp < NSI) {
 #pragma unroll
       for (int tt = 0; tt < RB; ++tt) smem[R_BASE + tt * RS + NSI * sg + rec_which(lp)] = res[tt];
     }
@@ -308,7 +319,7 @@ __global__ void __launch_bounds__(rec_threads(D)) rec_kernel(RecParams p) {
         for (int j = 0; j < NSI; ++j) st_any(p.hidden_final, p.bf, state_addr(i, j), st[i][j]);
     }
   } else if (MODE == REC_DQ) {
-    float s[NSI] = {0.f, 0.f, 0.f, 0.f};
+    float s[NSI] = {};
     if (p.dhidden_final) {
 #pragma unroll
       for (int i = 0; i < KP; ++i)
