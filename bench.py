@@ -380,6 +380,10 @@ def main():
                 ach = alg["flops"] / per_launch_s / 1e12
                 roof = {"bound": "tensor", "kernel": dom, "achieved": ach, "peak": peaks["tf_burst"],
                         "unit": "TFLOP/s", "frac": ach / peaks["tf_burst"], "traffic": None}
+            # DRAM bytes per launch of this kernel at this exact shape, from the committed ncu capture
+            # (profiles/tc_chunk_kernels_readme_shape_ncu_full.md); null for kernels without one
+            if args.op == "chunk_gla" and dom in NCU_TRAFFIC_README_SHAPE:
+                roof["traffic"] = NCU_TRAFFIC_README_SHAPE[dom]
             roof.update({"peak_source": peaks["source"], "launches": n_l, "ms_per_launch": 1e3 * per_launch_s,
                          "share_of_kernel_time": ms_l / total_k, "algorithmic": alg["what"]})
         line = {
@@ -438,6 +442,14 @@ def _alg_tc_bwd(B, T, H, D, C):
     return {"bound": "hbm", "bytes": th * 22 * D,
             "what": "backward: q,k,v,dout (bf16) + log_fgate (f32) in, dq,dk,dv (bf16) + dlog_fgate (f32) out: 22*D B per token-head"}
 
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch (bytes), README shape, one ncu capture
+NCU_TRAFFIC_README_SHAPE = {
+    "tc_chunk_bwd_kernel": 366.1e6,
+    "tc_chunk_fwd_kernel": 177.6e6,
+    "tc_state_kernel": 111.2e6,
+    "tc_dstate_scan_kernel": 111.1e6,
+}
 
 KERNEL_ALGORITHMIC = {
     "simt_intra_bwd_kernel": _alg_simt_intra_bwd,
