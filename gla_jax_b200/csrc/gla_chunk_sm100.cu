@@ -256,7 +256,7 @@ struct FwdSmem {
   static constexpr uint32_t P = S + 2 * TILE_BYTES;        // 32 KB;               TMA lands raw k here first
   static constexpr uint32_t TOT = P + 2 * TILE_BYTES;      // 8 x 128 float
   static constexpr uint32_t DIAG = TOT + 8 * TD * 4;       // 2 x 128 float
-  static constexpr uint32_t BAR = DIAG + 2 * TC * 4;       // 4 mbarriers + tmem slot
+  static constexpr uint32_t BAR = DIAG + 2 * TC * 4;       // 5 mbarriers + tmem slot
   static constexpr uint32_t END = BAR + 64;
 };
 constexpr uint32_t KC_TILE = 64 * 128;    // one SW128 tile of 64 rows
@@ -340,8 +340,8 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, 
   uint8_t* sm = align1024(smem_raw);
   float* tot = reinterpret_cast<float*>(sm + FwdSmem::TOT);
   float* diag = reinterpret_cast<float*>(sm + FwdSmem::DIAG);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + FwdSmem::BAR);   // [0],[1]: level buffers, [2]: output, [3]: loads
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + FwdSmem::BAR);   // [0],[1]: level buffers, [2]: output, [3]: g,q,k loads, [4]: v,S loads
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int rg = tid >> 6, cp = tid & 63;
@@ -356,18 +356,24 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, 
     mbar_init(smem_u32(bars + 1), 1);
     mbar_init(smem_u32(bars + 2), 1);
     mbar_init(smem_u32(bars + 3), 1);
+    mbar_init(smem_u32(bars + 4), 1);
     mbar_fence_init();
-    // ---- all global inputs of the chunk through TMA: 192 KB in flight on one barrier ----------
-    const uint32_t lb = smem_u32(bars + 3);
+    // ---- all global inputs of the chunk through TMA: 192 KB in flight.  g, q, k (needed at once) come first on
+    // their own barrier; v and S_prev are only needed by the output product and land while the levels run.
+    const uint32_t lb = smem_u32(bars + 3), lb2 = smem_u32(bars + 4);
     const int z = (int)(b * T + n * TC), y = (int)h_;
-    mbar_arrive_expect_tx(lb, 6 * 2 * TILE_BYTES);
+    mbar_arrive_expect_tx(lb, 4 * 2 * TILE_BYTES);
+    mbar_arrive_expect_tx(lb2, 2 * 2 * TILE_BYTES);
     tma_load_3d(smem_u32(sm + FwdSmem::Q), &maps.g, 0, y, z, lb);                       // 128 x 128 float, row pitch 512 B
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
       tma_load_3d(smem_u32(sm + FwdSmem::K + half * TILE_BYTES), &maps.q, 64 * half, y, z, lb);
       tma_load_3d(smem_u32(sm + FwdSmem::P + half * TILE_BYTES), &maps.k, 64 * half, y, z, lb);
-      tma_load_3d(smem_u32(sm + FwdSmem::V + half * TILE_BYTES), &maps.v, 64 * half, y, z, lb);
-      tma_load_2d(smem_u32(sm + FwdSmem::S + half * TILE_BYTES), &maps.s, 64 * half, (int)(chunk_id * TD), lb);
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      tma_load_3d(smem_u32(sm + FwdSmem::V + half * TILE_BYTES), &maps.v, 64 * half, y, z, lb2);
+      tma_load_2d(smem_u32(sm + FwdSmem::S + half * TILE_BYTES), &maps.s, 64 * half, (int)(chunk_id * TD), lb2);
     }
   }
   if (warp == 1) {
@@ -567,6 +573,7 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, 
   tc_fence_before();
   __syncthreads();
   if (tid == 0) {
+    ok = mbar_wait(smem_u32(bars + 4), 0) && ok;       // v and S_prev have landed (long ago, as a rule)
     tc_fence_after();
     constexpr uint32_t idesc = idesc_bf16(128, 128, 0, 1);
     const uint64_t aq = desc_kmajor(sQ0 + 2 * TILE_BYTES, TILE_BYTES, 0), bs = desc_mnmajor(smem_u32(sm + FwdSmem::S), TILE_BYTES, 0);
