@@ -237,6 +237,10 @@ int gla_chunk_local_state(void* stream, int64_t B, int64_t T, int64_t H, int64_t
   GLA_TRY(check_chunk_dims(B, T, H, D, chunk, dtype));
   int r = resolve_impl(impl, D, chunk, dtype);
   if (r < 0) return -r;
+  if (r == GLA_IMPL_TCGEN05 && !tc_supported_local_state(D, chunk, dtype)) {
+    if (impl == GLA_IMPL_TCGEN05) return GLA_ERR_UNSUPPORTED;
+    r = GLA_IMPL_FP32_SIMT;
+  }
   const size_t need = r == GLA_IMPL_TCGEN05 ? tc_fwd_ws_bytes(B, T, H, D, chunk) : simt_fwd_ws_bytes(B, T, H, D, chunk);
   if (!workspace || workspace_bytes < need) return GLA_ERR_WORKSPACE;
   if (r == GLA_IMPL_TCGEN05)

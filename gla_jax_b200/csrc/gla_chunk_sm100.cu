@@ -334,7 +334,7 @@ __device__ __forceinline__ void fwd_emit(const float2 (&f)[16], const uint32_t (
 
 
 __global__ void __launch_bounds__(TTHREADS, 1)
-tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, int64_t N, bf16* __restrict__ out,
+tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, int R, int64_t N, bf16* __restrict__ out,
                     bf16* __restrict__ P_saved) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = align1024(smem_raw);
@@ -345,7 +345,12 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, 
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int rg = tid >> 6, cp = tid & 63;
+  // H counts VIRTUAL heads of size 128: a head of size 128 R is R x R independent (key block a, value block c)
+  // problems, virtual head (h R + a) R + c, whose results the caller sums over a.  In the (B, T, H_real R, 128) view
+  // of the inputs the key-side tensors of a virtual head are head h R + a, the value-side ones head h R + c; the
+  // output is written per virtual head, (B, T, H, 128).  R = 1: everything coincides with the real layout.
   const int64_t n = blockIdx.x % N, bh = blockIdx.x / N, b = bh / H, h_ = bh % H;
+  const int64_t hk_ = (h_ / (R * R)) * R + (h_ % (R * R)) / R, hv_ = (h_ / (R * R)) * R + h_ % R;
   const int64_t HD = H * TD;
   const int64_t row0 = ((b * T + n * TC) * H + h_) * TD;
   const int64_t chunk_id = bh * N + n;
@@ -361,7 +366,7 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, 
     // ---- all global inputs of the chunk through TMA: 192 KB in flight.  g, q, k (needed at once) come first on
     // their own barrier; v and S_prev are only needed by the output product and land while the levels run.
     const uint32_t lb = smem_u32(bars + 3), lb2 = smem_u32(bars + 4);
-    const int z = (int)(b * T + n * TC), y = (int)h_;
+    const int z = (int)(b * T + n * TC), y = (int)hk_, yv = (int)hv_;
     mbar_arrive_expect_tx(lb, 4 * 2 * TILE_BYTES);
     mbar_arrive_expect_tx(lb2, 2 * 2 * TILE_BYTES);
     tma_load_3d(smem_u32(sm + FwdSmem::Q), &maps.g, 0, y, z, lb);                       // 128 x 128 float, row pitch 512 B
@@ -372,7 +377,7 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, 
     }
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
-      tma_load_3d(smem_u32(sm + FwdSmem::V + half * TILE_BYTES), &maps.v, 64 * half, y, z, lb2);
+      tma_load_3d(smem_u32(sm + FwdSmem::V + half * TILE_BYTES), &maps.v, 64 * half, yv, z, lb2);
       tma_load_2d(smem_u32(sm + FwdSmem::S + half * TILE_BYTES), &maps.s, 64 * half, (int)(chunk_id * TD), lb2);
     }
   }
@@ -727,7 +732,7 @@ __device__ __forceinline__ float bf16_hi(uint32_t u) { return __uint_as_float(u 
 __device__ __forceinline__ void st_bf16(uint8_t* p, float v) { *reinterpret_cast<bf16*>(p) = __float2bfloat16_rn(v); }
 
 __global__ void __launch_bounds__(TTHREADS, 1)
-tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, int64_t N, int pf_dist, const float* __restrict__ g, const bf16* __restrict__ v,
+tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, int R, int64_t N, int pf_dist, const float* __restrict__ g, const bf16* __restrict__ v,
                     const bf16* __restrict__ k, const bf16* __restrict__ q, const bf16* __restrict__ dO,
                     const bf16* __restrict__ S_prev, const bf16* __restrict__ dS_next, const bf16* __restrict__ P_saved,
                     bf16* __restrict__ dq_out, bf16* __restrict__ dk_out, bf16* __restrict__ dv_out,
@@ -745,9 +750,16 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int q4 = warp & 3, wq_ = warp >> 2;        // TMEM lane quadrant, and which quarter of the columns
   const int d = 32 * q4 + lane;                     // column layout: feature index
+  // H counts virtual heads (see the forward kernel).  Inputs are addressed in the (B, T, H / R, 128) view: key-side
+  // tensors (g, q, k) at head hk_, value-side tensors (v, dO) at head hv_; the gradients are written per virtual
+  // head, (B, T, H, 128), and the caller sums dq, dk, dg over the value blocks and dv over the key blocks.
   const int64_t n = blockIdx.x % N, bh = blockIdx.x / N, b = bh / H, h_ = bh % H;
-  const int64_t HD = H * TD;
-  const int64_t row0 = ((b * T + n * TC) * H + h_) * TD;
+  const int64_t hk_ = (h_ / (R * R)) * R + (h_ % (R * R)) / R, hv_ = (h_ / (R * R)) * R + h_ % R;
+  const int64_t HD = H * TD;                                          // output row pitch (virtual heads)
+  const int64_t HDi = (H / R) * TD;                                   // input row pitch
+  const int64_t row0 = ((b * T + n * TC) * H + h_) * TD;              // outputs
+  const int64_t row0k = ((b * T + n * TC) * (H / R) + hk_) * TD;      // g, q, k
+  const int64_t row0v = ((b * T + n * TC) * (H / R) + hv_) * TD;      // v, dO
   const int64_t chunk_id = bh * N + n;
 
   if (warp == 0) {
@@ -769,9 +781,9 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
   {
     // all 20 vector loads of the five operand tiles are issued before the first store consumes one
     const int crow = tid >> 4, cch = tid & 15;       // this thread's 16-byte chunk in rows crow + 32 j
-    const bf16* src[5] = {dO + row0, v + row0, S_prev + chunk_id * TD * TD, dS_next + chunk_id * TD * TD,
+    const bf16* src[5] = {dO + row0v, v + row0v, S_prev + chunk_id * TD * TD, dS_next + chunk_id * TD * TD,
                           P_saved + chunk_id * TC * TC};
-    const int64_t ld[5] = {HD, HD, TD, TD, TC};
+    const int64_t ld[5] = {HDi, HDi, TD, TD, TC};
     uint4 t[20];
 #pragma unroll
     for (int m = 0; m < 5; ++m)
@@ -788,9 +800,9 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
   float f32r[32];                                   // gates of rows 32 wq_ + [0, 32), feature d
   {
     float p0 = 1.f, p1 = 1.f;
-    const float* gp = g + row0 + (int64_t)(32 * wq_) * HD + d;
+    const float* gp = g + row0k + (int64_t)(32 * wq_) * HDi + d;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) f32r[i] = __ldg(gp + (int64_t)i * HD);       // all 32 loads in flight
+    for (int i = 0; i < 32; ++i) f32r[i] = __ldg(gp + (int64_t)i * HDi);      // all 32 loads in flight
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
       f32r[i] = __expf(f32r[i]);
@@ -811,10 +823,10 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
     // stored TRANSPOSED: row = feature dk, columns = chunk rows j, so the thread's 32 values are 64
     // contiguous bytes (four 16-byte stores instead of 32 two-byte ones)
     uint8_t* tile = sm + BwdSmem::KH + (wq_ >> 1) * TILE_BYTES;
-    const bf16* kp = k + row0 + (int64_t)(32 * wq_) * HD + d;
+    const bf16* kp = k + row0k + (int64_t)(32 * wq_) * HDi + d;
     uint32_t kraw[32];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) kraw[i] = ldg_u16(kp + (int64_t)i * HD);
+    for (int i = 0; i < 32; ++i) kraw[i] = ldg_u16(kp + (int64_t)i * HDi);
     uint32_t pk[16];
 #pragma unroll
     for (int i = 31; i >= 1; i -= 2) {
@@ -867,14 +879,16 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
   {
     const int64_t nb = (int64_t)blockIdx.x + pf_dist;
     if (pf_dist > 0 && nb < (int64_t)gridDim.x) {
-      const int64_t n2 = nb % N, bh2 = nb / N;
-      const int64_t r2 = (((bh2 / H) * T + n2 * TC) * H + (bh2 % H)) * TD;
+      const int64_t n2 = nb % N, bh2 = nb / N, h2 = bh2 % H;
+      const int64_t hk2 = (h2 / (R * R)) * R + (h2 % (R * R)) / R, hv2 = (h2 / (R * R)) * R + h2 % R;
+      const int64_t t2 = ((bh2 / H) * T + n2 * TC) * (H / R);
+      const int64_t r2k = (t2 + hk2) * TD, r2v = (t2 + hv2) * TD;
       const int64_t c2 = (bh2 * N + n2) * TD * TD;
       // strided rows: one 128-byte line per request (256-byte rows of dO, v, k, q; 512-byte rows of g)
-      const int64_t e2 = r2 + (int64_t)((tid >> 1) & (TC - 1)) * HD + (tid & 1) * 64;
-      l2_prefetch_line(tid < 256 ? dO + e2 : v + e2);
-      l2_prefetch_line(tid < 256 ? k + e2 : q + e2);
-      l2_prefetch_line(g + r2 + (int64_t)(tid >> 2) * HD + (tid & 3) * 32);
+      const int64_t eo = (int64_t)((tid >> 1) & (TC - 1)) * HDi + (tid & 1) * 64;
+      l2_prefetch_line(tid < 256 ? dO + r2v + eo : v + r2v + eo);
+      l2_prefetch_line(tid < 256 ? k + r2k + eo : q + r2k + eo);
+      l2_prefetch_line(g + r2k + (int64_t)(tid >> 2) * HDi + (tid & 3) * 32);
       // contiguous 32 KB tiles: one bulk request each
       if (tid == 0) l2_prefetch_bulk(S_prev + c2, 2 * TD * TD);
       else if (tid == 32) l2_prefetch_bulk(dS_next + c2, 2 * TD * TD);
@@ -886,7 +900,7 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
   TC_STAMP(1, 3);
   // dO, v and P have been consumed by the products: their regions take g, q, k of rows 64..127 and k of rows
   // 0..63 by TMA while phase 1.5 runs, so that the W64 build and the first pass read them from shared memory.
-  const int zrow = (int)(b * T + n * TC), yh = (int)h_;
+  const int zrow = (int)(b * T + n * TC), yh = (int)hk_;
   if (tid == 0) {
     const uint32_t lb = smem_u32(bars + 3);
     mbar_arrive_expect_tx(lb, 32768 + 3 * 16384);
@@ -1057,7 +1071,6 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
     // one level: build operands, issue; the accumulate of the previous level overlaps the MMA
     auto build_and_issue = [&](auto SC) {
       constexpr int S = decltype(SC)::value;
-      constexpr int HHv = 1 << S;
       const int bsel = S & 1;
       if (S < 6) {
         // W_l stored transposed (row = feature d, columns = the 64 rows of the half): this thread's 16
@@ -1267,27 +1280,92 @@ __global__ void __launch_bounds__(256) tc_gsum_kernel(int64_t BH, int64_t N, con
 // ---------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------
-bool tc_supported(int64_t D, int64_t C, int dtype) { return D == TD && C == TC && dtype == GLA_BF16; }
+// bf16; head size 128 or 256 (a head of 256 runs as 2 x 2 independent blocks of 128, see the kernels); any chunk
+// size that is a multiple of 128: the result does not depend on the chunk size, so the kernels always use 128.
+bool tc_supported(int64_t D, int64_t C, int dtype) {
+  return (D == TD || D == 2 * TD) && C >= TC && C % TC == 0 && dtype == GLA_BF16;
+}
+// the entry points that produce a rank's local state for sequence parallelism keep to the original shape
+bool tc_supported_local_state(int64_t D, int64_t C, int dtype) { return D == TD && C == TC && dtype == GLA_BF16; }
 bool tc_auto_default() { return true; }
 
 static size_t f32b(int64_t n) { return align_up((size_t)n * 4, 256); }
-
 static size_t b16b(int64_t n) { return align_up((size_t)n * 2, 256); }
 
-// saved: S_prev bf16 (BH,N,D,D) | Gc f32 (BH,N,D) | P bf16 (BH,N,C,C)
-size_t tc_saved_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t C) {
-  const int64_t N = T / C, BH = B * H;
-  return b16b(BH * N * D * D) + f32b(BH * N * D) + b16b(BH * N * C * C);
+// ---- head sizes above 128: layout changes around the kernels --------------------------------------------------
+// (BH, 128 R, 128 R) <-> (BH, R, R, 128, 128): the state of a head as R x R tiles, one per virtual head.
+__global__ void __launch_bounds__(256) state_block_kernel(const bf16* __restrict__ in, bf16* __restrict__ out,
+                                                          int64_t BH, int R, int to_blocked) {
+  const int64_t e = (int64_t)blockIdx.x * 256 + threadIdx.x;      // one 16-byte piece (8 elements)
+  if (e >= BH * R * R * TD * (TD / 8)) return;
+  const int j = (int)(e % (TD / 8));
+  const int r = (int)((e / (TD / 8)) % TD);
+  const int c = (int)((e / (TD / 8) / TD) % R);
+  const int a = (int)((e / (TD / 8) / TD / R) % R);
+  const int64_t bh = e / (TD / 8) / TD / R / R;
+  const int64_t real = ((bh * TD * R + a * TD + r) * (int64_t)(TD * R) + c * TD + j * 8);
+  const int64_t blocked = ((((bh * R + a) * R + c) * TD + r) * (int64_t)TD + j * 8);
+  if (to_blocked) *reinterpret_cast<uint4*>(out + blocked) = *reinterpret_cast<const uint4*>(in + real);
+  else            *reinterpret_cast<uint4*>(out + real) = *reinterpret_cast<const uint4*>(in + blocked);
 }
-// fwd workspace: kv f32 (BH,N,D,D) | Gc f32 | S_prev bf16 (used when nothing is saved)
-size_t tc_fwd_ws_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t C) {
-  const int64_t N = T / C, BH = B * H;
-  return f32b(BH * N * D * D) + f32b(BH * N * D) + b16b(BH * N * D * D);
+// Per-virtual-head results (rows, H R R, 128) summed into (rows, H, 128 R): key-side arrays (dq, dk, dg) keep the
+// key block a and sum over the value blocks c; value-side arrays (out, dv) keep c and sum over a.  Float32 sums.
+template <typename T, int KEYSIDE>
+__global__ void __launch_bounds__(256) sum_blocks_kernel(const T* __restrict__ in, T* __restrict__ out, int64_t rows,
+                                                         int64_t H, int R) {
+  const int64_t e = (int64_t)blockIdx.x * 256 + threadIdx.x;      // four consecutive features
+  if (e >= rows * H * R * (TD / 4)) return;
+  const int j = (int)(e % (TD / 4));
+  const int keep = (int)((e / (TD / 4)) % R);
+  const int64_t h = (e / (TD / 4) / R) % H, row = e / (TD / 4) / R / H;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int s2 = 0; s2 < R; ++s2) {
+    const int a = KEYSIDE ? keep : s2, c = KEYSIDE ? s2 : keep;
+    const T* p = in + ((row * H * R * R + (h * R + a) * R + c) * (int64_t)TD + j * 4);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) acc[u] += (float)p[u];
+  }
+  T* o = out + ((row * H + h) * (int64_t)(TD * R) + keep * TD + j * 4);
+#pragma unroll
+  for (int u = 0; u < 4; ++u) o[u] = (T)acc[u];
 }
-// bwd workspace: dstate f32 (BH,N,D,D) | dS_next bf16 (BH,N,D,D)
-size_t tc_bwd_ws_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t C) {
-  const int64_t N = T / C, BH = B * H;
-  return f32b(BH * N * D * D) + b16b(BH * N * D * D);
+static int launch_state_block(cudaStream_t st, const void* in, void* out, int64_t BH, int R, int to_blocked) {
+  const int64_t n = BH * R * R * TD * (TD / 8);
+  ProfScope ps("state_block_kernel", st);
+  state_block_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>((const bf16*)in, (bf16*)out, BH, R, to_blocked);
+  GLA_CHECK_LAUNCH();
+  return GLA_OK;
+}
+template <typename T, int KEYSIDE>
+static int launch_sum_blocks(cudaStream_t st, const T* in, T* out, int64_t rows, int64_t H, int R) {
+  const int64_t n = rows * H * R * (TD / 4);
+  ProfScope ps("sum_blocks_kernel", st);
+  sum_blocks_kernel<T, KEYSIDE><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(in, out, rows, H, R);
+  GLA_CHECK_LAUNCH();
+  return GLA_OK;
+}
+
+// Sizes.  R = D / 128, HV = H R R virtual heads, N = T / 128 chunks whatever chunk size the caller named.
+// saved: S_prev bf16 (B HV, N, 128, 128) | Gc f32 (B HV, N, 128) | P bf16 (B HV, N, 128, 128)
+size_t tc_saved_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t) {
+  const int64_t R = D / TD, N = T / TC, BHV = B * H * R * R;
+  return b16b(BHV * N * TD * TD) + f32b(BHV * N * TD) + b16b(BHV * N * TC * TC);
+}
+// fwd workspace: kv f32 (R = 1 only: the product + scan pair) | Gc f32 | S_prev bf16 (used when nothing is saved)
+//                | R > 1: blocked hidden_init, blocked hidden_final bf16 (B HV, 128, 128) | out per virtual head bf16
+size_t tc_fwd_ws_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t) {
+  const int64_t R = D / TD, N = T / TC, BHV = B * H * R * R;
+  size_t n = (R == 1 ? f32b(BHV * N * TD * TD) : 0) + f32b(BHV * N * TD) + b16b(BHV * N * TD * TD);
+  if (R > 1) n += 2 * b16b(BHV * TD * TD) + b16b(B * T * H * R * R * TD);
+  return n;
+}
+// bwd workspace: dstate f32 (R = 1 only) | dS_next bf16 | R > 1: blocked dhidden_final, dhidden_init |
+//                dq, dk, dv per virtual head bf16 | dg per virtual head f32
+size_t tc_bwd_ws_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t) {
+  const int64_t R = D / TD, N = T / TC, BHV = B * H * R * R;
+  size_t n = (R == 1 ? f32b(BHV * N * TD * TD) : 0) + b16b(BHV * N * TD * TD);
+  if (R > 1) n += 2 * b16b(BHV * TD * TD) + 3 * b16b(B * T * H * R * R * TD) + f32b(B * T * H * R * R * TD);
+  return n;
 }
 
 constexpr size_t FWD_SMEM = 1024 + FwdSmem::END;
@@ -1295,42 +1373,61 @@ constexpr size_t FWD_SMEM = 1024 + FwdSmem::END;
 int tc_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, int64_t C, const void* hidden_init,
                  const float* g, const void* v, const void* k, const void* q, void* hidden_final, void* out,
                  void* saved, void* ws, int state_only, float* G_total, float* S_local) {
-  const int64_t N = T / C, BH = B * H;
+  (void)C;
+  const int R = (int)(D / TD);
+  const int64_t N = T / TC, HV = H * R * R, HK = H * R, BHV = B * HV;
+  if (state_only && R != 1) return GLA_ERR_UNSUPPORTED;
   char* w = (char*)ws;
-  float* kv = (float*)w; w += f32b(BH * N * D * D);
-  float* Gc = (float*)w; w += f32b(BH * N * D);
-  bf16* S_prev = (bf16*)w;
+  float* kv = (float*)w; w += (R == 1 ? f32b(BHV * N * TD * TD) : 0);
+  float* Gc = (float*)w; w += f32b(BHV * N * TD);
+  bf16* S_prev = (bf16*)w; w += b16b(BHV * N * TD * TD);
+  bf16 *hib = nullptr, *hfb = nullptr, *out_v = nullptr;
+  if (R > 1) {
+    hib = (bf16*)w; w += b16b(BHV * TD * TD);
+    hfb = (bf16*)w; w += b16b(BHV * TD * TD);
+    out_v = (bf16*)w;
+  }
   bf16* P = nullptr;
   if (saved) {
     char* s = (char*)saved;
-    S_prev = (bf16*)s; s += b16b(BH * N * D * D);
-    Gc = (float*)s;    s += f32b(BH * N * D);
+    S_prev = (bf16*)s; s += b16b(BHV * N * TD * TD);
+    Gc = (float*)s;    s += f32b(BHV * N * TD);
     P = (bf16*)s;
   }
-  const bool fused_states = !state_only && tc_state_fused_preferred(BH, N);
-  if (fused_states) GLA_TRY(tc_state_fused(st, 0, B, T, H, g, k, v, hidden_init, S_prev, hidden_final, Gc));
+  const void* init_v = hidden_init;
+  void* fin_v = hidden_final;
+  if (R > 1) {
+    GLA_TRY(launch_state_block(st, hidden_init, hib, B * H, R, 1));
+    init_v = hib; fin_v = hfb;
+  }
+  const bool fused_states = !state_only && (R > 1 || tc_state_fused_preferred(BHV, N));
+  if (fused_states) GLA_TRY(tc_state_fused(st, 0, B, T, HV, R, g, k, v, init_v, S_prev, fin_v, Gc));
   else GLA_TRY((launch_tc_kv<0>(st, B, T, H, g, k, v, kv, Gc)));
   if (state_only) {
-    GLA_TRY(launch_state_scan(st, BH, N, D, Gc, kv, 0, nullptr, 0, nullptr, 0, S_local, 0, 0));
+    GLA_TRY(launch_state_scan(st, BHV, N, TD, Gc, kv, 0, nullptr, 0, nullptr, 0, S_local, 0, 0));
     ProfScope ps("tc_gsum_kernel", st);
-    tc_gsum_kernel<<<(unsigned)((BH * D + 255) / 256), 256, 0, st>>>(BH, N, Gc, G_total);
+    tc_gsum_kernel<<<(unsigned)((BHV * TD + 255) / 256), 256, 0, st>>>(BHV, N, Gc, G_total);
     GLA_CHECK_LAUNCH();
     return GLA_OK;
   }
-  if (!fused_states) GLA_TRY(launch_state_scan(st, BH, N, D, Gc, kv, 0, hidden_init, 1, S_prev, 1, hidden_final, 1, 0));
+  if (!fused_states) GLA_TRY(launch_state_scan(st, BHV, N, TD, Gc, kv, 0, hidden_init, 1, S_prev, 1, hidden_final, 1, 0));
   cudaError_t e = cudaFuncSetAttribute(tc_chunk_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FWD_SMEM);
   if (e != cudaSuccess) return record_cuda_error(e);
   FwdMaps maps;
-  GLA_TRY(make_map_bthd(&maps.g, g, 1, B, T, H, 128, 0));
-  GLA_TRY(make_map_bthd(&maps.q, q, 0, B, T, H, 64, 1));
-  GLA_TRY(make_map_bthd(&maps.k, k, 0, B, T, H, 64, 1));
-  GLA_TRY(make_map_bthd(&maps.v, v, 0, B, T, H, 64, 1));
-  GLA_TRY(make_map_rows(&maps.s, S_prev, BH * N * D, 64, 128));
+  GLA_TRY(make_map_bthd(&maps.g, g, 1, B, T, HK, 128, 0));
+  GLA_TRY(make_map_bthd(&maps.q, q, 0, B, T, HK, 64, 1));
+  GLA_TRY(make_map_bthd(&maps.k, k, 0, B, T, HK, 64, 1));
+  GLA_TRY(make_map_bthd(&maps.v, v, 0, B, T, HK, 64, 1));
+  GLA_TRY(make_map_rows(&maps.s, S_prev, BHV * N * TD, 64, 128));
   {
     ProfScope ps("tc_chunk_fwd_kernel", st);
-    tc_chunk_fwd_kernel<<<(unsigned)(BH * N), TTHREADS, FWD_SMEM, st>>>(maps, T, H, N, (bf16*)out, P);
+    tc_chunk_fwd_kernel<<<(unsigned)(BHV * N), TTHREADS, FWD_SMEM, st>>>(maps, T, HV, R, N, R > 1 ? out_v : (bf16*)out, P);
   }
   GLA_CHECK_LAUNCH();
+  if (R > 1) {
+    GLA_TRY((launch_sum_blocks<bf16, 0>(st, out_v, (bf16*)out, B * T, H, R)));
+    GLA_TRY(launch_state_block(st, hfb, hidden_final, B * H, R, 0));
+  }
   return GLA_OK;
 }
 
@@ -1339,33 +1436,58 @@ constexpr size_t BWD_SMEM = 1024 + BwdSmem::END;
 int tc_chunk_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, int64_t C, const float* g,
                  const void* v, const void* k, const void* q, const void* saved, const void* dhidden_final,
                  const void* dout, void* dhidden_init, float* dg, void* dv, void* dk, void* dq, void* ws) {
-  const int64_t N = T / C, BH = B * H;
+  (void)C;
+  const int R = (int)(D / TD);
+  const int64_t N = T / TC, HV = H * R * R, HK = H * R, BHV = B * HV;
   char* w = (char*)ws;
-  float* dstate = (float*)w; w += f32b(BH * N * D * D);
-  bf16* dS_next = (bf16*)w;
+  float* dstate = (float*)w; w += (R == 1 ? f32b(BHV * N * TD * TD) : 0);
+  bf16* dS_next = (bf16*)w; w += b16b(BHV * N * TD * TD);
+  bf16 *dhfb = nullptr, *dhib = nullptr, *dq_v = (bf16*)dq, *dk_v = (bf16*)dk, *dv_v = (bf16*)dv;
+  float* dg_v = dg;
+  if (R > 1) {
+    dhfb = (bf16*)w; w += b16b(BHV * TD * TD);
+    dhib = (bf16*)w; w += b16b(BHV * TD * TD);
+    dq_v = (bf16*)w; w += b16b(B * T * HV * TD);
+    dk_v = (bf16*)w; w += b16b(B * T * HV * TD);
+    dv_v = (bf16*)w; w += b16b(B * T * HV * TD);
+    dg_v = (float*)w;
+  }
   const char* s = (const char*)saved;
-  const bf16* S_prev = (const bf16*)s; s += b16b(BH * N * D * D);
-  const float* Gc = (const float*)s;   s += f32b(BH * N * D);
+  const bf16* S_prev = (const bf16*)s; s += b16b(BHV * N * TD * TD);
+  const float* Gc = (const float*)s;   s += f32b(BHV * N * TD);
   const bf16* P = (const bf16*)s;
-  if (tc_state_fused_preferred(BH, N)) {
-    GLA_TRY(tc_state_fused(st, 1, B, T, H, g, q, dout, dhidden_final, dS_next, dhidden_init, nullptr));
+  const void* dfin_v = dhidden_final;
+  void* dinit_v = dhidden_init;
+  if (R > 1) {
+    GLA_TRY(launch_state_block(st, dhidden_final, dhfb, B * H, R, 1));
+    dfin_v = dhfb; dinit_v = dhib;
+  }
+  if (R > 1 || tc_state_fused_preferred(BHV, N)) {
+    GLA_TRY(tc_state_fused(st, 1, B, T, HV, R, g, q, dout, dfin_v, dS_next, dinit_v, nullptr));
   } else {
     GLA_TRY((launch_tc_kv<1>(st, B, T, H, g, q, dout, dstate, nullptr)));
-    GLA_TRY(launch_state_scan(st, BH, N, D, Gc, dstate, 0, dhidden_final, 1, dS_next, 1, dhidden_init, 1, 1));
+    GLA_TRY(launch_state_scan(st, BHV, N, TD, Gc, dstate, 0, dhidden_final, 1, dS_next, 1, dhidden_init, 1, 1));
   }
   cudaError_t e = cudaFuncSetAttribute(tc_chunk_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)BWD_SMEM);
   if (e != cudaSuccess) return record_cuda_error(e);
   BwdMaps bmaps;
-  GLA_TRY(make_map_bthd(&bmaps.g, g, 1, B, T, H, 128, 0, 64));
-  GLA_TRY(make_map_bthd(&bmaps.q, q, 0, B, T, H, 128, 0, 64));
-  GLA_TRY(make_map_bthd(&bmaps.k, k, 0, B, T, H, 128, 0, 64));
+  GLA_TRY(make_map_bthd(&bmaps.g, g, 1, B, T, HK, 128, 0, 64));
+  GLA_TRY(make_map_bthd(&bmaps.q, q, 0, B, T, HK, 128, 0, 64));
+  GLA_TRY(make_map_bthd(&bmaps.k, k, 0, B, T, HK, 128, 0, 64));
   {
     ProfScope ps("tc_chunk_bwd_kernel", st);
-    tc_chunk_bwd_kernel<<<(unsigned)(BH * N), TTHREADS, BWD_SMEM, st>>>(
-        bmaps, T, H, N, prefetch_distance(1), g, (const bf16*)v, (const bf16*)k, (const bf16*)q, (const bf16*)dout, S_prev, dS_next, P, (bf16*)dq,
-        (bf16*)dk, (bf16*)dv, dg);
+    tc_chunk_bwd_kernel<<<(unsigned)(BHV * N), TTHREADS, BWD_SMEM, st>>>(
+        bmaps, T, HV, R, N, prefetch_distance(1), g, (const bf16*)v, (const bf16*)k, (const bf16*)q, (const bf16*)dout, S_prev, dS_next, P,
+        dq_v, dk_v, dv_v, dg_v);
   }
   GLA_CHECK_LAUNCH();
+  if (R > 1) {
+    GLA_TRY((launch_sum_blocks<bf16, 1>(st, dq_v, (bf16*)dq, B * T, H, R)));
+    GLA_TRY((launch_sum_blocks<bf16, 1>(st, dk_v, (bf16*)dk, B * T, H, R)));
+    GLA_TRY((launch_sum_blocks<float, 1>(st, dg_v, dg, B * T, H, R)));
+    GLA_TRY((launch_sum_blocks<bf16, 0>(st, dv_v, (bf16*)dv, B * T, H, R)));
+    GLA_TRY(launch_state_block(st, dhib, dhidden_init, B * H, R, 0));
+  }
   return GLA_OK;
 }
 

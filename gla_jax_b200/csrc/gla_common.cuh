@@ -88,6 +88,7 @@ int simt_chunk_dstate_only(cudaStream_t st, int64_t B, int64_t T, int64_t H, int
 
 // tcgen05 tensor-core chunk path (bf16, D = C = 128).
 bool tc_supported(int64_t D, int64_t C, int dtype);
+bool tc_supported_local_state(int64_t D, int64_t C, int dtype);
 bool tc_auto_default();
 unsigned int tc_read_wait_timeouts();
 void tc_read_trace(long long* out64);
@@ -100,7 +101,7 @@ int tc_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
                  float* G_total, float* S_local);
 // One-pass chunk states (product and recurrence fused); mode 0 forward states, mode 1 gradient states.
 bool tc_state_fused_preferred(int64_t BH, int64_t N);
-int tc_state_fused(cudaStream_t st, int mode, int64_t B, int64_t T, int64_t H, const float* g, const void* x,
+int tc_state_fused(cudaStream_t st, int mode, int64_t B, int64_t T, int64_t H, int R, const float* g, const void* x,
                    const void* y, const void* init, void* states, void* fin, float* Gc);
 unsigned int tc_state_read_wait_timeouts();
 int tc_chunk_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, int64_t C,

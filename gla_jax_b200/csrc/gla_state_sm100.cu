@@ -76,7 +76,7 @@ struct StMaps { CUtensorMap g, x, y; };
 
 template <int MODE>
 __global__ void __launch_bounds__(STHREADS, 1)
-tc_state_kernel(const __grid_constant__ StMaps maps, int64_t T, int64_t H, int N, const bf16* __restrict__ init,
+tc_state_kernel(const __grid_constant__ StMaps maps, int64_t T, int64_t H, int R, int N, const bf16* __restrict__ init,
                 bf16* __restrict__ states, bf16* __restrict__ fin, float* __restrict__ Gc) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -92,7 +92,11 @@ tc_state_kernel(const __grid_constant__ StMaps maps, int64_t T, int64_t H, int N
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int slice = blockIdx.x & 3;
-  const int64_t bh = blockIdx.x >> 2, b = bh / H, h = bh % H;
+  // H counts VIRTUAL heads: a head of size 128 R is R x R independent (key block a, value block c) problems of size
+  // 128, virtual head hh = (h R + a) R + c; in the (B, T, H_real R, 128) view of the arrays its key-side tensors are
+  // head h R + a and its value-side tensors head h R + c.  R = 1: all three coincide.
+  const int64_t bh = blockIdx.x >> 2, b = bh / H, hh = bh % H;
+  const int64_t hk = (hh / (R * R)) * R + (hh % (R * R)) / R, hv = (hh / (R * R)) * R + hh % R;
   auto chunk_of = [&](int i) { return MODE == 0 ? i : N - 1 - i; };
 
   if (tid == NBUILD + NUPD) {
@@ -117,20 +121,20 @@ tc_state_kernel(const __grid_constant__ StMaps maps, int64_t T, int64_t H, int N
 
   if (warp == (NBUILD + NUPD) / 32 + 1) {
     // ================= TMA producer warp =================
-    const int z0 = (int)(b * T), y = (int)h;
+    const int z0 = (int)(b * T), yk = (int)hk, yv = (int)hv;
     const int zstep = MODE == 0 ? SC : -SC;
     const uint32_t sm_base = smem_u32(sm), fully0 = smem_u32(fully), fullgx0 = smem_u32(fullgx);
     auto load_y = [&](int z, int s) {
       const uint32_t dst = sm_base + StSmem::Y + s * 32768, fb = fully0 + 8 * s;
       mbar_arrive_expect_tx(fb, 32768);
-      tma_load_3d(dst, &maps.y, 0, y, z, fb);
-      tma_load_3d(dst + 16384, &maps.y, 64, y, z, fb);
+      tma_load_3d(dst, &maps.y, 0, yv, z, fb);
+      tma_load_3d(dst + 16384, &maps.y, 64, yv, z, fb);
     };
     auto load_gx = [&](int z, int s) {
       const uint32_t dst = sm_base + StSmem::GX + s * StSmem::GXS, fb = fullgx0 + 8 * s;
       mbar_arrive_expect_tx(fb, StSmem::GXS);
-      tma_load_3d(dst, &maps.g, SL * slice, y, z, fb);
-      tma_load_3d(dst + 16384, &maps.x, SL * slice, y, z, fb);
+      tma_load_3d(dst, &maps.g, SL * slice, yk, z, fb);
+      tma_load_3d(dst + 16384, &maps.x, SL * slice, yk, z, fb);
     };
     const int zfirst = z0 + chunk_of(0) * SC;
     if (lane == 0) {
@@ -316,21 +320,24 @@ bool tc_state_fused_preferred(int64_t BH, int64_t N) {
   return t_fused < t_pair;
 }
 
+// H counts virtual heads of size 128 (real heads x R x R for head size 128 R; init/states/fin are laid out per
+// virtual head as 128 x 128 tiles).
 // mode 0: states[n] = state before chunk n (from init), fin = state after the last chunk, Gc = chunk gate sums.
 // mode 1: states[n] = gradient state after chunk n (from init = dhidden_final), fin = dhidden_init.
-int tc_state_fused(cudaStream_t st, int mode, int64_t B, int64_t T, int64_t H, const float* g, const void* x,
+int tc_state_fused(cudaStream_t st, int mode, int64_t B, int64_t T, int64_t H, int R, const float* g, const void* x,
                    const void* y, const void* init, void* states, void* fin, float* Gc) {
-  const int64_t N = T / SC, BH = B * H;
+  const int64_t N = T / SC, BH = B * H;          // H: virtual heads (real heads x R x R)
+  const int64_t HK = H / R;                      // heads of the (B, T, HK, 128) view of the arrays
   StMaps maps;
-  GLA_TRY(make_map_bthd(&maps.g, g, 1, B, T, H, SL, 0));
-  GLA_TRY(make_map_bthd(&maps.x, x, 0, B, T, H, SL, 0));
-  GLA_TRY(make_map_bthd(&maps.y, y, 0, B, T, H, 64, 1));
+  GLA_TRY(make_map_bthd(&maps.g, g, 1, B, T, HK, SL, 0));
+  GLA_TRY(make_map_bthd(&maps.x, x, 0, B, T, HK, SL, 0));
+  GLA_TRY(make_map_bthd(&maps.y, y, 0, B, T, HK, 64, 1));
   auto kern = mode == 0 ? tc_state_kernel<0> : tc_state_kernel<1>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ST_SMEM);
   if (e != cudaSuccess) return record_cuda_error(e);
   {
     ProfScope ps(mode == 0 ? "tc_state_kernel" : "tc_dstate_scan_kernel", st);
-    kern<<<(unsigned)(BH * 4), STHREADS, ST_SMEM, st>>>(maps, T, H, (int)N, (const bf16*)init, (bf16*)states, (bf16*)fin, Gc);
+    kern<<<(unsigned)(BH * 4), STHREADS, ST_SMEM, st>>>(maps, T, H, R, (int)N, (const bf16*)init, (bf16*)states, (bf16*)fin, Gc);
   }
   GLA_CHECK_LAUNCH();
   return GLA_OK;

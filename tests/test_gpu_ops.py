@@ -64,6 +64,7 @@ CHUNK_CASES = [
     (1, 128, 3, 16, 16, torch.float32, 5.0, True),       # smallest sizes, zero initial state
     (1, 256, 2, 128, 128, torch.float32, 5.0, False),
     (1, 512, 1, 256, 256, torch.float32, 0.0, False),    # config 5 head size, sharp gates
+    (1, 512, 1, 256, 256, torch.bfloat16, 0.0, False),   # ... in bf16 on the float32 kernels
     (2, 256, 2, 64, 64, torch.bfloat16, 5.0, False),
     (1, 512, 2, 128, 128, torch.bfloat16, 5.0, False),   # config 2 tile shape
     (1, 256, 2, 128, 128, torch.bfloat16, 0.0, False),   # config 2 tile shape, sharp gates
@@ -87,6 +88,28 @@ TC_CASES = [
     (1, 256, 2, -3.0, False),      # very sharp gates: every level's weights underflow gracefully
     (2, 384, 2, 5.0, True),        # zero initial state, three chunks
 ]
+
+
+TC_WIDE_CASES = [
+    # B, T, H, D, C, shift    bf16 shapes the tensor-core kernels serve beyond D = chunk = 128:
+    (1, 512, 2, 256, 256, 5.0),     # BASELINE config 5's head and chunk size (a head of 256 = 2 x 2 blocks of 128)
+    (1, 512, 1, 256, 256, 0.0),     # ... with its sharp gates
+    (2, 256, 2, 256, 128, 0.0),
+    (1, 512, 2, 128, 256, 5.0),     # a larger chunk size at head size 128 (the result does not depend on it)
+]
+
+
+@pytest.mark.parametrize("B,T,H,D,C,shift", TC_WIDE_CASES)
+def test_chunk_gla_tcgen05_wide_heads_vs_oracle(cuda_device, B, T, H, D, C, shift):
+    from gla_jax_b200 import chunk_gla, _lib
+    case = _case(B, T, H, D, torch.bfloat16, 23, shift)
+    ref = _oracle(*case)
+    got = _run_gpu(chunk_gla, cuda_device, *case, chunk_size=C, impl="tcgen05")
+    assert _lib.load().gla_device_wait_timeouts() == 0
+    _compare(ref, got, torch.bfloat16, f"chunk_gla tcgen05 {B,T,H,D,C,shift}")
+    # and impl='auto' takes the same path for these shapes
+    auto = _run_gpu(chunk_gla, cuda_device, *case, chunk_size=C)
+    assert torch.equal(auto[1], got[1])
 
 
 @pytest.mark.parametrize("B,T,H,shift,zero_init", TC_CASES)
