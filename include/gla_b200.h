@@ -59,7 +59,7 @@ typedef enum gla_dtype {
 } gla_dtype;
 
 /* Which implementation gla_chunk_fwd/bwd use. AUTO picks the tcgen05 tensor-core kernels
- * when the shape has one (bf16, D = chunk = 128) and the fp32 CUDA-core kernels otherwise. */
+ * when the shape has one (bf16, D = 128 or 256, chunk a multiple of 128) and the fp32 CUDA-core kernels otherwise. */
 typedef enum gla_chunk_impl {
   GLA_IMPL_AUTO = 0,
   GLA_IMPL_FP32_SIMT = 1,     /* fp32 math on CUDA cores: every dtype, D <= 256, chunk 16..256 */

@@ -81,7 +81,7 @@ def test_chunk_gla_fp32_kernels_vs_oracle(cuda_device, B, T, H, D, C, dtype, shi
 
 
 TC_CASES = [
-    # B, T, H, shift, zero_init   (bf16, D = chunk = 128: the shapes the tcgen05 kernels serve)
+    # B, T, H, shift, zero_init   (bf16, D = chunk = 128: the native shape of the tcgen05 kernels)
     (1, 128, 1, 5.0, False),       # one chunk
     (1, 512, 2, 5.0, False),
     (2, 512, 3, 0.0, False),       # sharp gates (BASELINE config 5's gate distribution)
