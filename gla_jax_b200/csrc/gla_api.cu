@@ -255,8 +255,16 @@ int gla_chunk_local_dstate(void* stream, int64_t B, int64_t T, int64_t H, int64_
                            void* workspace, size_t workspace_bytes) {
   if (!log_fgate || !query || !dout || !dS_local) return GLA_ERR_NULL_POINTER;
   GLA_TRY(check_chunk_dims(B, T, H, D, chunk, dtype));
-  (void)impl;   // the fp32 kernels serve every implementation here: two small products and a scan
-  if (!workspace || workspace_bytes < simt_bwd_ws_bytes(B, T, H, D, chunk)) return GLA_ERR_WORKSPACE;
+  int r = resolve_impl(impl, D, chunk, dtype);
+  if (r < 0) return -r;
+  if (r == GLA_IMPL_TCGEN05 && !tc_supported_local_state(D, chunk, dtype)) {
+    if (impl == GLA_IMPL_TCGEN05) return GLA_ERR_UNSUPPORTED;
+    r = GLA_IMPL_FP32_SIMT;
+  }
+  const size_t need = r == GLA_IMPL_TCGEN05 ? tc_bwd_ws_bytes(B, T, H, D, chunk) : simt_bwd_ws_bytes(B, T, H, D, chunk);
+  if (!workspace || workspace_bytes < need) return GLA_ERR_WORKSPACE;
+  if (r == GLA_IMPL_TCGEN05)
+    return tc_local_dstate((cudaStream_t)stream, B, T, H, log_fgate, query, dout, dS_local, workspace);
   return simt_chunk_dstate_only((cudaStream_t)stream, B, T, H, D, chunk, dtype == GLA_BF16, log_fgate, query, dout,
                                 dS_local, workspace);
 }

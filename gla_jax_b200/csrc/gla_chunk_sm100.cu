@@ -146,7 +146,7 @@ tc_kv_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g, const
       cross.x *= t.x; cross.y *= t.y;
     }
   }
-  if (MODE == 0 && Gc != nullptr && rg == 0) {
+  if (Gc != nullptr && rg == 0) {
     float2 s = make_float2(0.f, 0.f);
 #pragma unroll
     for (int r2 = 0; r2 < 8; ++r2) {
@@ -1432,6 +1432,19 @@ int tc_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
 }
 
 constexpr size_t BWD_SMEM = 1024 + BwdSmem::END;
+
+// Gradient reaching a slice's initial state when the gradient of its final state is zero (sequence parallelism):
+// q_hat^T dO per chunk on the tensor cores, then the reverse scan keeping only its last value.
+// ws: the backward workspace (dstate f32 | Gc in the region of dS_next).
+int tc_local_dstate(cudaStream_t st, int64_t B, int64_t T, int64_t H, const float* g, const void* q, const void* dout,
+                    float* dS_local, void* ws) {
+  const int64_t N = T / TC, BH = B * H;
+  char* w = (char*)ws;
+  float* dstate = (float*)w; w += f32b(BH * N * TD * TD);
+  float* Gc = (float*)w;
+  GLA_TRY((launch_tc_kv<1>(st, B, T, H, g, q, dout, dstate, Gc)));
+  return launch_state_scan(st, BH, N, TD, Gc, dstate, 0, nullptr, 0, nullptr, 0, dS_local, 0, 1);
+}
 
 int tc_chunk_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, int64_t C, const float* g,
                  const void* v, const void* k, const void* q, const void* saved, const void* dhidden_final,

@@ -89,6 +89,8 @@ int simt_chunk_dstate_only(cudaStream_t st, int64_t B, int64_t T, int64_t H, int
 // tcgen05 tensor-core chunk path (bf16, D = 128 or 256, chunk a multiple of 128).
 bool tc_supported(int64_t D, int64_t C, int dtype);
 bool tc_supported_local_state(int64_t D, int64_t C, int dtype);
+int tc_local_dstate(cudaStream_t st, int64_t B, int64_t T, int64_t H, const float* g, const void* q, const void* dout,
+                    float* dS_local, void* ws);
 bool tc_auto_default();
 unsigned int tc_read_wait_timeouts();
 void tc_read_trace(long long* out64);

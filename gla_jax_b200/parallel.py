@@ -65,7 +65,8 @@ class CudaOps:
     def local_state(self, g, v, k, chunk):
         B, T, H, D = v.shape
         dt = self._DT[v.dtype]
-        n = self.lib.gla_chunk_fwd_workspace_bytes(B, T, H, D, chunk, dt, self.impl)
+        n = max(self.lib.gla_chunk_fwd_workspace_bytes(B, T, H, D, chunk, dt, self.impl),
+                self.lib.gla_chunk_fwd_workspace_bytes(B, T, H, D, chunk, dt, _lib.IMPL_FP32_SIMT))
         ws = torch.empty(n, dtype=torch.uint8, device=v.device)
         G = torch.empty(B, H, D, dtype=torch.float32, device=v.device)
         S = torch.empty(B, H, D, D, dtype=torch.float32, device=v.device)
@@ -77,7 +78,8 @@ class CudaOps:
     def local_dstate(self, g, q, dout, chunk):
         B, T, H, D = q.shape
         dt = self._DT[q.dtype]
-        n = self.lib.gla_chunk_bwd_workspace_bytes(B, T, H, D, chunk, dt, _lib.IMPL_FP32_SIMT)
+        n = max(self.lib.gla_chunk_bwd_workspace_bytes(B, T, H, D, chunk, dt, self.impl),
+                self.lib.gla_chunk_bwd_workspace_bytes(B, T, H, D, chunk, dt, _lib.IMPL_FP32_SIMT))
         ws = torch.empty(n, dtype=torch.uint8, device=q.device)
         A = torch.empty(B, H, D, D, dtype=torch.float32, device=q.device)
         st = self.lib.gla_chunk_local_dstate(self._stream(q.device), B, T, H, D, chunk, dt, self.impl, g.data_ptr(),

@@ -257,7 +257,7 @@ GLA_API int gla_chunk_local_state(void* stream, int64_t B, int64_t T, int64_t H,
  * when the gradient of its final state is ZERO: sum_n exp(sum_{m<n} G_m) * (q_hat_n^T dO_n).
  * The slice's dhidden_init for a non-zero dhidden_final is A + exp(G_total) * dhidden_final
  * (the scan is linear), which is what gla_sp_combine evaluates across ranks with
- * reverse != 0.  Workspace: gla_chunk_bwd_workspace_bytes. */
+ * reverse != 0.  Workspace: gla_chunk_bwd_workspace_bytes for the same impl. */
 GLA_API int gla_chunk_local_dstate(void* stream, int64_t B, int64_t T, int64_t H, int64_t D, int64_t chunk,
                            int dtype, int impl,
                            const float* log_fgate, const void* query, const void* dout,
