@@ -54,6 +54,92 @@ def bytes_per_token_head(D):
     return 34 * D
 
 
+def bench_decode(args, lib, dev, rank, world, local_rank, W, K):
+    """Single-token step: B requests x H heads advance one token per step; the (B,H,D,D) float32 states live on the
+    device.  tokens/s = requests advanced per second; the step streams the state once in and once out."""
+    import torch
+    import torch.distributed as dist
+    from gla_jax_b200 import decode_step, _lib
+    B, H, D = 128, 16, 128
+    gen = torch.Generator(device=dev).manual_seed(1000 * rank + 5)
+    state = torch.randn(B, H, D, D, device=dev, generator=gen)                 # 134 MB > L2
+    mk = lambda: torch.randn(B, H, D, device=dev, generator=gen).to(torch.bfloat16)
+    g = torch.nn.functional.logsigmoid(5 + torch.randn(B, H, D, device=dev, generator=gen))
+    v, k, q = mk(), mk(), mk()
+    out = torch.empty(B, H, D, device=dev, dtype=torch.bfloat16)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+
+    def step():
+        st = lib.gla_decode_step(stream, B, H, D, _lib.GLA_BF16, state.data_ptr(), g.data_ptr(), v.data_ptr(),
+                                 k.data_ptr(), q.data_ptr(), out.data_ptr(), _lib.GLA_BF16)
+        _lib.check(st, "gla_decode_step")
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(W):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+    launches0 = lib.gla_launch_count()
+    for i in range(K):
+        evs[i][0].record()
+        step()
+        evs[i][1].record()
+    barrier()
+    launches = lib.gla_launch_count() - launches0
+    ms_total = sum(a.elapsed_time(b) for a, b in evs)
+    # end to end: this step's g, v, k, q from pinned host memory, its out back to the host
+    host = [x.cpu().pin_memory() for x in (g, v, k, q)]
+    hout = torch.empty(B, H, D, dtype=torch.bfloat16).pin_memory()
+    h2d = sum(x.numel() * x.element_size() for x in host)
+
+    def e2e_step():
+        gg, vv, kk, qq = (x.to(dev, non_blocking=True) for x in host)
+        o = decode_step(state, gg, vv, kk, qq)
+        hout.copy_(o, non_blocking=True)
+        torch.cuda.current_stream(dev).synchronize()
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e_evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+    for i in range(K):
+        e_evs[i][0].record()
+        e2e_step()
+        e_evs[i][1].record()
+    barrier()
+    e2e_ms = sum(a.elapsed_time(b) for a, b in e_evs)
+    sampler.stop_flag = True
+    sampler.join(timeout=1.0)
+    t = torch.tensor([ms_total, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total, e2e_ms = float(t[0]), float(t[1])
+    if rank == 0:
+        peaks = load_peaks()
+        per = ms_total / K * 1e-3
+        alg = 2 * 4 * D * D * B * H + B * H * D * (4 + 2 + 2 + 2 + 2)
+        ach = alg / per / 1e9
+        print(json.dumps({
+            "metric": "decode step tokens/sec", "value": B * world * K / (ms_total * 1e-3), "unit": "tokens/s",
+            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_total / K, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"single-token step: {B} requests x {H} heads x D={D}, float32 states (134 MB per GPU, "
+                                   "larger than L2), bf16 q/k/v/out, f32 log_fgate", "parallelism": f"request-shard x{world}"},
+            "e2e": {"value": B * world * K / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": B * H * D * 2, "ms_per_step": e2e_ms / K},
+            "gpu_launches": launches, "clocks": sampler.summary(),
+            "roofline": {"bound": "hbm", "kernel": "decode_step_kernel", "achieved": ach, "peak": peaks["hbm"],
+                         "unit": "GB/s", "frac": ach / peaks["hbm"], "traffic": None, "peak_source": peaks["source"],
+                         "algorithmic": "state read + write 2*4*D*D B per (request, head) + q,k,v,out bf16 + g f32"},
+        }))
+
+
 def load_peaks():
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
@@ -168,8 +254,9 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (for profiler runs)")
     ap.add_argument("--no-graph", action="store_true", help="time plain launches instead of CUDA-graph replays")
-    ap.add_argument("--op", default="chunk_gla", choices=["chunk_gla", "recurrent_gla"],
-                    help="chunk_gla is the headline metric; recurrent_gla times the exact recurrence on the same shape")
+    ap.add_argument("--op", default="chunk_gla", choices=["chunk_gla", "recurrent_gla", "decode"],
+                    help="chunk_gla is the headline metric; recurrent_gla times the exact recurrence on the same shape; "
+                         "decode times the single-token step with a persistent state (128 requests x 16 heads x 128)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -193,6 +280,11 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     W = max(args.warmup, 3)
     K = args.steps
+    if args.op == "decode":
+        bench_decode(args, lib, dev, rank, world, local_rank, W, K)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     B, T, H, D, C = (CFG[x] for x in "BTHDC")
     impl = _lib.IMPL_BY_NAME[args.chunk_impl]
     dt = _lib.GLA_BF16

@@ -144,6 +144,16 @@ int gla_recurrent_fwd(void* stream, int64_t B, int64_t T, int64_t H, int64_t D, 
                        query, hidden_final, out, out_dtype == GLA_BF16, reverse);
 }
 
+int gla_decode_step(void* stream, int64_t B, int64_t H, int64_t D, int dtype, float* state, const float* log_fgate,
+                    const void* value, const void* key, const void* query, void* out, int out_dtype) {
+  if (!state || !log_fgate || !value || !key || !query || !out) return GLA_ERR_NULL_POINTER;
+  if (B <= 0 || H <= 0 || D <= 0) return GLA_ERR_BAD_DIMS;
+  GLA_TRY(check_dtype(dtype));
+  GLA_TRY(check_dtype(out_dtype));
+  return decode_step((cudaStream_t)stream, B, H, D, dtype == GLA_BF16, state, log_fgate, value, key, query, out,
+                     out_dtype == GLA_BF16);
+}
+
 size_t gla_recurrent_bwd_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int dtype) {
   (void)dtype;
   if (B <= 0 || T <= 0 || H <= 0 || D <= 0) return 0;

@@ -70,6 +70,10 @@ int launch_state_scan(cudaStream_t st, int64_t BH, int64_t N, int64_t D, const f
                       int x_bf16, const void* init, int init_bf16, void* before, int before_bf16,
                       void* final_state, int final_bf16, int reverse);
 
+// Single-token step with a persistent float32 state.
+int decode_step(cudaStream_t st, int64_t B, int64_t H, int64_t D, int bf, float* state, const float* g, const void* v,
+                const void* k, const void* q, void* out, int out_bf);
+
 // fp32 CUDA-core chunk path.
 size_t simt_saved_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t C);
 size_t simt_fwd_ws_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t C);

@@ -208,6 +208,32 @@ def recurrent_gla_naive(hidden, log_fgate, value, key, query, reverse: bool = Fa
     return (hf, out) if batched else (hf[0], out[0])
 
 
+def decode_step(state, log_fgate, value, key, query, out_dtype=None):
+    """One token of the recurrence (reference: the loop body of gla.py:26-47) for a batch of requests.
+
+    ``state`` (B, H, D, D) float32 CUDA tensor is updated IN PLACE
+    (``S <- exp(log_fgate)[..., None] * S + key[..., None] * value[..., None, :]``); returns
+    ``out = query @ S`` of shape (B, H, D) in ``out_dtype`` (default: value's dtype).  ``log_fgate``,
+    ``value``, ``key``, ``query`` are (B, H, D).  T calls equal one ``recurrent_gla`` over T tokens
+    (``hidden_init`` -> ``hidden_final`` chaining, gla.py:720-723).  Not differentiable (serving path)."""
+    lib = _lib.load()
+    if state.dtype != torch.float32 or not state.is_contiguous() or state.dim() != 4:
+        raise TypeError("decode_step: state must be a contiguous float32 (B, H, D, D) tensor")
+    B, H, D, D2 = state.shape
+    if D != D2 or tuple(value.shape) != (B, H, D) or key.shape != value.shape or query.shape != value.shape \
+            or log_fgate.shape != value.shape:
+        raise ValueError("decode_step: expected state (B, H, D, D) and log_fgate, value, key, query (B, H, D)")
+    if key.dtype != value.dtype or query.dtype != value.dtype:
+        raise TypeError("decode_step: value, key, query must share a dtype")
+    g32 = log_fgate.float().contiguous()
+    v, k, q = value.contiguous(), key.contiguous(), query.contiguous()
+    out = torch.empty(B, H, D, dtype=out_dtype or v.dtype, device=v.device)
+    st = lib.gla_decode_step(_stream(v.device), B, H, D, _DT[v.dtype], _ptr(state), _ptr(g32), _ptr(v), _ptr(k), _ptr(q),
+                             _ptr(out), _DT[out.dtype])
+    _lib.check(st, "gla_decode_step")
+    return out
+
+
 def auto_block_size(value_dim: int, key_dim: int, num_heads: int, max_block_size: int):
     """Reference helper (gla.py:390-403) kept for callers that import it: the Triton block
     sizes it would have chosen.  The CUDA kernels do not use them."""

@@ -100,6 +100,19 @@ GLA_API void gla_profile_enable(int on);
 GLA_API size_t gla_profile_report(char* buf, size_t capacity);
 
 /* ------------------------------------------------------------------------------------
+ * decode step — one token of gla.py:26-47 (recurrent_gla_naive's loop body) for a batch of
+ * requests, with the state kept on the device between calls.  No counterpart in the reference,
+ * whose callers would run recurrent_gla with T = 1 and carry hidden_final to the next call
+ * (gla.py:405-416); T calls of this step equal one recurrent_gla call over T tokens.
+ *   state (B, H, D, D) float32, updated IN PLACE:  S <- exp(log_fgate) (.) S + key (x) value
+ *   out   (B, H, D) in out_dtype:                  out = query S
+ * log_fgate (B, H, D) float32; value, key, query (B, H, D) in dtype.  D in {32, 64, 128, 256}.
+ * ---------------------------------------------------------------------------------- */
+GLA_API int gla_decode_step(void* stream, int64_t B, int64_t H, int64_t D, int dtype,
+                    float* state, const float* log_fgate, const void* value, const void* key,
+                    const void* query, void* out, int out_dtype);
+
+/* ------------------------------------------------------------------------------------
  * cumsum — replaces ops.py:234 cumsum_recursive / ops.py:166 cumsum_pallas /
  * ops.py:152 cumsum_kernel.
  * Inclusive cumulative sum along the middle axis of src (N, T, D); `init` (N, D), if not

@@ -299,3 +299,47 @@ def test_chunk_equals_recurrent_on_gpu_full_size_slice(cuda_device):
     hf1, o1 = chunk_gla(h, g, v, k, q, chunk_size=128, impl="fp32")
     hf2, o2 = recurrent_gla(h, g, v, k, q)
     assert O.rel_l2(hf2.cpu(), hf1.cpu()) < 1e-4 and O.rel_l2(o2.cpu(), o1.cpu()) < 1e-4
+
+
+@pytest.mark.parametrize("B,H,D,dtype,steps,shift", [
+    (2, 3, 64, torch.float32, 40, 5.0),
+    (1, 2, 128, torch.float32, 24, 0.0),
+    (3, 2, 128, torch.bfloat16, 32, 5.0),
+    (1, 1, 256, torch.bfloat16, 16, 0.0),
+    (2, 2, 32, torch.float32, 8, 5.0),
+])
+def test_decode_step_chain_equals_recurrence(cuda_device, B, H, D, dtype, steps, shift):
+    """T calls of the single-token step from hidden_init equal the oracle's recurrence over T tokens
+    (out per token and the final state), and one recurrent_gla call on the GPU."""
+    from gla_jax_b200 import decode_step, recurrent_gla
+    h, g, v, k, q = O.make_inputs(B, steps, H, D, dtype, seed=41, shift=shift)
+    ref = [O.recurrent_gla_naive(h[b].double(), g[b].double(), v[b].double(), k[b].double(), q[b].double())
+           for b in range(B)]
+    ref_hf = torch.stack([r[0] for r in ref]).float()
+    ref_out = torch.stack([r[1] for r in ref]).float()
+    gd, vd, kd, qd = (x.to(cuda_device) for x in (g, v, k, q))
+    state = h.to(cuda_device).float().contiguous()
+    outs = []
+    for t in range(steps):
+        outs.append(decode_step(state, gd[:, t], vd[:, t], kd[:, t], qd[:, t]))
+    out = torch.stack(outs, dim=1)
+    torch.cuda.synchronize()
+    tol = 1e-4 if dtype == torch.float32 else 1e-2
+    assert O.rel_l2(ref_out, out.float().cpu()) < tol
+    assert O.rel_l2(ref_hf, state.cpu()) < (1e-4 if dtype == torch.float32 else 4e-3)   # state stays float32
+    hf2, out2 = recurrent_gla(h.to(cuda_device), gd, vd, kd, qd)
+    assert O.rel_l2(out2.float().cpu(), out.float().cpu()) < tol
+
+
+def test_decode_step_rejects_bad_arguments(cuda_device):
+    from gla_jax_b200 import decode_step
+    st = torch.zeros(1, 2, 64, 64, device=cuda_device)
+    x = torch.zeros(1, 2, 64, device=cuda_device)
+    with pytest.raises(TypeError):
+        decode_step(st.half(), x, x, x, x)
+    with pytest.raises(ValueError):
+        decode_step(st, x, x[:, :1], x, x)
+    st48 = torch.zeros(1, 1, 48, 48, device=cuda_device)
+    x48 = torch.zeros(1, 1, 48, device=cuda_device)
+    with pytest.raises(Exception):
+        decode_step(st48, x48, x48, x48, x48)       # head size without a kernel: GLA_ERR_UNSUPPORTED
