@@ -45,6 +45,12 @@ SIGNATURES = {
     "gla_chunk_bwd_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_int]),
     "gla_chunk_fwd": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p,
                               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t]),
+    "gla_chunk_fwd_packed": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_int64, c_void_p, c_void_p,
+                                     c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                     c_size_t]),
+    "gla_chunk_bwd_packed": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_int64, c_void_p, c_void_p,
+                                     c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                     c_void_p, c_void_p, c_void_p, c_void_p, c_size_t]),
     "gla_chunk_fwd_static_max_bytes": (c_size_t, []),
     "gla_chunk_fwd_static": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_int, c_void_p,
                                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),

@@ -240,6 +240,39 @@ int gla_chunk_bwd(void* stream, int64_t B, int64_t T, int64_t H, int64_t D, int6
                         dhidden_final, dout, dhidden_init, dlog_fgate, dvalue, dkey, dquery, workspace);
 }
 
+int gla_chunk_fwd_packed(void* stream, int64_t T, int64_t H, int64_t D, int64_t chunk, int dtype, int64_t nseq,
+                         const int32_t* cu_seqlens, const void* hidden_init, const float* log_fgate, const void* value,
+                         const void* key, const void* query, void* hidden_final, void* out, void* saved,
+                         void* workspace, size_t workspace_bytes) {
+  if (!cu_seqlens || !hidden_init || !log_fgate || !value || !key || !query || !hidden_final || !out)
+    return GLA_ERR_NULL_POINTER;
+  if (nseq <= 0) return GLA_ERR_BAD_DIMS;
+  GLA_TRY(check_chunk_dims(1, T, H, D, chunk, dtype));
+  if (!tc_supported_local_state(D, 128, dtype) || chunk % 128 != 0) return GLA_ERR_UNSUPPORTED;
+  if (!workspace || workspace_bytes < tc_fwd_ws_bytes(1, T, H, D, chunk)) return GLA_ERR_WORKSPACE;
+  const void* ptrs[] = {hidden_init, log_fgate, value, key, query, hidden_final, out, saved, workspace};
+  for (const void* p : ptrs)
+    if (p && !aligned16(p)) return GLA_ERR_ALIGNMENT;
+  return tc_chunk_fwd((cudaStream_t)stream, 1, T, H, D, chunk, hidden_init, log_fgate, value, key, query, hidden_final,
+                      out, saved, workspace, 0, nullptr, nullptr, nseq, cu_seqlens);
+}
+
+int gla_chunk_bwd_packed(void* stream, int64_t T, int64_t H, int64_t D, int64_t chunk, int dtype, int64_t nseq,
+                         const int32_t* cu_seqlens, const float* log_fgate, const void* value, const void* key,
+                         const void* query, const void* saved, const void* dhidden_final, const void* dout,
+                         void* dhidden_init, float* dlog_fgate, void* dvalue, void* dkey, void* dquery,
+                         void* workspace, size_t workspace_bytes) {
+  if (!cu_seqlens || !log_fgate || !value || !key || !query || !saved || !dhidden_final || !dout || !dhidden_init ||
+      !dlog_fgate || !dvalue || !dkey || !dquery)
+    return GLA_ERR_NULL_POINTER;
+  if (nseq <= 0) return GLA_ERR_BAD_DIMS;
+  GLA_TRY(check_chunk_dims(1, T, H, D, chunk, dtype));
+  if (!tc_supported_local_state(D, 128, dtype) || chunk % 128 != 0) return GLA_ERR_UNSUPPORTED;
+  if (!workspace || workspace_bytes < tc_bwd_ws_bytes(1, T, H, D, chunk)) return GLA_ERR_WORKSPACE;
+  return tc_chunk_bwd((cudaStream_t)stream, 1, T, H, D, chunk, log_fgate, value, key, query, saved, dhidden_final, dout,
+                      dhidden_init, dlog_fgate, dvalue, dkey, dquery, workspace, nseq, cu_seqlens);
+}
+
 int gla_chunk_local_state(void* stream, int64_t B, int64_t T, int64_t H, int64_t D, int64_t chunk, int dtype,
                           int impl, const float* log_fgate, const void* value, const void* key, float* G_total,
                           float* S_local, void* workspace, size_t workspace_bytes) {

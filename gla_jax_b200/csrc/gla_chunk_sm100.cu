@@ -1372,11 +1372,12 @@ constexpr size_t FWD_SMEM = 1024 + FwdSmem::END;
 
 int tc_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, int64_t C, const void* hidden_init,
                  const float* g, const void* v, const void* k, const void* q, void* hidden_final, void* out,
-                 void* saved, void* ws, int state_only, float* G_total, float* S_local) {
+                 void* saved, void* ws, int state_only, float* G_total, float* S_local, int64_t nseq, const int* cu) {
   (void)C;
   const int R = (int)(D / TD);
   const int64_t N = T / TC, HV = H * R * R, HK = H * R, BHV = B * HV;
   if (state_only && R != 1) return GLA_ERR_UNSUPPORTED;
+  if (cu != nullptr && (B != 1 || R != 1 || state_only || nseq <= 0)) return GLA_ERR_UNSUPPORTED;   // packed sequences
   char* w = (char*)ws;
   float* kv = (float*)w; w += (R == 1 ? f32b(BHV * N * TD * TD) : 0);
   float* Gc = (float*)w; w += f32b(BHV * N * TD);
@@ -1400,8 +1401,8 @@ int tc_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
     GLA_TRY(launch_state_block(st, hidden_init, hib, B * H, R, 1));
     init_v = hib; fin_v = hfb;
   }
-  const bool fused_states = !state_only && (R > 1 || tc_state_fused_preferred(BHV, N));
-  if (fused_states) GLA_TRY(tc_state_fused(st, 0, B, T, HV, R, g, k, v, init_v, S_prev, fin_v, Gc));
+  const bool fused_states = !state_only && (R > 1 || cu != nullptr || tc_state_fused_preferred(BHV, N));
+  if (fused_states) GLA_TRY(tc_state_fused(st, 0, B, T, HV, R, g, k, v, init_v, S_prev, fin_v, Gc, nseq, cu));
   else GLA_TRY((launch_tc_kv<0>(st, B, T, H, g, k, v, kv, Gc)));
   if (state_only) {
     GLA_TRY(launch_state_scan(st, BHV, N, TD, Gc, kv, 0, nullptr, 0, nullptr, 0, S_local, 0, 0));
@@ -1448,10 +1449,12 @@ int tc_local_dstate(cudaStream_t st, int64_t B, int64_t T, int64_t H, const floa
 
 int tc_chunk_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, int64_t C, const float* g,
                  const void* v, const void* k, const void* q, const void* saved, const void* dhidden_final,
-                 const void* dout, void* dhidden_init, float* dg, void* dv, void* dk, void* dq, void* ws) {
+                 const void* dout, void* dhidden_init, float* dg, void* dv, void* dk, void* dq, void* ws, int64_t nseq,
+                 const int* cu) {
   (void)C;
   const int R = (int)(D / TD);
   const int64_t N = T / TC, HV = H * R * R, HK = H * R, BHV = B * HV;
+  if (cu != nullptr && (B != 1 || R != 1 || nseq <= 0)) return GLA_ERR_UNSUPPORTED;   // packed sequences
   char* w = (char*)ws;
   float* dstate = (float*)w; w += (R == 1 ? f32b(BHV * N * TD * TD) : 0);
   bf16* dS_next = (bf16*)w; w += b16b(BHV * N * TD * TD);
@@ -1475,8 +1478,8 @@ int tc_chunk_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
     GLA_TRY(launch_state_block(st, dhidden_final, dhfb, B * H, R, 1));
     dfin_v = dhfb; dinit_v = dhib;
   }
-  if (R > 1 || tc_state_fused_preferred(BHV, N)) {
-    GLA_TRY(tc_state_fused(st, 1, B, T, HV, R, g, q, dout, dfin_v, dS_next, dinit_v, nullptr));
+  if (R > 1 || cu != nullptr || tc_state_fused_preferred(BHV, N)) {
+    GLA_TRY(tc_state_fused(st, 1, B, T, HV, R, g, q, dout, dfin_v, dS_next, dinit_v, nullptr, nseq, cu));
   } else {
     GLA_TRY((launch_tc_kv<1>(st, B, T, H, g, q, dout, dstate, nullptr)));
     GLA_TRY(launch_state_scan(st, BHV, N, TD, Gc, dstate, 0, dhidden_final, 1, dS_next, 1, dhidden_init, 1, 1));

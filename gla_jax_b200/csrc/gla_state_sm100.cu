@@ -76,8 +76,8 @@ struct StMaps { CUtensorMap g, x, y; };
 
 template <int MODE>
 __global__ void __launch_bounds__(STHREADS, 1)
-tc_state_kernel(const __grid_constant__ StMaps maps, int64_t T, int64_t H, int R, int N, const bf16* __restrict__ init,
-                bf16* __restrict__ states, bf16* __restrict__ fin, float* __restrict__ Gc) {
+tc_state_kernel(const __grid_constant__ StMaps maps, int64_t T, int64_t H, int R, int Nall, const int* __restrict__ cu,
+                const bf16* __restrict__ init, bf16* __restrict__ states, bf16* __restrict__ fin, float* __restrict__ Gc) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   float* tot = reinterpret_cast<float*>(sm + StSmem::TOT);
@@ -95,7 +95,14 @@ tc_state_kernel(const __grid_constant__ StMaps maps, int64_t T, int64_t H, int R
   // H counts VIRTUAL heads: a head of size 128 R is R x R independent (key block a, value block c) problems of size
   // 128, virtual head hh = (h R + a) R + c; in the (B, T, H_real R, 128) view of the arrays its key-side tensors are
   // head h R + a and its value-side tensors head h R + c.  R = 1: all three coincide.
-  const int64_t bh = blockIdx.x >> 2, b = bh / H, hh = bh % H;
+  // Packed sequences (cu != null): the arrays hold ONE time axis (B = 1) with sequences laid end to end, cu[s] the
+  // token offset of sequence s (a multiple of 128); blockIdx then ranges over (sequence, head, slice), the block
+  // walks only its sequence's chunks, and init / fin are per (sequence, head).
+  const int64_t bh = blockIdx.x >> 2, hh = bh % H;
+  const int64_t b = cu ? 0 : bh / H;
+  const int base = cu ? cu[bh / H] / SC : 0;                       // first chunk of this block's sequence
+  const int N = cu ? (cu[bh / H + 1] - cu[bh / H]) / SC : Nall;    // its number of chunks
+  const int64_t rowbase = cu ? hh * (int64_t)Nall + base : bh * (int64_t)Nall;   // row of chunk 0 in states / Gc
   const int64_t hk = (hh / (R * R)) * R + (hh % (R * R)) / R, hv = (hh / (R * R)) * R + hh % R;
   auto chunk_of = [&](int i) { return MODE == 0 ? i : N - 1 - i; };
 
@@ -121,7 +128,7 @@ tc_state_kernel(const __grid_constant__ StMaps maps, int64_t T, int64_t H, int R
 
   if (warp == (NBUILD + NUPD) / 32 + 1) {
     // ================= TMA producer warp =================
-    const int z0 = (int)(b * T), yk = (int)hk, yv = (int)hv;
+    const int z0 = (int)(b * T) + base * SC, yk = (int)hk, yv = (int)hv;
     const int zstep = MODE == 0 ? SC : -SC;
     const uint32_t sm_base = smem_u32(sm), fully0 = smem_u32(fully), fullgx0 = smem_u32(fullgx);
     auto load_y = [&](int z, int s) {
@@ -228,7 +235,7 @@ tc_state_kernel(const __grid_constant__ StMaps maps, int64_t T, int64_t H, int R
         for (int w2 = 0; w2 < 8; ++w2) { e *= tw[w2]; if (MODE == 0) sg += gg[w2 * SL + lane]; }
         eG[(i & 3) * SL + lane] = e;
         mbar_arrive(smem_u32(egbar + (i & 3)));       // release: the updaters acquire it before reading e^G
-        if (MODE == 0 && Gc != nullptr) Gc[(bh * N + chunk_of(i)) * SD + SL * slice + lane] = sg;
+        if (MODE == 0 && Gc != nullptr) Gc[(rowbase + chunk_of(i)) * SD + SL * slice + lane] = sg;
       }
       // weights by running product from the cross-group factor, applied on the fly
       float v[16];
@@ -277,7 +284,7 @@ tc_state_kernel(const __grid_constant__ StMaps maps, int64_t T, int64_t H, int R
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(smem_u32(accfree + g));    // accumulator g may be overwritten by step i + 2
-      bf16* so = states + (int64_t)(bh * N + chunk_of(i)) * SD * SD + (el0 - bh * SD * SD);
+      bf16* so = states + (rowbase + chunk_of(i)) * SD * SD + (el0 - bh * SD * SD);
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         so[(int64_t)j * SD] = __float2bfloat16_rn(S[j]);
@@ -325,8 +332,9 @@ bool tc_state_fused_preferred(int64_t BH, int64_t N) {
 // mode 0: states[n] = state before chunk n (from init), fin = state after the last chunk, Gc = chunk gate sums.
 // mode 1: states[n] = gradient state after chunk n (from init = dhidden_final), fin = dhidden_init.
 int tc_state_fused(cudaStream_t st, int mode, int64_t B, int64_t T, int64_t H, int R, const float* g, const void* x,
-                   const void* y, const void* init, void* states, void* fin, float* Gc) {
-  const int64_t N = T / SC, BH = B * H;          // H: virtual heads (real heads x R x R)
+                   const void* y, const void* init, void* states, void* fin, float* Gc, int64_t nseq, const int* cu) {
+  // packed sequences: B == 1, cu (device, nseq + 1 token offsets) non-null, init / fin are (nseq, H, 128, 128)
+  const int64_t N = T / SC, BH = (cu ? nseq : B) * H;          // H: virtual heads (real heads x R x R)
   const int64_t HK = H / R;                      // heads of the (B, T, HK, 128) view of the arrays
   StMaps maps;
   GLA_TRY(make_map_bthd(&maps.g, g, 1, B, T, HK, SL, 0));
@@ -337,7 +345,7 @@ int tc_state_fused(cudaStream_t st, int mode, int64_t B, int64_t T, int64_t H, i
   if (e != cudaSuccess) return record_cuda_error(e);
   {
     ProfScope ps(mode == 0 ? "tc_state_kernel" : "tc_dstate_scan_kernel", st);
-    kern<<<(unsigned)(BH * 4), STHREADS, ST_SMEM, st>>>(maps, T, H, R, (int)N, (const bf16*)init, (bf16*)states, (bf16*)fin, Gc);
+    kern<<<(unsigned)(BH * 4), STHREADS, ST_SMEM, st>>>(maps, T, H, R, (int)N, cu, (const bf16*)init, (bf16*)states, (bf16*)fin, Gc);
   }
   GLA_CHECK_LAUNCH();
   return GLA_OK;

@@ -208,6 +208,79 @@ def recurrent_gla_naive(hidden, log_fgate, value, key, query, reverse: bool = Fa
     return (hf, out) if batched else (hf[0], out[0])
 
 
+class _ChunkGLAPacked(torch.autograd.Function):
+    """chunk_gla over sequences laid end to end on one time axis (gla_chunk_fwd_packed / gla_chunk_bwd_packed)."""
+
+    @staticmethod
+    def forward(ctx, hidden, g, v, k, q, cu, chunk):
+        lib = _lib.load()
+        T, H, D = v.shape
+        nseq = hidden.shape[0]
+        dt = _DT[v.dtype]
+        g32 = g if g.dtype == torch.float32 else g.float()
+        ws_n = lib.gla_chunk_fwd_workspace_bytes(1, T, H, D, chunk, dt, _lib.IMPL_TCGEN05)
+        if ws_n == 0:
+            raise _lib.GlaError(f"chunk_gla_packed: unsupported configuration T={T} H={H} D={D} chunk={chunk} dtype={v.dtype}")
+        need_grad = any(ctx.needs_input_grad[:5])
+        saved = torch.empty(lib.gla_chunk_saved_bytes(1, T, H, D, chunk, dt, _lib.IMPL_TCGEN05), dtype=torch.uint8,
+                            device=v.device) if need_grad else None
+        ws = torch.empty(ws_n, dtype=torch.uint8, device=v.device)
+        hf, out = torch.empty_like(hidden), torch.empty_like(v)
+        st = lib.gla_chunk_fwd_packed(_stream(v.device), T, H, D, chunk, dt, nseq, _ptr(cu), _ptr(hidden), _ptr(g32), _ptr(v),
+                                      _ptr(k), _ptr(q), _ptr(hf), _ptr(out), _ptr(saved), _ptr(ws), ws_n)
+        _lib.check(st, "gla_chunk_fwd_packed")
+        if need_grad:
+            ctx.save_for_backward(g32, v, k, q, cu, saved)
+        ctx.chunk, ctx.g_dtype, ctx.nseq = chunk, g.dtype, nseq
+        return hf, out
+
+    @staticmethod
+    def backward(ctx, dhf, dout):
+        lib = _lib.load()
+        g32, v, k, q, cu, saved = ctx.saved_tensors
+        T, H, D = v.shape
+        dt = _DT[v.dtype]
+        dhf = torch.zeros(ctx.nseq, H, D, D, dtype=v.dtype, device=v.device) if dhf is None else dhf.to(v.dtype).contiguous()
+        dout = torch.zeros_like(v) if dout is None else dout.to(v.dtype).contiguous()
+        ws_n = lib.gla_chunk_bwd_workspace_bytes(1, T, H, D, ctx.chunk, dt, _lib.IMPL_TCGEN05)
+        ws = torch.empty(ws_n, dtype=torch.uint8, device=v.device)
+        dh = torch.empty_like(dhf)
+        dg = torch.empty_like(g32)
+        dv, dk, dq = torch.empty_like(v), torch.empty_like(k), torch.empty_like(q)
+        st = lib.gla_chunk_bwd_packed(_stream(v.device), T, H, D, ctx.chunk, dt, ctx.nseq, _ptr(cu), _ptr(g32), _ptr(v),
+                                      _ptr(k), _ptr(q), _ptr(saved), _ptr(dhf), _ptr(dout), _ptr(dh), _ptr(dg), _ptr(dv),
+                                      _ptr(dk), _ptr(dq), _ptr(ws), ws_n)
+        _lib.check(st, "gla_chunk_bwd_packed")
+        return dh, dg.to(ctx.g_dtype), dv, dk, dq, None, None
+
+
+def chunk_gla_packed(hidden_init, log_fgate, value, key, query, cu_seqlens, chunk_size: int = 128):
+    """``chunk_gla`` for variable-length sequences packed end to end on one time axis.
+
+    ``value/key/query/log_fgate`` are (T, H, D) holding ``nseq`` sequences back to back; ``cu_seqlens`` is an int32
+    tensor of ``nseq + 1`` token offsets (0 first, T last, every offset a multiple of 128); ``hidden_init`` is
+    (nseq, H, D, D).  Returns ``(hidden_final (nseq, H, D, D), out (T, H, D))``, equal to calling ``chunk_gla`` on
+    each sequence; differentiable.  The reference has one length per call (gla.py:499-500, 674); this runs on the
+    tensor-core kernels only (bf16, D = 128)."""
+    if value.dim() != 3 or hidden_init.dim() != 4:
+        raise ValueError("chunk_gla_packed: expected value (T, H, D) and hidden_init (nseq, H, D, D)")
+    T, H, D = value.shape
+    cu = torch.as_tensor(cu_seqlens, dtype=torch.int32)
+    nseq = cu.numel() - 1
+    if nseq < 1 or tuple(hidden_init.shape) != (nseq, H, D, D):
+        raise ValueError("chunk_gla_packed: cu_seqlens must have nseq + 1 entries for hidden_init (nseq, H, D, D)")
+    host = cu.cpu()
+    if int(host[0]) != 0 or int(host[-1]) != T or bool(((host[1:] - host[:-1]) <= 0).any()) or bool((host % 128 != 0).any()):
+        raise ValueError("chunk_gla_packed: cu_seqlens must rise from 0 to T in multiples of 128")
+    if key.shape != value.shape or query.shape != value.shape or log_fgate.shape != value.shape:
+        raise ValueError("chunk_gla_packed: log_fgate, value, key, query must all be (T, H, D)")
+    if not value.is_cuda:
+        raise TypeError("chunk_gla_packed: CUDA tensors required (there is no CPU path)")
+    cu = cu.to(value.device).contiguous()
+    return _ChunkGLAPacked.apply(hidden_init.contiguous(), log_fgate.contiguous(), value.contiguous(), key.contiguous(),
+                                 query.contiguous(), cu, int(chunk_size))
+
+
 def decode_step(state, log_fgate, value, key, query, out_dtype=None):
     """One token of the recurrence (reference: the loop body of gla.py:26-47) for a batch of requests.
 

@@ -239,6 +239,29 @@ GLA_API int gla_chunk_fwd_static(void* stream, int64_t B, int64_t T, int64_t H, 
                          void* hidden_final, void* out);
 
 /* ------------------------------------------------------------------------------------
+ * Packed (variable-length) sequences — no counterpart in the reference, which asserts one
+ * length per call (gla.py:499-500, 674); the survey's "next" item 2.
+ * The arrays hold ONE time axis of T tokens with nseq sequences laid end to end:
+ * log_fgate/value/key/query/out are (T, H, D); cu_seqlens is a DEVICE array of nseq + 1 int32
+ * token offsets (cu_seqlens[0] = 0, cu_seqlens[nseq] = T), every offset a multiple of 128;
+ * hidden_init / hidden_final (and their gradients) are (nseq, H, D, D).  Results equal nseq
+ * separate gla_chunk_fwd / gla_chunk_bwd calls.  Tensor-core path only: bf16, D = 128, chunk
+ * a multiple of 128; other shapes return GLA_ERR_UNSUPPORTED.  saved / workspace sizes:
+ * gla_chunk_saved_bytes / gla_chunk_{fwd,bwd}_workspace_bytes with B = 1 and impl GLA_IMPL_TCGEN05.
+ * ---------------------------------------------------------------------------------- */
+GLA_API int gla_chunk_fwd_packed(void* stream, int64_t T, int64_t H, int64_t D, int64_t chunk, int dtype,
+                         int64_t nseq, const int32_t* cu_seqlens,
+                         const void* hidden_init, const float* log_fgate, const void* value,
+                         const void* key, const void* query, void* hidden_final, void* out,
+                         void* saved, void* workspace, size_t workspace_bytes);
+GLA_API int gla_chunk_bwd_packed(void* stream, int64_t T, int64_t H, int64_t D, int64_t chunk, int dtype,
+                         int64_t nseq, const int32_t* cu_seqlens,
+                         const float* log_fgate, const void* value, const void* key, const void* query,
+                         const void* saved, const void* dhidden_final, const void* dout,
+                         void* dhidden_init, float* dlog_fgate, void* dvalue, void* dkey, void* dquery,
+                         void* workspace, size_t workspace_bytes);
+
+/* ------------------------------------------------------------------------------------
  * Sequence-parallel support (no counterpart in the reference, which is single-device; the
  * algebra is ops.py:286 binary_operator applied across ranks and the exact chaining of
  * hidden_init -> hidden_final, gla.py:720-723).

@@ -343,3 +343,54 @@ def test_decode_step_rejects_bad_arguments(cuda_device):
     x48 = torch.zeros(1, 1, 48, device=cuda_device)
     with pytest.raises(Exception):
         decode_step(st48, x48, x48, x48, x48)       # head size without a kernel: GLA_ERR_UNSUPPORTED
+
+
+@pytest.mark.parametrize("lengths,H,shift", [
+    ([128, 384, 256], 2, 5.0),
+    ([512], 1, 5.0),                       # a single sequence: must equal chunk_gla
+    ([256, 128, 128, 640, 128], 3, 0.0),   # sharp gates, single-chunk sequences in the mix
+])
+def test_chunk_gla_packed_equals_per_sequence_calls(cuda_device, lengths, H, shift, monkeypatch):
+    """Variable-length sequences packed on one time axis: forward and backward equal separate chunk_gla calls
+    (the packed path always takes the one-pass state kernel, so the separate calls are pinned to it as well and the
+    results must agree to the last bit or nearly), and parity with the oracle."""
+    from gla_jax_b200 import chunk_gla, chunk_gla_packed, _lib
+    monkeypatch.setenv("GLA_B200_STATE_FUSED", "1")
+    D, T, nseq = 128, sum(lengths), len(lengths)
+    cu = [0]
+    for L in lengths:
+        cu.append(cu[-1] + L)
+    _, g, v, k, q = O.make_inputs(1, T, H, D, torch.bfloat16, seed=51, shift=shift)
+    gen = torch.Generator().manual_seed(52)
+    h = torch.randn(nseq, H, D, D, generator=gen).to(torch.bfloat16)
+    dhf = torch.randn(nseq, H, D, D, generator=gen).to(torch.bfloat16)
+    do = torch.randn(T, H, D, generator=gen).to(torch.bfloat16)
+    dev = cuda_device
+    leaves = [x.to(dev).requires_grad_(True) for x in (h, g[0], v[0], k[0], q[0])]
+    hf, out = chunk_gla_packed(*leaves, torch.tensor(cu, dtype=torch.int32), chunk_size=128)
+    loss = (hf.float() * dhf.to(dev).float()).sum() + (out.float() * do.to(dev).float()).sum()
+    grads = torch.autograd.grad(loss, leaves)
+    torch.cuda.synchronize()
+    assert _lib.load().gla_device_wait_timeouts() == 0
+    for s in range(nseq):
+        sl = slice(cu[s], cu[s + 1])
+        case = (h[s:s + 1], g[:, sl], v[:, sl], k[:, sl], q[:, sl], dhf[s:s + 1], do[sl].unsqueeze(0))
+        ref = _run_gpu(chunk_gla, dev, *case, chunk_size=128, impl="tcgen05")
+        got = (hf[s:s + 1].cpu(), out[sl].unsqueeze(0).cpu(),
+               [grads[0][s:s + 1].cpu(), grads[1][sl].unsqueeze(0).cpu(), grads[2][sl].unsqueeze(0).cpu(),
+                grads[3][sl].unsqueeze(0).cpu(), grads[4][sl].unsqueeze(0).cpu()])
+        for name, a, b in zip(["hidden_final", "out", *NAMES], [ref[0], ref[1], *ref[2]], [got[0], got[1], *got[2]]):
+            assert O.rel_l2(a, b) <= 1e-6, f"sequence {s} {name}: packed vs separate {O.rel_l2(a, b):.3e}"
+        if lengths[s] <= 256:
+            _compare(_oracle(*case), got, torch.bfloat16, f"chunk_gla_packed sequence {s}")
+
+
+def test_chunk_gla_packed_rejects_bad_offsets(cuda_device):
+    from gla_jax_b200 import chunk_gla_packed
+    H, D = 1, 128
+    x = torch.zeros(256, H, D, device=cuda_device, dtype=torch.bfloat16)
+    g = torch.zeros(256, H, D, device=cuda_device)
+    h = torch.zeros(2, H, D, D, device=cuda_device, dtype=torch.bfloat16)
+    for cu in ([0, 100, 256], [0, 128, 384], [128, 256, 256], [0, 256]):
+        with pytest.raises(ValueError):
+            chunk_gla_packed(h, g, x, x, x, cu)
