@@ -5,7 +5,7 @@
         --master-port P bench.py --gpus N --steps K --warmup W
 
 A step is one forward+backward of ``chunk_gla`` with the reference harness loss
-``hidden_final.sum() + out.sum()`` (gla.py:1336-1340) on the README shape (BASELINE config 2:
+``hidden_final.sum() + out.sum()`` (gla.py:1336-1340) on the README shape (benchmark config 2:
 B=4, H=6, D=128, T=4096, bf16, chunk 128, log_fgate = log_sigmoid(5 + N(0,1)) in float32), with
 seeded synthetic inputs.  With N GPUs every rank runs that shape on its own batch shard
 (batch x heads sharding needs no collective), so scaling is weak and ``value`` is the whole-job
@@ -39,7 +39,7 @@ ROOT = Path(__file__).resolve().parent
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
-# README shape (BASELINE config 2), per GPU
+# README shape (benchmark config 2), per GPU
 CFG = dict(B=4, T=4096, H=6, D=128, C=128)
 METRIC = "chunk_gla fwd+bwd tokens/sec"
 
@@ -234,7 +234,7 @@ def run_reference(args, rank, world):
         "impl": "reference", "metric": METRIC, "value": val, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * el / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "README shape B=4,H=6,D=128,T=4096,chunk=128 (BASELINE config 2); CPU sample B=1"},
+        "config": {"workload": "README shape B=4,H=6,D=128,T=4096,chunk=128 (benchmark config 2); CPU sample B=1"},
         "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "reference needs jax==0.4.29 + Pallas/Triton (not installable here); this is its chunk "
@@ -473,7 +473,7 @@ def main():
                 roof = {"bound": "tensor", "kernel": dom, "achieved": ach, "peak": peaks["tf_burst"],
                         "unit": "TFLOP/s", "frac": ach / peaks["tf_burst"], "traffic": None}
             # DRAM bytes per launch of this kernel at this exact shape, from the committed ncu capture
-            # (profiles/tc_chunk_kernels_readme_shape_ncu_full.md); null for kernels without one
+            # (summarised with its command under profiles/); null for kernels without one
             if args.op == "chunk_gla" and dom in NCU_TRAFFIC_README_SHAPE:
                 roof["traffic"] = NCU_TRAFFIC_README_SHAPE[dom]
             roof.update({"peak_source": peaks["source"], "launches": n_l, "ms_per_launch": 1e3 * per_launch_s,
@@ -484,7 +484,7 @@ def main():
             "ms_per_step": ms_total / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "README shape per GPU: B=4,H=6,D=128,T=4096,chunk=128,bf16 q/k/v/hidden, f32 "
-                                   "log_fgate=log_sigmoid(5+N(0,1)) (BASELINE config 2); loss=hidden_final.sum()+out.sum()",
+                                   "log_fgate=log_sigmoid(5+N(0,1)) (benchmark config 2); loss=hidden_final.sum()+out.sum()",
                        "global_batch": B * world, "seq_len": T, "parallelism": f"batch-shard x{world}, no collectives",
                        "l2": f"{NSETS} rotating input/output sets; one step touches > 400 MB (L2 = 126 MB)",
                        "chunk_impl": args.chunk_impl,

@@ -58,7 +58,7 @@ def _compare(ref, got, dtype, what):
 
 CHUNK_CASES = [
     # B, T, H, D, C, dtype, shift, zero_init
-    (1, 256, 2, 64, 64, torch.float32, 5.0, False),      # BASELINE config 1
+    (1, 256, 2, 64, 64, torch.float32, 5.0, False),      # benchmark config 1
     (2, 128, 2, 32, 32, torch.float32, 0.0, False),      # sharp gates
     (1, 64, 1, 64, 64, torch.float32, 5.0, False),       # a single chunk
     (1, 128, 3, 16, 16, torch.float32, 5.0, True),       # smallest sizes, zero initial state
@@ -84,7 +84,7 @@ TC_CASES = [
     # B, T, H, shift, zero_init   (bf16, D = chunk = 128: the native shape of the tcgen05 kernels)
     (1, 128, 1, 5.0, False),       # one chunk
     (1, 512, 2, 5.0, False),
-    (2, 512, 3, 0.0, False),       # sharp gates (BASELINE config 5's gate distribution)
+    (2, 512, 3, 0.0, False),       # sharp gates (benchmark config 5's gate distribution)
     (1, 256, 2, -3.0, False),      # very sharp gates: every level's weights underflow gracefully
     (2, 384, 2, 5.0, True),        # zero initial state, three chunks
 ]
@@ -92,7 +92,7 @@ TC_CASES = [
 
 TC_WIDE_CASES = [
     # B, T, H, D, C, shift    bf16 shapes the tensor-core kernels serve beyond D = chunk = 128:
-    (1, 512, 2, 256, 256, 5.0),     # BASELINE config 5's head and chunk size (a head of 256 = 2 x 2 blocks of 128)
+    (1, 512, 2, 256, 256, 5.0),     # benchmark config 5's head and chunk size (a head of 256 = 2 x 2 blocks of 128)
     (1, 512, 1, 256, 256, 0.0),     # ... with its sharp gates
     (2, 256, 2, 256, 128, 0.0),
     (1, 512, 2, 128, 256, 5.0),     # a larger chunk size at head size 128 (the result does not depend on it)
@@ -166,7 +166,7 @@ def test_auto_picks_tcgen05_for_readme_shape(cuda_device):
 
 
 def test_tcgen05_matches_recurrent_at_readme_shape(cuda_device):
-    """Full BASELINE config 2 shape (B=4, H=6, D=128, T=4096, bf16), forward and backward: the
+    """Full benchmark config 2 shape (B=4, H=6, D=128, T=4096, bf16), forward and backward: the
     tensor-core chunk path against recurrent_gla (exact fp32 recurrence) on the GPU, since the
     CPU oracle cannot afford this size.  Same tolerances as against the oracle."""
     from gla_jax_b200 import chunk_gla, recurrent_gla
