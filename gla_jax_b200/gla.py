@@ -257,21 +257,23 @@ class _ChunkGLAPacked(torch.autograd.Function):
 def chunk_gla_packed(hidden_init, log_fgate, value, key, query, cu_seqlens, chunk_size: int = 128):
     """``chunk_gla`` for variable-length sequences packed end to end on one time axis.
 
-    ``value/key/query/log_fgate`` are (T, H, D) holding ``nseq`` sequences back to back; ``cu_seqlens`` is an int32
-    tensor of ``nseq + 1`` token offsets (0 first, T last, every offset a multiple of 128); ``hidden_init`` is
+    ``value/key/query/log_fgate`` are (T, H, D) holding ``nseq`` sequences back to back; ``cu_seqlens`` holds the
+    ``nseq + 1`` token offsets (0 first, T last, every offset a multiple of 128; a list or CPU tensor is validated,
+    a CUDA int32 tensor is used as is without a host round trip); ``hidden_init`` is
     (nseq, H, D, D).  Returns ``(hidden_final (nseq, H, D, D), out (T, H, D))``, equal to calling ``chunk_gla`` on
     each sequence; differentiable.  The reference has one length per call (gla.py:499-500, 674); this runs on the
     tensor-core kernels only (bf16, D = 128)."""
     if value.dim() != 3 or hidden_init.dim() != 4:
         raise ValueError("chunk_gla_packed: expected value (T, H, D) and hidden_init (nseq, H, D, D)")
     T, H, D = value.shape
-    cu = torch.as_tensor(cu_seqlens, dtype=torch.int32)
+    cu = torch.as_tensor(cu_seqlens, dtype=torch.int32) if not torch.is_tensor(cu_seqlens) else cu_seqlens.to(torch.int32)
     nseq = cu.numel() - 1
     if nseq < 1 or tuple(hidden_init.shape) != (nseq, H, D, D):
         raise ValueError("chunk_gla_packed: cu_seqlens must have nseq + 1 entries for hidden_init (nseq, H, D, D)")
-    host = cu.cpu()
-    if int(host[0]) != 0 or int(host[-1]) != T or bool(((host[1:] - host[:-1]) <= 0).any()) or bool((host % 128 != 0).any()):
-        raise ValueError("chunk_gla_packed: cu_seqlens must rise from 0 to T in multiples of 128")
+    if not cu.is_cuda:
+        # offsets given on the host are checked here; a CUDA tensor is taken as is (checking it would synchronise)
+        if int(cu[0]) != 0 or int(cu[-1]) != T or bool(((cu[1:] - cu[:-1]) <= 0).any()) or bool((cu % 128 != 0).any()):
+            raise ValueError("chunk_gla_packed: cu_seqlens must rise from 0 to T in multiples of 128")
     if key.shape != value.shape or query.shape != value.shape or log_fgate.shape != value.shape:
         raise ValueError("chunk_gla_packed: log_fgate, value, key, query must all be (T, H, D)")
     if not value.is_cuda:
