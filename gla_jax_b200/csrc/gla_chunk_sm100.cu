@@ -655,7 +655,7 @@ struct BwdSmem {
   static constexpr uint32_t DIAG = GRP + 8 * TD * 4;       // [128] float: dP[i][i]
   static constexpr uint32_t DG1 = DIAG + TC * 4;           // [128] float
   static constexpr uint32_t DG2 = DG1 + TD * 4;            // [128] float
-  static constexpr uint32_t BAR = DG2 + TD * 4;            // 5 mbarriers + tmem slot
+  static constexpr uint32_t BAR = DG2 + TD * 4;            // 6 mbarriers + tmem slot
   static constexpr uint32_t END = BAR + 64;
   // After the phase-1 products have completed, dO, v and P are dead; after phase 1.5 the rest is.  Reuse:
   static constexpr uint32_t W64 = KH;                      // 32 KB: k~ / q~ at the h = 64 anchor, all 128 rows
@@ -668,7 +668,11 @@ struct BwdSmem {
   static constexpr uint32_t K1 = P + 16384;                // [64][128] bf16: k of rows 64..127
   static constexpr uint32_t K0 = V;                        // [64][128] bf16: k of rows 0..63
 };
-struct BwdMaps { CUtensorMap g, q, k; };                   // boxes of 128 features x 64 rows, unswizzled
+struct BwdMaps {
+  CUtensorMap g, q, k;          // boxes of 128 features x 64 rows, unswizzled (row passes)
+  CUtensorMap dO, v;            // boxes of 64 features x 128 rows, 128-byte swizzle (operand tiles)
+  CUtensorMap sp, ds, p;        // dense (rows, 128) matrices: boxes of 64 columns x 128 rows, 128-byte swizzle
+};
 constexpr uint32_t TM_DP = 0, TM_DQH = 128, TM_DKH = 256, TM_DV = 384, TM_T = 384;
 
 // Decay weights of the thread's 16 rows at level slot S (half size 2^S), column layout.
@@ -744,8 +748,8 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
   float* diag = reinterpret_cast<float*>(sm + BwdSmem::DIAG);
   float* dG1 = reinterpret_cast<float*>(sm + BwdSmem::DG1);
   float* dG2 = reinterpret_cast<float*>(sm + BwdSmem::DG2);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + BwdSmem::BAR);   // [0]: phase 1, [1],[2]: level buffers, [3],[4]: pass loads
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + BwdSmem::BAR);   // [0]: phase 1, [1],[2]: level buffers, [3],[4]: pass loads, [5]: tiles
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int q4 = warp & 3, wq_ = warp >> 2;        // TMEM lane quadrant, and which quarter of the columns
@@ -772,31 +776,26 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
     mbar_init(smem_u32(bars + 2), 1);
     mbar_init(smem_u32(bars + 3), 1);
     mbar_init(smem_u32(bars + 4), 1);
+    mbar_init(smem_u32(bars + 5), 1);
     mbar_fence_init();
+    // the five operand tiles of the chunk by TMA (160 KB in flight); they are first needed by the products, which
+    // are issued after the gates and k_hat have been computed, so the copies run under that work
+    const uint32_t lb = smem_u32(bars + 5);
+    const int z = (int)(b * T + n * TC), yv = (int)hv_, cr = (int)(chunk_id * TD);
+    mbar_arrive_expect_tx(lb, 5 * 2 * TILE_BYTES);
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      tma_load_3d(smem_u32(sm + BwdSmem::DO + half * TILE_BYTES), &maps.dO, 64 * half, yv, z, lb);
+      tma_load_3d(smem_u32(sm + BwdSmem::V + half * TILE_BYTES), &maps.v, 64 * half, yv, z, lb);
+      tma_load_2d(smem_u32(sm + BwdSmem::SP + half * TILE_BYTES), &maps.sp, 64 * half, cr, lb);
+      tma_load_2d(smem_u32(sm + BwdSmem::DS + half * TILE_BYTES), &maps.ds, 64 * half, cr, lb);
+      tma_load_2d(smem_u32(sm + BwdSmem::P + half * TILE_BYTES), &maps.p, 64 * half, cr, lb);
+    }
   }
   if (tid < TD) { dG1[tid] = 0.f; dG2[tid] = 0.f; }
   TC_STAMP(1, 0);
 
-  // ---- phase 0: operand tiles; gate products per 16 rows; k_hat -------------------------------
-  {
-    // all 20 vector loads of the five operand tiles are issued before the first store consumes one
-    const int crow = tid >> 4, cch = tid & 15;       // this thread's 16-byte chunk in rows crow + 32 j
-    const bf16* src[5] = {dO + row0v, v + row0v, S_prev + chunk_id * TD * TD, dS_next + chunk_id * TD * TD,
-                          P_saved + chunk_id * TC * TC};
-    const int64_t ld[5] = {HDi, HDi, TD, TD, TC};
-    uint4 t[20];
-#pragma unroll
-    for (int m = 0; m < 5; ++m)
-#pragma unroll
-      for (int j = 0; j < 4; ++j)
-        t[4 * m + j] = __ldg(reinterpret_cast<const uint4*>(src[m] + (int64_t)(crow + 32 * j) * ld[m] + cch * 8));
-#pragma unroll
-    for (int m = 0; m < 5; ++m)
-#pragma unroll
-      for (int j = 0; j < 4; ++j)
-        *reinterpret_cast<uint4*>(sm + BwdSmem::DO + m * 2 * TILE_BYTES + (cch >> 3) * TILE_BYTES +
-                                  sw128_chunk(crow + 32 * j, cch & 7)) = t[4 * m + j];
-  }
+  // ---- phase 0: gate products per 16 rows; k_hat (the operand tiles are arriving by TMA) ------------------
   float f32r[32];                                   // gates of rows 32 wq_ + [0, 32), feature d
   {
     float p0 = 1.f, p1 = 1.f;
@@ -847,7 +846,9 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
 
   TC_STAMP(1, 2);
   // ---- phase 1: the four dense products --------------------------------------------------------------
+  bool ok = true;
   if (tid == 0) {
+    ok = mbar_wait(smem_u32(bars + 5), 0);          // operand tiles landed
     tc_fence_after();
     constexpr uint32_t iKK = idesc_bf16(128, 128, 0, 0), iMM = idesc_bf16(128, 128, 1, 1);
     const uint32_t aDO = smem_u32(sm + BwdSmem::DO), aV = smem_u32(sm + BwdSmem::V), aSP = smem_u32(sm + BwdSmem::SP),
@@ -895,7 +896,8 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
       else if (tid == 64) l2_prefetch_bulk(P_saved + (bh2 * N + n2) * TC * TC, 2 * TC * TC);
     }
   }
-  bool ok = mbar_wait(smem_u32(bars + 0), 0);
+  ok = mbar_wait(smem_u32(bars + 0), 0) && ok;
+  ok = mbar_wait(smem_u32(bars + 5), 0) && ok;      // every thread observes the tiles' arrival itself before reading them
   tc_fence_after();
   TC_STAMP(1, 3);
   // dO, v and P have been consumed by the products: their regions take g, q, k of rows 64..127 and k of rows
@@ -1490,6 +1492,11 @@ int tc_chunk_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
   GLA_TRY(make_map_bthd(&bmaps.g, g, 1, B, T, HK, 128, 0, 64));
   GLA_TRY(make_map_bthd(&bmaps.q, q, 0, B, T, HK, 128, 0, 64));
   GLA_TRY(make_map_bthd(&bmaps.k, k, 0, B, T, HK, 128, 0, 64));
+  GLA_TRY(make_map_bthd(&bmaps.dO, dout, 0, B, T, HK, 64, 1));
+  GLA_TRY(make_map_bthd(&bmaps.v, v, 0, B, T, HK, 64, 1));
+  GLA_TRY(make_map_rows(&bmaps.sp, S_prev, BHV * N * TD, 64, 128));
+  GLA_TRY(make_map_rows(&bmaps.ds, dS_next, BHV * N * TD, 64, 128));
+  GLA_TRY(make_map_rows(&bmaps.p, P, BHV * N * TC, 64, 128));
   {
     ProfScope ps("tc_chunk_bwd_kernel", st);
     tc_chunk_bwd_kernel<<<(unsigned)(BHV * N), TTHREADS, BWD_SMEM, st>>>(
