@@ -771,7 +771,7 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
     tmem_relinquish();
   }
   if (tid == 0) {
-    mbar_init(smem_u32(bars + 0), 1);
+    mbar_init(smem_u32(bars + 0), 4);        // four issuing threads commit the phase-1 products
     mbar_init(smem_u32(bars + 1), 1);
     mbar_init(smem_u32(bars + 2), 1);
     mbar_init(smem_u32(bars + 3), 1);
@@ -846,34 +846,43 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
 
   TC_STAMP(1, 2);
   // ---- phase 1: the four dense products --------------------------------------------------------------
+  // Issued by four threads of four warps on different schedulers (8 to 16 MMAs each instead of 40 from one): the
+  // issuing thread's instruction stream is serial, so this shortens the wait of everybody else.  The two halves of
+  // dV come from the same thread, in order.
   bool ok = true;
-  if (tid == 0) {
+  if (lane == 0 && (warp == 3 || warp == 6 || warp == 9 || warp == 12)) {
     ok = mbar_wait(smem_u32(bars + 5), 0);          // operand tiles landed
     tc_fence_after();
     constexpr uint32_t iKK = idesc_bf16(128, 128, 0, 0), iMM = idesc_bf16(128, 128, 1, 1);
-    const uint32_t aDO = smem_u32(sm + BwdSmem::DO), aV = smem_u32(sm + BwdSmem::V), aSP = smem_u32(sm + BwdSmem::SP),
-                   aDS = smem_u32(sm + BwdSmem::DS), aP = smem_u32(sm + BwdSmem::P), aKH = smem_u32(sm + BwdSmem::KH);
-    const uint64_t kDO = desc_kmajor(aDO, TILE_BYTES, 0), kV = desc_kmajor(aV, TILE_BYTES, 0), kSP = desc_kmajor(aSP, TILE_BYTES, 0),
-                   kDS = desc_kmajor(aDS, TILE_BYTES, 0);
-    const uint64_t mP = desc_mnmajor(aP, TILE_BYTES, 0), mDO = desc_mnmajor(aDO, TILE_BYTES, 0), mKH = desc_mnmajor(aKH, TILE_BYTES, 0),
-                   mDS = desc_mnmajor(aDS, TILE_BYTES, 0);
+    const uint32_t aDO = smem_u32(sm + BwdSmem::DO), aV = smem_u32(sm + BwdSmem::V);
+    if (warp == 3) {
+      const uint64_t kDO = desc_kmajor(aDO, TILE_BYTES, 0), kV = desc_kmajor(aV, TILE_BYTES, 0);
 #pragma unroll
-    for (int ks = 0; ks < 8; ++ks)   // dP[i][j] = sum_dv dO[i][dv] v[j][dv]
-      umma_bf16(tmem + TM_DP, kslice_kmajor(kDO, TILE_BYTES, ks), kslice_kmajor(kV, TILE_BYTES, ks), iKK, ks > 0);
+      for (int ks = 0; ks < 8; ++ks)   // dP[i][j] = sum_dv dO[i][dv] v[j][dv]
+        umma_bf16(tmem + TM_DP, kslice_kmajor(kDO, TILE_BYTES, ks), kslice_kmajor(kV, TILE_BYTES, ks), iKK, ks > 0);
+    } else if (warp == 6) {
+      const uint64_t kSP = desc_kmajor(smem_u32(sm + BwdSmem::SP), TILE_BYTES, 0), kDO = desc_kmajor(aDO, TILE_BYTES, 0);
 #pragma unroll
-    for (int ks = 0; ks < 8; ++ks)   // dQh^T[dk][i] = sum_dv S_prev[dk][dv] dO[i][dv]
-      umma_bf16(tmem + TM_DQH, kslice_kmajor(kSP, TILE_BYTES, ks), kslice_kmajor(kDO, TILE_BYTES, ks), iKK, ks > 0);
+      for (int ks = 0; ks < 8; ++ks)   // dQh^T[dk][i] = sum_dv S_prev[dk][dv] dO[i][dv]
+        umma_bf16(tmem + TM_DQH, kslice_kmajor(kSP, TILE_BYTES, ks), kslice_kmajor(kDO, TILE_BYTES, ks), iKK, ks > 0);
+    } else if (warp == 9) {
+      const uint64_t kDS = desc_kmajor(smem_u32(sm + BwdSmem::DS), TILE_BYTES, 0), kV = desc_kmajor(aV, TILE_BYTES, 0);
 #pragma unroll
-    for (int ks = 0; ks < 8; ++ks)   // dKh^T[dk][j] = sum_dv dS_next[dk][dv] v[j][dv]
-      umma_bf16(tmem + TM_DKH, kslice_kmajor(kDS, TILE_BYTES, ks), kslice_kmajor(kV, TILE_BYTES, ks), iKK, ks > 0);
+      for (int ks = 0; ks < 8; ++ks)   // dKh^T[dk][j] = sum_dv dS_next[dk][dv] v[j][dv]
+        umma_bf16(tmem + TM_DKH, kslice_kmajor(kDS, TILE_BYTES, ks), kslice_kmajor(kV, TILE_BYTES, ks), iKK, ks > 0);
+    } else {
+      const uint64_t mP = desc_mnmajor(smem_u32(sm + BwdSmem::P), TILE_BYTES, 0), mDO = desc_mnmajor(aDO, TILE_BYTES, 0);
+      const uint64_t mKH = desc_mnmajor(smem_u32(sm + BwdSmem::KH), TILE_BYTES, 0), mDS = desc_mnmajor(smem_u32(sm + BwdSmem::DS), TILE_BYTES, 0);
 #pragma unroll
-    for (int ks = 0; ks < 8; ++ks)   // dV[j][dv] = sum_i P[i][j] dO[i][dv]
-      umma_bf16(tmem + TM_DV, kslice_mnmajor(mP, ks), kslice_mnmajor(mDO, ks), iMM, ks > 0);
+      for (int ks = 0; ks < 8; ++ks)   // dV[j][dv] = sum_i P[i][j] dO[i][dv]
+        umma_bf16(tmem + TM_DV, kslice_mnmajor(mP, ks), kslice_mnmajor(mDO, ks), iMM, ks > 0);
 #pragma unroll
-    for (int ks = 0; ks < 8; ++ks)   //          + sum_dk k_hat[j][dk] dS_next[dk][dv]
-      umma_bf16(tmem + TM_DV, kslice_mnmajor(mKH, ks), kslice_mnmajor(mDS, ks), iMM, 1);
+      for (int ks = 0; ks < 8; ++ks)   //          + sum_dk k_hat[j][dk] dS_next[dk][dv]
+        umma_bf16(tmem + TM_DV, kslice_mnmajor(mKH, ks), kslice_mnmajor(mDS, ks), iMM, 1);
+    }
     umma_commit(smem_u32(bars + 0));
   }
+  __syncwarp();
   // This chunk's operands have landed: ask L2 for those of the chunk that the block scheduler will
   // start on this SM when this block retires (pf_dist blocks ahead), so that its load phase streams
   // from L2 while DRAM is busy during everybody's compute phases instead of everybody's load phases.
