@@ -601,14 +601,13 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, 
     tmem_ld32(tmem + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(cg * 32), r);
     tmem_ld_wait();
     bf16* o = out + row0 + (int64_t)(q4 * 32 + lane) * HD + cg * 32;
+    // 64 contiguous bytes of one row per thread, rows of a warp far apart: two 32-byte stores
 #pragma unroll
-    for (int c4 = 0; c4 < 4; ++c4) {
-      uint4 u;
-      u.x = pack_bf16x2(__uint_as_float(r[8 * c4 + 0]), __uint_as_float(r[8 * c4 + 1]));
-      u.y = pack_bf16x2(__uint_as_float(r[8 * c4 + 2]), __uint_as_float(r[8 * c4 + 3]));
-      u.z = pack_bf16x2(__uint_as_float(r[8 * c4 + 4]), __uint_as_float(r[8 * c4 + 5]));
-      u.w = pack_bf16x2(__uint_as_float(r[8 * c4 + 6]), __uint_as_float(r[8 * c4 + 7]));
-      *reinterpret_cast<uint4*>(o + 8 * c4) = u;
+    for (int c8 = 0; c8 < 2; ++c8) {
+      uint32_t u[8];
+#pragma unroll
+      for (int m = 0; m < 8; ++m) u[m] = pack_bf16x2(__uint_as_float(r[16 * c8 + 2 * m]), __uint_as_float(r[16 * c8 + 2 * m + 1]));
+      st_global_v8(o + 16 * c8, u);
     }
   } else if (tid == 0) {
     atomicAdd(&g_tc_wait_timeouts, 1u);
@@ -928,14 +927,14 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
     tmem_ld_wait();
     if (ok) {
       bf16* o = dv_out + row0 + (int64_t)d * HD + 32 * wq_;
+      // a thread owns 64 contiguous bytes of one row; the rows of a warp are far apart, so what counts is the
+      // number of store requests: two 32-byte stores instead of four 16-byte ones
 #pragma unroll
-      for (int c4 = 0; c4 < 4; ++c4) {
-        uint4 u;
-        u.x = pack_bf16x2(__uint_as_float(r[8 * c4 + 0]), __uint_as_float(r[8 * c4 + 1]));
-        u.y = pack_bf16x2(__uint_as_float(r[8 * c4 + 2]), __uint_as_float(r[8 * c4 + 3]));
-        u.z = pack_bf16x2(__uint_as_float(r[8 * c4 + 4]), __uint_as_float(r[8 * c4 + 5]));
-        u.w = pack_bf16x2(__uint_as_float(r[8 * c4 + 6]), __uint_as_float(r[8 * c4 + 7]));
-        *reinterpret_cast<uint4*>(o + 8 * c4) = u;
+      for (int c8 = 0; c8 < 2; ++c8) {
+        uint32_t u[8];
+#pragma unroll
+        for (int m = 0; m < 8; ++m) u[m] = pack_bf16x2(__uint_as_float(r[16 * c8 + 2 * m]), __uint_as_float(r[16 * c8 + 2 * m + 1]));
+        st_global_v8(o + 16 * c8, u);
       }
     }
     if (wq_ == q4) {          // the 32 x 32 diagonal block of dP: pick dP[i][i]

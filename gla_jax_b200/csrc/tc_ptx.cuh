@@ -60,6 +60,12 @@ __host__ __device__ constexpr uint32_t idesc_bf16(int M, int N, int a_mn_major, 
          ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
+// 32-byte global store (sm_100: 256-bit vector stores); p must be 32-byte aligned.
+__device__ __forceinline__ void st_global_v8(void* p, const uint32_t (&r)[8]) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               :: "l"(p), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]) : "memory");
+}
+
 // ---- L2 prefetch --------------------------------------------------------------------------
 // Asks the memory system to bring [p, p + bytes) into L2 (p and bytes multiples of 16); nothing waits on it.
 __device__ __forceinline__ void l2_prefetch_bulk(const void* p, uint32_t bytes) {
