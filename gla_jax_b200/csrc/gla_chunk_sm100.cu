@@ -510,7 +510,6 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, 
       u.x = pack_bf16x2(x[0], x[1]); u.y = pack_bf16x2(x[2], x[3]);
       u.z = pack_bf16x2(x[4], x[5]); u.w = pack_bf16x2(x[6], x[7]);
       *reinterpret_cast<uint4*>(sm + FwdSmem::P + (col0 >> 6) * TILE_BYTES + sw128_chunk(i, (col0 & 63) >> 3)) = u;
-      if (P_saved) *reinterpret_cast<uint4*>(P_saved + (chunk_id * TC + i) * TC + col0) = u;
     };
     // below the diagonal block
     for (int ch = 0; ch < q4; ++ch) {
@@ -590,6 +589,18 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, 
     for (int ks = 0; ks < 8; ++ks)
       umma_bf16(tmem, kslice_kmajor(ap, TILE_BYTES, ks), kslice_mnmajor(bv, ks), idesc, 1);
     umma_commit(smem_u32(bars + 2));
+  }
+  // The saved copy of P goes out from the assembled shared-memory tile while the output product runs: rows are
+  // written whole (a warp stores two full 256-byte rows per instruction) instead of in 16-byte pieces of 32
+  // different rows from the read-back above.
+  if (P_saved) {
+    bf16* pg = P_saved + chunk_id * TC * TC;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int id = tid + TTHREADS * j, row = id >> 4, ch = id & 15;
+      const uint4 u = *reinterpret_cast<const uint4*>(sm + FwdSmem::P + (ch >> 3) * TILE_BYTES + sw128_chunk(row, ch & 7));
+      *reinterpret_cast<uint4*>(pg + row * TC + ch * 8) = u;
+    }
   }
   TC_STAMP(0, 12);
   ok = mbar_wait(smem_u32(bars + 2), 0) && ok;
