@@ -420,14 +420,20 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, 
       const float2 a = unpack_bf16x2(qv[i]), c = unpack_bf16x2(kv[i]);
       part[i] = a.x * c.x + a.y * c.y;
     }
+    // Sum of each of the 16 values over the warp's 32 lanes by a transposing butterfly: at every stage a lane keeps
+    // half of its values and hands the other half to its partner, so 16 + 8 + 4 + 2 + 1 shuffles do what
+    // 16 x 5 would; lanes 2r and 2r + 1 end up with the total of row r.
+    const bool h4 = (lane & 16) != 0, h3 = (lane & 8) != 0, h2 = (lane & 4) != 0, h1 = (lane & 2) != 0;
+    float a8[8], a4[4], a2[2];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1)
+    for (int j = 0; j < 8; ++j) a8[j] = (h4 ? part[j + 8] : part[j]) + __shfl_xor_sync(0xffffffffu, h4 ? part[j] : part[j + 8], 16);
 #pragma unroll
-      for (int i = 0; i < 16; ++i) part[i] += __shfl_xor_sync(0xffffffffu, part[i], o);
-    if (lane == 0) {
+    for (int j = 0; j < 4; ++j) a4[j] = (h3 ? a8[j + 4] : a8[j]) + __shfl_xor_sync(0xffffffffu, h3 ? a8[j] : a8[j + 4], 8);
 #pragma unroll
-      for (int i = 0; i < 16; ++i) diag[(warp & 1) * TC + rg * 16 + i] = part[i];
-    }
+    for (int j = 0; j < 2; ++j) a2[j] = (h2 ? a4[j + 2] : a4[j]) + __shfl_xor_sync(0xffffffffu, h2 ? a4[j] : a4[j + 2], 4);
+    float a1 = (h1 ? a2[1] : a2[0]) + __shfl_xor_sync(0xffffffffu, h1 ? a2[0] : a2[1], 2);
+    a1 += __shfl_xor_sync(0xffffffffu, a1, 1);
+    if ((lane & 1) == 0) diag[(warp & 1) * TC + rg * 16 + (lane >> 1)] = a1;
   }
   __syncthreads();          // raw g and q have been consumed: their regions become the level buffers
   TC_STAMP(0, 2);
