@@ -764,8 +764,8 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
   float* diag = reinterpret_cast<float*>(sm + BwdSmem::DIAG);
   float* dG1 = reinterpret_cast<float*>(sm + BwdSmem::DG1);
   float* dG2 = reinterpret_cast<float*>(sm + BwdSmem::DG2);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + BwdSmem::BAR);   // [0]: phase 1, [1],[2]: level buffers, [3],[4]: pass loads, [5]: tiles
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + BwdSmem::BAR);   // [0]: phase 1, [1],[2]: level buffers, [3],[4]: pass loads, [5]: tiles, [6]: raw k
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int q4 = warp & 3, wq_ = warp >> 2;        // TMEM lane quadrant, and which quarter of the columns
@@ -793,7 +793,16 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
     mbar_init(smem_u32(bars + 3), 1);
     mbar_init(smem_u32(bars + 4), 1);
     mbar_init(smem_u32(bars + 5), 1);
+    mbar_init(smem_u32(bars + 6), 1);
     mbar_fence_init();
+    // raw k of the whole chunk (row-major) into the region that k_hat will occupy: every thread reads its 32
+    // values from there before the barrier that precedes the k_hat stores
+    {
+      const uint32_t kb = smem_u32(bars + 6);
+      mbar_arrive_expect_tx(kb, 2 * TILE_BYTES);
+      tma_load_3d(smem_u32(sm + BwdSmem::KH), &maps.k, 0, (int)hk_, (int)(b * T + n * TC), kb);
+      tma_load_3d(smem_u32(sm + BwdSmem::KH + TILE_BYTES), &maps.k, 0, (int)hk_, (int)(b * T + n * TC) + 64, kb);
+    }
     // the five operand tiles of the chunk by TMA (160 KB in flight); they are first needed by the products, which
     // are issued after the gates and k_hat have been computed, so the copies run under that work
     const uint32_t lb = smem_u32(bars + 5);
@@ -826,6 +835,13 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
     tot[(2 * wq_) * TD + d] = p0;
     tot[(2 * wq_ + 1) * TD + d] = p1;
   }
+  uint32_t kraw[32];                                // k of the same rows and feature, from the staged tile
+  {
+    const bool kok = mbar_wait(smem_u32(bars + 6), 0);
+    const unsigned short* ks = reinterpret_cast<const unsigned short*>(sm + BwdSmem::KH) + (32 * wq_) * TD + d;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) kraw[i] = kok ? ks[i * TD] : 0u;
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -838,10 +854,6 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
     // stored TRANSPOSED: row = feature dk, columns = chunk rows j, so the thread's 32 values are 64
     // contiguous bytes (four 16-byte stores instead of 32 two-byte ones)
     uint8_t* tile = sm + BwdSmem::KH + (wq_ >> 1) * TILE_BYTES;
-    const bf16* kp = k + row0k + (int64_t)(32 * wq_) * HDi + d;
-    uint32_t kraw[32];
-#pragma unroll
-    for (int i = 0; i < 32; ++i) kraw[i] = ldg_u16(kp + (int64_t)i * HDi);
     uint32_t pk[16];
 #pragma unroll
     for (int i = 31; i >= 1; i -= 2) {
