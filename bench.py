@@ -537,10 +537,10 @@ def _alg_tc_bwd(B, T, H, D, C):
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch (bytes), README shape, one ncu capture
 NCU_TRAFFIC_README_SHAPE = {
-    "tc_chunk_bwd_kernel": 366.1e6,
-    "tc_chunk_fwd_kernel": 177.6e6,
-    "tc_state_kernel": 111.2e6,
-    "tc_dstate_scan_kernel": 111.1e6,
+    "tc_chunk_bwd_kernel": 372.5e6,
+    "tc_chunk_fwd_kernel": 179.0e6,
+    "tc_state_kernel": 111.7e6,
+    "tc_dstate_scan_kernel": 111.6e6,
 }
 
 KERNEL_ALGORITHMIC = {
