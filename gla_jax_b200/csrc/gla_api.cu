@@ -210,6 +210,8 @@ int gla_chunk_fwd(void* stream, int64_t B, int64_t T, int64_t H, int64_t D, int6
   const void* ptrs[] = {hidden_init, log_fgate, value, key, query, hidden_final, out, saved, workspace};
   for (const void* p : ptrs)
     if (p && !aligned16(p)) return GLA_ERR_ALIGNMENT;
+  // the tensor-core kernels write rows with 32-byte vector stores
+  if (r == GLA_IMPL_TCGEN05 && (!aligned32(out) || !aligned32(workspace))) return GLA_ERR_ALIGNMENT;
   if (r == GLA_IMPL_TCGEN05)
     return tc_chunk_fwd((cudaStream_t)stream, B, T, H, D, chunk, hidden_init, log_fgate, value, key, query,
                         hidden_final, out, saved, workspace, 0, nullptr, nullptr);
@@ -233,6 +235,7 @@ int gla_chunk_bwd(void* stream, int64_t B, int64_t T, int64_t H, int64_t D, int6
                         dvalue, dkey, dquery, workspace};
   for (const void* p : ptrs)
     if (!aligned16(p)) return GLA_ERR_ALIGNMENT;
+  if (r == GLA_IMPL_TCGEN05 && (!aligned32(dvalue) || !aligned32(workspace))) return GLA_ERR_ALIGNMENT;
   if (r == GLA_IMPL_TCGEN05)
     return tc_chunk_bwd((cudaStream_t)stream, B, T, H, D, chunk, log_fgate, value, key, query, saved, dhidden_final,
                         dout, dhidden_init, dlog_fgate, dvalue, dkey, dquery, workspace);
@@ -253,6 +256,7 @@ int gla_chunk_fwd_packed(void* stream, int64_t T, int64_t H, int64_t D, int64_t 
   const void* ptrs[] = {hidden_init, log_fgate, value, key, query, hidden_final, out, saved, workspace};
   for (const void* p : ptrs)
     if (p && !aligned16(p)) return GLA_ERR_ALIGNMENT;
+  if (!aligned32(out)) return GLA_ERR_ALIGNMENT;
   return tc_chunk_fwd((cudaStream_t)stream, 1, T, H, D, chunk, hidden_init, log_fgate, value, key, query, hidden_final,
                       out, saved, workspace, 0, nullptr, nullptr, nseq, cu_seqlens);
 }
@@ -269,6 +273,11 @@ int gla_chunk_bwd_packed(void* stream, int64_t T, int64_t H, int64_t D, int64_t 
   GLA_TRY(check_chunk_dims(1, T, H, D, chunk, dtype));
   if (!tc_supported_local_state(D, 128, dtype) || chunk % 128 != 0) return GLA_ERR_UNSUPPORTED;
   if (!workspace || workspace_bytes < tc_bwd_ws_bytes(1, T, H, D, chunk)) return GLA_ERR_WORKSPACE;
+  const void* ptrs[] = {log_fgate, value, key, query, saved, dhidden_final, dout, dhidden_init, dlog_fgate, dvalue, dkey,
+                        dquery, workspace};
+  for (const void* p : ptrs)
+    if (!aligned16(p)) return GLA_ERR_ALIGNMENT;
+  if (!aligned32(dvalue)) return GLA_ERR_ALIGNMENT;
   return tc_chunk_bwd((cudaStream_t)stream, 1, T, H, D, chunk, log_fgate, value, key, query, saved, dhidden_final, dout,
                       dhidden_init, dlog_fgate, dvalue, dkey, dquery, workspace, nseq, cu_seqlens);
 }

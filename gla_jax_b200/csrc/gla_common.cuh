@@ -56,6 +56,7 @@ struct ProfScope {
 static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 static inline bool is_pow2(int64_t x) { return x > 0 && (x & (x - 1)) == 0; }
 static inline bool aligned16(const void* p) { return (((uintptr_t)p) & 15) == 0; }
+static inline bool aligned32(const void* p) { return (((uintptr_t)p) & 31) == 0; }
 
 // ---- internal launchers shared between translation units -------------------------------
 

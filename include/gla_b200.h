@@ -46,7 +46,8 @@ typedef enum gla_status {
   GLA_ERR_NULL_POINTER = 1,   /* a required pointer is NULL */
   GLA_ERR_BAD_DIMS = 2,       /* non-positive size, T % chunk != 0, chunk not a power of two, ... */
   GLA_ERR_UNSUPPORTED = 3,    /* dtype / size combination this build has no kernel for */
-  GLA_ERR_ALIGNMENT = 4,      /* a pointer is not 16-byte aligned */
+  GLA_ERR_ALIGNMENT = 4,      /* a pointer is not 16-byte aligned (32-byte for out, dvalue and the workspace of the
+                                 tensor-core chunk path, whose kernels store rows with 32-byte vector stores) */
   GLA_ERR_WORKSPACE = 5,      /* workspace missing or smaller than *_workspace_bytes() */
   GLA_ERR_LAUNCH = 6,         /* the CUDA runtime rejected a launch (see gla_last_cuda_error) */
   GLA_ERR_NO_DEVICE = 7,      /* no usable sm_100 device / driver */

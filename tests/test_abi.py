@@ -55,6 +55,16 @@ def test_validation_without_gpu(lib):
     # misaligned pointer
     q = ctypes.c_void_p(4100)
     assert lib.gla_chunk_fwd(None, 1, 128, 2, 64, 64, 0, 0, q, p, p, p, p, p, p, None, p, 1 << 40) == 4
+    # the tensor-core path (bf16, D = 128) stores rows with 32-byte vector stores: out must be 32-byte aligned
+    o16 = ctypes.c_void_p(4096 + 16)
+    assert lib.gla_chunk_fwd(None, 1, 128, 2, 128, 128, 1, 2, p, p, p, p, p, p, o16, None, p, 1 << 40) == 4
+    assert lib.gla_chunk_bwd(None, 1, 128, 2, 128, 128, 1, 2, p, p, p, p, p, p, p, p, p, o16, p, p, p, 1 << 40) == 4
+    # packed sequences: only the tensor-core shapes; bad sequence count
+    assert lib.gla_chunk_fwd_packed(None, 256, 2, 64, 64, 1, 2, p, p, p, p, p, p, p, p, None, p, 1 << 40) == 3
+    assert lib.gla_chunk_fwd_packed(None, 256, 2, 128, 128, 1, 0, p, p, p, p, p, p, p, p, None, p, 1 << 40) == 2
+    # decode step: null pointer, bad dims
+    assert lib.gla_decode_step(None, 1, 1, 64, 0, None, p, p, p, p, p, 0) == 1
+    assert lib.gla_decode_step(None, 0, 1, 64, 0, p, p, p, p, p, p, 0) == 2
     # workspace sizes are positive and grow with the problem
     a = lib.gla_chunk_fwd_workspace_bytes(1, 128, 2, 64, 64, 0, 0)
     b = lib.gla_chunk_fwd_workspace_bytes(2, 128, 2, 64, 64, 0, 0)
