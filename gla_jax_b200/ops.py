@@ -114,3 +114,32 @@ def rnn_recursive(log_fgate, kv, init_log_fgate: Optional[torch.Tensor] = None,
     """Reference: ops.py:396-456.  Same kernel as ``rnn_pallas``; no length limit."""
     del block_size_t
     return rnn_pallas(log_fgate, kv, init_log_fgate, init_kv, reverse=reverse)
+
+
+def triton_scan(fn, args, axis, init=None, reverse: bool = False):
+    """Host-level counterpart of the reference's generic in-kernel scan (ops.py:82-104):
+    ``out = scan(fn, args)`` along ``axis`` and then ``out = fn(init, out)`` if ``init`` is given.
+
+    The reference traces an arbitrary combine function into Triton; here the two combine rules the
+    reference itself uses are recognised and run on the CUDA scan kernels:
+
+    * addition (``torch.add``, ``operator.add``, or the string ``"add"``) on one array -> the cumsum kernel
+      (any ``axis``);
+    * ``binary_operator`` (or ``"linear_rnn"``) on a pair ``(log_fgate (..., T, K), kv (..., T, K, V))`` scanned
+      along the T axis (``axis`` = 0 for unbatched arrays, 1 with a leading batch axis) -> the linear-RNN kernel,
+      ``init`` being the pair ``(init_log_fgate (K), init_kv (K, V))``.
+
+    Any other function raises ``NotImplementedError`` (there is no tracing compiler behind this library)."""
+    import operator
+    if fn in (torch.add, operator.add, "add"):
+        if isinstance(args, (tuple, list)):
+            raise ValueError("triton_scan(add): expected a single array")
+        return cumsum_pallas(args, axis, init=init, reverse=reverse)
+    if fn is binary_operator or fn == "linear_rnn":
+        log_fgate, kv = args
+        t_axis = kv.dim() - 3
+        if axis not in (t_axis, t_axis - kv.dim()):
+            raise ValueError(f"triton_scan(binary_operator): the scan runs along the time axis ({t_axis})")
+        ig, ikv = (None, None) if init is None else init
+        return rnn_pallas(log_fgate, kv, ig, ikv, reverse=reverse)
+    raise NotImplementedError("triton_scan: only addition and binary_operator are available as CUDA scans")

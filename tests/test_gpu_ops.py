@@ -394,3 +394,24 @@ def test_chunk_gla_packed_rejects_bad_offsets(cuda_device):
     for cu in ([0, 100, 256], [0, 128, 384], [128, 256, 256], [0, 256]):
         with pytest.raises(ValueError):
             chunk_gla_packed(h, g, x, x, x, cu)
+
+
+def test_triton_scan_dispatches_to_the_cuda_scans(cuda_device):
+    """The host-level generic scan recognises the reference's two combine rules (ops.py:161, 318)."""
+    import operator
+    from gla_jax_b200 import triton_scan, binary_operator
+    gen = torch.Generator().manual_seed(61)
+    x = torch.randn(3, 100, 24, generator=gen)
+    init = torch.randn(3, 24, generator=gen)
+    got = triton_scan(operator.add, x.to(cuda_device), axis=1, init=init.to(cuda_device), reverse=True)
+    ref = torch.flip(torch.cumsum(torch.flip(x.double(), [1]), 1), [1]) + init.double().unsqueeze(1)
+    assert O.rel_l2(ref.float(), got.cpu()) < 1e-5
+    g = torch.nn.functional.logsigmoid(torch.randn(50, 16, generator=gen))
+    kv = torch.randn(50, 16, 8, generator=gen)
+    ig, ikv = torch.randn(16, generator=gen).clamp(max=0), torch.randn(16, 8, generator=gen)
+    out_log, out_state = triton_scan(binary_operator, (g.to(cuda_device), kv.to(cuda_device)), axis=0,
+                                     init=(ig.to(cuda_device), ikv.to(cuda_device)))
+    ref_log, ref_state = O.rnn_scan(g.double(), kv.double(), ig.double(), ikv.double())
+    assert O.rel_l2(ref_log.float(), out_log.cpu()) < 1e-5 and O.rel_l2(ref_state.float(), out_state.cpu()) < 1e-5
+    with pytest.raises(NotImplementedError):
+        triton_scan(torch.maximum, x.to(cuda_device), axis=1)
