@@ -60,9 +60,14 @@ static inline bool aligned32(const void* p) { return (((uintptr_t)p) & 31) == 0;
 
 // ---- internal launchers shared between translation units -------------------------------
 
-// Inclusive cumsum along the middle axis of (N, T, D), fp32 math.
+// Inclusive cumsum along the middle axis of (N, T, D), fp32 math.  `sub`, when given, has src's
+// shape and type and is subtracted from it element-wise before the scan.  With `scratch` of
+// cumsum_scratch_bytes(N, T, D) the scan axis is cut into segments that run as separate blocks
+// (segment sums first, then the scans), which fills the device when N * D alone is small.
 int launch_cumsum(cudaStream_t st, int64_t N, int64_t T, int64_t D, const void* src, const void* init,
-                  void* dst, int reverse, int in_bf16, int out_bf16);
+                  void* dst, int reverse, int in_bf16, int out_bf16, const void* sub = nullptr,
+                  float* scratch = nullptr);
+size_t cumsum_scratch_bytes(int64_t N, int64_t T, int64_t D);
 
 // Exclusive state scan over chunks: for every (bh): S <- init; for n in order:
 // before[n] = S; S = exp(G[n]) (x) S + X[n].  final = S.  X, before: (BH, N, D, D);

@@ -47,7 +47,8 @@ struct RecParams {
   void* hidden_final;
   void* out;
   void *dq, *dk, *dv, *dhidden_init;
-  float* E;                  // (B,T,H,D) float32: q dq - k dk
+  float* E;                  // (B,T,H,D) float32: q dq
+  float* F;                  // (B,T,H,D) float32: k dk  (dlog_fgate is a suffix sum of E - F)
   float* boundary;           // (B,H,D) float32: sum_v dS_T * S_T
   int time_reversed;         // process tokens from last to first
 };
@@ -305,7 +306,7 @@ __global__ void __launch_bounds__(rec_threads(D)) rec_kernel(RecParams p) {
           st_any(p.dv, p.bf, addr, r);
         } else {
           st_any(p.dk, p.bf, addr, r);
-          p.E[addr] -= smem[S_BASE + S_OFF + e] * r;
+          p.F[addr] = smem[S_BASE + S_OFF + e] * r;
         }
       }
     }
@@ -377,7 +378,8 @@ int recurrent_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, i
 }
 
 size_t recurrent_bwd_ws_bytes(int64_t B, int64_t T, int64_t H, int64_t D) {
-  return align_up((size_t)B * T * H * D * 4, 256) + align_up((size_t)B * H * D * 4, 256);
+  return 2 * align_up((size_t)B * T * H * D * 4, 256) + align_up((size_t)B * H * D * 4, 256) +
+         align_up(cumsum_scratch_bytes(B, T, H * D), 256);
 }
 
 int recurrent_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, int bf, const void* hidden_init,
@@ -389,14 +391,17 @@ int recurrent_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, i
   p.hidden_init = hidden_init; p.g = g; p.v = v; p.k = k; p.q = q;
   p.dhidden_final = dhidden_final; p.dout = dout;
   p.dq = dq; p.dk = dk; p.dv = dv; p.dhidden_init = dhidden_init;
+  const size_t plane = align_up((size_t)B * T * H * D * 4, 256);
   p.E = (float*)ws;
-  p.boundary = (float*)((char*)ws + align_up((size_t)B * T * H * D * 4, 256));
+  p.F = (float*)((char*)ws + plane);
+  p.boundary = (float*)((char*)ws + 2 * plane);
+  float* seg_sums = (float*)((char*)ws + 2 * plane + align_up((size_t)B * H * D * 4, 256));
   p.time_reversed = reverse;
   GLA_TRY((launch_rec_d<REC_DQ>(st, (int)D, p)));
   GLA_TRY((launch_rec_d<REC_DV>(st, (int)D, p)));
   GLA_TRY((launch_rec_d<REC_DK>(st, (int)D, p)));
-  // dg[t] = sum over the tokens processed at or after t of E, plus the boundary term
-  return launch_cumsum(st, B, T, H * D, p.E, p.boundary, dg, reverse ? 0 : 1, 0, 0);
+  // dg[t] = sum over the tokens processed at or after t of (E - F), plus the boundary term
+  return launch_cumsum(st, B, T, H * D, p.E, p.boundary, dg, reverse ? 0 : 1, 0, 0, p.F, seg_sums);
 }
 
 }  // namespace gla

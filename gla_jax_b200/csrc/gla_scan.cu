@@ -18,27 +18,44 @@ namespace gla {
 constexpr int CS_RPT = 8;    // rows per thread
 constexpr int CS_RL = 8;     // row lanes
 
-template <typename TI, typename TO>
-__global__ void __launch_bounds__(256) cumsum_kernel(const TI* __restrict__ src, const TI* __restrict__ init,
-                                                     TO* __restrict__ dst, int64_t T, int64_t D, int reverse) {
+// The scan axis may be cut into `nseg` segments of `seg_len` positions (in scan order) that run
+// as separate blocks: a first launch with TOTALS = true leaves every segment's column sums in
+// `totals` (N, nseg, D); the second adds the sums of the segments before its own to its carry.
+// nseg = 1 with totals = nullptr is the plain one-pass scan.
+template <typename TI, typename TO, bool TOTALS>
+__global__ void __launch_bounds__(256) cumsum_kernel(const TI* __restrict__ src, const TI* __restrict__ sub,
+                                                     const TI* __restrict__ init, TO* __restrict__ dst, int64_t T,
+                                                     int64_t D, int reverse, int nseg, int64_t seg_len,
+                                                     float* __restrict__ totals) {
   __shared__ float tot[CS_RL][33];
-  const int64_t n = blockIdx.x;
+  const int64_t n = blockIdx.x / nseg;
+  const int seg = (int)(blockIdx.x % nseg);
   const int tx = threadIdx.x, rl = threadIdx.y;
   const int64_t c = (int64_t)blockIdx.y * 32 + tx;
   const bool cvalid = c < D;
-  float carry = (init != nullptr && cvalid) ? ld_f(init, n * D + c) : 0.f;
+  float carry = (!TOTALS && init != nullptr && cvalid) ? ld_f(init, n * D + c) : 0.f;
+  if (!TOTALS && totals != nullptr && cvalid)
+    for (int s2 = 0; s2 < seg; ++s2) carry += totals[(n * nseg + s2) * D + c];
   const TI* s = src + n * T * D;
+  const TI* s2 = sub ? sub + n * T * D : nullptr;   // optional second source, subtracted element-wise
   TO* o = dst + n * T * D;
-  for (int64_t t0 = 0; t0 < T; t0 += CS_RPT * CS_RL) {
+  const int64_t tbeg = (int64_t)seg * seg_len;
+  const int64_t tend = tbeg + seg_len < T ? tbeg + seg_len : T;
+  for (int64_t t0 = tbeg; t0 < tend; t0 += CS_RPT * CS_RL) {
     float x[CS_RPT];
 #pragma unroll
     for (int r = 0; r < CS_RPT; ++r) {
       int64_t tt = t0 + rl * CS_RPT + r;
       int64_t tp = reverse ? (T - 1 - tt) : tt;
-      x[r] = (cvalid && tt < T) ? ld_f(s, tp * D + c) : 0.f;
+      x[r] = (cvalid && tt < tend) ? ld_f(s, tp * D + c) : 0.f;
+      if (s2 && cvalid && tt < tend) x[r] -= ld_f(s2, tp * D + c);
     }
 #pragma unroll
     for (int r = 1; r < CS_RPT; ++r) x[r] += x[r - 1];
+    if (TOTALS) {
+      carry += x[CS_RPT - 1];
+      continue;
+    }
     tot[rl][tx] = x[CS_RPT - 1];
     __syncthreads();
     float off = carry, total = 0.f;
@@ -52,28 +69,69 @@ __global__ void __launch_bounds__(256) cumsum_kernel(const TI* __restrict__ src,
     for (int r = 0; r < CS_RPT; ++r) {
       int64_t tt = t0 + rl * CS_RPT + r;
       int64_t tp = reverse ? (T - 1 - tt) : tt;
-      if (cvalid && tt < T) st_f(o, tp * D + c, x[r] + off);
+      if (cvalid && tt < tend) st_f(o, tp * D + c, x[r] + off);
     }
     carry += total;
     __syncthreads();
   }
+  if (TOTALS) {
+    tot[rl][tx] = carry;
+    __syncthreads();
+    if (rl == 0 && cvalid) {
+      float total = 0.f;
+#pragma unroll
+      for (int r2 = 0; r2 < CS_RL; ++r2) total += tot[r2][tx];
+      totals[(n * nseg + seg) * D + c] = total;
+    }
+  }
+}
+
+// Segments for a scan of N rows of length T: enough blocks to fill the device when N alone
+// gives too few, but never segments shorter than 256 positions.
+static int cumsum_segments(int64_t N, int64_t T, int64_t D) {
+  const int64_t blocks = N * ((D + 31) / 32);
+  const int64_t want = (4 * 148 + blocks - 1) / blocks;
+  int64_t nseg = want < 1 ? 1 : want;
+  if (nseg > T / 256) nseg = T / 256;
+  if (nseg < 1) nseg = 1;
+  if (nseg > 64) nseg = 64;
+  return (int)nseg;
+}
+
+size_t cumsum_scratch_bytes(int64_t N, int64_t T, int64_t D) {
+  return (size_t)N * cumsum_segments(N, T, D) * D * sizeof(float);
+}
+
+template <typename TI, typename TO>
+static void cumsum_dispatch(cudaStream_t st, dim3 grid, dim3 block, const void* src, const void* sub,
+                            const void* init, void* dst, int64_t T, int64_t D, int reverse, int nseg,
+                            int64_t seg_len, float* totals) {
+  if (nseg > 1)
+    cumsum_kernel<TI, TO, true><<<grid, block, 0, st>>>((const TI*)src, (const TI*)sub, (const TI*)init, (TO*)dst, T, D,
+                                                         reverse, nseg, seg_len, totals);
+  cumsum_kernel<TI, TO, false><<<grid, block, 0, st>>>((const TI*)src, (const TI*)sub, (const TI*)init, (TO*)dst, T, D,
+                                                        reverse, nseg, seg_len, nseg > 1 ? totals : nullptr);
 }
 
 int launch_cumsum(cudaStream_t st, int64_t N, int64_t T, int64_t D, const void* src, const void* init,
-                  void* dst, int reverse, int in_bf16, int out_bf16) {
+                  void* dst, int reverse, int in_bf16, int out_bf16, const void* sub, float* scratch) {
   if (N <= 0 || T <= 0 || D <= 0) return GLA_ERR_BAD_DIMS;
   int64_t gy = (D + 31) / 32;
-  if (gy > 65535 || N > 2147483647LL) return GLA_ERR_TOO_LARGE;
-  dim3 grid((unsigned)N, (unsigned)gy), block(32, CS_RL);
+  // without scratch for the segment sums the scan runs in one pass, one block per row and column group
+  const int nseg = scratch ? cumsum_segments(N, T, D) : 1;
+  int64_t seg_len = (T + nseg - 1) / nseg;
+  seg_len = (seg_len + CS_RPT * CS_RL - 1) / (CS_RPT * CS_RL) * (CS_RPT * CS_RL);
+  if (gy > 65535 || N * nseg > 2147483647LL) return GLA_ERR_TOO_LARGE;
+  dim3 grid((unsigned)(N * nseg), (unsigned)gy), block(32, CS_RL);
   ProfScope ps("cumsum_kernel", st);
   if (!in_bf16 && !out_bf16)
-    cumsum_kernel<float, float><<<grid, block, 0, st>>>((const float*)src, (const float*)init, (float*)dst, T, D, reverse);
+    cumsum_dispatch<float, float>(st, grid, block, src, sub, init, dst, T, D, reverse, nseg, seg_len, scratch);
   else if (!in_bf16 && out_bf16)
-    cumsum_kernel<float, bf16><<<grid, block, 0, st>>>((const float*)src, (const float*)init, (bf16*)dst, T, D, reverse);
+    cumsum_dispatch<float, bf16>(st, grid, block, src, sub, init, dst, T, D, reverse, nseg, seg_len, scratch);
   else if (in_bf16 && !out_bf16)
-    cumsum_kernel<bf16, float><<<grid, block, 0, st>>>((const bf16*)src, (const bf16*)init, (float*)dst, T, D, reverse);
+    cumsum_dispatch<bf16, float>(st, grid, block, src, sub, init, dst, T, D, reverse, nseg, seg_len, scratch);
   else
-    cumsum_kernel<bf16, bf16><<<grid, block, 0, st>>>((const bf16*)src, (const bf16*)init, (bf16*)dst, T, D, reverse);
+    cumsum_dispatch<bf16, bf16>(st, grid, block, src, sub, init, dst, T, D, reverse, nseg, seg_len, scratch);
   GLA_CHECK_LAUNCH();
   return GLA_OK;
 }

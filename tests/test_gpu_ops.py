@@ -190,6 +190,8 @@ def test_tcgen05_matches_recurrent_at_readme_shape(cuda_device):
     (1, 64, 1, 256, torch.float32, 0.0, False),
     (2, 256, 2, 128, torch.bfloat16, 5.0, False),
     (1, 128, 2, 64, torch.bfloat16, 0.0, True),
+    (1, 841, 2, 32, torch.float32, 5.0, False),          # long enough that the dlog_fgate scan runs in segments
+    (1, 600, 1, 64, torch.float32, 5.0, True),
 ])
 def test_recurrent_gla_vs_oracle(cuda_device, B, T, H, D, dtype, shift, reverse):
     from gla_jax_b200 import recurrent_gla
