@@ -53,6 +53,31 @@ struct RecParams {
   int time_reversed;         // process tokens from last to first
 };
 
+// Packed pairs of float32 in one 64-bit register: Blackwell's two-wide FMA halves the issue slots
+// of the state update, which is what bounds these kernels (few warps per SM, long straight-line steps).
+#ifndef REC_X2
+#define REC_X2 1
+#endif
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 x2_pack(float lo, float hi) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void x2_unpack(f32x2 v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 x2_fma(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ f32x2 x2_mul(f32x2 a, f32x2 b) {
+  f32x2 r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+
 // Sum over the LP consecutive lanes of a lane group.
 template <int LP>
 __device__ __forceinline__ float reduce_lanes(float x) {
@@ -207,6 +232,14 @@ __global__ void __launch_bounds__(rec_threads(D)) rec_kernel(RecParams p) {
     for (int a = 0; a < NS; ++a) tile_fetch<RS, SG, RTHREADS>(sreg[a], Ssrc[a], base, HD, step0, T, trev, c0);
   };
   fetch(0);
+#if REC_X2
+  // the state as pairs along the long axis: st2[i][j] = (st[2i][j], st[2i+1][j])
+  f32x2 st2[KP / 2][NSI];
+#pragma unroll
+  for (int i = 0; i < KP / 2; ++i)
+#pragma unroll
+    for (int j = 0; j < NSI; ++j) st2[i][j] = x2_pack(st[2 * i][j], st[2 * i + 1][j]);
+#endif
   for (int64_t step0 = 0; step0 < T; step0 += RB) {
     __syncthreads();   // previous block's readers of the tiles and of Rs are done
 #pragma unroll
@@ -217,6 +250,66 @@ __global__ void __launch_bounds__(rec_threads(D)) rec_kernel(RecParams p) {
     if (step0 + RB < T) fetch(step0 + RB);
     const int nt = (int)((T - step0) < RB ? (T - step0) : RB);
     // One step of the recurrence for this thread's state; returns the four per-step sums (not yet reduced).
+#if REC_X2
+    auto step = [&](int tt, float (&red)[NSI]) {
+      f32x2 red2[NSI], s0d[NSI], s1d[NSI], s2d[NSI];
+      // the step's slice-axis scalars, each broadcast to both halves of a pair (duplicating them in
+      // shared memory instead costs more in extra shared-memory loads than the moves do here)
+#pragma unroll
+      for (int j = 0; j < NSI; ++j) {
+        red2[j] = 0ull;
+        const float s0 = smem[S_BASE + tt * RS + NSI * sg + j];
+        s0d[j] = x2_pack(s0, s0);
+        if (NS == 3) {
+          const float s1 = smem[S_BASE + S_OFF + tt * RS + NSI * sg + j];
+          const float s2 = smem[S_BASE + 2 * S_OFF + tt * RS + NSI * sg + j];
+          s1d[j] = x2_pack(s1, s1);
+          s2d[j] = x2_pack(s2, s2);
+        } else {
+          s1d[j] = 0ull; s2d[j] = 0ull;
+        }
+      }
+#pragma unroll
+      for (int m = 0; m < KP / 4; ++m) {
+        const int off = tt * D + 4 * LP * m + 4 * lp;
+        const ulonglong2 a4 = *reinterpret_cast<const ulonglong2*>(smem + off);
+        const ulonglong2 b4 = *reinterpret_cast<const ulonglong2*>(smem + L_OFF + off);
+        ulonglong2 c4 = make_ulonglong2(0ull, 0ull);
+        if (NL == 3) c4 = *reinterpret_cast<const ulonglong2*>(smem + 2 * L_OFF + off);
+        const f32x2 av[2] = {a4.x, a4.y};
+        const f32x2 bv[2] = {b4.x, b4.y};
+        const f32x2 cv[2] = {c4.x, c4.y};
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+#pragma unroll
+          for (int j = 0; j < NSI; ++j) {
+            f32x2& S = st2[2 * m + e][j];
+            if (MODE == REC_FWD) {          // a = f, b = k, c = q ; s0 = v
+              S = x2_fma(av[e], S, x2_mul(bv[e], s0d[j]));
+              red2[j] = x2_fma(cv[e], S, red2[j]);
+            } else if (MODE == REC_DQ) {    // a = v, b = dO ; s0 = f, s1 = k
+              S = x2_fma(s0d[j], S, x2_mul(s1d[j], av[e]));
+              red2[j] = x2_fma(bv[e], S, red2[j]);
+            } else if (MODE == REC_DV) {    // a = f, b = k, c = q ; s0 = dO
+              const f32x2 tmp = x2_fma(cv[e], s0d[j], S);
+              red2[j] = x2_fma(bv[e], tmp, red2[j]);
+              S = x2_mul(av[e], tmp);
+            } else {                        // a = v, b = dO ; s0 = f, s1 = k, s2 = q
+              const f32x2 tmp = x2_fma(s2d[j], bv[e], S);
+              red2[j] = x2_fma(av[e], tmp, red2[j]);
+              S = x2_mul(s0d[j], tmp);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < NSI; ++j) {
+        float lo, hi;
+        x2_unpack(red2[j], lo, hi);
+        red[j] = lo + hi;
+      }
+    };
+#else
     auto step = [&](int tt, float (&red)[NSI]) {
 #pragma unroll
       for (int j = 0; j < NSI; ++j) red[j] = 0.f;
@@ -262,6 +355,7 @@ __global__ void __launch_bounds__(rec_threads(D)) rec_kernel(RecParams p) {
         }
       }
     };
+#endif
     // The block's steps are fully unrolled with the reduced sums kept in registers until the end: with no
     // shared-memory store between the steps the compiler is free to issue a step's loads and FMAs while the
     // previous step's shuffle chain is still in flight (an in-order warp otherwise waits out every chain).
@@ -311,6 +405,12 @@ __global__ void __launch_bounds__(rec_threads(D)) rec_kernel(RecParams p) {
       }
     }
   }
+#if REC_X2
+#pragma unroll
+  for (int i = 0; i < KP / 2; ++i)
+#pragma unroll
+    for (int j = 0; j < NSI; ++j) x2_unpack(st2[i][j], st[2 * i][j], st[2 * i + 1][j]);
+#endif
   // final state
   if (MODE == REC_FWD) {
     if (p.hidden_final) {
