@@ -170,7 +170,7 @@ __device__ __forceinline__ void tile_commit(float* sm, const uint4 (&raw)[NG], i
 }
 
 template <int D, int MODE>
-__global__ void __launch_bounds__(rec_threads(D)) rec_kernel(RecParams p) {
+__device__ __forceinline__ void rec_body(const RecParams& p, const int64_t b) {
   constexpr int LP = rec_lanes(D), RTHREADS = rec_threads(D);
   constexpr int KP = D / LP;                      // long entries per thread (x NSI slice entries of state)
   constexpr int NL = (MODE == REC_FWD || MODE == REC_DV) ? 3 : 2;   // long tiles
@@ -184,7 +184,7 @@ __global__ void __launch_bounds__(rec_threads(D)) rec_kernel(RecParams p) {
 
   const int lp = threadIdx.x % LP, sg = threadIdx.x / LP;     // lane on the long axis, group of NSI slice entries
   const int c0 = blockIdx.x * RS;                 // slice window
-  const int64_t h = blockIdx.y, b = blockIdx.z;
+  const int64_t h = blockIdx.y;
   const int64_t T = p.T, HD = p.H * D;
   const int64_t base = (b * T * p.H + h) * D;     // element (b, 0, h, 0)
   const int64_t hbase = (b * p.H + h) * (int64_t)D * D;
@@ -441,31 +441,65 @@ __global__ void __launch_bounds__(rec_threads(D)) rec_kernel(RecParams p) {
 }
 
 template <int D, int MODE>
-static int launch_rec(cudaStream_t st, const RecParams& p) {
-  constexpr int NL = (MODE == REC_FWD || MODE == REC_DV) ? 3 : 2;
-  constexpr int NS = (MODE == REC_FWD || MODE == REC_DV) ? 1 : 3;
-  const size_t smem = (size_t)(NL * RB * D + NS * RB * RS + RB * RS) * sizeof(float);
+__global__ void __launch_bounds__(rec_threads(D)) rec_kernel(RecParams p) {
+  rec_body<D, MODE>(p, blockIdx.z);
+}
+
+// The three passes of the backward in one grid (blockIdx.z = 3 b + pass).  They are independent of
+// one another, and one pass alone leaves each scheduler with one or two warps: side by side, two
+// CTAs of different passes share an SM and fill each other's issue gaps.
+template <int D>
+__global__ void __launch_bounds__(rec_threads(D)) rec_bwd_kernel(RecParams p) {
+  const int pass = blockIdx.z % 3;
+  const int64_t b = blockIdx.z / 3;
+  if (pass == 0) rec_body<D, REC_DV>(p, b);
+  else if (pass == 1) rec_body<D, REC_DQ>(p, b);
+  else rec_body<D, REC_DK>(p, b);
+}
+
+template <int MODE>
+constexpr size_t rec_smem_bytes(int D) {
+  return (size_t)(((MODE == REC_FWD || MODE == REC_DV) ? 3 : 2) * RB * D +
+                  ((MODE == REC_FWD || MODE == REC_DV) ? 1 : 3) * RB * RS + RB * RS) * sizeof(float);
+}
+
+template <int D>
+static int launch_rec_fwd(cudaStream_t st, const RecParams& p) {
+  const size_t smem = rec_smem_bytes<REC_FWD>(D);
   if (p.H > 65535 || p.B > 65535) return GLA_ERR_TOO_LARGE;
-  cudaError_t e = cudaFuncSetAttribute(rec_kernel<D, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  cudaError_t e = cudaFuncSetAttribute(rec_kernel<D, REC_FWD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return record_cuda_error(e);
   dim3 grid(D / RS, (unsigned)p.H, (unsigned)p.B);
-  static const char* names[4] = {"rec_kernel_fwd", "rec_kernel_dq", "rec_kernel_dv", "rec_kernel_dk"};
-  ProfScope ps(names[MODE], st);
-  rec_kernel<D, MODE><<<grid, rec_threads(D), smem, st>>>(p);
+  ProfScope ps("rec_kernel_fwd", st);
+  rec_kernel<D, REC_FWD><<<grid, rec_threads(D), smem, st>>>(p);
   GLA_CHECK_LAUNCH();
   return GLA_OK;
 }
 
-template <int MODE>
-static int launch_rec_d(cudaStream_t st, int D, const RecParams& p) {
-  switch (D) {
-    case 32: return launch_rec<32, MODE>(st, p);
-    case 64: return launch_rec<64, MODE>(st, p);
-    case 128: return launch_rec<128, MODE>(st, p);
-    case 256: return launch_rec<256, MODE>(st, p);
-    default: return GLA_ERR_UNSUPPORTED;
-  }
+template <int D>
+static int launch_rec_bwd(cudaStream_t st, const RecParams& p) {
+  const size_t a = rec_smem_bytes<REC_DV>(D), c = rec_smem_bytes<REC_DQ>(D);
+  const size_t smem = a > c ? a : c;
+  if (p.H > 65535 || 3 * p.B > 65535) return GLA_ERR_TOO_LARGE;
+  cudaError_t e = cudaFuncSetAttribute(rec_bwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return record_cuda_error(e);
+  dim3 grid(D / RS, (unsigned)p.H, (unsigned)(3 * p.B));
+  ProfScope ps("rec_bwd_kernel", st);
+  rec_bwd_kernel<D><<<grid, rec_threads(D), smem, st>>>(p);
+  GLA_CHECK_LAUNCH();
+  return GLA_OK;
 }
+
+#define REC_DISPATCH_D(fn, st, D, p)          \
+  switch (D) {                                \
+    case 32: return fn<32>(st, p);            \
+    case 64: return fn<64>(st, p);            \
+    case 128: return fn<128>(st, p);          \
+    case 256: return fn<256>(st, p);          \
+    default: return GLA_ERR_UNSUPPORTED;      \
+  }
+static int launch_rec_fwd_d(cudaStream_t st, int D, const RecParams& p) { REC_DISPATCH_D(launch_rec_fwd, st, D, p) }
+static int launch_rec_bwd_d(cudaStream_t st, int D, const RecParams& p) { REC_DISPATCH_D(launch_rec_bwd, st, D, p) }
 
 int recurrent_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, int bf, const void* hidden_init,
                   const float* g, const void* v, const void* k, const void* q, void* hidden_final, void* out,
@@ -474,7 +508,7 @@ int recurrent_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, i
   p.B = B; p.T = T; p.H = H; p.bf = bf; p.out_bf = out_bf;
   p.hidden_init = hidden_init; p.g = g; p.v = v; p.k = k; p.q = q;
   p.hidden_final = hidden_final; p.out = out; p.time_reversed = reverse;
-  return launch_rec_d<REC_FWD>(st, (int)D, p);
+  return launch_rec_fwd_d(st, (int)D, p);
 }
 
 size_t recurrent_bwd_ws_bytes(int64_t B, int64_t T, int64_t H, int64_t D) {
@@ -497,9 +531,7 @@ int recurrent_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, i
   p.boundary = (float*)((char*)ws + 2 * plane);
   float* seg_sums = (float*)((char*)ws + 2 * plane + align_up((size_t)B * H * D * 4, 256));
   p.time_reversed = reverse;
-  GLA_TRY((launch_rec_d<REC_DQ>(st, (int)D, p)));
-  GLA_TRY((launch_rec_d<REC_DV>(st, (int)D, p)));
-  GLA_TRY((launch_rec_d<REC_DK>(st, (int)D, p)));
+  GLA_TRY(launch_rec_bwd_d(st, (int)D, p));
   // dg[t] = sum over the tokens processed at or after t of (E - F), plus the boundary term
   return launch_cumsum(st, B, T, H * D, p.E, p.boundary, dg, reverse ? 0 : 1, 0, 0, p.F, seg_sums);
 }
