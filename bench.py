@@ -54,6 +54,119 @@ def bytes_per_token_head(D):
     return 34 * D
 
 
+def bench_layer(args, lib, dev, rank, world, local_rank, W, K):
+    """The GLA layer around the op (projections, gate stage, chunk_gla, norm + output gate, projection), forward and
+    backward, at the README op shape with d_model = H * D.  Reported: layer tokens/s and, per element-wise stage
+    kernel, the achieved HBM bandwidth (algorithmic bytes: what the stage must read and write once)."""
+    import torch
+    import torch.distributed as dist
+    from gla_jax_b200 import GLALayer
+    B, T, H, D = 4, 4096, 6, 128
+    d_model = H * D
+    torch.manual_seed(1000 * rank + 3)
+    layer = GLALayer(d_model, H, head_dim=D, chunk_size=128, device=dev, dtype=torch.bfloat16)
+    xs = [torch.randn(B, T, d_model, device=dev).to(torch.bfloat16).requires_grad_(True) for _ in range(2)]
+
+    def step(i):
+        x = xs[i % 2]
+        y, hf = layer(x)
+        (y.float().sum() + hf.float().sum()).backward()
+        x.grad = None
+        layer.zero_grad(set_to_none=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(W):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(K):
+        step(i)
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    launches0 = lib.gla_launch_count()
+    for i in range(K):
+        step(i)
+    barrier()
+    launches = lib.gla_launch_count() - launches0
+    # the four element-wise stage kernels, timed one by one through the C ABI on two rotating buffer sets
+    # (2 x ~250 MB > L2); the backward of a layer step runs on autograd's own thread, so per-launch events
+    # bracketed inside the library on this thread would only see the forward half
+    from gla_jax_b200 import _lib
+    n_el = B * T * H * D
+    rows = B * T * H
+    mkb = lambda: torch.randn(B, T, H, D, device=dev).to(torch.bfloat16)
+    sets = [dict(z=mkb(), x=mkb(), gate=mkb(), dy=mkb(), y=mkb(), dx=mkb(), dgate=mkb(), dz=mkb(),
+                 g=torch.empty(B, T, H, D, device=dev), dg=torch.randn(B, T, H, D, device=dev),
+                 rstd=torch.empty(rows, device=dev)) for _ in range(2)]
+    w = torch.ones(D, device=dev)
+    dw = torch.empty(D, device=dev)
+    ws_n = lib.gla_layer_headnorm_gate_bwd_workspace_bytes(rows, D)
+    ws = torch.empty(ws_n, dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    BF = _lib.GLA_BF16
+    calls = {
+        "gate_fwd_kernel": lambda a: lib.gla_layer_gate_fwd(stream, n_el, BF, a["z"].data_ptr(), 1 / 16, a["g"].data_ptr()),
+        "gate_bwd_kernel": lambda a: lib.gla_layer_gate_bwd(stream, n_el, BF, a["z"].data_ptr(), a["dg"].data_ptr(), 1 / 16,
+                                                            a["dz"].data_ptr()),
+        "headnorm_gate_fwd_kernel": lambda a: lib.gla_layer_headnorm_gate_fwd(
+            stream, rows, D, BF, a["x"].data_ptr(), a["gate"].data_ptr(), w.data_ptr(), 1e-5, a["y"].data_ptr(),
+            a["rstd"].data_ptr()),
+        "headnorm_gate_bwd_kernel": lambda a: lib.gla_layer_headnorm_gate_bwd(
+            stream, rows, D, BF, a["x"].data_ptr(), a["gate"].data_ptr(), w.data_ptr(), a["rstd"].data_ptr(),
+            a["dy"].data_ptr(), a["dx"].data_ptr(), a["dgate"].data_ptr(), dw.data_ptr(), ws.data_ptr(), ws_n),
+    }
+    kern = {}
+    for name, fn in calls.items():
+        for i in range(4):
+            _lib.check(fn(sets[i % 2]), name)
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(2 * K)]
+        for i, (a, b) in enumerate(evs):
+            a.record()
+            _lib.check(fn(sets[i % 2]), name)
+            b.record()
+        torch.cuda.synchronize()
+        kern[name] = (len(evs), sum(a.elapsed_time(b) for a, b in evs))
+    sampler.stop_flag = True
+    sampler.join(timeout=1.0)
+    t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total = float(t[0])
+    if rank == 0:
+        peaks = load_peaks()
+        stage_bytes = {"gate_fwd_kernel": 6, "gate_bwd_kernel": 8, "headnorm_gate_fwd_kernel": 6,
+                       "headnorm_gate_bwd_kernel": 10}
+        stages = {}
+        for name, per_el in stage_bytes.items():
+            if name in kern and kern[name][0]:
+                per = kern[name][1] / kern[name][0] * 1e-3
+                stages[name] = {"ms_per_launch": per * 1e3, "achieved_gbs": per_el * n_el / per / 1e9,
+                                "frac_of_measured_copy": per_el * n_el / per / 1e9 / peaks["hbm"]}
+        top = max(stages, key=lambda k: stages[k]["ms_per_launch"]) if stages else None
+        print(json.dumps({
+            "metric": "GLA layer fwd+bwd tokens/sec", "value": B * T * world * K / (ms_total * 1e-3), "unit": "tokens/s",
+            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_total / K, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"GLA layer: B={B},T={T},d_model={d_model},H={H},D={D},chunk=128, bf16 parameters "
+                                   "and activations, float32 log_fgate; loss=y.sum()+hidden_final.sum()",
+                       "l2": "2 rotating inputs; one step touches > 1 GB (L2 = 126 MB)", "launch": "plain launches"},
+            "gpu_launches": launches, "clocks": sampler.summary(),
+            "roofline": None if top is None else {
+                "bound": "hbm", "kernel": top, "achieved": stages[top]["achieved_gbs"], "peak": peaks["hbm"],
+                "unit": "GB/s", "frac": stages[top]["frac_of_measured_copy"], "traffic": None,
+                "peak_source": peaks["source"]},
+            "layer_stages": stages,
+        }))
+
+
 def bench_decode(args, lib, dev, rank, world, local_rank, W, K):
     """Single-token step: B requests x H heads advance one token per step; the (B,H,D,D) float32 states live on the
     device.  tokens/s = requests advanced per second; the step streams the state once in and once out."""
@@ -254,7 +367,7 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (for profiler runs)")
     ap.add_argument("--no-graph", action="store_true", help="time plain launches instead of CUDA-graph replays")
-    ap.add_argument("--op", default="chunk_gla", choices=["chunk_gla", "recurrent_gla", "decode"],
+    ap.add_argument("--op", default="chunk_gla", choices=["chunk_gla", "recurrent_gla", "decode", "layer"],
                     help="chunk_gla is the headline metric; recurrent_gla times the exact recurrence on the same shape; "
                          "decode times the single-token step with a persistent state (128 requests x 16 heads x 128)")
     args = ap.parse_args()
@@ -280,8 +393,8 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     W = max(args.warmup, 3)
     K = args.steps
-    if args.op == "decode":
-        bench_decode(args, lib, dev, rank, world, local_rank, W, K)
+    if args.op in ("decode", "layer"):
+        (bench_decode if args.op == "decode" else bench_layer)(args, lib, dev, rank, world, local_rank, W, K)
         if world > 1:
             dist.destroy_process_group()
         return

@@ -36,6 +36,13 @@ SIGNATURES = {
                                   c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int]),
     "gla_decode_step": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_void_p, c_void_p, c_int]),
+    "gla_layer_gate_fwd": (c_int, [c_void_p, c_int64, c_int, c_void_p, ctypes.c_float, c_void_p]),
+    "gla_layer_gate_bwd": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p, ctypes.c_float, c_void_p]),
+    "gla_layer_headnorm_gate_fwd": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p,
+                                            ctypes.c_float, c_void_p, c_void_p]),
+    "gla_layer_headnorm_gate_bwd_workspace_bytes": (c_size_t, [c_int64, c_int64]),
+    "gla_layer_headnorm_gate_bwd": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                            c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t]),
     "gla_recurrent_bwd_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int64, c_int]),
     "gla_recurrent_bwd": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p,
                                   c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,

@@ -16,7 +16,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libgla_b200.so"
-SOURCES = ["gla_api.cu", "gla_scan.cu", "gla_simt.cu", "gla_recurrent.cu", "gla_chunk_sm100.cu", "gla_state_sm100.cu", "gla_static.cu", "gla_decode.cu"]
+SOURCES = ["gla_api.cu", "gla_scan.cu", "gla_simt.cu", "gla_recurrent.cu", "gla_chunk_sm100.cu", "gla_state_sm100.cu", "gla_static.cu", "gla_decode.cu", "gla_layer.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

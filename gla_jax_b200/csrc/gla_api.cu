@@ -1,5 +1,6 @@
 // C ABI of libgla_b200.so: argument validation and dispatch.  See include/gla_b200.h for
 // the contract of every entry point and the reference operator it replaces.
+#include <atomic>
 #include "gla_common.cuh"
 #include <cstdio>
 
@@ -14,8 +15,8 @@ int record_cuda_error(cudaError_t e) {
 }
 
 // ---- launch counter and optional per-kernel event timing (thread-local) -----------------
-static thread_local long long g_launches = 0;
-void count_launch() { ++g_launches; }
+static std::atomic<long long> g_launches{0};   // process-wide: autograd runs backward launches on its own thread
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 struct ProfRec { const char* name; cudaEvent_t a, b; };
 static thread_local bool g_prof_on = false;
@@ -79,7 +80,7 @@ const char* gla_version(void) { return "gla_b200 0.1 (sm_100a)"; }
 
 int gla_last_cuda_error(void) { return g_last_cuda_error; }
 
-long long gla_launch_count(void) { return g_launches; }
+long long gla_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 unsigned int gla_device_wait_timeouts(void) { return tc_read_wait_timeouts() + tc_state_read_wait_timeouts(); }
 
@@ -152,6 +153,51 @@ int gla_decode_step(void* stream, int64_t B, int64_t H, int64_t D, int dtype, fl
   GLA_TRY(check_dtype(out_dtype));
   return decode_step((cudaStream_t)stream, B, H, D, dtype == GLA_BF16, state, log_fgate, value, key, query, out,
                      out_dtype == GLA_BF16);
+}
+
+int gla_layer_gate_fwd(void* stream, int64_t n, int dtype, const void* z, float inv_tau, float* log_fgate) {
+  if (!z || !log_fgate) return GLA_ERR_NULL_POINTER;
+  if (n <= 0) return GLA_ERR_BAD_DIMS;
+  GLA_TRY(check_dtype(dtype));
+  return layer_gate_fwd((cudaStream_t)stream, n, dtype == GLA_BF16, z, inv_tau, log_fgate);
+}
+
+int gla_layer_gate_bwd(void* stream, int64_t n, int dtype, const void* z, const float* dlog_fgate, float inv_tau,
+                       void* dz) {
+  if (!z || !dlog_fgate || !dz) return GLA_ERR_NULL_POINTER;
+  if (n <= 0) return GLA_ERR_BAD_DIMS;
+  GLA_TRY(check_dtype(dtype));
+  return layer_gate_bwd((cudaStream_t)stream, n, dtype == GLA_BF16, z, dlog_fgate, inv_tau, dz);
+}
+
+static int check_head_dim(int64_t D) { return (D == 32 || D == 64 || D == 128 || D == 256) ? GLA_OK : GLA_ERR_UNSUPPORTED; }
+
+int gla_layer_headnorm_gate_fwd(void* stream, int64_t rows, int64_t D, int dtype, const void* x, const void* gate,
+                                const float* weight, float eps, void* y, float* rstd) {
+  if (!x || !gate || !y || !rstd) return GLA_ERR_NULL_POINTER;
+  if (rows <= 0 || D <= 0) return GLA_ERR_BAD_DIMS;
+  GLA_TRY(check_dtype(dtype));
+  GLA_TRY(check_head_dim(D));
+  if (!aligned16(x) || !aligned16(gate) || !aligned16(y)) return GLA_ERR_ALIGNMENT;
+  return layer_headnorm_gate_fwd((cudaStream_t)stream, rows, D, dtype == GLA_BF16, x, gate, weight, eps, y, rstd);
+}
+
+size_t gla_layer_headnorm_gate_bwd_workspace_bytes(int64_t rows, int64_t D) {
+  if (rows <= 0 || D <= 0) return 0;
+  return layer_headnorm_gate_bwd_ws_bytes(rows, D);
+}
+
+int gla_layer_headnorm_gate_bwd(void* stream, int64_t rows, int64_t D, int dtype, const void* x, const void* gate,
+                                const float* weight, const float* rstd, const void* dy, void* dx, void* dgate,
+                                float* dweight, void* workspace, size_t workspace_bytes) {
+  if (!x || !gate || !rstd || !dy || !dx || !dgate) return GLA_ERR_NULL_POINTER;
+  if (rows <= 0 || D <= 0) return GLA_ERR_BAD_DIMS;
+  GLA_TRY(check_dtype(dtype));
+  GLA_TRY(check_head_dim(D));
+  if (!aligned16(x) || !aligned16(gate) || !aligned16(dy) || !aligned16(dx) || !aligned16(dgate)) return GLA_ERR_ALIGNMENT;
+  if (dweight && (!workspace || workspace_bytes < layer_headnorm_gate_bwd_ws_bytes(rows, D))) return GLA_ERR_WORKSPACE;
+  return layer_headnorm_gate_bwd((cudaStream_t)stream, rows, D, dtype == GLA_BF16, x, gate, weight, rstd, dy, dx, dgate,
+                                 dweight, workspace);
 }
 
 size_t gla_recurrent_bwd_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int dtype) {

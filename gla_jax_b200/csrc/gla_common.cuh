@@ -80,6 +80,16 @@ int launch_state_scan(cudaStream_t st, int64_t BH, int64_t N, int64_t D, const f
 int decode_step(cudaStream_t st, int64_t B, int64_t H, int64_t D, int bf, float* state, const float* g, const void* v,
                 const void* k, const void* q, void* out, int out_bf);
 
+// Element-wise stages of a GLA layer either side of the op.
+int layer_gate_fwd(cudaStream_t st, int64_t n, int bf, const void* z, float inv_tau, float* g);
+int layer_gate_bwd(cudaStream_t st, int64_t n, int bf, const void* z, const float* dg, float inv_tau, void* dz);
+int layer_headnorm_gate_fwd(cudaStream_t st, int64_t rows, int64_t D, int bf, const void* x, const void* gate,
+                            const float* w, float eps, void* y, float* rstd);
+size_t layer_headnorm_gate_bwd_ws_bytes(int64_t rows, int64_t D);
+int layer_headnorm_gate_bwd(cudaStream_t st, int64_t rows, int64_t D, int bf, const void* x, const void* gate,
+                            const float* w, const float* rstd, const void* dy, void* dx, void* dgate, float* dweight,
+                            void* ws);
+
 // fp32 CUDA-core chunk path.
 size_t simt_saved_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t C);
 size_t simt_fwd_ws_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t C);

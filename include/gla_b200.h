@@ -76,8 +76,8 @@ GLA_API const char* gla_version(void);
 /* cudaError_t value of the most recent failed launch on the calling thread (0 if none). */
 GLA_API int gla_last_cuda_error(void);
 
-/* Number of kernels this library has launched from the calling thread since load
- * (monotonic).  Diagnostic; the reference has no counterpart. */
+/* Number of kernels this library has launched since load, from all threads (monotonic).
+ * Diagnostic; the reference has no counterpart. */
 GLA_API long long gla_launch_count(void);
 
 /* Every device-side wait in this library (on an mbarrier that a tensor-core operation
@@ -112,6 +112,33 @@ GLA_API size_t gla_profile_report(char* buf, size_t capacity);
 GLA_API int gla_decode_step(void* stream, int64_t B, int64_t H, int64_t D, int dtype,
                     float* state, const float* log_fgate, const void* value, const void* key,
                     const void* query, void* out, int out_dtype);
+
+/* ------------------------------------------------------------------------------------
+ * layer stages — the element-wise steps a gated-linear-attention layer runs either side of the
+ * op.  No counterpart in the reference, which ships the op only (gla.py:657); they produce the
+ * float32 log_fgate the op takes (gla.py:483) and consume its `out`.
+ *   gate:          log_fgate[i] = inv_tau * log_sigmoid(z[i])      z in dtype, log_fgate float32
+ *                  dz[i]        = dlog_fgate[i] * inv_tau * sigmoid(-z[i])
+ *   headnorm_gate: rows of D elements (rows = B*T*H, D in {32, 64, 128, 256}), x/gate/y in dtype:
+ *                  rstd[r] = rsqrt(mean_d x[r,d]^2 + eps)
+ *                  y[r,d]  = x[r,d] * rstd[r] * weight[d] * gate[r,d] * sigmoid(gate[r,d])
+ *                  weight (D) float32 or NULL (= 1); rstd (rows) float32 is kept for the backward.
+ *                  The backward returns dx, dgate (dtype) and, if dweight (D, float32) is not NULL,
+ *                  the weight gradient (deterministic: per-block partial sums in `workspace`).
+ * x, gate, y, dy, dx, dgate must be 16-byte aligned.
+ * ---------------------------------------------------------------------------------- */
+GLA_API int gla_layer_gate_fwd(void* stream, int64_t n, int dtype, const void* z, float inv_tau,
+                       float* log_fgate);
+GLA_API int gla_layer_gate_bwd(void* stream, int64_t n, int dtype, const void* z,
+                       const float* dlog_fgate, float inv_tau, void* dz);
+GLA_API int gla_layer_headnorm_gate_fwd(void* stream, int64_t rows, int64_t D, int dtype,
+                                const void* x, const void* gate, const float* weight, float eps,
+                                void* y, float* rstd);
+GLA_API size_t gla_layer_headnorm_gate_bwd_workspace_bytes(int64_t rows, int64_t D);
+GLA_API int gla_layer_headnorm_gate_bwd(void* stream, int64_t rows, int64_t D, int dtype,
+                                const void* x, const void* gate, const float* weight,
+                                const float* rstd, const void* dy, void* dx, void* dgate,
+                                float* dweight, void* workspace, size_t workspace_bytes);
 
 /* ------------------------------------------------------------------------------------
  * cumsum — replaces ops.py:234 cumsum_recursive / ops.py:166 cumsum_pallas /
