@@ -65,6 +65,13 @@ def test_validation_without_gpu(lib):
     # decode step: null pointer, bad dims
     assert lib.gla_decode_step(None, 1, 1, 64, 0, None, p, p, p, p, p, 0) == 1
     assert lib.gla_decode_step(None, 0, 1, 64, 0, p, p, p, p, p, p, 0) == 2
+    # layer stages: null pointer, bad element count, unsupported row width, misaligned rows, missing workspace
+    assert lib.gla_layer_gate_fwd(None, 8, 1, None, 1.0, p) == 1
+    assert lib.gla_layer_gate_bwd(None, 0, 1, p, p, 1.0, p) == 2
+    assert lib.gla_layer_headnorm_gate_fwd(None, 4, 48, 1, p, p, None, 1e-5, p, p) == 3
+    assert lib.gla_layer_headnorm_gate_fwd(None, 4, 64, 1, q, p, None, 1e-5, p, p) == 4
+    assert lib.gla_layer_headnorm_gate_bwd(None, 4, 64, 1, p, p, p, p, p, p, p, p, None, 0) == 5
+    assert lib.gla_layer_headnorm_gate_bwd_workspace_bytes(4, 64) > 0
     # workspace sizes are positive and grow with the problem
     a = lib.gla_chunk_fwd_workspace_bytes(1, 128, 2, 64, 64, 0, 0)
     b = lib.gla_chunk_fwd_workspace_bytes(2, 128, 2, 64, 64, 0, 0)
@@ -80,3 +87,8 @@ def test_cpu_tensors_raise():
     x = torch.zeros(32, 2, 16)
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         chunk_gla(h, x, x, x, x, 16)
+    from gla_jax_b200 import headnorm_gate, log_forget_gate
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        log_forget_gate(torch.zeros(4))
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        headnorm_gate(torch.zeros(2, 32), torch.zeros(2, 32))
