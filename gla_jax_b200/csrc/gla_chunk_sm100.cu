@@ -333,15 +333,32 @@ __device__ __forceinline__ void fwd_emit(const float2 (&f)[16], const uint32_t (
 }
 
 
+// Out of line on purpose (the forward kernel's straight-line code is sensitive to anything added to it): the
+// late path of a block that started beside the state kernel.  Bounded wait for that kernel's blocks (all
+// resident, and they need nothing from this grid), then the state tile's two TMA loads.
+__device__ __noinline__ bool fwd_load_state_late(const unsigned int* state_done, unsigned int state_target,
+                                                 const CUtensorMap* map_s, uint32_t dst, int row, uint32_t bar) {
+  bool done = false;
+  for (uint32_t it = 0; it < (1u << 20) && !done; ++it) {
+    done = ld_acquire_u32(state_done) >= state_target;
+    if (!done) __nanosleep(64);
+  }
+  fence_proxy_async_global();
+  tma_load_2d(dst, map_s, 0, row, bar);
+  tma_load_2d(dst + TILE_BYTES, map_s, 64, row, bar);
+  return done;
+}
+
 __global__ void __launch_bounds__(TTHREADS, 1)
 tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, int R, int64_t N, bf16* __restrict__ out,
-                    bf16* __restrict__ P_saved) {
+                    bf16* __restrict__ P_saved, const unsigned int* __restrict__ state_done, unsigned int state_target) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = align1024(smem_raw);
   float* tot = reinterpret_cast<float*>(sm + FwdSmem::TOT);
   float* diag = reinterpret_cast<float*>(sm + FwdSmem::DIAG);
   uint64_t* bars = reinterpret_cast<uint64_t*>(sm + FwdSmem::BAR);   // [0],[1]: level buffers, [2]: output, [3]: g,q,k loads, [4]: v,S loads
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
+  volatile uint32_t* s_pending_sm = tmem_slot + 1;     // thread 0's note to itself: the state tile's load is still to be issued
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int rg = tid >> 6, cp = tid & 63;
@@ -375,10 +392,17 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, 
       tma_load_3d(smem_u32(sm + FwdSmem::K + half * TILE_BYTES), &maps.q, 64 * half, y, z, lb);
       tma_load_3d(smem_u32(sm + FwdSmem::P + half * TILE_BYTES), &maps.k, 64 * half, y, z, lb);
     }
+    // state_done (optional): this grid was launched as a programmatic dependent of the state kernel and may be
+    // running beside it, on SMs that kernel leaves idle.  The state tile is only loaded once the counter shows
+    // that every state block has finished; a block that finds it short defers that load to the point where
+    // the tile is needed (everything before it needs no state).
+    const bool s_pending = state_done != nullptr && ld_acquire_u32(state_done) < state_target;
+    *s_pending_sm = s_pending ? 1u : 0u;
+    if (!s_pending && state_done != nullptr) fence_proxy_async_global();
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
       tma_load_3d(smem_u32(sm + FwdSmem::V + half * TILE_BYTES), &maps.v, 64 * half, yv, z, lb2);
-      tma_load_2d(smem_u32(sm + FwdSmem::S + half * TILE_BYTES), &maps.s, 64 * half, (int)(chunk_id * TD), lb2);
+      if (!s_pending) tma_load_2d(smem_u32(sm + FwdSmem::S + half * TILE_BYTES), &maps.s, 64 * half, (int)(chunk_id * TD), lb2);
     }
   }
   if (warp == 1) {
@@ -595,6 +619,11 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, 
     for (int ks = 0; ks < 8; ++ks)
       umma_bf16(tmem, kslice_kmajor(ap, TILE_BYTES, ks), kslice_mnmajor(bv, ks), idesc, 1);
     umma_commit(smem_u32(bars + 2));
+  } else if (tid == 32) {
+    // a block that started beside the state kernel: the state tile's load, issued here by another warp than the
+    // one that waits for it, so that the common path above carries nothing extra
+    if (*s_pending_sm != 0u && !fwd_load_state_late(state_done, state_target, &maps.s, smem_u32(sm + FwdSmem::S), (int)(chunk_id * TD), smem_u32(bars + 4)))
+      atomicAdd(&g_tc_wait_timeouts, 1u);
   }
   // The saved copy of P goes out from the assembled shared-memory tile while the output product runs: rows are
   // written whole (a warp stores two full 256-byte rows per instruction) instead of in 16-byte pieces of 32
@@ -1409,6 +1438,12 @@ size_t tc_bwd_ws_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t) {
 
 constexpr size_t FWD_SMEM = 1024 + FwdSmem::END;
 
+// GLA_B200_EARLY_START=0 keeps the chunk kernel strictly behind the state kernel (read per call).
+static bool early_start_enabled() {
+  const char* e = getenv("GLA_B200_EARLY_START");
+  return !(e != nullptr && e[0] == '0');
+}
+
 int tc_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, int64_t C, const void* hidden_init,
                  const float* g, const void* v, const void* k, const void* q, void* hidden_final, void* out,
                  void* saved, void* ws, int state_only, float* G_total, float* S_local, int64_t nseq, const int* cu) {
@@ -1441,7 +1476,11 @@ int tc_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
     init_v = hib; fin_v = hfb;
   }
   const bool fused_states = !state_only && (R > 1 || cu != nullptr || tc_state_fused_preferred(BHV, N));
-  if (fused_states) GLA_TRY(tc_state_fused(st, 0, B, T, HV, R, g, k, v, init_v, S_prev, fin_v, Gc, nseq, cu));
+  // The chunk kernel may start beside the one-pass state kernel (which fills only 4 x batch x heads SMs) when it
+  // is the very next launch: plain head size, and the kv area of the workspace, unused then, holds the counter.
+  unsigned int* early_flag = (fused_states && R == 1 && early_start_enabled()) ? (unsigned int*)kv : nullptr;
+  unsigned int early_target = 0;
+  if (fused_states) GLA_TRY(tc_state_fused(st, 0, B, T, HV, R, g, k, v, init_v, S_prev, fin_v, Gc, nseq, cu, early_flag, &early_target));
   else GLA_TRY((launch_tc_kv<0>(st, B, T, H, g, k, v, kv, Gc)));
   if (state_only) {
     GLA_TRY(launch_state_scan(st, BHV, N, TD, Gc, kv, 0, nullptr, 0, nullptr, 0, S_local, 0, 0));
@@ -1461,7 +1500,25 @@ int tc_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
   GLA_TRY(make_map_rows(&maps.s, S_prev, BHV * N * TD, 64, 128));
   {
     ProfScope ps("tc_chunk_fwd_kernel", st);
-    tc_chunk_fwd_kernel<<<(unsigned)(BHV * N), TTHREADS, FWD_SMEM, st>>>(maps, T, HV, R, N, R > 1 ? out_v : (bf16*)out, P);
+    bf16* out_p = R > 1 ? out_v : (bf16*)out;
+    if (early_flag != nullptr) {
+      // programmatic dependent of the state kernel launched just before: may start while that one runs
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3((unsigned)(BHV * N));
+      cfg.blockDim = dim3(TTHREADS);
+      cfg.dynamicSmemBytes = FWD_SMEM;
+      cfg.stream = st;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[0].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      e = cudaLaunchKernelEx(&cfg, tc_chunk_fwd_kernel, maps, T, HV, R, N, out_p, P, (const unsigned int*)early_flag,
+                             early_target);
+      if (e != cudaSuccess) return record_cuda_error(e);
+    } else {
+      tc_chunk_fwd_kernel<<<(unsigned)(BHV * N), TTHREADS, FWD_SMEM, st>>>(maps, T, HV, R, N, out_p, P, nullptr, 0u);
+    }
   }
   GLA_CHECK_LAUNCH();
   if (R > 1) {

@@ -77,7 +77,8 @@ struct StMaps { CUtensorMap g, x, y; };
 template <int MODE>
 __global__ void __launch_bounds__(STHREADS, 1)
 tc_state_kernel(const __grid_constant__ StMaps maps, int64_t T, int64_t H, int R, int Nall, const int* __restrict__ cu,
-                const bf16* __restrict__ init, bf16* __restrict__ states, bf16* __restrict__ fin, float* __restrict__ Gc) {
+                const bf16* __restrict__ init, bf16* __restrict__ states, bf16* __restrict__ fin, float* __restrict__ Gc,
+                unsigned int* __restrict__ done) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   float* tot = reinterpret_cast<float*>(sm + StSmem::TOT);
@@ -106,6 +107,11 @@ tc_state_kernel(const __grid_constant__ StMaps maps, int64_t T, int64_t H, int R
   const int64_t hk = (hh / (R * R)) * R + (hh % (R * R)) / R, hv = (hh / (R * R)) * R + hh % R;
   auto chunk_of = [&](int i) { return MODE == 0 ? i : N - 1 - i; };
 
+  // `done` (optional): a counter in global memory that every block bumps once its states are written.  The
+  // consumer kernel may then be launched as a programmatic dependent of this grid: it starts on the SMs this
+  // grid leaves idle (4 x batch x heads blocks), does the part of its work that needs no state, and reads the
+  // counter before it loads one.  Letting dependents go at once is safe: nothing here reads what they write.
+  if (done != nullptr && tid == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (tid == NBUILD + NUPD) {
     for (int s = 0; s < NY; ++s) mbar_init(smem_u32(fully + s), 1);
     for (int s = 0; s < NGX; ++s) mbar_init(smem_u32(fullgx + s), 1);
@@ -299,6 +305,10 @@ tc_state_kernel(const __grid_constant__ StMaps maps, int64_t T, int64_t H, int R
   }
   tc_fence_before();
   __syncthreads();
+  if (done != nullptr && tid == 0) {       // the block's stores are ordered before the bump (barrier, then a device-scope fence)
+    __threadfence();
+    atomicAdd(done, 1u);
+  }
   if (warp == 1) tmem_dealloc(tmem, 64);
 }
 
@@ -332,7 +342,8 @@ bool tc_state_fused_preferred(int64_t BH, int64_t N) {
 // mode 0: states[n] = state before chunk n (from init), fin = state after the last chunk, Gc = chunk gate sums.
 // mode 1: states[n] = gradient state after chunk n (from init = dhidden_final), fin = dhidden_init.
 int tc_state_fused(cudaStream_t st, int mode, int64_t B, int64_t T, int64_t H, int R, const float* g, const void* x,
-                   const void* y, const void* init, void* states, void* fin, float* Gc, int64_t nseq, const int* cu) {
+                   const void* y, const void* init, void* states, void* fin, float* Gc, int64_t nseq, const int* cu,
+                   unsigned int* done, unsigned int* done_target) {
   // packed sequences: B == 1, cu (device, nseq + 1 token offsets) non-null, init / fin are (nseq, H, 128, 128)
   const int64_t N = T / SC, BH = (cu ? nseq : B) * H;          // H: virtual heads (real heads x R x R)
   const int64_t HK = H / R;                      // heads of the (B, T, HK, 128) view of the arrays
@@ -343,9 +354,15 @@ int tc_state_fused(cudaStream_t st, int mode, int64_t B, int64_t T, int64_t H, i
   auto kern = mode == 0 ? tc_state_kernel<0> : tc_state_kernel<1>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ST_SMEM);
   if (e != cudaSuccess) return record_cuda_error(e);
+  if (done != nullptr) {
+    e = cudaMemsetAsync(done, 0, sizeof(unsigned int), st);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    if (done_target) *done_target = (unsigned int)(BH * 4);
+  }
   {
     ProfScope ps(mode == 0 ? "tc_state_kernel" : "tc_dstate_scan_kernel", st);
-    kern<<<(unsigned)(BH * 4), STHREADS, ST_SMEM, st>>>(maps, T, H, R, (int)N, cu, (const bf16*)init, (bf16*)states, (bf16*)fin, Gc);
+    kern<<<(unsigned)(BH * 4), STHREADS, ST_SMEM, st>>>(maps, T, H, R, (int)N, cu, (const bf16*)init, (bf16*)states, (bf16*)fin, Gc,
+                                                        done);
   }
   GLA_CHECK_LAUNCH();
   return GLA_OK;

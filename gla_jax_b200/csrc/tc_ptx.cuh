@@ -193,4 +193,13 @@ __device__ __forceinline__ float2 unpack_bf16x2(uint32_t u) {
 }
 
 }  // namespace tc
+// Device-scope acquire load (flag written by another grid with a fence + atomic), and the fence that orders
+// such generic-proxy observations before this thread's later TMA (async proxy) reads of global memory.
+__device__ __forceinline__ uint32_t ld_acquire_u32(const unsigned int* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
+
 }  // namespace gla
