@@ -334,15 +334,14 @@ __device__ __forceinline__ void fwd_emit(const float2 (&f)[16], const uint32_t (
 
 
 // Out of line on purpose (the forward kernel's straight-line code is sensitive to anything added to it): the
-// late path of a block that started beside the state kernel.  Bounded wait for that kernel's blocks (all
-// resident, and they need nothing from this grid), then the state tile's two TMA loads.
+// late path of a block that started beside the state kernel.  It blocks on the grid dependency itself
+// (griddepcontrol.wait returns once the state kernel has completed and its writes are visible; no polling of
+// memory between the two grids), then issues the state tile's two TMA loads.  The counter is read once more
+// only to report a dependency that did not hold.
 __device__ __noinline__ bool fwd_load_state_late(const unsigned int* state_done, unsigned int state_target,
                                                  const CUtensorMap* map_s, uint32_t dst, int row, uint32_t bar) {
-  bool done = false;
-  for (uint32_t it = 0; it < (1u << 20) && !done; ++it) {
-    done = ld_acquire_u32(state_done) >= state_target;
-    if (!done) __nanosleep(64);
-  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const bool done = ld_acquire_u32(state_done) >= state_target;
   fence_proxy_async_global();
   tma_load_2d(dst, map_s, 0, row, bar);
   tma_load_2d(dst + TILE_BYTES, map_s, 64, row, bar);
@@ -393,9 +392,9 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, 
       tma_load_3d(smem_u32(sm + FwdSmem::P + half * TILE_BYTES), &maps.k, 64 * half, y, z, lb);
     }
     // state_done (optional): this grid was launched as a programmatic dependent of the state kernel and may be
-    // running beside it, on SMs that kernel leaves idle.  The state tile is only loaded once the counter shows
-    // that every state block has finished; a block that finds it short defers that load to the point where
-    // the tile is needed (everything before it needs no state).
+    // running beside it, on SMs that kernel leaves idle.  One look at the counter (no waiting on it): if every
+    // state block has finished, the state tile is loaded now; otherwise its load is left to thread 32 at the
+    // point where the tile is needed, behind the grid dependency (everything before that needs no state).
     const bool s_pending = state_done != nullptr && ld_acquire_u32(state_done) < state_target;
     *s_pending_sm = s_pending ? 1u : 0u;
     if (!s_pending && state_done != nullptr) fence_proxy_async_global();
