@@ -417,3 +417,45 @@ def test_triton_scan_dispatches_to_the_cuda_scans(cuda_device):
     assert O.rel_l2(ref_log.float(), out_log.cpu()) < 1e-5 and O.rel_l2(ref_state.float(), out_state.cpu()) < 1e-5
     with pytest.raises(NotImplementedError):
         triton_scan(torch.maximum, x.to(cuda_device), axis=1)
+
+
+def test_early_start_gives_the_same_bits_under_graph_replay(cuda_device, monkeypatch):
+    """The forward chunk kernel is launched as a programmatic dependent of the state kernel and starts beside it
+    (README shape: the state kernel fills 96 of 148 SMs).  Results must not depend on that: forward+backward
+    captured in a CUDA graph and replayed 20 times gives, every time, exactly the bits of a run with the chunk
+    kernel kept strictly behind the state kernel (GLA_B200_EARLY_START=0), and no bounded wait gave up.
+    dlog_fgate alone is compared to 1e-6: its per-chunk sums are accumulated with float32 shared-memory atomics,
+    whose order differs from run to run in either mode."""
+    from gla_jax_b200 import chunk_gla, _lib
+    lib = _lib.load()
+    case = _case(4, 4096, 6, 128, torch.bfloat16, 77, 5.0)
+    h, g, v, k, q, dhf, do = (x.to(cuda_device) for x in case)
+
+    def run():
+        leaves = [x.clone().requires_grad_(True) for x in (h, g, v, k, q)]
+        hf, out = chunk_gla(*leaves, chunk_size=128)
+        grads = torch.autograd.grad((hf.float() * dhf.float()).sum() + (out.float() * do.float()).sum(), leaves)
+        return [hf, out, *grads]
+
+    monkeypatch.setenv("GLA_B200_EARLY_START", "0")
+    ref = [t.clone() for t in run()]
+    torch.cuda.synchronize()
+    monkeypatch.setenv("GLA_B200_EARLY_START", "1")
+    run()                                           # warm-up outside the capture
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream(device=cuda_device)
+    side.wait_stream(torch.cuda.current_stream(cuda_device))
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            outs = run()
+    t0 = lib.gla_device_wait_timeouts()
+    for _ in range(20):
+        graph.replay()
+        torch.cuda.synchronize()
+        for i, (a, b) in enumerate(zip(ref, outs)):
+            if i == 3:
+                assert O.rel_l2(a.cpu(), b.cpu()) < 1e-6
+            else:
+                assert torch.equal(a, b), i
+    assert lib.gla_device_wait_timeouts() == t0
