@@ -268,7 +268,7 @@ GLA_API int gla_chunk_fwd_static(void* stream, int64_t B, int64_t T, int64_t H, 
 
 /* ------------------------------------------------------------------------------------
  * Packed (variable-length) sequences — no counterpart in the reference, which asserts one
- * length per call (gla.py:499-500, 674); the survey's "next" item 2.
+ * length per call (gla.py:499-500, 674).
  * The arrays hold ONE time axis of T tokens with nseq sequences laid end to end:
  * log_fgate/value/key/query/out are (T, H, D); cu_seqlens is a DEVICE array of nseq + 1 int32
  * token offsets (cu_seqlens[0] = 0, cu_seqlens[nseq] = T), every offset a multiple of 128;
