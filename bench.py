@@ -605,6 +605,7 @@ def main():
             "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
                     "ms_per_step": e2e_ms / K},
             "gpu_launches": int(launches),
+            "device_wait_timeouts": int(lib.gla_device_wait_timeouts()),     # bounded device-side waits that gave up: must be 0
             "clocks": sampler.summary(),
             "roofline": roof,
             "step_fractions": {"tensor_frac_of_burst_peak": tensor_frac, "hbm_frac_of_measured_copy": hbm_frac,
