@@ -459,3 +459,21 @@ def test_early_start_gives_the_same_bits_under_graph_replay(cuda_device, monkeyp
             else:
                 assert torch.equal(a, b), i
     assert lib.gla_device_wait_timeouts() == t0
+
+
+@pytest.mark.parametrize("B,T,H", [(64, 128, 16), (16, 512, 12)])
+def test_early_start_with_more_state_blocks_than_sms(cuda_device, monkeypatch, B, T, H):
+    """The one-pass state kernel forced on shapes where its grid (4 x batch x heads blocks) is many waves: the
+    dependent chunk kernel may only start once the last wave is resident.  Forward against the exact recurrence
+    kernel, and no bounded wait gave up."""
+    from gla_jax_b200 import chunk_gla, recurrent_gla, _lib
+    lib = _lib.load()
+    monkeypatch.setenv("GLA_B200_STATE_FUSED", "1")
+    h, g, v, k, q = (x.to(cuda_device) for x in O.make_inputs(B, T, H, 128, torch.bfloat16, seed=3))
+    t0 = lib.gla_device_wait_timeouts()
+    with torch.no_grad():
+        hf, out = chunk_gla(h, g, v, k, q, chunk_size=128)
+        hf2, out2 = recurrent_gla(h, g, v, k, q)
+    torch.cuda.synchronize()
+    assert O.rel_l2(hf2.cpu(), hf.cpu()) < 1e-2 and O.rel_l2(out2.cpu(), out.cpu()) < 1e-2
+    assert lib.gla_device_wait_timeouts() == t0
