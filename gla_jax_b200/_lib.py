@@ -9,15 +9,33 @@ import ctypes
 from ctypes import c_char_p, c_int, c_int64, c_size_t, c_void_p
 from pathlib import Path
 
-import os
-
-# GLA_B200_LIB may point at another build of the library (used to compare kernel variants).
-_LIB_PATH = Path(os.environ.get("GLA_B200_LIB") or (Path(__file__).resolve().parent / "libgla_b200.so"))
+_LIB_PATH = Path(__file__).resolve().parent / "libgla_b200.so"
 _lib = None
 
 GLA_F32, GLA_BF16 = 0, 1
 IMPL_AUTO, IMPL_FP32_SIMT, IMPL_TCGEN05 = 0, 1, 2
-IMPL_BY_NAME = {"auto": IMPL_AUTO, "fp32": IMPL_FP32_SIMT, "simt": IMPL_FP32_SIMT, "tcgen05": IMPL_TCGEN05}
+_FAMILY = {"auto": IMPL_AUTO, "fp32": IMPL_FP32_SIMT, "simt": IMPL_FP32_SIMT, "tcgen05": IMPL_TCGEN05}
+# gla_chunk_option bits of include/gla_b200.h, by the names accepted after a "+" in an impl string
+OPTIONS = {"two_kernels": 0x100, "one_pass": 0x200, "no_early_start": 0x400, "all_scales": 0x800,
+           "no_l2_prefetch": 0x1000}
+
+
+class _ImplNames(dict):
+    """``IMPL_BY_NAME["tcgen05+all_scales+one_pass"]`` -> family | option bits (the `impl` argument of the chunk
+    entry points).  Plain family names are ordinary keys."""
+
+    def __missing__(self, name):
+        fam, *opts = str(name).split("+")
+        if fam not in _FAMILY or any(o not in OPTIONS for o in opts):
+            raise KeyError(f"unknown chunk implementation {name!r}: family one of {sorted(_FAMILY)}, "
+                           f"options {sorted(OPTIONS)} joined by '+'")
+        v = _FAMILY[fam]
+        for o in opts:
+            v |= OPTIONS[o]
+        return v
+
+
+IMPL_BY_NAME = _ImplNames(_FAMILY)
 
 # name -> (restype, argtypes); must list every symbol include/gla_b200.h declares.
 SIGNATURES = {
@@ -26,7 +44,6 @@ SIGNATURES = {
     "gla_last_cuda_error": (c_int, []),
     "gla_launch_count": (ctypes.c_longlong, []),
     "gla_device_wait_timeouts": (ctypes.c_uint, []),
-    "gla_debug_phase_clocks": (None, [c_void_p]),
     "gla_profile_enable": (None, [c_int]),
     "gla_profile_report": (c_size_t, [c_char_p, c_size_t]),
     "gla_cumsum": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int]),

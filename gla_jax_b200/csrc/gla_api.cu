@@ -47,8 +47,13 @@ static int check_chunk_dims(int64_t B, int64_t T, int64_t H, int64_t D, int64_t 
   return check_dtype(dtype);
 }
 
-// Resolve GLA_IMPL_AUTO; returns a negative status (as -status) if the request is invalid.
-static int resolve_impl(int impl, int64_t D, int64_t C, int dtype) {
+// Resolve GLA_IMPL_AUTO; returns a negative status (as -status) if the request is invalid.  The option bits
+// above the low byte are passed on to the tensor-core path as they are.
+constexpr int OPT_BITS = GLA_OPT_STATE_TWO_KERNELS | GLA_OPT_STATE_ONE_PASS | GLA_OPT_NO_EARLY_START | GLA_OPT_ALL_SCALES |
+                         GLA_OPT_NO_L2_PREFETCH;
+static int resolve_impl(int impl_and_opts, int64_t D, int64_t C, int dtype) {
+  if (impl_and_opts < 0 || (impl_and_opts & ~(0xff | OPT_BITS)) != 0) return -GLA_ERR_UNSUPPORTED;
+  const int impl = impl_and_opts & 0xff;
   if (impl == GLA_IMPL_AUTO) return (tc_auto_default() && tc_supported(D, C, dtype)) ? GLA_IMPL_TCGEN05 : GLA_IMPL_FP32_SIMT;
   if (impl == GLA_IMPL_TCGEN05) return tc_supported(D, C, dtype) ? GLA_IMPL_TCGEN05 : -GLA_ERR_UNSUPPORTED;
   if (impl == GLA_IMPL_FP32_SIMT) return GLA_IMPL_FP32_SIMT;
@@ -83,8 +88,6 @@ int gla_last_cuda_error(void) { return g_last_cuda_error; }
 long long gla_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 unsigned int gla_device_wait_timeouts(void) { return tc_read_wait_timeouts() + tc_state_read_wait_timeouts(); }
-
-void gla_debug_phase_clocks(long long* out64) { tc_read_trace(out64); }
 
 void gla_profile_enable(int on) {
   g_prof_on = on != 0;
@@ -260,7 +263,7 @@ int gla_chunk_fwd(void* stream, int64_t B, int64_t T, int64_t H, int64_t D, int6
   if (r == GLA_IMPL_TCGEN05 && (!aligned32(out) || !aligned32(workspace))) return GLA_ERR_ALIGNMENT;
   if (r == GLA_IMPL_TCGEN05)
     return tc_chunk_fwd((cudaStream_t)stream, B, T, H, D, chunk, hidden_init, log_fgate, value, key, query,
-                        hidden_final, out, saved, workspace, 0, nullptr, nullptr);
+                        hidden_final, out, saved, workspace, 0, nullptr, nullptr, impl & OPT_BITS);
   return simt_chunk_fwd((cudaStream_t)stream, B, T, H, D, chunk, dtype == GLA_BF16, hidden_init, log_fgate, value, key,
                         query, hidden_final, out, saved, workspace, 0, nullptr, nullptr);
 }
@@ -284,7 +287,7 @@ int gla_chunk_bwd(void* stream, int64_t B, int64_t T, int64_t H, int64_t D, int6
   if (r == GLA_IMPL_TCGEN05 && (!aligned32(dvalue) || !aligned32(workspace))) return GLA_ERR_ALIGNMENT;
   if (r == GLA_IMPL_TCGEN05)
     return tc_chunk_bwd((cudaStream_t)stream, B, T, H, D, chunk, log_fgate, value, key, query, saved, dhidden_final,
-                        dout, dhidden_init, dlog_fgate, dvalue, dkey, dquery, workspace);
+                        dout, dhidden_init, dlog_fgate, dvalue, dkey, dquery, workspace, impl & OPT_BITS);
   return simt_chunk_bwd((cudaStream_t)stream, B, T, H, D, chunk, dtype == GLA_BF16, log_fgate, value, key, query, saved,
                         dhidden_final, dout, dhidden_init, dlog_fgate, dvalue, dkey, dquery, workspace);
 }
@@ -304,7 +307,7 @@ int gla_chunk_fwd_packed(void* stream, int64_t T, int64_t H, int64_t D, int64_t 
     if (p && !aligned16(p)) return GLA_ERR_ALIGNMENT;
   if (!aligned32(out)) return GLA_ERR_ALIGNMENT;
   return tc_chunk_fwd((cudaStream_t)stream, 1, T, H, D, chunk, hidden_init, log_fgate, value, key, query, hidden_final,
-                      out, saved, workspace, 0, nullptr, nullptr, nseq, cu_seqlens);
+                      out, saved, workspace, 0, nullptr, nullptr, 0, nseq, cu_seqlens);
 }
 
 int gla_chunk_bwd_packed(void* stream, int64_t T, int64_t H, int64_t D, int64_t chunk, int dtype, int64_t nseq,
@@ -325,7 +328,7 @@ int gla_chunk_bwd_packed(void* stream, int64_t T, int64_t H, int64_t D, int64_t 
     if (!aligned16(p)) return GLA_ERR_ALIGNMENT;
   if (!aligned32(dvalue)) return GLA_ERR_ALIGNMENT;
   return tc_chunk_bwd((cudaStream_t)stream, 1, T, H, D, chunk, log_fgate, value, key, query, saved, dhidden_final, dout,
-                      dhidden_init, dlog_fgate, dvalue, dkey, dquery, workspace, nseq, cu_seqlens);
+                      dhidden_init, dlog_fgate, dvalue, dkey, dquery, workspace, 0, nseq, cu_seqlens);
 }
 
 int gla_chunk_local_state(void* stream, int64_t B, int64_t T, int64_t H, int64_t D, int64_t chunk, int dtype,
@@ -343,7 +346,7 @@ int gla_chunk_local_state(void* stream, int64_t B, int64_t T, int64_t H, int64_t
   if (!workspace || workspace_bytes < need) return GLA_ERR_WORKSPACE;
   if (r == GLA_IMPL_TCGEN05)
     return tc_chunk_fwd((cudaStream_t)stream, B, T, H, D, chunk, nullptr, log_fgate, value, key, nullptr, nullptr,
-                        nullptr, nullptr, workspace, 1, G_total, S_local);
+                        nullptr, nullptr, workspace, 1, G_total, S_local, impl & OPT_BITS);
   return simt_chunk_fwd((cudaStream_t)stream, B, T, H, D, chunk, dtype == GLA_BF16, nullptr, log_fgate, value, key,
                         nullptr, nullptr, nullptr, nullptr, workspace, 1, G_total, S_local);
 }

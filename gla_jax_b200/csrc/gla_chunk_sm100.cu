@@ -33,11 +33,6 @@ constexpr uint32_t TILE_BYTES = 128 * 128;     // one SW128 tile of 128 rows
 
 __device__ unsigned int g_tc_wait_timeouts = 0;   // incremented when a bounded wait gives up
 
-// Phase clock stamps of one thread block (block 100, thread 0) of the last forward / backward
-// chunk kernel: a cheap always-on diagnostic read back by gla_debug_phase_clocks().
-__device__ long long g_tc_trace[2][32];
-#define TC_STAMP(which, idx) do { if (blockIdx.x == 500 && threadIdx.x == 0) g_tc_trace[which][idx] = clock64(); } while (0)
-
 // K slice ks of an operand whose slice-0 descriptor is d0 (K-major: 32 bytes per slice, next 64-column
 // block after four; MN-major: 2048 bytes per slice).  One 32-bit add instead of a descriptor rebuild, which
 // matters because the issuing thread's instruction stream is serial and on the critical path.
@@ -69,11 +64,8 @@ __device__ __forceinline__ void copy_tile_128x128(uint8_t* dst, const bf16* __re
 // Also writes the chunk's total log decay G[d] (MODE 0).  One CTA per chunk.
 // MMA: M = dk (128), N = dv (128), K = c (128); both operands MN-major.
 // ---------------------------------------------------------------------------------------
-#ifndef KV_MINB
-#define KV_MINB 1
-#endif
 template <int MODE>
-__global__ void __launch_bounds__(TTHREADS, KV_MINB)
+__global__ void __launch_bounds__(TTHREADS, 1)
 tc_kv_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g, const bf16* __restrict__ x,
              const bf16* __restrict__ y, float* __restrict__ out, float* __restrict__ Gc) {
   extern __shared__ uint8_t smem_raw[];
@@ -204,12 +196,9 @@ tc_kv_kernel(int64_t T, int64_t H, int64_t N, const float* __restrict__ g, const
 }
 
 // Number of thread blocks resident at a time (SMs x blocks per SM) = how far ahead in block index the
-// block that follows on the same SM lies; 0 disables the L2 prefetch.  GLA_B200_PREFETCH=0 turns it off.
+// block that follows on the same SM lies; 0 disables the L2 prefetch.
 static int prefetch_distance(int blocks_per_sm) {
   static int sms[64] = {0};
-  static int enabled = -1;
-  if (enabled < 0) { const char* e = getenv("GLA_B200_PREFETCH"); enabled = (e && e[0] == '0') ? 0 : 1; }
-  if (!enabled) return 0;
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
   if (sms[dev] == 0) {
@@ -226,8 +215,8 @@ template <int MODE>
 static int launch_tc_kv(cudaStream_t st, int64_t B, int64_t T, int64_t H, const float* g, const void* x, const void* y,
                         float* out, float* Gc) {
   const int64_t N = T / TC;
-  cudaError_t e = cudaFuncSetAttribute(tc_kv_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)KV_SMEM);
-  if (e != cudaSuccess) return record_cuda_error(e);
+  static SmemAttrOnce attr;
+  GLA_TRY(attr.ensure(tc_kv_kernel<MODE>, KV_SMEM));
   ProfScope ps(MODE == 0 ? "tc_kv_kernel" : "tc_dstate_kernel", st);
   tc_kv_kernel<MODE><<<(unsigned)(B * H * N), TTHREADS, KV_SMEM, st>>>(T, H, N, g, (const bf16*)x, (const bf16*)y, out, Gc);
   GLA_CHECK_LAUNCH();
@@ -256,9 +245,14 @@ struct FwdSmem {
   static constexpr uint32_t P = S + 2 * TILE_BYTES;        // 32 KB;               TMA lands raw k here first
   static constexpr uint32_t TOT = P + 2 * TILE_BYTES;      // 8 x 128 float
   static constexpr uint32_t DIAG = TOT + 8 * TD * 4;       // 2 x 128 float
-  static constexpr uint32_t BAR = DIAG + 2 * TC * 4;       // 5 mbarriers + tmem slot
+  static constexpr uint32_t GAB = DIAG + 2 * TC * 4;       // 8 x 128 float: sums of |g| per 16 rows
+  static constexpr uint32_t BAR = GAB + 8 * TD * 4;        // 5 mbarriers + tmem slot
   static constexpr uint32_t END = BAR + 64;
 };
+// A chunk whose gates satisfy sum_rows |g| <= ONE_SCALE_LIMIT for every feature needs no secondary chunking: with
+// one anchor for the whole chunk every decay weight stays within exp(+-limit), far inside the range of bf16 and
+// float32, so the dyadic levels (which exist to keep exponents non-positive, gla.py:986-993) collapse into one.
+constexpr float ONE_SCALE_LIMIT = 60.f;
 constexpr uint32_t KC_TILE = 64 * 128;    // one SW128 tile of 64 rows
 
 // TMA descriptors of one launch (built on the host per call, passed by value).
@@ -350,11 +344,13 @@ __device__ __noinline__ bool fwd_load_state_late(const unsigned int* state_done,
 
 __global__ void __launch_bounds__(TTHREADS, 1)
 tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, int R, int64_t N, bf16* __restrict__ out,
-                    bf16* __restrict__ P_saved, const unsigned int* __restrict__ state_done, unsigned int state_target) {
+                    bf16* __restrict__ P_saved, const unsigned int* __restrict__ state_done, unsigned int state_target,
+                    int all_scales) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = align1024(smem_raw);
   float* tot = reinterpret_cast<float*>(sm + FwdSmem::TOT);
   float* diag = reinterpret_cast<float*>(sm + FwdSmem::DIAG);
+  float* gab = reinterpret_cast<float*>(sm + FwdSmem::GAB);
   uint64_t* bars = reinterpret_cast<uint64_t*>(sm + FwdSmem::BAR);   // [0],[1]: level buffers, [2]: output, [3]: g,q,k loads, [4]: v,S loads
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
   volatile uint32_t* s_pending_sm = tmem_slot + 1;     // thread 0's note to itself: the state tile's load is still to be issued
@@ -370,7 +366,6 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, 
   const int64_t HD = H * TD;
   const int64_t row0 = ((b * T + n * TC) * H + h_) * TD;
   const int64_t chunk_id = bh * N + n;
-  TC_STAMP(0, 0);
 
   if (tid == 0) {
     mbar_init(smem_u32(bars + 0), 1);
@@ -413,17 +408,17 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, 
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   bool ok = mbar_wait(smem_u32(bars + 3), 0);
-  TC_STAMP(0, 1);
 
   // ---- gates, q, k of the thread's 16 rows x 2 columns from the landed tiles ---------------------
   float2 f[16];
   uint32_t qv[16], kv[16];
+  float2 prod = make_float2(1.f, 1.f);          // product of the thread's 16 gates, per column
   {
     const uint8_t* gq = sm + FwdSmem::Q;
     const uint8_t* qt = sm + FwdSmem::K + (cp >> 5) * TILE_BYTES;
     const uint8_t* kt = sm + FwdSmem::P + (cp >> 5) * TILE_BYTES;
     const int col = (2 * cp) & 63;
-    float2 prod = make_float2(1.f, 1.f);
+    float2 gsum = make_float2(0.f, 0.f);
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       const int r = rg * 16 + i;
@@ -432,9 +427,98 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, 
       kv[i] = *reinterpret_cast<const uint32_t*>(kt + sw128_off(r, col));
       f[i] = make_float2(__expf(gg.x), __expf(gg.y));
       prod.x *= f[i].x; prod.y *= f[i].y;
+      gsum.x += fabsf(gg.x); gsum.y += fabsf(gg.y);
     }
     *reinterpret_cast<float2*>(tot + rg * TD + 2 * cp) = prod;
+    *reinterpret_cast<float2*>(gab + rg * TD + 2 * cp) = gsum;
   }
+  __syncthreads();          // raw g, q, k have been consumed (their regions become operand buffers); tot and gab are visible
+  // One scale or all of them: the chunk's total |log decay| per feature decides, the same way for every thread.
+  bool one_scale;
+  {
+    float2 tsum = make_float2(0.f, 0.f);
+#pragma unroll
+    for (int r2 = 0; r2 < 8; ++r2) {
+      const float2 t = *reinterpret_cast<const float2*>(gab + r2 * TD + 2 * cp);
+      tsum.x += t.x; tsum.y += t.y;
+    }
+    // (a NaN gate fails the comparison and takes the general path)
+    const int over = !(tsum.x <= ONE_SCALE_LIMIT && tsum.y <= ONE_SCALE_LIMIT) || all_scales != 0;
+    one_scale = __syncthreads_or(over) == 0;
+  }
+  const uint32_t sQ0 = smem_u32(sm + FwdSmem::Q), sK0 = smem_u32(sm + FwdSmem::K);
+  uint8_t* sQb[2] = {sm + FwdSmem::Q, sm + FwdSmem::Q + 2 * TILE_BYTES};
+  uint8_t* sKb[2] = {sm + FwdSmem::K, sm + FwdSmem::K + 2 * KC_TILE};
+
+  if (one_scale) {
+    // ---- one anchor for the whole chunk (the row before its first): q_hat = q exp(lam) serves both the scores and
+    // the inter-chunk product, k~ = k exp(-lam); P = q_hat k~^T is ONE 128 x 128 x 128 product into TMEM columns
+    // [128, 256), masked to the lower triangle on the way back.  exp(-lam) is formed as
+    // (1 / prod of the gates up to the end of the thread's run) x (running product back from that end),
+    // so it costs two reciprocals per thread.
+    {
+      float2 crossq = make_float2(1.f, 1.f);
+      for (int r2 = 0; r2 < rg; ++r2) {
+        const float2 t = *reinterpret_cast<const float2*>(tot + r2 * TD + 2 * cp);
+        crossq.x *= t.x; crossq.y *= t.y;
+      }
+      const int tile = cp >> 5, col = (2 * cp) & 63;
+      uint8_t* qb = sQb[1] + tile * TILE_BYTES;        // q_hat: where the output product expects it
+      uint8_t* kb = sQb[0] + tile * TILE_BYTES;        // k~: 128 rows x 128 features, two tiles
+      float2 run = crossq;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        run.x *= f[i].x; run.y *= f[i].y;
+        const float2 x = unpack_bf16x2(qv[i]);
+        *reinterpret_cast<uint32_t*>(qb + sw128_off(rg * 16 + i, col)) = pack_bf16x2(x.x * run.x, x.y * run.y);
+      }
+      run = make_float2(1.f / (crossq.x * prod.x), 1.f / (crossq.y * prod.y));
+#pragma unroll
+      for (int i = 15; i >= 0; --i) {
+        const float2 x = unpack_bf16x2(kv[i]);
+        *reinterpret_cast<uint32_t*>(kb + sw128_off(rg * 16 + i, col)) = pack_bf16x2(x.x * run.x, x.y * run.y);
+        run.x *= f[i].x; run.y *= f[i].y;
+      }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after();
+      constexpr uint32_t idesc = idesc_bf16(128, 128, 0, 0);
+      const uint64_t a0 = desc_kmajor(sQ0 + 2 * TILE_BYTES, TILE_BYTES, 0), b0 = desc_kmajor(sQ0, TILE_BYTES, 0);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)
+        umma_bf16(tmem + 128, kslice_kmajor(a0, TILE_BYTES, ks), kslice_kmajor(b0, TILE_BYTES, ks), idesc, ks > 0);
+      umma_commit(smem_u32(bars + 0));
+    }
+    ok = mbar_wait(smem_u32(bars + 0), 0) && ok;
+    tc_fence_after();
+    // scores back into the bf16 P tile: row i = 32 q4 + lane, columns 32 cj + [0, 32); the diagonal entry
+    // q_hat_i . k~_i = q_i . k_i comes out of the same product
+    {
+      const int q4 = warp & 3, cj = warp >> 2;
+      const int i = 32 * q4 + lane;
+      uint32_t r[32];
+      if (cj <= q4) {
+        tmem_ld32(tmem + ((uint32_t)(q4 * 32) << 16) + 128u + (uint32_t)(32 * cj), r);
+        tmem_ld_wait();
+      }
+#pragma unroll
+      for (int c8 = 0; c8 < 4; ++c8) {
+        uint4 u = make_uint4(0u, 0u, 0u, 0u);
+        if (cj <= q4) {
+          float x[8];
+#pragma unroll
+          for (int m = 0; m < 8; ++m) x[m] = (cj < q4 || 8 * c8 + m <= lane) ? __uint_as_float(r[8 * c8 + m]) : 0.f;
+          u.x = pack_bf16x2(x[0], x[1]); u.y = pack_bf16x2(x[2], x[3]);
+          u.z = pack_bf16x2(x[4], x[5]); u.w = pack_bf16x2(x[6], x[7]);
+        }
+        const int col0 = 32 * cj + 8 * c8;
+        *reinterpret_cast<uint4*>(sm + FwdSmem::P + (col0 >> 6) * TILE_BYTES + sw128_chunk(i, (col0 & 63) >> 3)) = u;
+      }
+    }
+  } else {
   // diagonal: sum_d q k, reduced over the 64 column-pair threads of a row group (two warps)
   {
     float part[16];
@@ -456,11 +540,8 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, 
     for (int j = 0; j < 2; ++j) a2[j] = (h2 ? a4[j + 2] : a4[j]) + __shfl_xor_sync(0xffffffffu, h2 ? a4[j] : a4[j + 2], 4);
     float a1 = (h1 ? a2[1] : a2[0]) + __shfl_xor_sync(0xffffffffu, h1 ? a2[0] : a2[1], 2);
     a1 += __shfl_xor_sync(0xffffffffu, a1, 1);
-    if ((lane & 1) == 0) diag[(warp & 1) * TC + rg * 16 + (lane >> 1)] = a1;
+    if ((lane & 1) == 0) diag[(warp & 1) * TC + rg * 16 + (lane >> 1)] = a1;     // read after the level barriers below
   }
-  __syncthreads();          // raw g and q have been consumed: their regions become the level buffers
-  TC_STAMP(0, 2);
-  const uint32_t sQ0 = smem_u32(sm + FwdSmem::Q), sK0 = smem_u32(sm + FwdSmem::K);
 
   auto issue_level = [&](int slot) {
     const int bsel = slot & 1;
@@ -480,14 +561,11 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, 
       tc_fence_after();
       issue_level(slot);
     }
-    TC_STAMP(0, 3 + slot);
   };
   auto wait_buffer_free = [&](int slot) {
     // before rebuilding buffer (slot & 1): the MMA of level slot-2 must have consumed it
     if (slot >= 2) ok = mbar_wait(smem_u32(bars + (slot & 1)), (uint32_t)(((slot - 2) >> 1) & 1)) && ok;
   };
-  uint8_t* sQb[2] = {sm + FwdSmem::Q, sm + FwdSmem::Q + 2 * TILE_BYTES};
-  uint8_t* sKb[2] = {sm + FwdSmem::K, sm + FwdSmem::K + 2 * KC_TILE};
 
   fwd_emit<0>(f, qv, kv, sQb[0], sKb[0], rg, cp, tot); level_sync_and_issue(0);
   fwd_emit<1>(f, qv, kv, sQb[1], sKb[1], rg, cp, tot); level_sync_and_issue(1);
@@ -519,11 +597,9 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, 
       *reinterpret_cast<uint32_t*>(tile + sw128_off(rg * 16 + i, col)) = pack_bf16x2(x.x * run.x, x.y * run.y);
     }
   }
-  TC_STAMP(0, 10);
   // all seven level MMAs done when the last commit (buffer 0, fourth use) completes
   ok = mbar_wait(smem_u32(bars + 0), 1) && ok;
   tc_fence_after();
-  TC_STAMP(0, 11);
 
   // ---- read the scores back into the bf16 P tile -----------------------------------------------------
   // Rows 32 q4 + lane belong to the four warps of TMEM quadrant q4; each of them (cj = 0..3) writes
@@ -602,6 +678,7 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, 
       for (int ch = 0; ch < 3 - q4; ++ch) put_chunk(32 * (q4 + 1) + 8 * ((3 - q4) * cj + ch), z);
     }
   }
+  }   // all scales
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
@@ -636,10 +713,8 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, 
       *reinterpret_cast<uint4*>(pg + row * TC + ch * 8) = u;
     }
   }
-  TC_STAMP(0, 12);
   ok = mbar_wait(smem_u32(bars + 2), 0) && ok;
   tc_fence_after();
-  TC_STAMP(0, 13);
   if (ok) {
     const int q4 = warp & 3, cg = warp >> 2;
     uint32_t r[32];
@@ -657,7 +732,6 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, 
   } else if (tid == 0) {
     atomicAdd(&g_tc_wait_timeouts, 1u);
   }
-  TC_STAMP(0, 14);
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, 512);
@@ -697,10 +771,11 @@ struct BwdSmem {
   static constexpr uint32_t TOT = KH + 2 * TILE_BYTES;     // [8][128] float: gate products per 16 rows
   static constexpr uint32_t GRP = TOT + 8 * TD * 4;        // [8][128] float: dlam totals per 16 rows
   static constexpr uint32_t DIAG = GRP + 8 * TD * 4;       // [128] float: dP[i][i]
-  static constexpr uint32_t DG1 = DIAG + TC * 4;           // [128] float
-  static constexpr uint32_t DG2 = DG1 + TD * 4;            // [128] float
-  static constexpr uint32_t BAR = DG2 + TD * 4;            // 6 mbarriers + tmem slot
-  static constexpr uint32_t END = BAR + 64;
+  static constexpr uint32_t DG1 = DIAG + TC * 4;           // [4][128] float: partial sums of the two dG terms, one slot per
+  static constexpr uint32_t DG2 = DG1 + 4 * TD * 4;        // [4][128] float  quarter of the rows (summed in a fixed order)
+  static constexpr uint32_t GAB = DG2 + 4 * TD * 4;        // [4][128] float: sums of |g| per 32 rows
+  static constexpr uint32_t BAR = GAB + 4 * TD * 4;        // 7 mbarriers + tmem slot
+  static constexpr uint32_t END = BAR + 96;
   // After the phase-1 products have completed, dO, v and P are dead; after phase 1.5 the rest is.  Reuse:
   static constexpr uint32_t W64 = KH;                      // 32 KB: k~ / q~ at the h = 64 anchor, all 128 rows
   static constexpr uint32_t WL = DS;                       // 2 x 16 KB: per-level W_l
@@ -711,6 +786,12 @@ struct BwdSmem {
   static constexpr uint32_t QH = P;                        // [64][128] bf16: q of the pass's rows
   static constexpr uint32_t K1 = P + 16384;                // [64][128] bf16: k of rows 64..127
   static constexpr uint32_t K0 = V;                        // [64][128] bf16: k of rows 0..63
+  // One-scale path (chunks whose gates need no secondary chunking), after the phase-1 products:
+  static constexpr uint32_t QA = DO;                       // [128][128] bf16 row-major: raw q of the chunk (TMA)
+  static constexpr uint32_t KA = P;                        // [128][128] bf16 row-major: raw k of the chunk (TMA)
+  static constexpr uint32_t DPM = V;                       // 32 KB: dP masked to the strict lower triangle (rows i, cols j)
+  static constexpr uint32_t QT = SP;                       // 32 KB: q~ = q exp(lam - G), stored like k_hat (rows = feature)
+  static constexpr uint32_t DLB = V;                       // [32][512] float (64 KB over V and S_prev): dlam suffix sums
 };
 struct BwdMaps {
   CUtensorMap g, q, k;          // boxes of 128 features x 64 rows, unswizzled (row passes)
@@ -784,7 +865,7 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
                     const bf16* __restrict__ k, const bf16* __restrict__ q, const bf16* __restrict__ dO,
                     const bf16* __restrict__ S_prev, const bf16* __restrict__ dS_next, const bf16* __restrict__ P_saved,
                     bf16* __restrict__ dq_out, bf16* __restrict__ dk_out, bf16* __restrict__ dv_out,
-                    float* __restrict__ dg_out) {
+                    float* __restrict__ dg_out, int all_scales) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = align1024(smem_raw);
   float* tot = reinterpret_cast<float*>(sm + BwdSmem::TOT);
@@ -792,6 +873,7 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
   float* diag = reinterpret_cast<float*>(sm + BwdSmem::DIAG);
   float* dG1 = reinterpret_cast<float*>(sm + BwdSmem::DG1);
   float* dG2 = reinterpret_cast<float*>(sm + BwdSmem::DG2);
+  float* gab = reinterpret_cast<float*>(sm + BwdSmem::GAB);
   uint64_t* bars = reinterpret_cast<uint64_t*>(sm + BwdSmem::BAR);   // [0]: phase 1, [1],[2]: level buffers, [3],[4]: pass loads, [5]: tiles, [6]: raw k
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
 
@@ -807,7 +889,6 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
   const int64_t HDi = (H / R) * TD;                                   // input row pitch
   const int64_t row0 = ((b * T + n * TC) * H + h_) * TD;              // outputs
   const int64_t row0k = ((b * T + n * TC) * (H / R) + hk_) * TD;      // g, q, k
-  const int64_t row0v = ((b * T + n * TC) * (H / R) + hv_) * TD;      // v, dO
   const int64_t chunk_id = bh * N + n;
 
   if (warp == 0) {
@@ -845,8 +926,6 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
       tma_load_2d(smem_u32(sm + BwdSmem::P + half * TILE_BYTES), &maps.p, 64 * half, cr, lb);
     }
   }
-  if (tid < TD) { dG1[tid] = 0.f; dG2[tid] = 0.f; }
-  TC_STAMP(1, 0);
 
   // ---- phase 0: gate products per 16 rows; k_hat (the operand tiles are arriving by TMA) ------------------
   float f32r[32];                                   // gates of rows 32 wq_ + [0, 32), feature d
@@ -855,13 +934,16 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
     const float* gp = g + row0k + (int64_t)(32 * wq_) * HDi + d;
 #pragma unroll
     for (int i = 0; i < 32; ++i) f32r[i] = __ldg(gp + (int64_t)i * HDi);      // all 32 loads in flight
+    float ga = 0.f;
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
+      ga += fabsf(f32r[i]);
       f32r[i] = __expf(f32r[i]);
       if (i < 16) p0 *= f32r[i]; else p1 *= f32r[i];
     }
     tot[(2 * wq_) * TD + d] = p0;
     tot[(2 * wq_ + 1) * TD + d] = p1;
+    gab[wq_ * TD + d] = ga;
   }
   uint32_t kraw[32];                                // k of the same rows and feature, from the staged tile
   {
@@ -874,7 +956,13 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  TC_STAMP(1, 1);
+  // One scale or all of them (see ONE_SCALE_LIMIT): decided from the chunk's total |log decay| per feature, the
+  // same way for every thread of the block.
+  bool one_scale;
+  {
+    const float tsum = (gab[d] + gab[TD + d]) + (gab[2 * TD + d] + gab[3 * TD + d]);
+    one_scale = __syncthreads_or(!(tsum <= ONE_SCALE_LIMIT) || all_scales != 0) == 0;
+  }
   {
     // k_hat[r][d] = k[r][d] * prod_{t > r} f_t   (rows of this thread: 32 wq_ + i)
     float run = 1.f;
@@ -900,7 +988,6 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
   tc_fence_before();
   __syncthreads();
 
-  TC_STAMP(1, 2);
   // ---- phase 1: the four dense products --------------------------------------------------------------
   // Issued by four threads of four warps on different schedulers (8 to 16 MMAs each instead of 40 from one): the
   // issuing thread's instruction stream is serial, so this shortens the wait of everybody else.  The two halves of
@@ -964,17 +1051,25 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
   ok = mbar_wait(smem_u32(bars + 0), 0) && ok;
   ok = mbar_wait(smem_u32(bars + 5), 0) && ok;      // every thread observes the tiles' arrival itself before reading them
   tc_fence_after();
-  TC_STAMP(1, 3);
   // dO, v and P have been consumed by the products: their regions take g, q, k of rows 64..127 and k of rows
   // 0..63 by TMA while phase 1.5 runs, so that the W64 build and the first pass read them from shared memory.
   const int zrow = (int)(b * T + n * TC), yh = (int)hk_;
   if (tid == 0) {
     const uint32_t lb = smem_u32(bars + 3);
-    mbar_arrive_expect_tx(lb, 32768 + 3 * 16384);
-    tma_load_3d(smem_u32(sm + BwdSmem::GH), &maps.g, 0, yh, zrow + 64, lb);
-    tma_load_3d(smem_u32(sm + BwdSmem::QH), &maps.q, 0, yh, zrow + 64, lb);
-    tma_load_3d(smem_u32(sm + BwdSmem::K1), &maps.k, 0, yh, zrow + 64, lb);
-    tma_load_3d(smem_u32(sm + BwdSmem::K0), &maps.k, 0, yh, zrow, lb);
+    if (one_scale) {
+      // raw q and k of the whole chunk, row-major, for the q~ operand and the closing pass
+      mbar_arrive_expect_tx(lb, 4 * 16384);
+      tma_load_3d(smem_u32(sm + BwdSmem::QA), &maps.q, 0, yh, zrow, lb);
+      tma_load_3d(smem_u32(sm + BwdSmem::QA + 16384), &maps.q, 0, yh, zrow + 64, lb);
+      tma_load_3d(smem_u32(sm + BwdSmem::KA), &maps.k, 0, yh, zrow, lb);
+      tma_load_3d(smem_u32(sm + BwdSmem::KA + 16384), &maps.k, 0, yh, zrow + 64, lb);
+    } else {
+      mbar_arrive_expect_tx(lb, 32768 + 3 * 16384);
+      tma_load_3d(smem_u32(sm + BwdSmem::GH), &maps.g, 0, yh, zrow + 64, lb);
+      tma_load_3d(smem_u32(sm + BwdSmem::QH), &maps.q, 0, yh, zrow + 64, lb);
+      tma_load_3d(smem_u32(sm + BwdSmem::K1), &maps.k, 0, yh, zrow + 64, lb);
+      tma_load_3d(smem_u32(sm + BwdSmem::K0), &maps.k, 0, yh, zrow, lb);
+    }
   }
 
   // ---- phase 1.5: dV out, dP diagonal, the two dG sums ---------------------------------------------------
@@ -1002,14 +1097,33 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
       for (int m = 0; m < 32; ++m)
         if (m == lane) dv_ = __uint_as_float(r[m]);
       diag[d] = dv_;
-      // this row's 16 x 16 diagonal block of dP in float32, for the small levels done on the CUDA cores
-      // (the P tile this overwrites was last read by the dV product, which has completed)
-      float4* dpd = reinterpret_cast<float4*>(sm + BwdSmem::DPD + d * 64);
-      const bool hi = (lane & 16) != 0;
+      if (!one_scale) {
+        // this row's 16 x 16 diagonal block of dP in float32, for the small levels done on the CUDA cores
+        // (the v tile this overwrites was last read by the phase-1 products, which have completed)
+        float4* dpd = reinterpret_cast<float4*>(sm + BwdSmem::DPD + d * 64);
+        const bool hi = (lane & 16) != 0;
 #pragma unroll
-      for (int c4 = 0; c4 < 4; ++c4)
-        dpd[c4] = make_float4(__uint_as_float(hi ? r[16 + 4 * c4 + 0] : r[4 * c4 + 0]), __uint_as_float(hi ? r[16 + 4 * c4 + 1] : r[4 * c4 + 1]),
-                              __uint_as_float(hi ? r[16 + 4 * c4 + 2] : r[4 * c4 + 2]), __uint_as_float(hi ? r[16 + 4 * c4 + 3] : r[4 * c4 + 3]));
+        for (int c4 = 0; c4 < 4; ++c4)
+          dpd[c4] = make_float4(__uint_as_float(hi ? r[16 + 4 * c4 + 0] : r[4 * c4 + 0]), __uint_as_float(hi ? r[16 + 4 * c4 + 1] : r[4 * c4 + 1]),
+                                __uint_as_float(hi ? r[16 + 4 * c4 + 2] : r[4 * c4 + 2]), __uint_as_float(hi ? r[16 + 4 * c4 + 3] : r[4 * c4 + 3]));
+      }
+    }
+    if (one_scale) {
+      // dP restricted to j < i as a bf16 operand tile (row i = d here, columns 32 wq_ + [0, 32)); the v tile it
+      // overwrites was last read by the phase-1 products
+      tmem_ld32(tmem + ((uint32_t)(q4 * 32) << 16) + TM_DP + 32 * wq_, r);
+      tmem_ld_wait();
+      uint8_t* tile = sm + BwdSmem::DPM + (wq_ >> 1) * TILE_BYTES;
+#pragma unroll
+      for (int c4 = 0; c4 < 4; ++c4) {
+        uint32_t pk[4];
+#pragma unroll
+        for (int m = 0; m < 8; m += 2) {
+          const int j = 32 * wq_ + 8 * c4 + m;
+          pk[m >> 1] = pack_bf16x2(j < d ? __uint_as_float(r[8 * c4 + m]) : 0.f, j + 1 < d ? __uint_as_float(r[8 * c4 + m + 1]) : 0.f);
+        }
+        *reinterpret_cast<uint4*>(tile + sw128_chunk(d, (wq_ & 1) * 4 + c4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      }
     }
     // dG1[d] = sum_r dKh^T[d][r] k_hat[r][d]   (this thread: rows 32 wq_ + m)
     tmem_ld32(tmem + ((uint32_t)(q4 * 32) << 16) + TM_DKH + 32 * wq_, r);
@@ -1024,7 +1138,7 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
       s1 = fmaf(__uint_as_float(r[8 * c4 + 4]), bf16_lo(a.z), s1); s1 = fmaf(__uint_as_float(r[8 * c4 + 5]), bf16_hi(a.z), s1);
       s1 = fmaf(__uint_as_float(r[8 * c4 + 6]), bf16_lo(a.w), s1); s1 = fmaf(__uint_as_float(r[8 * c4 + 7]), bf16_hi(a.w), s1);
     }
-    atomicAdd(dG1 + d, s1);
+    dG1[wq_ * TD + d] = s1;
     // dG2[d] = sum_v S_prev[d][v] dS_next[d][v]    (this thread: v in 32 wq_ + [0, 32))
     float s2 = 0.f;
     const uint8_t* ts = sm + BwdSmem::SP + (wq_ >> 1) * TILE_BYTES;
@@ -1036,13 +1150,124 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
       s2 += bf16_lo(a.x) * bf16_lo(c.x) + bf16_hi(a.x) * bf16_hi(c.x) + bf16_lo(a.y) * bf16_lo(c.y) + bf16_hi(a.y) * bf16_hi(c.y) +
             bf16_lo(a.z) * bf16_lo(c.z) + bf16_hi(a.z) * bf16_hi(c.z) + bf16_lo(a.w) * bf16_lo(c.w) + bf16_hi(a.w) * bf16_hi(c.w);
     }
-    atomicAdd(dG2 + d, s2);
+    dG2[wq_ * TD + d] = s2;
   }
   tc_fence_before();
   __syncthreads();      // all readers of the phase-1 tiles are done: the regions can be reused
   tc_fence_after();
 
-  TC_STAMP(1, 4);
+  float eG = 1.f;
+#pragma unroll
+  for (int b2 = 0; b2 < 8; ++b2) eG *= tot[b2 * TD + d];
+  // the four partial sums of each dG term in a fixed order: the result does not depend on which warp came first
+  const float dG = ((dG1[d] + dG1[TD + d]) + (dG1[2 * TD + d] + dG1[3 * TD + d])) +
+                   eG * ((dG2[d] + dG2[TD + d]) + (dG2[2 * TD + d] + dG2[3 * TD + d]));
+
+  if (one_scale) {
+    // ---- one anchor (the chunk's last row) for all intra-chunk terms:
+    //   dq~^T[d][i] = sum_j k_hat[j][d] dPm[i][j],   dq_intra = dq~ exp(lam_i - G)
+    //   dk~^T[d][j] = sum_i q~[i][d]   dPm[i][j],   dk_intra = dk~ exp(G - lam_j),   q~ = q exp(lam - G)
+    // two 128 x 128 x 128 products; a thread (feature d, rows 32 wq_ + [0, 32)) then finishes its rows in one pass.
+    const uint32_t lane_base = tmem + ((uint32_t)(q4 * 32) << 16);
+    ok = mbar_wait(smem_u32(bars + 3), 0) && ok;        // raw q and k have landed
+    const float t0 = tot[(2 * wq_) * TD + d], t1 = tot[(2 * wq_ + 1) * TD + d];
+    float Cq = 1.f, Ck = 1.f;                           // gate products of the rows before / after this thread's 32
+    for (int b2 = 0; b2 < 2 * wq_; ++b2) Cq *= tot[b2 * TD + d];
+    for (int b2 = 2 * wq_ + 2; b2 < 8; ++b2) Ck *= tot[b2 * TD + d];
+    const unsigned short* qp = reinterpret_cast<const unsigned short*>(sm + BwdSmem::QA) + (32 * wq_) * TD + d;
+    const unsigned short* kp = reinterpret_cast<const unsigned short*>(sm + BwdSmem::KA) + (32 * wq_) * TD + d;
+    {
+      uint32_t qr[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) qr[i] = qp[i * TD];
+      // q~[r] = q[r] / prod_{t > r} f_t = q[r] * (prod_{first <= t <= r} f_t) / (prod_{t >= first} f_t): one reciprocal
+      float run = 1.f / (t0 * t1 * Ck);
+      uint32_t pk[16];
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        run *= f32r[i];
+        const float lo = bf16_lo(qr[i]) * run;
+        run *= f32r[i + 1];
+        const float hi = bf16_lo(qr[i + 1]) * run;
+        pk[i >> 1] = pack_bf16x2(lo, hi);
+      }
+      uint8_t* tile = sm + BwdSmem::QT + (wq_ >> 1) * TILE_BYTES;       // transposed like k_hat: row = feature
+#pragma unroll
+      for (int c4 = 0; c4 < 4; ++c4)
+        *reinterpret_cast<uint4*>(tile + sw128_chunk(d, (wq_ & 1) * 4 + c4)) =
+            make_uint4(pk[4 * c4], pk[4 * c4 + 1], pk[4 * c4 + 2], pk[4 * c4 + 3]);
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after();
+      constexpr uint32_t iK = idesc_bf16(128, 128, 0, 0);
+      const uint64_t kA = desc_kmajor(smem_u32(sm + BwdSmem::KH), TILE_BYTES, 0), kB = desc_kmajor(smem_u32(sm + BwdSmem::DPM), TILE_BYTES, 0);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)     // dq~^T[d][i] = sum_j k_hat^T[d][j] dPm[i][j]
+        umma_bf16(tmem + TM_DV, kslice_kmajor(kA, TILE_BYTES, ks), kslice_kmajor(kB, TILE_BYTES, ks), iK, ks > 0);
+      umma_commit(smem_u32(bars + 1));
+    } else if (tid == 32) {
+      tc_fence_after();
+      constexpr uint32_t iM = idesc_bf16(128, 128, 0, 1);
+      const uint64_t kA = desc_kmajor(smem_u32(sm + BwdSmem::QT), TILE_BYTES, 0), mB = desc_mnmajor(smem_u32(sm + BwdSmem::DPM), TILE_BYTES, 0);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)     // dk~^T[d][j] = sum_i q~^T[d][i] dPm[i][j]
+        umma_bf16(tmem + TM_DP, kslice_kmajor(kA, TILE_BYTES, ks), kslice_mnmajor(mB, ks), iM, ks > 0);
+      umma_commit(smem_u32(bars + 2));
+    }
+    ok = mbar_wait(smem_u32(bars + 1), 0) && ok;
+    ok = mbar_wait(smem_u32(bars + 2), 0) && ok;
+    tc_fence_after();
+    const float invG = 1.f / eG;
+    float* dlb = reinterpret_cast<float*>(sm + BwdSmem::DLB);      // the operands it overwrites have been consumed
+    float carry = 0.f;            // sum of dlam over this thread's rows after the current half
+#pragma unroll
+    for (int hh = 1; hh >= 0; --hh) {
+      const int rb = 32 * wq_ + 16 * hh;
+      uint32_t a[16], c[16], qk[16];     // qk: q in the low half, k in the high half
+      float dl[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) qk[i] = (uint32_t)qp[(16 * hh + i) * TD] | ((uint32_t)kp[(16 * hh + i) * TD] << 16);
+      tmem_ld16(lane_base + TM_DQH + rb, a);
+      tmem_ld16(lane_base + TM_DV + rb, c);
+      tmem_ld_wait();
+      float run = hh ? Cq * t0 : Cq;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        run *= f32r[16 * hh + i];          // exp(lam_r)
+        const float dqv = run * fmaf(invG, __uint_as_float(c[i]), __uint_as_float(a[i])) + diag[rb + i] * bf16_hi(qk[i]);
+        dl[i] = bf16_lo(qk[i]) * dqv;
+        if (ok) dq_out[row0 + (int64_t)(rb + i) * HD + d] = __float2bfloat16_rn(dqv);
+      }
+      tmem_ld16(lane_base + TM_DKH + rb, a);
+      tmem_ld16(lane_base + TM_DP + rb, c);
+      tmem_ld_wait();
+      run = hh ? Ck : Ck * t1;
+#pragma unroll
+      for (int i = 15; i >= 0; --i) {      // run = exp(G - lam_r)
+        const float dkv = run * (__uint_as_float(a[i]) + __uint_as_float(c[i])) + diag[rb + i] * bf16_lo(qk[i]);
+        run *= f32r[16 * hh + i];
+        dl[i] -= bf16_hi(qk[i]) * dkv;
+        if (ok) dk_out[row0 + (int64_t)(rb + i) * HD + d] = __float2bfloat16_rn(dkv);
+      }
+#pragma unroll
+      for (int i = 14; i >= 0; --i) dl[i] += dl[i + 1];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) dlb[(16 * hh + i) * TTHREADS + tid] = dl[i] + carry;
+      carry += dl[0];
+    }
+    grp[wq_ * TD + d] = carry;
+    tc_fence_before();
+    __syncthreads();
+    float off = dG;
+    for (int w2 = wq_ + 1; w2 < 4; ++w2) off += grp[w2 * TD + d];
+    if (ok) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) dg_out[row0 + (int64_t)(32 * wq_ + i) * HD + d] = dlb[i * TTHREADS + tid] + off;
+    }
+  } else {
   // ---- phase 1.9: W64 for all 128 rows (rows < 64: k~, rows >= 64: q~, anchor row 63) ----------------------
   {
     uint8_t* tile = sm + BwdSmem::W64 + (wq_ >> 1) * TILE_BYTES;       // transposed like k_hat: row = feature
@@ -1080,12 +1305,7 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
       *reinterpret_cast<uint4*>(tile + sw128_chunk(d, (wq_ & 1) * 4 + c4)) =
           make_uint4(pk[4 * c4], pk[4 * c4 + 1], pk[4 * c4 + 2], pk[4 * c4 + 3]);
   }
-  float eG = 1.f;
-#pragma unroll
-  for (int b2 = 0; b2 < 8; ++b2) eG *= tot[b2 * TD + d];
-  const float dG = dG1[d] + eG * dG2[d];
 
-  TC_STAMP(1, 5);
   // ---- phase 2: two passes over the rows ----------------------------------------------------------------------
   uint32_t ph1 = 0, ph2 = 0;      // completed-phase counters of bars[1], bars[2]
   const uint32_t aW64 = smem_u32(sm + BwdSmem::W64), aWL = smem_u32(sm + BwdSmem::WL), aDPL = smem_u32(sm + BwdSmem::DPL);
@@ -1134,7 +1354,6 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
       }
     }
 
-    TC_STAMP(1, 6 + 10 * (1 - p));
     // one level: build operands, issue; the accumulate of the previous level overlaps the MMA
     auto build_and_issue = [&](auto SC) {
       constexpr int S = decltype(SC)::value;
@@ -1288,16 +1507,12 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
         }
       }
     }
-    TC_STAMP(1, 7 + 10 * (1 - p));
     accumulate(I3{});
-    TC_STAMP(1, 8 + 10 * (1 - p));
     build_and_issue(I5{});
     accumulate(I4{});
-    TC_STAMP(1, 9 + 10 * (1 - p));
     build_and_issue(I6{});
     accumulate(I5{});
     accumulate(I6{});
-    TC_STAMP(1, 10 + 10 * (1 - p));
 
     // ---- outputs of this pass ---------------------------------------------------------------------------
     float dl[16];
@@ -1321,12 +1536,12 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
 #pragma unroll
       for (int i = 0; i < 16; ++i) dg_out[row0 + (int64_t)(rbase + i) * HD + d] = dl[i] + off;
     }
-    TC_STAMP(1, 11 + 10 * (1 - p));
     if (p == 1) {
       later = 0.f;
       for (int g2 = 4; g2 < 8; ++g2) later += grp[g2 * TD + d];
     }
   }
+  }   // all scales
   if (!ok && tid == 0) atomicAdd(&g_tc_wait_timeouts, 1u);
   tc_fence_before();
   __syncthreads();
@@ -1437,15 +1652,10 @@ size_t tc_bwd_ws_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t) {
 
 constexpr size_t FWD_SMEM = 1024 + FwdSmem::END;
 
-// GLA_B200_EARLY_START=0 keeps the chunk kernel strictly behind the state kernel (read per call).
-static bool early_start_enabled() {
-  const char* e = getenv("GLA_B200_EARLY_START");
-  return !(e != nullptr && e[0] == '0');
-}
-
 int tc_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, int64_t C, const void* hidden_init,
                  const float* g, const void* v, const void* k, const void* q, void* hidden_final, void* out,
-                 void* saved, void* ws, int state_only, float* G_total, float* S_local, int64_t nseq, const int* cu) {
+                 void* saved, void* ws, int state_only, float* G_total, float* S_local, int opts, int64_t nseq,
+                 const int* cu) {
   (void)C;
   const int R = (int)(D / TD);
   const int64_t N = T / TC, HV = H * R * R, HK = H * R, BHV = B * HV;
@@ -1474,10 +1684,10 @@ int tc_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
     GLA_TRY(launch_state_block(st, hidden_init, hib, B * H, R, 1));
     init_v = hib; fin_v = hfb;
   }
-  const bool fused_states = !state_only && (R > 1 || cu != nullptr || tc_state_fused_preferred(BHV, N));
+  const bool fused_states = !state_only && (R > 1 || cu != nullptr || tc_state_fused_preferred(BHV, N, opts));
   // The chunk kernel may start beside the one-pass state kernel (which fills only 4 x batch x heads SMs) when it
   // is the very next launch: plain head size, and the kv area of the workspace, unused then, holds the counter.
-  unsigned int* early_flag = (fused_states && R == 1 && early_start_enabled()) ? (unsigned int*)kv : nullptr;
+  unsigned int* early_flag = (fused_states && R == 1 && !(opts & GLA_OPT_NO_EARLY_START)) ? (unsigned int*)kv : nullptr;
   unsigned int early_target = 0;
   if (fused_states) GLA_TRY(tc_state_fused(st, 0, B, T, HV, R, g, k, v, init_v, S_prev, fin_v, Gc, nseq, cu, early_flag, &early_target));
   else GLA_TRY((launch_tc_kv<0>(st, B, T, H, g, k, v, kv, Gc)));
@@ -1489,8 +1699,10 @@ int tc_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
     return GLA_OK;
   }
   if (!fused_states) GLA_TRY(launch_state_scan(st, BHV, N, TD, Gc, kv, 0, hidden_init, 1, S_prev, 1, hidden_final, 1, 0));
-  cudaError_t e = cudaFuncSetAttribute(tc_chunk_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FWD_SMEM);
-  if (e != cudaSuccess) return record_cuda_error(e);
+  static SmemAttrOnce fwd_attr;
+  GLA_TRY(fwd_attr.ensure(tc_chunk_fwd_kernel, FWD_SMEM));
+  cudaError_t e;
+  const int all_scales = (opts & GLA_OPT_ALL_SCALES) ? 1 : 0;
   FwdMaps maps;
   GLA_TRY(make_map_bthd(&maps.g, g, 1, B, T, HK, 128, 0));
   GLA_TRY(make_map_bthd(&maps.q, q, 0, B, T, HK, 64, 1));
@@ -1513,10 +1725,10 @@ int tc_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
       cfg.attrs = attr;
       cfg.numAttrs = 1;
       e = cudaLaunchKernelEx(&cfg, tc_chunk_fwd_kernel, maps, T, HV, R, N, out_p, P, (const unsigned int*)early_flag,
-                             early_target);
+                             early_target, all_scales);
       if (e != cudaSuccess) return record_cuda_error(e);
     } else {
-      tc_chunk_fwd_kernel<<<(unsigned)(BHV * N), TTHREADS, FWD_SMEM, st>>>(maps, T, HV, R, N, out_p, P, nullptr, 0u);
+      tc_chunk_fwd_kernel<<<(unsigned)(BHV * N), TTHREADS, FWD_SMEM, st>>>(maps, T, HV, R, N, out_p, P, nullptr, 0u, all_scales);
     }
   }
   GLA_CHECK_LAUNCH();
@@ -1544,8 +1756,8 @@ int tc_local_dstate(cudaStream_t st, int64_t B, int64_t T, int64_t H, const floa
 
 int tc_chunk_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, int64_t C, const float* g,
                  const void* v, const void* k, const void* q, const void* saved, const void* dhidden_final,
-                 const void* dout, void* dhidden_init, float* dg, void* dv, void* dk, void* dq, void* ws, int64_t nseq,
-                 const int* cu) {
+                 const void* dout, void* dhidden_init, float* dg, void* dv, void* dk, void* dq, void* ws, int opts,
+                 int64_t nseq, const int* cu) {
   (void)C;
   const int R = (int)(D / TD);
   const int64_t N = T / TC, HV = H * R * R, HK = H * R, BHV = B * HV;
@@ -1573,14 +1785,14 @@ int tc_chunk_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
     GLA_TRY(launch_state_block(st, dhidden_final, dhfb, B * H, R, 1));
     dfin_v = dhfb; dinit_v = dhib;
   }
-  if (R > 1 || cu != nullptr || tc_state_fused_preferred(BHV, N)) {
+  if (R > 1 || cu != nullptr || tc_state_fused_preferred(BHV, N, opts)) {
     GLA_TRY(tc_state_fused(st, 1, B, T, HV, R, g, q, dout, dfin_v, dS_next, dinit_v, nullptr, nseq, cu));
   } else {
     GLA_TRY((launch_tc_kv<1>(st, B, T, H, g, q, dout, dstate, nullptr)));
     GLA_TRY(launch_state_scan(st, BHV, N, TD, Gc, dstate, 0, dhidden_final, 1, dS_next, 1, dhidden_init, 1, 1));
   }
-  cudaError_t e = cudaFuncSetAttribute(tc_chunk_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)BWD_SMEM);
-  if (e != cudaSuccess) return record_cuda_error(e);
+  static SmemAttrOnce bwd_attr;
+  GLA_TRY(bwd_attr.ensure(tc_chunk_bwd_kernel, BWD_SMEM));
   BwdMaps bmaps;
   GLA_TRY(make_map_bthd(&bmaps.g, g, 1, B, T, HK, 128, 0, 64));
   GLA_TRY(make_map_bthd(&bmaps.q, q, 0, B, T, HK, 128, 0, 64));
@@ -1593,8 +1805,8 @@ int tc_chunk_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
   {
     ProfScope ps("tc_chunk_bwd_kernel", st);
     tc_chunk_bwd_kernel<<<(unsigned)(BHV * N), TTHREADS, BWD_SMEM, st>>>(
-        bmaps, T, HV, R, N, prefetch_distance(1), g, (const bf16*)v, (const bf16*)k, (const bf16*)q, (const bf16*)dout, S_prev, dS_next, P,
-        dq_v, dk_v, dv_v, dg_v);
+        bmaps, T, HV, R, N, (opts & GLA_OPT_NO_L2_PREFETCH) ? 0 : prefetch_distance(1), g, (const bf16*)v, (const bf16*)k,
+        (const bf16*)q, (const bf16*)dout, S_prev, dS_next, P, dq_v, dk_v, dv_v, dg_v, (opts & GLA_OPT_ALL_SCALES) ? 1 : 0);
   }
   GLA_CHECK_LAUNCH();
   if (R > 1) {
@@ -1605,10 +1817,6 @@ int tc_chunk_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
     GLA_TRY(launch_state_block(st, dhib, dhidden_init, B * H, R, 0));
   }
   return GLA_OK;
-}
-
-void tc_read_trace(long long* out64) {
-  cudaMemcpyFromSymbol(out64, g_tc_trace, sizeof(long long) * 64);
 }
 
 unsigned int tc_read_wait_timeouts() {

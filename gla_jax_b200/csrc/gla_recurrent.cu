@@ -55,9 +55,6 @@ struct RecParams {
 
 // Packed pairs of float32 in one 64-bit register: Blackwell's two-wide FMA halves the issue slots
 // of the state update, which is what bounds these kernels (few warps per SM, long straight-line steps).
-#ifndef REC_X2
-#define REC_X2 1
-#endif
 typedef unsigned long long f32x2;
 __device__ __forceinline__ f32x2 x2_pack(float lo, float hi) {
   f32x2 r;
@@ -232,14 +229,12 @@ __device__ __forceinline__ void rec_body(const RecParams& p, const int64_t b) {
     for (int a = 0; a < NS; ++a) tile_fetch<RS, SG, RTHREADS>(sreg[a], Ssrc[a], base, HD, step0, T, trev, c0);
   };
   fetch(0);
-#if REC_X2
   // the state as pairs along the long axis: st2[i][j] = (st[2i][j], st[2i+1][j])
   f32x2 st2[KP / 2][NSI];
 #pragma unroll
   for (int i = 0; i < KP / 2; ++i)
 #pragma unroll
     for (int j = 0; j < NSI; ++j) st2[i][j] = x2_pack(st[2 * i][j], st[2 * i + 1][j]);
-#endif
   for (int64_t step0 = 0; step0 < T; step0 += RB) {
     __syncthreads();   // previous block's readers of the tiles and of Rs are done
 #pragma unroll
@@ -250,7 +245,6 @@ __device__ __forceinline__ void rec_body(const RecParams& p, const int64_t b) {
     if (step0 + RB < T) fetch(step0 + RB);
     const int nt = (int)((T - step0) < RB ? (T - step0) : RB);
     // One step of the recurrence for this thread's state; returns the four per-step sums (not yet reduced).
-#if REC_X2
     auto step = [&](int tt, float (&red)[NSI]) {
       f32x2 red2[NSI], s0d[NSI], s1d[NSI], s2d[NSI];
       // the step's slice-axis scalars, each broadcast to both halves of a pair (duplicating them in
@@ -309,53 +303,6 @@ __device__ __forceinline__ void rec_body(const RecParams& p, const int64_t b) {
         red[j] = lo + hi;
       }
     };
-#else
-    auto step = [&](int tt, float (&red)[NSI]) {
-#pragma unroll
-      for (int j = 0; j < NSI; ++j) red[j] = 0.f;
-      // the step's slice-axis scalars for this thread's four slice entries (one broadcast 16-byte load each)
-      float s0v[NSI], s1v[NSI], s2v[NSI];
-#pragma unroll
-      for (int j = 0; j < NSI; ++j) {
-        s0v[j] = smem[S_BASE + tt * RS + NSI * sg + j];
-        s1v[j] = NS == 3 ? smem[S_BASE + S_OFF + tt * RS + NSI * sg + j] : 0.f;
-        s2v[j] = NS == 3 ? smem[S_BASE + 2 * S_OFF + tt * RS + NSI * sg + j] : 0.f;
-      }
-#pragma unroll
-      for (int m = 0; m < KP / 4; ++m) {
-        const int off = tt * D + 4 * LP * m + 4 * lp;
-        const float4 a4 = *reinterpret_cast<const float4*>(smem + off);
-        const float4 b4 = *reinterpret_cast<const float4*>(smem + L_OFF + off);
-        float4 c4 = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (NL == 3) c4 = *reinterpret_cast<const float4*>(smem + 2 * L_OFF + off);
-        const float av[4] = {a4.x, a4.y, a4.z, a4.w};
-        const float bv[4] = {b4.x, b4.y, b4.z, b4.w};
-        const float cv[4] = {c4.x, c4.y, c4.z, c4.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-#pragma unroll
-          for (int j = 0; j < NSI; ++j) {
-            float& S = st[4 * m + e][j];
-            if (MODE == REC_FWD) {          // a = f, b = k, c = q ; s0 = v
-              S = fmaf(av[e], S, bv[e] * s0v[j]);
-              red[j] = fmaf(cv[e], S, red[j]);
-            } else if (MODE == REC_DQ) {    // a = v, b = dO ; s0 = f, s1 = k
-              S = fmaf(s0v[j], S, s1v[j] * av[e]);
-              red[j] = fmaf(bv[e], S, red[j]);
-            } else if (MODE == REC_DV) {    // a = f, b = k, c = q ; s0 = dO
-              const float tmp = fmaf(cv[e], s0v[j], S);
-              red[j] = fmaf(bv[e], tmp, red[j]);
-              S = av[e] * tmp;
-            } else {                        // a = v, b = dO ; s0 = f, s1 = k, s2 = q
-              const float tmp = fmaf(s2v[j], bv[e], S);
-              red[j] = fmaf(av[e], tmp, red[j]);
-              S = s0v[j] * tmp;
-            }
-          }
-        }
-      }
-    };
-#endif
     // The block's steps are fully unrolled with the reduced sums kept in registers until the end: with no
     // shared-memory store between the steps the compiler is free to issue a step's loads and FMAs while the
     // previous step's shuffle chain is still in flight (an in-order warp otherwise waits out every chain).
@@ -405,12 +352,10 @@ __device__ __forceinline__ void rec_body(const RecParams& p, const int64_t b) {
       }
     }
   }
-#if REC_X2
 #pragma unroll
   for (int i = 0; i < KP / 2; ++i)
 #pragma unroll
     for (int j = 0; j < NSI; ++j) x2_unpack(st2[i][j], st[2 * i][j], st[2 * i + 1][j]);
-#endif
   // final state
   if (MODE == REC_FWD) {
     if (p.hidden_final) {

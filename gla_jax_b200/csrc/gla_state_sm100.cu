@@ -322,15 +322,23 @@ unsigned int tc_state_read_wait_timeouts() {
 
 // Whether the one-pass kernel is expected to beat the product + scan pair for this shape.
 // Its time is (waves of (B*H*4) blocks over the SMs) x N sequential steps; the pair's time grows with
-// the total number of chunks.  Step and per-chunk costs measured on B200; the environment variable
-// GLA_B200_STATE_FUSED=0/1
-// overrides the estimate.
-bool tc_state_fused_preferred(int64_t BH, int64_t N) {
-  const char* e = getenv("GLA_B200_STATE_FUSED");      // read per call: tests switch it within one process
-  if (e != nullptr && e[0] != 0) return e[0] != '0';
-  int dev = 0, sms = 148;
-  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  if (sms <= 0) sms = 148;
+// the total number of chunks.  Step and per-chunk costs measured on B200; the caller's option bits
+// GLA_OPT_STATE_ONE_PASS / GLA_OPT_STATE_TWO_KERNELS override the estimate.
+static int sm_count() {
+  static int sms[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (sms[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 148;
+    sms[dev] = n;
+  }
+  return sms[dev];
+}
+bool tc_state_fused_preferred(int64_t BH, int64_t N, int opts) {
+  if (opts & GLA_OPT_STATE_ONE_PASS) return true;
+  if (opts & GLA_OPT_STATE_TWO_KERNELS) return false;
+  const int sms = sm_count();
   const double waves = (double)((4 * BH + sms - 1) / sms);
   const double t_fused = waves * (double)N * 1.0 + 8.0;          // us
   const double t_pair = (double)(BH * N) * 0.1 + 10.0;           // us
@@ -352,8 +360,9 @@ int tc_state_fused(cudaStream_t st, int mode, int64_t B, int64_t T, int64_t H, i
   GLA_TRY(make_map_bthd(&maps.x, x, 0, B, T, HK, SL, 0));
   GLA_TRY(make_map_bthd(&maps.y, y, 0, B, T, HK, 64, 1));
   auto kern = mode == 0 ? tc_state_kernel<0> : tc_state_kernel<1>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ST_SMEM);
-  if (e != cudaSuccess) return record_cuda_error(e);
+  static SmemAttrOnce attr[2];
+  GLA_TRY(attr[mode != 0].ensure(kern, ST_SMEM));
+  cudaError_t e;
   if (done != nullptr) {
     e = cudaMemsetAsync(done, 0, sizeof(unsigned int), st);
     if (e != cudaSuccess) return record_cuda_error(e);

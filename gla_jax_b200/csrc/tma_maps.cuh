@@ -22,9 +22,34 @@ inline EncodeTiledFn encode_fn() {
   }
   return fn;
 }
+// A descriptor depends only on (address, extents, box, swizzle), and callers hand the library the same buffers
+// step after step (a training loop's allocator returns the same blocks), so every host thread keeps the last
+// few it built: encoding one costs a driver call, looking one up a few compares.
+struct MapKey {
+  const void* ptr; int64_t a, b; int kind, c, d, e;
+  bool operator==(const MapKey& o) const { return ptr == o.ptr && a == o.a && b == o.b && kind == o.kind && c == o.c && d == o.d && e == o.e; }
+};
+struct MapCache {
+  static constexpr int N = 48;
+  MapKey key[N];
+  CUtensorMap map[N];
+  int used = 0, next = 0;
+  const CUtensorMap* find(const MapKey& k) const {
+    for (int i = 0; i < used; ++i) if (key[i] == k) return &map[i];
+    return nullptr;
+  }
+  void put(const MapKey& k, const CUtensorMap& m) {
+    const int i = used < N ? used++ : (next = (next + 1) % N);
+    key[i] = k; map[i] = m;
+  }
+};
+inline MapCache& map_cache() { static thread_local MapCache c; return c; }
+
 // (B,T,H,128) array seen as 3-d (d, h, b*T + t); box = (box_cols, 1, box_rows); float32 or bf16.
 inline int make_map_bthd(CUtensorMap* m, const void* ptr, int is_f32, int64_t B, int64_t T, int64_t H, int box_cols,
                          int swizzle128, int box_rows = 128) {
+  const MapKey key{ptr, B * T, H, 1 + is_f32, box_cols, swizzle128, box_rows};
+  if (const CUtensorMap* hit = map_cache().find(key)) { *m = *hit; return GLA_OK; }
   EncodeTiledFn fn = encode_fn();
   if (!fn) return GLA_ERR_NO_DEVICE;
   const cuuint64_t es = is_f32 ? 4 : 2;
@@ -36,10 +61,14 @@ inline int make_map_bthd(CUtensorMap* m, const void* ptr, int is_f32, int64_t B,
                   strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? GLA_OK : GLA_ERR_LAUNCH;
+  if (r != CUDA_SUCCESS) return GLA_ERR_LAUNCH;
+  map_cache().put(key, *m);
+  return GLA_OK;
 }
 // dense bf16 matrix of `rows` rows x 128 columns; box = (box_cols, box_rows), 128-byte swizzle.
 inline int make_map_rows(CUtensorMap* m, const void* ptr, int64_t rows, int box_cols, int box_rows) {
+  const MapKey key{ptr, rows, 0, 0, box_cols, box_rows, 0};
+  if (const CUtensorMap* hit = map_cache().find(key)) { *m = *hit; return GLA_OK; }
   EncodeTiledFn fn = encode_fn();
   if (!fn) return GLA_ERR_NO_DEVICE;
   cuuint64_t dims[2] = {(cuuint64_t)128, (cuuint64_t)rows};
@@ -49,8 +78,25 @@ inline int make_map_rows(CUtensorMap* m, const void* ptr, int64_t rows, int box_
   CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)ptr, dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? GLA_OK : GLA_ERR_LAUNCH;
+  if (r != CUDA_SUCCESS) return GLA_ERR_LAUNCH;
+  map_cache().put(key, *m);
+  return GLA_OK;
 }
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (kernel, device) instead of on every call.
+struct SmemAttrOnce {
+  unsigned long long done = 0;       // bit per device; a lost update only repeats an idempotent call
+  template <typename K>
+  int ensure(K kern, size_t bytes) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return GLA_ERR_NO_DEVICE;
+    if (dev >= 0 && dev < 64 && ((done >> dev) & 1ull)) return GLA_OK;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) return record_cuda_error(e);
+    if (dev >= 0 && dev < 64) done |= 1ull << dev;
+    return GLA_OK;
+  }
+};
 
 
 }  // namespace gla

@@ -67,6 +67,27 @@ typedef enum gla_chunk_impl {
   GLA_IMPL_TCGEN05 = 2        /* bf16 operands, fp32 TMEM accumulators (sm_100a tensor cores) */
 } gla_chunk_impl;
 
+/* Options that may be OR-ed into the `impl` argument of the chunk entry points (the low byte is the
+ * gla_chunk_impl).  They select between equivalent ways of running the tensor-core path; results agree to
+ * rounding.  Tests and benchmarks use them to pin a path; callers normally pass none.
+ *   STATE_TWO_KERNELS / STATE_ONE_PASS  how the per-chunk states (gla.py:705-723) are produced: a batched
+ *       k_hat^T v product followed by a streaming scan, or one kernel that keeps the state on chip.  Default:
+ *       chosen from the shape.
+ *   NO_EARLY_START   keep the forward chunk kernel strictly behind the state kernel (default: it is launched as
+ *       a programmatic dependent and its first blocks start on the SMs the state kernel leaves idle).
+ *   ALL_SCALES       always run every level of the secondary chunking (gla.py:843-852, 985-1027).  Default: a
+ *       chunk whose total |log decay| is at most 60 for every feature uses a single anchor, because all its decay
+ *       weights then lie within exp(+-60); sharper chunks take all levels.  The choice is made per chunk on the
+ *       device from the gates themselves.
+ *   NO_L2_PREFETCH   no L2 prefetch of the next chunk's operands in the backward chunk kernel. */
+typedef enum gla_chunk_option {
+  GLA_OPT_STATE_TWO_KERNELS = 0x100,
+  GLA_OPT_STATE_ONE_PASS = 0x200,
+  GLA_OPT_NO_EARLY_START = 0x400,
+  GLA_OPT_ALL_SCALES = 0x800,
+  GLA_OPT_NO_L2_PREFETCH = 0x1000
+} gla_chunk_option;
+
 /* Human-readable text for a status code. Never NULL. (Reference: Python assert messages.) */
 GLA_API const char* gla_status_string(int status);
 
@@ -85,11 +106,6 @@ GLA_API long long gla_launch_count(void);
  * increments a device counter instead of spinning forever.  This reads that counter
  * (synchronises the device; diagnostic).  0 means no wait has ever given up. */
 GLA_API unsigned int gla_device_wait_timeouts(void);
-
-/* SM clock stamps taken at the phase boundaries of one thread block (block 100) of the most
- * recent tensor-core forward ([0..31]) and backward ([32..63]) chunk kernels; diagnostic for
- * tuning, synchronises the device.  No counterpart in the reference. */
-GLA_API void gla_debug_phase_clocks(long long* out64);
 
 /* Per-kernel device timing for benchmarks (diagnostic; no counterpart in the reference, whose
  * harness times whole calls with timeit, gla.py:1430-1434).  While enabled on the calling
