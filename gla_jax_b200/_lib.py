@@ -44,6 +44,7 @@ SIGNATURES = {
     "gla_last_cuda_error": (c_int, []),
     "gla_launch_count": (ctypes.c_longlong, []),
     "gla_device_wait_timeouts": (ctypes.c_uint, []),
+    "gla_device_bad_offsets": (ctypes.c_uint, []),
     "gla_profile_enable": (None, [c_int]),
     "gla_profile_report": (c_size_t, [c_char_p, c_size_t]),
     "gla_cumsum": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int]),
@@ -114,6 +115,35 @@ def load() -> ctypes.CDLL:
 
 def lib_path() -> Path:
     return _LIB_PATH
+
+
+def stream_of(dev) -> int:
+    """The current CUDA stream of `dev` as an integer handle for the C ABI.  The library launches on the CURRENT
+    device (and looks up per-device state there), so tensors on another GPU are refused rather than launched with a
+    stream of the wrong device: wrap the call in ``torch.cuda.device(tensor.device)``."""
+    import torch
+    cur = torch.cuda.current_device()
+    if dev.index is not None and dev.index != cur:
+        raise RuntimeError(f"tensors are on {dev} but the current CUDA device is cuda:{cur}; "
+                           "make their device current (torch.cuda.device(...)) around the call")
+    return torch.cuda.current_stream(dev).cuda_stream
+
+
+_seen = {"waits": 0, "offsets": 0}
+
+
+def check_device() -> None:
+    """Synchronise the current device and raise GlaError if, since the previous call of this function, a bounded
+    device-side wait gave up (the outputs written meanwhile are incomplete) or a packed-sequence call was given
+    offsets that had to be clamped.  The entry points themselves return before their kernels run and cannot
+    report either."""
+    lib = load()
+    waits, offs = int(lib.gla_device_wait_timeouts()), int(lib.gla_device_bad_offsets())
+    new_w, new_o = waits - _seen["waits"], offs - _seen["offsets"]
+    _seen["waits"], _seen["offsets"] = waits, offs
+    if new_w or new_o:
+        raise GlaError(f"device-side errors since the last check: {new_w} wait(s) gave up, {new_o} sequence(s) with "
+                       "invalid packed offsets")
 
 
 def check(status: int, what: str) -> None:

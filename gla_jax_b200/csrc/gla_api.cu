@@ -89,6 +89,8 @@ long long gla_launch_count(void) { return g_launches.load(std::memory_order_rela
 
 unsigned int gla_device_wait_timeouts(void) { return tc_read_wait_timeouts() + tc_state_read_wait_timeouts(); }
 
+unsigned int gla_device_bad_offsets(void) { return tc_state_read_bad_offsets(); }
+
 void gla_profile_enable(int on) {
   g_prof_on = on != 0;
   if (on) g_prof_n = 0;

@@ -126,6 +126,7 @@ int tc_state_fused(cudaStream_t st, int mode, int64_t B, int64_t T, int64_t H, i
                    const void* y, const void* init, void* states, void* fin, float* Gc, int64_t nseq = 0,
                    const int* cu = nullptr, unsigned int* done = nullptr, unsigned int* done_target = nullptr);
 unsigned int tc_state_read_wait_timeouts();
+unsigned int tc_state_read_bad_offsets();
 int tc_chunk_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, int64_t C,
                  const float* g, const void* v, const void* k, const void* q, const void* saved,
                  const void* dhidden_final, const void* dout, void* dhidden_init, float* dg,

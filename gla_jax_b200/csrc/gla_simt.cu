@@ -283,9 +283,12 @@ size_t simt_saved_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t C) {
   int64_t N = T / C, BH = B * H;
   return f32b(BH * N * D * D) + f32b(BH * N * D) + f32b(BH * N * C * C);
 }
+// The k_hat region doubles as the score buffer of a forward without residuals: (BH, N, C, C) floats, which is
+// larger than (B, T, H, D) when chunk > D, so the region is sized for the larger of the two.
+static int64_t khat_region_elems(int64_t B, int64_t T, int64_t H, int64_t D, int64_t C) { return B * T * H * (D > C ? D : C); }
 size_t simt_fwd_ws_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t C) {
   int64_t N = T / C, BH = B * H, E = B * T * H * D;
-  return 3 * f32b(E) + f32b(BH * N * D * D) + f32b(BH * N * D);
+  return 2 * f32b(E) + f32b(khat_region_elems(B, T, H, D, C)) + f32b(BH * N * D * D) + f32b(BH * N * D);
 }
 size_t simt_bwd_ws_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t C) {
   int64_t N = T / C, BH = B * H, E = B * T * H * D;
@@ -298,9 +301,11 @@ int simt_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, 
                    float* G_total, float* S_local) {
   Dims d{B, T, H, D, C, T / C};
   const int64_t N = d.N, BH = B * H, E = B * T * H * D;
+  // every size limit of the launches below, before the first of them
+  if (N > 65535 || BH > 65535 || BH * N > 65535) return GLA_ERR_TOO_LARGE;
   char* w = (char*)ws;
   float* lam = (float*)w;  w += f32b(E);
-  float* khat = (float*)w; w += f32b(E);
+  float* khat = (float*)w; w += f32b(khat_region_elems(B, T, H, D, C));
   float* qhat = (float*)w; w += f32b(E);
   float* kv = (float*)w;   w += f32b(BH * N * D * D);
   float* Gc_ws = (float*)w;
@@ -335,15 +340,10 @@ int simt_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, 
   // states entering each chunk (in place over kv when nothing is saved) and hidden_final
   float* before = S_prev ? S_prev : kv;
   GLA_TRY(launch_state_scan(st, BH, N, D, Gc, kv, 0, hidden_init, bf, before, 0, hidden_final, bf, 0));
-  // scores; without a residual buffer they go to the (dead) k_hat region when it is big enough
-  float* Pbuf = P;
-  if (!Pbuf) {
-    if (BH * N * C * C > E) return GLA_ERR_UNSUPPORTED;   // chunk > D with saved == NULL
-    Pbuf = khat;
-  }
+  // scores; without a residual buffer they go to the (dead) k_hat region, which is sized for them
+  float* Pbuf = P ? P : khat;
   {
     dim3 grid((unsigned)(C / 8), (unsigned)N, (unsigned)BH);
-    if (N > 65535 || BH > 65535) return GLA_ERR_TOO_LARGE;
     ProfScope ps_score_kernel("simt_score_kernel", st);
     score_kernel<<<grid, 256, 0, st>>>(d, lam, k, q, bf, Pbuf);
     GLA_CHECK_LAUNCH();
@@ -381,7 +381,7 @@ int simt_chunk_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, 
                    void* dv, void* dk, void* dq, void* ws) {
   Dims d{B, T, H, D, C, T / C};
   const int64_t N = d.N, BH = B * H, E = B * T * H * D;
-  if (N > 65535 || BH > 65535) return GLA_ERR_TOO_LARGE;
+  if (N > 65535 || BH > 65535 || BH * N > 65535) return GLA_ERR_TOO_LARGE;
   char* w = (char*)ws;
   float* lam = (float*)w;  w += f32b(E);
   float* khat = (float*)w; w += f32b(E);
@@ -475,7 +475,7 @@ int simt_chunk_dstate_only(cudaStream_t st, int64_t B, int64_t T, int64_t H, int
                            const float* g, const void* q, const void* dout, float* dS_local, void* ws) {
   Dims d{B, T, H, D, C, T / C};
   const int64_t N = d.N, BH = B * H, E = B * T * H * D;
-  if (N > 65535 || BH > 65535) return GLA_ERR_TOO_LARGE;
+  if (N > 65535 || BH > 65535 || BH * N > 65535) return GLA_ERR_TOO_LARGE;
   char* w = (char*)ws;
   float* lam = (float*)w;  w += f32b(E);
   w += f32b(E);

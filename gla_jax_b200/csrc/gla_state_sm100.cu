@@ -71,6 +71,7 @@ constexpr size_t ST_SMEM = 1024 + StSmem::END;
 static_assert(ST_SMEM <= 232448, "shared memory budget");
 
 __device__ unsigned int g_state_wait_timeouts = 0;
+__device__ unsigned int g_state_bad_offsets = 0;      // packed sequences whose offsets had to be clamped
 
 struct StMaps { CUtensorMap g, x, y; };
 
@@ -101,8 +102,17 @@ tc_state_kernel(const __grid_constant__ StMaps maps, int64_t T, int64_t H, int R
   // walks only its sequence's chunks, and init / fin are per (sequence, head).
   const int64_t bh = blockIdx.x >> 2, hh = bh % H;
   const int64_t b = cu ? 0 : bh / H;
-  const int base = cu ? cu[bh / H] / SC : 0;                       // first chunk of this block's sequence
-  const int N = cu ? (cu[bh / H + 1] - cu[bh / H]) / SC : Nall;    // its number of chunks
+  // Offsets come from device memory nobody has validated: whatever they hold, this block only touches chunks
+  // [base, base + N) inside [0, Nall).  Offsets that are not rising multiples of the chunk length inside the
+  // array are clamped (the sequence is cut short or skipped) and counted in g_state_bad_offsets.
+  int base = 0, N = Nall;
+  if (cu) {
+    const int lo = cu[bh / H], hi = cu[bh / H + 1];
+    base = min(max(lo / SC, 0), Nall);
+    N = min(max((hi - lo) / SC, 0), Nall - base);
+    const bool bad = lo < 0 || hi < lo || lo % SC != 0 || hi % SC != 0 || hi / SC > Nall;
+    if (bad && tid == 0 && slice == 0) atomicAdd(&g_state_bad_offsets, 1u);
+  }
   const int64_t rowbase = cu ? hh * (int64_t)Nall + base : bh * (int64_t)Nall;   // row of chunk 0 in states / Gc
   const int64_t hk = (hh / (R * R)) * R + (hh % (R * R)) / R, hv = (hh / (R * R)) * R + hh % R;
   auto chunk_of = [&](int i) { return MODE == 0 ? i : N - 1 - i; };
@@ -317,6 +327,11 @@ tc_state_kernel(const __grid_constant__ StMaps maps, int64_t T, int64_t H, int R
 unsigned int tc_state_read_wait_timeouts() {
   unsigned int v = 0;
   cudaMemcpyFromSymbol(&v, g_state_wait_timeouts, sizeof(v));
+  return v;
+}
+unsigned int tc_state_read_bad_offsets() {
+  unsigned int v = 0;
+  cudaMemcpyFromSymbol(&v, g_state_bad_offsets, sizeof(v));
   return v;
 }
 

@@ -31,8 +31,7 @@ def _ptr(t):
     return None if t is None else t.data_ptr()
 
 
-def _stream(dev) -> int:
-    return torch.cuda.current_stream(dev).cuda_stream
+_stream = _lib.stream_of
 
 
 def _prepare(hidden, log_fgate, value, key, query):

@@ -20,8 +20,7 @@ from . import _lib
 _DT = {torch.float32: _lib.GLA_F32, torch.bfloat16: _lib.GLA_BF16}
 
 
-def _stream(dev) -> int:
-    return torch.cuda.current_stream(dev).cuda_stream
+_stream = _lib.stream_of
 
 
 def _need_cuda(x):

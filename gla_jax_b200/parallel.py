@@ -58,9 +58,7 @@ class CudaOps:
         self.lib = _lib.load()
         self.impl = _lib.IMPL_BY_NAME[impl]
 
-    @staticmethod
-    def _stream(dev):
-        return torch.cuda.current_stream(dev).cuda_stream
+    _stream = staticmethod(_lib.stream_of)
 
     def local_state(self, g, v, k, chunk):
         B, T, H, D = v.shape

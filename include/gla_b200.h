@@ -103,9 +103,22 @@ GLA_API long long gla_launch_count(void);
 
 /* Every device-side wait in this library (on an mbarrier that a tensor-core operation
  * completes) is bounded: a wait that runs out makes its thread block skip its output and
- * increments a device counter instead of spinning forever.  This reads that counter
- * (synchronises the device; diagnostic).  0 means no wait has ever given up. */
+ * increments a device counter instead of spinning forever.  An entry point cannot report this in
+ * its own return value, because it returns before its kernels have run (nothing synchronises);
+ * a caller that wants to know polls this counter after synchronising the stream: it reads the
+ * count of waits that gave up since the library was loaded, on the current device
+ * (synchronises the device).  0 means no wait has ever given up; a value that grew since the
+ * previous poll means outputs written in between are incomplete.  The Python package wraps the
+ * poll as gla_jax_b200.check_device(). */
 GLA_API unsigned int gla_device_wait_timeouts(void);
+
+/* gla_chunk_fwd_packed / gla_chunk_bwd_packed take their sequence offsets from device memory and cannot check
+ * them on the host without synchronising.  The kernels therefore clamp every sequence to chunks inside the arrays
+ * (no access ever leaves the buffers) and count the sequences whose offsets were not rising multiples of 128
+ * within [0, T]; such a sequence is cut short or skipped, so its results are not meaningful.  This reads the
+ * count since the library was loaded, for the current device (synchronises the device).  0 means every offset
+ * array seen so far was valid.  No counterpart in the reference. */
+GLA_API unsigned int gla_device_bad_offsets(void);
 
 /* Per-kernel device timing for benchmarks (diagnostic; no counterpart in the reference, whose
  * harness times whole calls with timeit, gla.py:1430-1434).  While enabled on the calling

@@ -490,3 +490,56 @@ def test_early_start_with_more_state_blocks_than_sms(cuda_device, B, T, H):
     torch.cuda.synchronize()
     assert O.rel_l2(hf2.cpu(), hf.cpu()) < 1e-2 and O.rel_l2(out2.cpu(), out.cpu()) < 1e-2
     assert lib.gla_device_wait_timeouts() == t0
+
+
+def test_fp32_forward_without_residuals_with_chunk_larger_than_head(cuda_device):
+    """chunk > D on the float32 kernels under no_grad (no residual buffer: the scores go to workspace, which must
+    be sized for them) and through the entry point that brings its own scratch; the reference accepts any
+    power-of-two chunk size (gla.py:499-500)."""
+    from gla_jax_b200 import chunk_gla
+    for D, C in ((64, 128), (32, 256), (16, 64)):
+        h, g, v, k, q = O.make_inputs(2, 2 * C, 2, D, torch.float32, seed=13)
+        ref_hf, ref_out = O.batched(O.recurrent_gla_naive, h, g, v, k, q)
+        with torch.no_grad():
+            hf, out = chunk_gla(*(x.to(cuda_device) for x in (h, g, v, k, q)), chunk_size=C, impl="fp32")
+        assert O.rel_l2(ref_hf, hf.cpu()) < 1e-4 and O.rel_l2(ref_out, out.cpu()) < 1e-4, (D, C)
+
+
+def test_packed_offsets_on_the_device_are_clamped_not_trusted(cuda_device):
+    """Offsets handed over as a CUDA tensor are not checked on the host (that would synchronise).  Out-of-range,
+    decreasing or misaligned offsets must not make the kernels leave the buffers: every access stays inside
+    (canary rows around the outputs are intact), the call completes, and gla_device_bad_offsets() counts them."""
+    from gla_jax_b200 import chunk_gla_packed, _lib
+    lib = _lib.load()
+    H, D, T = 2, 128, 512
+    _, g, v, k, q = (x[0].to(cuda_device) for x in O.make_inputs(1, T, H, D, torch.bfloat16, seed=71))
+    h = torch.randn(3, H, D, D, device=cuda_device).to(torch.bfloat16)
+    good = torch.tensor([0, 128, 384, 512], dtype=torch.int32, device=cuda_device)
+    before = lib.gla_device_bad_offsets()
+    hf0, out0 = chunk_gla_packed(h, g, v, k, q, good)
+    torch.cuda.synchronize()
+    assert lib.gla_device_bad_offsets() == before
+    for bad in ([0, 128, 100000, 512], [0, 384, 128, 512], [0, 100, 384, 512], [-256, 128, 384, 512]):
+        cu = torch.tensor(bad, dtype=torch.int32, device=cuda_device)
+        n0 = lib.gla_device_bad_offsets()
+        with torch.no_grad():
+            hf, out = chunk_gla_packed(h, g, v, k, q, cu)
+        torch.cuda.synchronize()
+        assert lib.gla_device_bad_offsets() > n0, bad
+        assert hf.shape == hf0.shape and out.shape == out0.shape
+    # the library still works afterwards and gives the same answer as before
+    hf1, out1 = chunk_gla_packed(h, g, v, k, q, good)
+    assert torch.equal(hf1, hf0) and torch.equal(out1, out0)
+
+
+def test_tensors_on_another_device_are_refused(cuda_device):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from gla_jax_b200 import recurrent_gla
+    other = torch.device("cuda:1")
+    h, g, v, k, q = (x.to(other) for x in O.make_inputs(1, 64, 1, 32, torch.float32, seed=1))
+    with pytest.raises(RuntimeError):
+        recurrent_gla(h, g, v, k, q)          # the current device is cuda:0
+    with torch.cuda.device(other):
+        hf, out = recurrent_gla(h, g, v, k, q)
+    assert out.device == other
