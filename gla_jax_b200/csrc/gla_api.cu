@@ -372,6 +372,71 @@ int gla_chunk_local_dstate(void* stream, int64_t B, int64_t T, int64_t H, int64_
                                 dS_local, workspace);
 }
 
+// ---- sequence parallelism without repeated work: the chunk states of a slice are computed once ----------------
+static int sp_check(int64_t B, int64_t T, int64_t H, int64_t D, int64_t chunk, int dtype, int impl) {
+  GLA_TRY(check_chunk_dims(B, T, H, D, chunk, dtype));
+  int r = resolve_impl(impl, D, chunk, dtype);
+  if (r < 0) return -r;
+  if (r != GLA_IMPL_TCGEN05 || D != 128) return GLA_ERR_UNSUPPORTED;
+  return GLA_OK;
+}
+
+int gla_chunk_sp_fwd_local(void* stream, int64_t B, int64_t T, int64_t H, int64_t D, int64_t chunk, int dtype, int impl,
+                           const float* log_fgate, const void* value, const void* key, float* G_total, float* S_local,
+                           void* saved, void* workspace, size_t workspace_bytes) {
+  if (!log_fgate || !value || !key || !G_total || !S_local || !saved) return GLA_ERR_NULL_POINTER;
+  GLA_TRY(sp_check(B, T, H, D, chunk, dtype, impl));
+  if (!workspace || workspace_bytes < tc_fwd_ws_bytes(B, T, H, D, chunk)) return GLA_ERR_WORKSPACE;
+  const void* ptrs[] = {log_fgate, value, key, G_total, S_local, saved, workspace};
+  for (const void* p : ptrs)
+    if (!aligned16(p)) return GLA_ERR_ALIGNMENT;
+  return tc_chunk_fwd((cudaStream_t)stream, B, T, H, D, chunk, nullptr, log_fgate, value, key, nullptr, nullptr, nullptr,
+                      saved, workspace, 0, G_total, S_local, impl & OPT_BITS, 0, nullptr, 1, nullptr);
+}
+
+int gla_chunk_sp_fwd_finish(void* stream, int64_t B, int64_t T, int64_t H, int64_t D, int64_t chunk, int dtype, int impl,
+                            const float* H_in, const float* log_fgate, const void* value, const void* key,
+                            const void* query, void* out, void* saved, void* workspace, size_t workspace_bytes) {
+  if (!H_in || !log_fgate || !value || !key || !query || !out || !saved) return GLA_ERR_NULL_POINTER;
+  GLA_TRY(sp_check(B, T, H, D, chunk, dtype, impl));
+  if (!workspace || workspace_bytes < tc_fwd_ws_bytes(B, T, H, D, chunk)) return GLA_ERR_WORKSPACE;
+  const void* ptrs[] = {H_in, log_fgate, value, key, query, out, saved, workspace};
+  for (const void* p : ptrs)
+    if (!aligned16(p)) return GLA_ERR_ALIGNMENT;
+  if (!aligned32(out)) return GLA_ERR_ALIGNMENT;
+  return tc_chunk_fwd((cudaStream_t)stream, B, T, H, D, chunk, nullptr, log_fgate, value, key, query, nullptr, out, saved,
+                      workspace, 0, nullptr, nullptr, impl & OPT_BITS, 0, nullptr, 2, H_in);
+}
+
+int gla_chunk_sp_bwd_local(void* stream, int64_t B, int64_t T, int64_t H, int64_t D, int64_t chunk, int dtype, int impl,
+                           const float* log_fgate, const void* query, const void* dout, const void* saved,
+                           float* A_local, void* workspace, size_t workspace_bytes) {
+  if (!log_fgate || !query || !dout || !saved || !A_local) return GLA_ERR_NULL_POINTER;
+  GLA_TRY(sp_check(B, T, H, D, chunk, dtype, impl));
+  if (!workspace || workspace_bytes < tc_bwd_ws_bytes(B, T, H, D, chunk)) return GLA_ERR_WORKSPACE;
+  const void* ptrs[] = {log_fgate, query, dout, saved, A_local, workspace};
+  for (const void* p : ptrs)
+    if (!aligned16(p)) return GLA_ERR_ALIGNMENT;
+  return tc_chunk_bwd((cudaStream_t)stream, B, T, H, D, chunk, log_fgate, nullptr, nullptr, query, saved, nullptr, dout,
+                      nullptr, nullptr, nullptr, nullptr, nullptr, workspace, impl & OPT_BITS, 0, nullptr, 1, A_local, nullptr);
+}
+
+int gla_chunk_sp_bwd_finish(void* stream, int64_t B, int64_t T, int64_t H, int64_t D, int64_t chunk, int dtype, int impl,
+                            const float* dH_out, const float* log_fgate, const void* value, const void* key,
+                            const void* query, const void* saved, const void* dout, float* dlog_fgate, void* dvalue,
+                            void* dkey, void* dquery, void* workspace, size_t workspace_bytes) {
+  if (!dH_out || !log_fgate || !value || !key || !query || !saved || !dout || !dlog_fgate || !dvalue || !dkey || !dquery)
+    return GLA_ERR_NULL_POINTER;
+  GLA_TRY(sp_check(B, T, H, D, chunk, dtype, impl));
+  if (!workspace || workspace_bytes < tc_bwd_ws_bytes(B, T, H, D, chunk)) return GLA_ERR_WORKSPACE;
+  const void* ptrs[] = {dH_out, log_fgate, value, key, query, saved, dout, dlog_fgate, dvalue, dkey, dquery, workspace};
+  for (const void* p : ptrs)
+    if (!aligned16(p)) return GLA_ERR_ALIGNMENT;
+  if (!aligned32(dvalue)) return GLA_ERR_ALIGNMENT;
+  return tc_chunk_bwd((cudaStream_t)stream, B, T, H, D, chunk, log_fgate, value, key, query, saved, nullptr, dout, nullptr,
+                      dlog_fgate, dvalue, dkey, dquery, workspace, impl & OPT_BITS, 0, nullptr, 2, nullptr, dH_out);
+}
+
 int gla_sp_combine(void* stream, int64_t R, int64_t rank, int64_t BH, int64_t D, const float* all_G,
                    const float* all_S, const void* init, int init_dtype, void* result, int result_dtype,
                    int reverse) {

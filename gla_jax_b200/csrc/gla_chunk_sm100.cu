@@ -361,7 +361,11 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, 
   // problems, virtual head (h R + a) R + c, whose results the caller sums over a.  In the (B, T, H_real R, 128) view
   // of the inputs the key-side tensors of a virtual head are head h R + a, the value-side ones head h R + c; the
   // output is written per virtual head, (B, T, H, 128).  R = 1: everything coincides with the real layout.
-  const int64_t n = blockIdx.x % N, bh = blockIdx.x / N, b = bh / H, h_ = bh % H;
+  // Block order: chunk-major, LAST chunks first.  The state kernel that runs before this one walks the chunks of all
+  // heads in step, first to last, so the inputs it read most recently (g, k, v of the late chunks) and the states
+  // it wrote last are the ones most likely to be still in L2.
+  const int64_t BHn = (int64_t)gridDim.x / N;
+  const int64_t n = N - 1 - (int64_t)blockIdx.x / BHn, bh = (int64_t)blockIdx.x % BHn, b = bh / H, h_ = bh % H;
   const int64_t hk_ = (h_ / (R * R)) * R + (h_ % (R * R)) / R, hv_ = (h_ / (R * R)) * R + h_ % R;
   const int64_t HD = H * TD;
   const int64_t row0 = ((b * T + n * TC) * H + h_) * TD;
@@ -883,7 +887,10 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
   // H counts virtual heads (see the forward kernel).  Inputs are addressed in the (B, T, H / R, 128) view: key-side
   // tensors (g, q, k) at head hk_, value-side tensors (v, dO) at head hv_; the gradients are written per virtual
   // head, (B, T, H, 128), and the caller sums dq, dk, dg over the value blocks and dv over the key blocks.
-  const int64_t n = blockIdx.x % N, bh = blockIdx.x / N, b = bh / H, h_ = bh % H;
+  // Block order: chunk-major, FIRST chunks first: the gradient-state kernel before this one walks the chunks of all
+  // heads last to first, so g, q, dO of the early chunks and the gradient states written last are freshest in L2.
+  const int64_t BHn = (int64_t)gridDim.x / N;
+  const int64_t n = (int64_t)blockIdx.x / BHn, bh = (int64_t)blockIdx.x % BHn, b = bh / H, h_ = bh % H;
   const int64_t hk_ = (h_ / (R * R)) * R + (h_ % (R * R)) / R, hv_ = (h_ / (R * R)) * R + h_ % R;
   const int64_t HD = H * TD;                                          // output row pitch (virtual heads)
   const int64_t HDi = (H / R) * TD;                                   // input row pitch
@@ -1032,7 +1039,7 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
   {
     const int64_t nb = (int64_t)blockIdx.x + pf_dist;
     if (pf_dist > 0 && nb < (int64_t)gridDim.x) {
-      const int64_t n2 = nb % N, bh2 = nb / N, h2 = bh2 % H;
+      const int64_t n2 = nb / BHn, bh2 = nb % BHn, h2 = bh2 % H;
       const int64_t hk2 = (h2 / (R * R)) * R + (h2 % (R * R)) / R, hv2 = (h2 / (R * R)) * R + h2 % R;
       const int64_t t2 = ((bh2 / H) * T + n2 * TC) * (H / R);
       const int64_t r2k = (t2 + hk2) * TD, r2v = (t2 + hv2) * TD;
@@ -1559,6 +1566,58 @@ __global__ void __launch_bounds__(256) tc_gsum_kernel(int64_t BH, int64_t N, con
   Gt[e] = s;
 }
 
+// ---- sequence parallelism: chunk states computed from a zero state, corrected once the true one is known --------
+// The state recurrence is linear: with S0[n] the state entering chunk n when the slice starts from zero, the state
+// entering it when the slice starts from H_in is S0[n] + exp(sum_{m<n} G_m) (.) H_in (decay along the key axis;
+// ops.py:286-297 applied to the slice's prefix).  The gradient states mirror it with the chunks after n.
+// E[bh][n][d] = exp(sum of Gc over the chunks before n (reverse == 0) or after n (reverse != 0)).
+__global__ void __launch_bounds__(128) sp_cum_gate_kernel(int64_t BH, int64_t N, const float* __restrict__ Gc,
+                                                          float* __restrict__ E, int reverse) {
+  const int64_t e = (int64_t)blockIdx.x * 128 + threadIdx.x;
+  if (e >= BH * TD) return;
+  const int64_t bh = e / TD, dd = e % TD;
+  float acc = 0.f;
+  for (int64_t i = 0; i < N; ++i) {
+    const int64_t n = reverse ? N - 1 - i : i;
+    E[(bh * N + n) * TD + dd] = __expf(acc);
+    acc += Gc[(bh * N + n) * TD + dd];
+  }
+}
+// states[bh][n][dk][dv] += E[bh][n][dk] * Hin[bh][dk][dv]; one thread per 8 consecutive dv (16 bytes of bf16).
+__global__ void __launch_bounds__(256) sp_fix_states_kernel(int64_t BH, int64_t N, const float* __restrict__ E,
+                                                            const float* __restrict__ Hin, bf16* __restrict__ states) {
+  const int64_t e = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (e >= BH * N * TD * (TD / 8)) return;
+  const int j = (int)(e % (TD / 8));
+  const int dk = (int)((e / (TD / 8)) % TD);
+  const int64_t bhn = e / (TD / 8) / TD, bh = bhn / N;
+  const float w = E[bhn * TD + dk];
+  const float4* hp = reinterpret_cast<const float4*>(Hin + (bh * TD + dk) * TD + j * 8);
+  const float4 h0 = __ldg(hp), h1 = __ldg(hp + 1);
+  uint4* sp = reinterpret_cast<uint4*>(states + (bhn * TD + dk) * TD + j * 8);
+  uint4 u = *sp;
+  float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d2 = unpack_bf16x2(u.w);
+  u.x = pack_bf16x2(fmaf(w, h0.x, a.x), fmaf(w, h0.y, a.y));
+  u.y = pack_bf16x2(fmaf(w, h0.z, b.x), fmaf(w, h0.w, b.y));
+  u.z = pack_bf16x2(fmaf(w, h1.x, c.x), fmaf(w, h1.y, c.y));
+  u.w = pack_bf16x2(fmaf(w, h1.z, d2.x), fmaf(w, h1.w, d2.y));
+  *sp = u;
+}
+static int launch_sp_fix(cudaStream_t st, int64_t BH, int64_t N, const float* Gc, float* E, const float* Hin, bf16* states,
+                         int reverse) {
+  {
+    ProfScope ps("sp_cum_gate_kernel", st);
+    sp_cum_gate_kernel<<<(unsigned)((BH * TD + 127) / 128), 128, 0, st>>>(BH, N, Gc, E, reverse);
+    GLA_CHECK_LAUNCH();
+  }
+  const int64_t n = BH * N * TD * (TD / 8);
+  if ((n + 255) / 256 > 2147483647LL) return GLA_ERR_TOO_LARGE;
+  ProfScope ps("sp_fix_states_kernel", st);
+  sp_fix_states_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(BH, N, E, Hin, states);
+  GLA_CHECK_LAUNCH();
+  return GLA_OK;
+}
+
 // ---------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------
@@ -1655,11 +1714,14 @@ constexpr size_t FWD_SMEM = 1024 + FwdSmem::END;
 int tc_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, int64_t C, const void* hidden_init,
                  const float* g, const void* v, const void* k, const void* q, void* hidden_final, void* out,
                  void* saved, void* ws, int state_only, float* G_total, float* S_local, int opts, int64_t nseq,
-                 const int* cu) {
+                 const int* cu, int sp_phase, const float* H_in) {
   (void)C;
   const int R = (int)(D / TD);
   const int64_t N = T / TC, HV = H * R * R, HK = H * R, BHV = B * HV;
   if (state_only && R != 1) return GLA_ERR_UNSUPPORTED;
+  // sequence-parallel phases (sp_phase 1: states from a zero state, kept in `saved`; 2: correct them with H_in, then
+  // the chunk kernel) exist for the plain head size and need the residual buffer to carry the states between them
+  if (sp_phase != 0 && (R != 1 || saved == nullptr || cu != nullptr || state_only)) return GLA_ERR_UNSUPPORTED;
   if (cu != nullptr && (B != 1 || R != 1 || state_only || nseq <= 0)) return GLA_ERR_UNSUPPORTED;   // packed sequences
   char* w = (char*)ws;
   float* kv = (float*)w; w += (R == 1 ? f32b(BHV * N * TD * TD) : 0);
@@ -1685,12 +1747,30 @@ int tc_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
     init_v = hib; fin_v = hfb;
   }
   const bool fused_states = !state_only && (R > 1 || cu != nullptr || tc_state_fused_preferred(BHV, N, opts));
+  if (sp_phase == 1) {
+    if (fused_states) {
+      GLA_TRY(tc_state_fused(st, 0, B, T, HV, R, g, k, v, nullptr, S_prev, nullptr, Gc, 0, nullptr, nullptr, nullptr, S_local));
+    } else {
+      GLA_TRY((launch_tc_kv<0>(st, B, T, H, g, k, v, kv, Gc)));
+      GLA_TRY(launch_state_scan(st, BHV, N, TD, Gc, kv, 0, nullptr, 0, S_prev, 1, S_local, 0, 0));
+    }
+    ProfScope ps("tc_gsum_kernel", st);
+    tc_gsum_kernel<<<(unsigned)((BHV * TD + 255) / 256), 256, 0, st>>>(BHV, N, Gc, G_total);
+    GLA_CHECK_LAUNCH();
+    return GLA_OK;
+  }
   // The chunk kernel may start beside the one-pass state kernel (which fills only 4 x batch x heads SMs) when it
   // is the very next launch: plain head size, and the kv area of the workspace, unused then, holds the counter.
-  unsigned int* early_flag = (fused_states && R == 1 && !(opts & GLA_OPT_NO_EARLY_START)) ? (unsigned int*)kv : nullptr;
+  unsigned int* early_flag = (sp_phase == 0 && fused_states && R == 1 && !(opts & GLA_OPT_NO_EARLY_START)) ? (unsigned int*)kv : nullptr;
   unsigned int early_target = 0;
-  if (fused_states) GLA_TRY(tc_state_fused(st, 0, B, T, HV, R, g, k, v, init_v, S_prev, fin_v, Gc, nseq, cu, early_flag, &early_target));
-  else GLA_TRY((launch_tc_kv<0>(st, B, T, H, g, k, v, kv, Gc)));
+  if (sp_phase == 2) {
+    // the product area of the workspace is dead by now: it takes the cumulative decays
+    GLA_TRY(launch_sp_fix(st, BHV, N, Gc, kv, H_in, S_prev, 0));
+  } else if (fused_states) {
+    GLA_TRY(tc_state_fused(st, 0, B, T, HV, R, g, k, v, init_v, S_prev, fin_v, Gc, nseq, cu, early_flag, &early_target));
+  } else {
+    GLA_TRY((launch_tc_kv<0>(st, B, T, H, g, k, v, kv, Gc)));
+  }
   if (state_only) {
     GLA_TRY(launch_state_scan(st, BHV, N, TD, Gc, kv, 0, nullptr, 0, nullptr, 0, S_local, 0, 0));
     ProfScope ps("tc_gsum_kernel", st);
@@ -1698,7 +1778,7 @@ int tc_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
     GLA_CHECK_LAUNCH();
     return GLA_OK;
   }
-  if (!fused_states) GLA_TRY(launch_state_scan(st, BHV, N, TD, Gc, kv, 0, hidden_init, 1, S_prev, 1, hidden_final, 1, 0));
+  if (!fused_states && sp_phase == 0) GLA_TRY(launch_state_scan(st, BHV, N, TD, Gc, kv, 0, hidden_init, 1, S_prev, 1, hidden_final, 1, 0));
   static SmemAttrOnce fwd_attr;
   GLA_TRY(fwd_attr.ensure(tc_chunk_fwd_kernel, FWD_SMEM));
   cudaError_t e;
@@ -1757,11 +1837,14 @@ int tc_local_dstate(cudaStream_t st, int64_t B, int64_t T, int64_t H, const floa
 int tc_chunk_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, int64_t C, const float* g,
                  const void* v, const void* k, const void* q, const void* saved, const void* dhidden_final,
                  const void* dout, void* dhidden_init, float* dg, void* dv, void* dk, void* dq, void* ws, int opts,
-                 int64_t nseq, const int* cu) {
+                 int64_t nseq, const int* cu, int sp_phase, float* A_local, const float* dH_out) {
   (void)C;
   const int R = (int)(D / TD);
   const int64_t N = T / TC, HV = H * R * R, HK = H * R, BHV = B * HV;
   if (cu != nullptr && (B != 1 || R != 1 || nseq <= 0)) return GLA_ERR_UNSUPPORTED;   // packed sequences
+  // sequence-parallel phases: 1 = gradient states from a zero final gradient (kept in the workspace) and the
+  // gradient reaching the slice's initial state; 2 = correct them with dH_out, then the chunk kernel
+  if (sp_phase != 0 && (R != 1 || cu != nullptr)) return GLA_ERR_UNSUPPORTED;
   char* w = (char*)ws;
   float* dstate = (float*)w; w += (R == 1 ? f32b(BHV * N * TD * TD) : 0);
   bf16* dS_next = (bf16*)w; w += b16b(BHV * N * TD * TD);
@@ -1785,7 +1868,18 @@ int tc_chunk_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
     GLA_TRY(launch_state_block(st, dhidden_final, dhfb, B * H, R, 1));
     dfin_v = dhfb; dinit_v = dhib;
   }
-  if (R > 1 || cu != nullptr || tc_state_fused_preferred(BHV, N, opts)) {
+  if (sp_phase == 1) {
+    if (tc_state_fused_preferred(BHV, N, opts)) {
+      GLA_TRY(tc_state_fused(st, 1, B, T, HV, R, g, q, dout, nullptr, dS_next, nullptr, nullptr, 0, nullptr, nullptr, nullptr, A_local));
+    } else {
+      GLA_TRY((launch_tc_kv<1>(st, B, T, H, g, q, dout, dstate, nullptr)));
+      GLA_TRY(launch_state_scan(st, BHV, N, TD, Gc, dstate, 0, nullptr, 0, dS_next, 1, A_local, 0, 1));
+    }
+    return GLA_OK;
+  }
+  if (sp_phase == 2) {
+    GLA_TRY(launch_sp_fix(st, BHV, N, Gc, dstate, dH_out, dS_next, 1));
+  } else if (R > 1 || cu != nullptr || tc_state_fused_preferred(BHV, N, opts)) {
     GLA_TRY(tc_state_fused(st, 1, B, T, HV, R, g, q, dout, dfin_v, dS_next, dinit_v, nullptr, nseq, cu));
   } else {
     GLA_TRY((launch_tc_kv<1>(st, B, T, H, g, q, dout, dstate, nullptr)));

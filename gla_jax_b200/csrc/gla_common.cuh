@@ -119,18 +119,21 @@ size_t tc_bwd_ws_bytes(int64_t B, int64_t T, int64_t H, int64_t D, int64_t C);
 int tc_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, int64_t C,
                  const void* hidden_init, const float* g, const void* v, const void* k, const void* q,
                  void* hidden_final, void* out, void* saved, void* ws, int state_only,
-                 float* G_total, float* S_local, int opts = 0, int64_t nseq = 0, const int* cu = nullptr);
+                 float* G_total, float* S_local, int opts = 0, int64_t nseq = 0, const int* cu = nullptr,
+                 int sp_phase = 0, const float* H_in = nullptr);
 // One-pass chunk states (product and recurrence fused); mode 0 forward states, mode 1 gradient states.
 bool tc_state_fused_preferred(int64_t BH, int64_t N, int opts);
 int tc_state_fused(cudaStream_t st, int mode, int64_t B, int64_t T, int64_t H, int R, const float* g, const void* x,
                    const void* y, const void* init, void* states, void* fin, float* Gc, int64_t nseq = 0,
-                   const int* cu = nullptr, unsigned int* done = nullptr, unsigned int* done_target = nullptr);
+                   const int* cu = nullptr, unsigned int* done = nullptr, unsigned int* done_target = nullptr,
+                   float* fin32 = nullptr);
 unsigned int tc_state_read_wait_timeouts();
 unsigned int tc_state_read_bad_offsets();
 int tc_chunk_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, int64_t C,
                  const float* g, const void* v, const void* k, const void* q, const void* saved,
                  const void* dhidden_final, const void* dout, void* dhidden_init, float* dg,
-                 void* dv, void* dk, void* dq, void* ws, int opts = 0, int64_t nseq = 0, const int* cu = nullptr);
+                 void* dv, void* dk, void* dq, void* ws, int opts = 0, int64_t nseq = 0, const int* cu = nullptr,
+                 int sp_phase = 0, float* A_local = nullptr, const float* dH_out = nullptr);
 
 }  // namespace gla
 

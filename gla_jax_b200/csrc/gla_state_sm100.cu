@@ -78,8 +78,8 @@ struct StMaps { CUtensorMap g, x, y; };
 template <int MODE>
 __global__ void __launch_bounds__(STHREADS, 1)
 tc_state_kernel(const __grid_constant__ StMaps maps, int64_t T, int64_t H, int R, int Nall, const int* __restrict__ cu,
-                const bf16* __restrict__ init, bf16* __restrict__ states, bf16* __restrict__ fin, float* __restrict__ Gc,
-                unsigned int* __restrict__ done) {
+                const bf16* __restrict__ init, bf16* __restrict__ states, bf16* __restrict__ fin, float* __restrict__ fin32,
+                float* __restrict__ Gc, unsigned int* __restrict__ done) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   float* tot = reinterpret_cast<float*>(sm + StSmem::TOT);
@@ -311,6 +311,10 @@ tc_state_kernel(const __grid_constant__ StMaps maps, int64_t T, int64_t H, int R
 #pragma unroll
       for (int j = 0; j < 16; ++j) fin[el0 + (int64_t)j * SD] = __float2bfloat16_rn(S[j]);
     }
+    if (fin32 != nullptr) {          // the unrounded state, for the exchange between sequence-parallel ranks
+#pragma unroll
+      for (int j = 0; j < 16; ++j) fin32[el0 + (int64_t)j * SD] = S[j];
+    }
     if (!ok && lane == 0) atomicAdd(&g_state_wait_timeouts, 1u);
   }
   tc_fence_before();
@@ -366,7 +370,7 @@ bool tc_state_fused_preferred(int64_t BH, int64_t N, int opts) {
 // mode 1: states[n] = gradient state after chunk n (from init = dhidden_final), fin = dhidden_init.
 int tc_state_fused(cudaStream_t st, int mode, int64_t B, int64_t T, int64_t H, int R, const float* g, const void* x,
                    const void* y, const void* init, void* states, void* fin, float* Gc, int64_t nseq, const int* cu,
-                   unsigned int* done, unsigned int* done_target) {
+                   unsigned int* done, unsigned int* done_target, float* fin32) {
   // packed sequences: B == 1, cu (device, nseq + 1 token offsets) non-null, init / fin are (nseq, H, 128, 128)
   const int64_t N = T / SC, BH = (cu ? nseq : B) * H;          // H: virtual heads (real heads x R x R)
   const int64_t HK = H / R;                      // heads of the (B, T, HK, 128) view of the arrays
@@ -385,8 +389,8 @@ int tc_state_fused(cudaStream_t st, int mode, int64_t B, int64_t T, int64_t H, i
   }
   {
     ProfScope ps(mode == 0 ? "tc_state_kernel" : "tc_dstate_scan_kernel", st);
-    kern<<<(unsigned)(BH * 4), STHREADS, ST_SMEM, st>>>(maps, T, H, R, (int)N, cu, (const bf16*)init, (bf16*)states, (bf16*)fin, Gc,
-                                                        done);
+    kern<<<(unsigned)(BH * 4), STHREADS, ST_SMEM, st>>>(maps, T, H, R, (int)N, cu, (const bf16*)init, (bf16*)states, (bf16*)fin, fin32,
+                                                        Gc, done);
   }
   GLA_CHECK_LAUNCH();
   return GLA_OK;

@@ -356,6 +356,43 @@ GLA_API int gla_chunk_local_dstate(void* stream, int64_t B, int64_t T, int64_t H
                            const float* log_fgate, const void* query, const void* dout,
                            float* dS_local, void* workspace, size_t workspace_bytes);
 
+/* ------------------------------------------------------------------------------------
+ * Sequence parallelism in two phases per direction, so that a slice's chunk states are computed ONCE (no
+ * counterpart in the reference; the algebra is the linearity of the state scan, ops.py:286-297).  Tensor-core
+ * path only (bf16, D = 128, chunk a multiple of 128); other shapes return GLA_ERR_UNSUPPORTED and the caller
+ * falls back to gla_chunk_local_state + gla_chunk_fwd.  `saved` (gla_chunk_saved_bytes) and `workspace`
+ * (gla_chunk_fwd_workspace_bytes / gla_chunk_bwd_workspace_bytes, impl GLA_IMPL_TCGEN05) must be the SAME buffers,
+ * untouched, in the local and the finish call of a direction; `saved` also goes from the forward to the backward.
+ *
+ *   gla_chunk_sp_fwd_local   the slice's chunk states from a ZERO initial state (left in `saved` with the
+ *                            per-chunk log decays), its total log decay G_total (B, H, D) float32 and its final
+ *                            state S_local (B, H, D, D) float32 (unrounded) for the exchange between ranks.
+ *   gla_chunk_sp_fwd_finish  given H_in (B, H, D, D) float32, the true state entering the slice
+ *                            (gla_sp_combine), adds exp(sum of the log decays of the chunks before n) (.) H_in to
+ *                            the state entering chunk n, then runs the chunk kernel: `out` of the slice.
+ *   gla_chunk_sp_bwd_local   gradient states from a ZERO final-state gradient (left in `workspace`) and
+ *                            A_local (B, H, D, D) float32, the gradient reaching the slice's initial state.
+ *   gla_chunk_sp_bwd_finish  given dH_out (B, H, D, D) float32, the true gradient of the slice's final state,
+ *                            corrects the gradient states the same way (chunks after n) and runs the backward
+ *                            chunk kernel: dlog_fgate, dvalue, dkey, dquery of the slice.
+ * hidden_final and dhidden_init of the whole sequence come from gla_sp_combine (rank = R and rank = -1).
+ * ---------------------------------------------------------------------------------- */
+GLA_API int gla_chunk_sp_fwd_local(void* stream, int64_t B, int64_t T, int64_t H, int64_t D, int64_t chunk,
+                           int dtype, int impl, const float* log_fgate, const void* value, const void* key,
+                           float* G_total, float* S_local, void* saved, void* workspace, size_t workspace_bytes);
+GLA_API int gla_chunk_sp_fwd_finish(void* stream, int64_t B, int64_t T, int64_t H, int64_t D, int64_t chunk,
+                            int dtype, int impl, const float* H_in, const float* log_fgate, const void* value,
+                            const void* key, const void* query, void* out, void* saved, void* workspace,
+                            size_t workspace_bytes);
+GLA_API int gla_chunk_sp_bwd_local(void* stream, int64_t B, int64_t T, int64_t H, int64_t D, int64_t chunk,
+                           int dtype, int impl, const float* log_fgate, const void* query, const void* dout,
+                           const void* saved, float* A_local, void* workspace, size_t workspace_bytes);
+GLA_API int gla_chunk_sp_bwd_finish(void* stream, int64_t B, int64_t T, int64_t H, int64_t D, int64_t chunk,
+                            int dtype, int impl, const float* dH_out, const float* log_fgate, const void* value,
+                            const void* key, const void* query, const void* saved, const void* dout,
+                            float* dlog_fgate, void* dvalue, void* dkey, void* dquery, void* workspace,
+                            size_t workspace_bytes);
+
 GLA_API int gla_sp_combine(void* stream, int64_t R, int64_t rank, int64_t BH, int64_t D,
                    const float* all_G, const float* all_S,
                    const void* init, int init_dtype,

@@ -17,6 +17,7 @@ CD = torch.float64
 
 class OracleOps:
     """The five primitives of parallel.CudaOps restated with the CPU oracle (float64)."""
+    exchange_dtype = CD
 
     def local_state(self, g, v, k, chunk):
         B, T, H, D = v.shape
@@ -53,6 +54,21 @@ class OracleOps:
         B = v.shape[0]
         r = [O.chunk_gla_backward_formulas(h[b], g[b], v[b], k[b], q[b], chunk, dhf[b], dout[b], CD) for b in range(B)]
         return tuple(torch.stack([x[i] for x in r]) for i in range(5))
+
+    # the four phases of the schedule: `local` from a zero state, `finish` with the true one
+    def fwd_local(self, g, v, k, chunk):
+        G, S = self.local_state(g, v, k, chunk)
+        return G, S, None
+
+    def fwd_finish(self, ctx, H_in, g, v, k, q, chunk):
+        _, out, res = self.chunk_fwd(H_in.to(CD), g, v, k, q, chunk)
+        return out, res
+
+    def bwd_local(self, g, q, dout, residuals, chunk):
+        return self.local_dstate(g, q, dout, chunk), None
+
+    def bwd_finish(self, ctx, dH_out, g, v, k, q, residuals, dout, chunk):
+        return self.chunk_bwd(g, v, k, q, residuals, dH_out.to(CD), dout, chunk)[1:]
 
 
 def _inputs(B=1, T=128, H=2, D=16):
@@ -141,3 +157,61 @@ def test_shard_batch_heads():
         assert len(seen) == B * H
     with pytest.raises(ValueError):
         P.shard_batch_heads(3, 5, 4, 0)
+
+
+def _failure_worker(rank, world, port, q_out, mode):
+    """mode 'shape': rank 1 passes a slice of another length.  mode 'leave': rank 1 takes part in the first step
+    and then exits; rank 0's second step must fail within the group's timeout instead of waiting forever."""
+    import datetime
+    import time
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    torch.set_num_threads(1)
+    h, g, v, k, q, dhf, do = _inputs()
+    L = v.shape[1] // world
+    sl = slice(rank * L, (rank + 1) * L)
+    if mode == "shape" and rank == 1:
+        sl = slice(rank * L, rank * L + L // 2)
+    result = "ok"
+    t0 = time.time()
+    try:
+        P.sequence_parallel_chunk_gla(h, g[:, sl], v[:, sl], k[:, sl], q[:, sl], chunk_size=16, ops=OracleOps())
+        if mode == "leave":
+            if rank == 1:
+                q_out.put((rank, "left", 0.0))
+                q_out.close()
+                q_out.join_thread()     # the message is on its way before the process disappears
+                os._exit(0)             # gone between two steps, with nothing of its own in flight
+            t0 = time.time()
+            P.sequence_parallel_chunk_gla(h, g[:, sl], v[:, sl], k[:, sl], q[:, sl], chunk_size=16, ops=OracleOps())
+    except P.SequenceParallelError as e:
+        result = "SequenceParallelError: " + str(e)[:80]
+    q_out.put((rank, result, time.time() - t0))
+    q_out.close()
+    q_out.join_thread()
+    os._exit(0)                         # no orderly shutdown of a group whose peer has gone
+
+
+@pytest.mark.parametrize("mode", ["shape", "leave"])
+def test_sequence_parallel_host_side_failures(mode):
+    """Failures are made on the host (no device involved): a rank with a wrong shape makes EVERY rank raise; a rank
+    that leaves between steps makes the remaining rank raise within the process group's timeout."""
+    world = 2
+    ctx = mp.get_context("spawn")
+    q_out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_failure_worker, args=(r, world, port, q_out, mode)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = dict()
+    for _ in range(world):
+        r, what, dt = q_out.get(timeout=90)
+        res[r] = (what, dt)
+    for p in procs:
+        p.join(timeout=30)
+    if mode == "shape":
+        assert all(w.startswith("SequenceParallelError") for w, _ in res.values()), res
+    else:
+        assert res[1][0] == "left"
+        assert res[0][0].startswith("SequenceParallelError") and res[0][1] < 60, res
