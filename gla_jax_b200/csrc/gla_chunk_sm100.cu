@@ -257,6 +257,9 @@ constexpr uint32_t KC_TILE = 64 * 128;    // one SW128 tile of 64 rows
 
 // TMA descriptors of one launch (built on the host per call, passed by value).
 struct FwdMaps { CUtensorMap g, q, k, v, s; };
+// The same arrays as plain pointers, for the L2 prefetch of the chunk that follows on this SM (pf_dist blocks ahead;
+// 0 = no prefetch).
+struct FwdPtrs { const float* g; const bf16 *q, *k, *v, *s; int pf_dist; };
 
 // Operands of level slot S (half size 2^S) for the thread's 16 rows x 2 columns, with the decay
 // weights formed on the fly as running products of the gates f (no weight arrays are kept):
@@ -343,9 +346,9 @@ __device__ __noinline__ bool fwd_load_state_late(const unsigned int* state_done,
 }
 
 __global__ void __launch_bounds__(TTHREADS, 1)
-tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, int R, int64_t N, bf16* __restrict__ out,
-                    bf16* __restrict__ P_saved, const unsigned int* __restrict__ state_done, unsigned int state_target,
-                    int all_scales) {
+tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdPtrs ptrs, int64_t T, int64_t H, int R, int64_t N,
+                    bf16* __restrict__ out, bf16* __restrict__ P_saved, const unsigned int* __restrict__ state_done,
+                    unsigned int state_target, int all_scales) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = align1024(smem_raw);
   float* tot = reinterpret_cast<float*>(sm + FwdSmem::TOT);
@@ -412,6 +415,25 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, 
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   bool ok = mbar_wait(smem_u32(bars + 3), 0);
+  // This chunk's g, q, k have landed: ask L2 for the inputs of the chunk that the block scheduler will start on this
+  // SM when this block retires, so that its load phase streams from L2 instead of waiting for DRAM.  (A state tile
+  // that the state kernel has not written yet is simply fetched again later: L2 is the point of coherence.)
+  {
+    const int64_t nb = (int64_t)blockIdx.x + ptrs.pf_dist;
+    if (ptrs.pf_dist > 0 && nb < (int64_t)gridDim.x) {
+      const int64_t n2 = N - 1 - nb / BHn, bh2 = nb % BHn, h2 = bh2 % H;
+      const int64_t hk2 = (h2 / (R * R)) * R + (h2 % (R * R)) / R, hv2 = (h2 / (R * R)) * R + h2 % R;
+      const int64_t HDi = (H / R) * TD;                                  // input row pitch
+      const int64_t t2 = ((bh2 / H) * T + n2 * TC) * (H / R);
+      const int64_t r2k = (t2 + hk2) * TD, r2v = (t2 + hv2) * TD;
+      // strided rows, one 128-byte line per request: 256-byte rows of q, k, v; 512-byte rows of g
+      const int64_t eo = (int64_t)((tid >> 1) & (TC - 1)) * HDi + (tid & 1) * 64;
+      l2_prefetch_line(tid < 256 ? ptrs.q + r2k + eo : ptrs.k + r2k + eo);
+      if (tid < 256) l2_prefetch_line(ptrs.v + r2v + eo);
+      l2_prefetch_line(ptrs.g + r2k + (int64_t)(tid >> 2) * HDi + (tid & 3) * 32);
+      if (tid == 256) l2_prefetch_bulk(ptrs.s + (bh2 * N + n2) * TD * TD, 2 * TD * TD);
+    }
+  }
 
   // ---- gates, q, k of the thread's 16 rows x 2 columns from the landed tiles ---------------------
   float2 f[16];
@@ -791,11 +813,13 @@ struct BwdSmem {
   static constexpr uint32_t K1 = P + 16384;                // [64][128] bf16: k of rows 64..127
   static constexpr uint32_t K0 = V;                        // [64][128] bf16: k of rows 0..63
   // One-scale path (chunks whose gates need no secondary chunking), after the phase-1 products:
-  static constexpr uint32_t QA = DO;                       // [128][128] bf16 row-major: raw q of the chunk (TMA)
-  static constexpr uint32_t KA = P;                        // [128][128] bf16 row-major: raw k of the chunk (TMA)
+  static constexpr uint32_t ST0 = DO;                      // [16][512] u32: every thread's own (k | q << 16) of its rows 0..15
+  static constexpr uint32_t ST1 = P;                       // [16][512] u32: ... of its rows 16..31
   static constexpr uint32_t DPM = V;                       // 32 KB: dP masked to the strict lower triangle (rows i, cols j)
   static constexpr uint32_t QT = SP;                       // 32 KB: q~ = q exp(lam - G), stored like k_hat (rows = feature)
-  static constexpr uint32_t DLB = V;                       // [32][512] float (64 KB over V and S_prev): dlam suffix sums
+  static constexpr uint32_t DLB = V;                       // [128][128] float row-major (64 KB over V and S_prev): dlam suffix sums
+  static constexpr uint32_t DQT = DS;                      // [128][128] bf16 row-major: dq of the chunk, staged for whole-row stores
+  static constexpr uint32_t DKT = KH;                      // [128][128] bf16 row-major: dk
 };
 struct BwdMaps {
   CUtensorMap g, q, k;          // boxes of 128 features x 64 rows, unswizzled (row passes)
@@ -936,11 +960,15 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
 
   // ---- phase 0: gate products per 16 rows; k_hat (the operand tiles are arriving by TMA) ------------------
   float f32r[32];                                   // gates of rows 32 wq_ + [0, 32), feature d
+  uint32_t qraw[32];                                // q of the same rows (bf16 bits)
   {
     float p0 = 1.f, p1 = 1.f;
     const float* gp = g + row0k + (int64_t)(32 * wq_) * HDi + d;
+    const bf16* qp0 = q + row0k + (int64_t)(32 * wq_) * HDi + d;
 #pragma unroll
     for (int i = 0; i < 32; ++i) f32r[i] = __ldg(gp + (int64_t)i * HDi);      // all 32 loads in flight
+#pragma unroll
+    for (int i = 0; i < 32; ++i) qraw[i] = ldg_u16(qp0 + (int64_t)i * HDi);   // ... and q of the same rows behind them
     float ga = 0.f;
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
@@ -952,12 +980,12 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
     tot[(2 * wq_ + 1) * TD + d] = p1;
     gab[wq_ * TD + d] = ga;
   }
-  uint32_t kraw[32];                                // k of the same rows and feature, from the staged tile
+  uint32_t kraw[32];                                // k of the same rows and feature from the staged tile (low half), q above it
   {
     const bool kok = mbar_wait(smem_u32(bars + 6), 0);
     const unsigned short* ks = reinterpret_cast<const unsigned short*>(sm + BwdSmem::KH) + (32 * wq_) * TD + d;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) kraw[i] = kok ? ks[i * TD] : 0u;
+    for (int i = 0; i < 32; ++i) kraw[i] = (kok ? (uint32_t)ks[i * TD] : 0u) | (qraw[i] << 16);
   }
   tc_fence_before();
   __syncthreads();
@@ -1061,22 +1089,23 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
   // dO, v and P have been consumed by the products: their regions take g, q, k of rows 64..127 and k of rows
   // 0..63 by TMA while phase 1.5 runs, so that the W64 build and the first pass read them from shared memory.
   const int zrow = (int)(b * T + n * TC), yh = (int)hk_;
-  if (tid == 0) {
-    const uint32_t lb = smem_u32(bars + 3);
-    if (one_scale) {
-      // raw q and k of the whole chunk, row-major, for the q~ operand and the closing pass
-      mbar_arrive_expect_tx(lb, 4 * 16384);
-      tma_load_3d(smem_u32(sm + BwdSmem::QA), &maps.q, 0, yh, zrow, lb);
-      tma_load_3d(smem_u32(sm + BwdSmem::QA + 16384), &maps.q, 0, yh, zrow + 64, lb);
-      tma_load_3d(smem_u32(sm + BwdSmem::KA), &maps.k, 0, yh, zrow, lb);
-      tma_load_3d(smem_u32(sm + BwdSmem::KA + 16384), &maps.k, 0, yh, zrow + 64, lb);
-    } else {
-      mbar_arrive_expect_tx(lb, 32768 + 3 * 16384);
-      tma_load_3d(smem_u32(sm + BwdSmem::GH), &maps.g, 0, yh, zrow + 64, lb);
-      tma_load_3d(smem_u32(sm + BwdSmem::QH), &maps.q, 0, yh, zrow + 64, lb);
-      tma_load_3d(smem_u32(sm + BwdSmem::K1), &maps.k, 0, yh, zrow + 64, lb);
-      tma_load_3d(smem_u32(sm + BwdSmem::K0), &maps.k, 0, yh, zrow, lb);
+  if (one_scale) {
+    // every thread parks the raw k and q of its 32 rows in the regions the products have released; it alone reads
+    // them back (for the q~ operand and in the closing pass), so no barrier is involved
+    uint32_t* st0 = reinterpret_cast<uint32_t*>(sm + BwdSmem::ST0) + tid;
+    uint32_t* st1 = reinterpret_cast<uint32_t*>(sm + BwdSmem::ST1) + tid;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      st0[i * TTHREADS] = kraw[i];
+      st1[i * TTHREADS] = kraw[16 + i];
     }
+  } else if (tid == 0) {
+    const uint32_t lb = smem_u32(bars + 3);
+    mbar_arrive_expect_tx(lb, 32768 + 3 * 16384);
+    tma_load_3d(smem_u32(sm + BwdSmem::GH), &maps.g, 0, yh, zrow + 64, lb);
+    tma_load_3d(smem_u32(sm + BwdSmem::QH), &maps.q, 0, yh, zrow + 64, lb);
+    tma_load_3d(smem_u32(sm + BwdSmem::K1), &maps.k, 0, yh, zrow + 64, lb);
+    tma_load_3d(smem_u32(sm + BwdSmem::K0), &maps.k, 0, yh, zrow, lb);
   }
 
   // ---- phase 1.5: dV out, dP diagonal, the two dG sums ---------------------------------------------------
@@ -1176,26 +1205,25 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
     //   dk~^T[d][j] = sum_i q~[i][d]   dPm[i][j],   dk_intra = dk~ exp(G - lam_j),   q~ = q exp(lam - G)
     // two 128 x 128 x 128 products; a thread (feature d, rows 32 wq_ + [0, 32)) then finishes its rows in one pass.
     const uint32_t lane_base = tmem + ((uint32_t)(q4 * 32) << 16);
-    ok = mbar_wait(smem_u32(bars + 3), 0) && ok;        // raw q and k have landed
     const float t0 = tot[(2 * wq_) * TD + d], t1 = tot[(2 * wq_ + 1) * TD + d];
     float Cq = 1.f, Ck = 1.f;                           // gate products of the rows before / after this thread's 32
     for (int b2 = 0; b2 < 2 * wq_; ++b2) Cq *= tot[b2 * TD + d];
     for (int b2 = 2 * wq_ + 2; b2 < 8; ++b2) Ck *= tot[b2 * TD + d];
-    const unsigned short* qp = reinterpret_cast<const unsigned short*>(sm + BwdSmem::QA) + (32 * wq_) * TD + d;
-    const unsigned short* kp = reinterpret_cast<const unsigned short*>(sm + BwdSmem::KA) + (32 * wq_) * TD + d;
+    const uint32_t* st0 = reinterpret_cast<const uint32_t*>(sm + BwdSmem::ST0) + tid;     // this thread's parked (k | q << 16)
+    const uint32_t* st1 = reinterpret_cast<const uint32_t*>(sm + BwdSmem::ST1) + tid;
     {
       uint32_t qr[32];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) qr[i] = qp[i * TD];
+      for (int i = 0; i < 16; ++i) { qr[i] = st0[i * TTHREADS]; qr[16 + i] = st1[i * TTHREADS]; }
       // q~[r] = q[r] / prod_{t > r} f_t = q[r] * (prod_{first <= t <= r} f_t) / (prod_{t >= first} f_t): one reciprocal
       float run = 1.f / (t0 * t1 * Ck);
       uint32_t pk[16];
 #pragma unroll
       for (int i = 0; i < 32; i += 2) {
         run *= f32r[i];
-        const float lo = bf16_lo(qr[i]) * run;
+        const float lo = bf16_hi(qr[i]) * run;
         run *= f32r[i + 1];
-        const float hi = bf16_lo(qr[i + 1]) * run;
+        const float hi = bf16_hi(qr[i + 1]) * run;
         pk[i >> 1] = pack_bf16x2(lo, hi);
       }
       uint8_t* tile = sm + BwdSmem::QT + (wq_ >> 1) * TILE_BYTES;       // transposed like k_hat: row = feature
@@ -1227,16 +1255,21 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
     ok = mbar_wait(smem_u32(bars + 1), 0) && ok;
     ok = mbar_wait(smem_u32(bars + 2), 0) && ok;
     tc_fence_after();
+    // The operands of the two products are consumed: their regions stage the chunk's dq, dk (bf16) and the dlam suffix
+    // sums (float32) row-major, so that they leave for global memory as whole rows instead of two or four bytes per
+    // thread and row.
     const float invG = 1.f / eG;
-    float* dlb = reinterpret_cast<float*>(sm + BwdSmem::DLB);      // the operands it overwrites have been consumed
+    float* dlb = reinterpret_cast<float*>(sm + BwdSmem::DLB);
+    unsigned short* dqt = reinterpret_cast<unsigned short*>(sm + BwdSmem::DQT);
+    unsigned short* dkt = reinterpret_cast<unsigned short*>(sm + BwdSmem::DKT);
     float carry = 0.f;            // sum of dlam over this thread's rows after the current half
 #pragma unroll
     for (int hh = 1; hh >= 0; --hh) {
       const int rb = 32 * wq_ + 16 * hh;
-      uint32_t a[16], c[16], qk[16];     // qk: q in the low half, k in the high half
+      uint32_t a[16], c[16], qk[16];     // qk: k in the low half, q in the high half
       float dl[16];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) qk[i] = (uint32_t)qp[(16 * hh + i) * TD] | ((uint32_t)kp[(16 * hh + i) * TD] << 16);
+      for (int i = 0; i < 16; ++i) qk[i] = (hh ? st1 : st0)[i * TTHREADS];
       tmem_ld16(lane_base + TM_DQH + rb, a);
       tmem_ld16(lane_base + TM_DV + rb, c);
       tmem_ld_wait();
@@ -1244,9 +1277,9 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
         run *= f32r[16 * hh + i];          // exp(lam_r)
-        const float dqv = run * fmaf(invG, __uint_as_float(c[i]), __uint_as_float(a[i])) + diag[rb + i] * bf16_hi(qk[i]);
-        dl[i] = bf16_lo(qk[i]) * dqv;
-        if (ok) dq_out[row0 + (int64_t)(rb + i) * HD + d] = __float2bfloat16_rn(dqv);
+        const float dqv = run * fmaf(invG, __uint_as_float(c[i]), __uint_as_float(a[i])) + diag[rb + i] * bf16_lo(qk[i]);
+        dl[i] = bf16_hi(qk[i]) * dqv;
+        dqt[(rb + i) * TD + d] = __bfloat16_as_ushort(__float2bfloat16_rn(dqv));
       }
       tmem_ld16(lane_base + TM_DKH + rb, a);
       tmem_ld16(lane_base + TM_DP + rb, c);
@@ -1254,25 +1287,47 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
       run = hh ? Ck : Ck * t1;
 #pragma unroll
       for (int i = 15; i >= 0; --i) {      // run = exp(G - lam_r)
-        const float dkv = run * (__uint_as_float(a[i]) + __uint_as_float(c[i])) + diag[rb + i] * bf16_lo(qk[i]);
+        const float dkv = run * (__uint_as_float(a[i]) + __uint_as_float(c[i])) + diag[rb + i] * bf16_hi(qk[i]);
         run *= f32r[16 * hh + i];
-        dl[i] -= bf16_hi(qk[i]) * dkv;
-        if (ok) dk_out[row0 + (int64_t)(rb + i) * HD + d] = __float2bfloat16_rn(dkv);
+        dl[i] -= bf16_lo(qk[i]) * dkv;
+        dkt[(rb + i) * TD + d] = __bfloat16_as_ushort(__float2bfloat16_rn(dkv));
       }
 #pragma unroll
       for (int i = 14; i >= 0; --i) dl[i] += dl[i + 1];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) dlb[(16 * hh + i) * TTHREADS + tid] = dl[i] + carry;
+      for (int i = 0; i < 16; ++i) dlb[(rb + i) * TD + d] = dl[i] + carry;
       carry += dl[0];
     }
     grp[wq_ * TD + d] = carry;
+    if (wq_ == 0) gab[d] = dG;             // (the |g| sums kept here were last read at the path decision)
     tc_fence_before();
     __syncthreads();
-    float off = dG;
-    for (int w2 = wq_ + 1; w2 < 4; ++w2) off += grp[w2 * TD + d];
     if (ok) {
+      // dq, dk: 2048 pieces of 16 bytes each; a warp writes two whole 256-byte rows per instruction
 #pragma unroll
-      for (int i = 0; i < 32; ++i) dg_out[row0 + (int64_t)(32 * wq_ + i) * HD + d] = dlb[i * TTHREADS + tid] + off;
+      for (int j = 0; j < 4; ++j) {
+        const int id = tid + TTHREADS * j, row = id >> 4, ch = id & 15;
+        const int64_t e = row0 + (int64_t)row * HD + ch * 8;
+        *reinterpret_cast<uint4*>(dq_out + e) = *reinterpret_cast<const uint4*>(dqt + row * TD + ch * 8);
+        *reinterpret_cast<uint4*>(dk_out + e) = *reinterpret_cast<const uint4*>(dkt + row * TD + ch * 8);
+      }
+      // dg = suffix sum inside the thread's rows + the totals of the later quarters of the chunk + dG: 4096 pieces of
+      // four floats; a warp writes one whole 512-byte row per instruction
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int id = tid + TTHREADS * j, row = id >> 5, d0 = 4 * (id & 31), w = row >> 5;
+        float4 x = *reinterpret_cast<const float4*>(dlb + row * TD + d0);
+        float4 o = *reinterpret_cast<const float4*>(gab + d0);
+#pragma unroll
+        for (int w2 = 1; w2 < 4; ++w2) {
+          if (w2 > w) {
+            const float4 t = *reinterpret_cast<const float4*>(grp + w2 * TD + d0);
+            o.x += t.x; o.y += t.y; o.z += t.z; o.w += t.w;
+          }
+        }
+        x.x += o.x; x.y += o.y; x.z += o.z; x.w += o.w;
+        *reinterpret_cast<float4*>(dg_out + row0 + (int64_t)row * HD + d0) = x;
+      }
     }
   } else {
   // ---- phase 1.9: W64 for all 128 rows (rows < 64: k~, rows >= 64: q~, anchor row 63) ----------------------
@@ -1789,6 +1844,7 @@ int tc_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
   GLA_TRY(make_map_bthd(&maps.k, k, 0, B, T, HK, 64, 1));
   GLA_TRY(make_map_bthd(&maps.v, v, 0, B, T, HK, 64, 1));
   GLA_TRY(make_map_rows(&maps.s, S_prev, BHV * N * TD, 64, 128));
+  const FwdPtrs ptrs{g, (const bf16*)q, (const bf16*)k, (const bf16*)v, S_prev, (opts & GLA_OPT_NO_L2_PREFETCH) ? 0 : prefetch_distance(1)};
   {
     ProfScope ps("tc_chunk_fwd_kernel", st);
     bf16* out_p = R > 1 ? out_v : (bf16*)out;
@@ -1804,11 +1860,11 @@ int tc_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
       attr[0].val.programmaticStreamSerializationAllowed = 1;
       cfg.attrs = attr;
       cfg.numAttrs = 1;
-      e = cudaLaunchKernelEx(&cfg, tc_chunk_fwd_kernel, maps, T, HV, R, N, out_p, P, (const unsigned int*)early_flag,
+      e = cudaLaunchKernelEx(&cfg, tc_chunk_fwd_kernel, maps, ptrs, T, HV, R, N, out_p, P, (const unsigned int*)early_flag,
                              early_target, all_scales);
       if (e != cudaSuccess) return record_cuda_error(e);
     } else {
-      tc_chunk_fwd_kernel<<<(unsigned)(BHV * N), TTHREADS, FWD_SMEM, st>>>(maps, T, HV, R, N, out_p, P, nullptr, 0u, all_scales);
+      tc_chunk_fwd_kernel<<<(unsigned)(BHV * N), TTHREADS, FWD_SMEM, st>>>(maps, ptrs, T, HV, R, N, out_p, P, nullptr, 0u, all_scales);
     }
   }
   GLA_CHECK_LAUNCH();
