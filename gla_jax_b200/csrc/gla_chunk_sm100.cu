@@ -415,26 +415,6 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdPtrs ptrs, in
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   bool ok = mbar_wait(smem_u32(bars + 3), 0);
-  // This chunk's g, q, k have landed: ask L2 for the inputs of the chunk that the block scheduler will start on this
-  // SM when this block retires, so that its load phase streams from L2 instead of waiting for DRAM.  (A state tile
-  // that the state kernel has not written yet is simply fetched again later: L2 is the point of coherence.)
-  {
-    const int64_t nb = (int64_t)blockIdx.x + ptrs.pf_dist;
-    if (ptrs.pf_dist > 0 && nb < (int64_t)gridDim.x) {
-      const int64_t n2 = N - 1 - nb / BHn, bh2 = nb % BHn, h2 = bh2 % H;
-      const int64_t hk2 = (h2 / (R * R)) * R + (h2 % (R * R)) / R, hv2 = (h2 / (R * R)) * R + h2 % R;
-      const int64_t HDi = (H / R) * TD;                                  // input row pitch
-      const int64_t t2 = ((bh2 / H) * T + n2 * TC) * (H / R);
-      const int64_t r2k = (t2 + hk2) * TD, r2v = (t2 + hv2) * TD;
-      // strided rows, one 128-byte line per request: 256-byte rows of q, k, v; 512-byte rows of g
-      const int64_t eo = (int64_t)((tid >> 1) & (TC - 1)) * HDi + (tid & 1) * 64;
-      l2_prefetch_line(tid < 256 ? ptrs.q + r2k + eo : ptrs.k + r2k + eo);
-      if (tid < 256) l2_prefetch_line(ptrs.v + r2v + eo);
-      l2_prefetch_line(ptrs.g + r2k + (int64_t)(tid >> 2) * HDi + (tid & 3) * 32);
-      if (tid == 256) l2_prefetch_bulk(ptrs.s + (bh2 * N + n2) * TD * TD, 2 * TD * TD);
-    }
-  }
-
   // ---- gates, q, k of the thread's 16 rows x 2 columns from the landed tiles ---------------------
   float2 f[16];
   uint32_t qv[16], kv[16];
@@ -739,6 +719,28 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdPtrs ptrs, in
       *reinterpret_cast<uint4*>(pg + row * TC + ch * 8) = u;
     }
   }
+  // While the output product runs: ask L2 for the inputs of the chunk that the block scheduler will start on this SM
+  // when this block retires, so that its load phase streams from L2 instead of waiting for DRAM.  (Issued here
+  // and not earlier because the requests occupy the load/store path, which the earlier phases need for shared
+  // memory.  A state tile that the state kernel has not written yet is simply fetched again later: L2 is the point
+  // of coherence.)
+  {
+    const int64_t nb = (int64_t)blockIdx.x + ptrs.pf_dist;
+    if (ptrs.pf_dist > 0 && nb < (int64_t)gridDim.x) {
+      const int64_t n2 = N - 1 - nb / BHn, bh2 = nb % BHn, h2 = bh2 % H;
+      const int64_t hk2 = (h2 / (R * R)) * R + (h2 % (R * R)) / R, hv2 = (h2 / (R * R)) * R + h2 % R;
+      const int64_t HDi = (H / R) * TD;                                  // input row pitch
+      const int64_t t2 = ((bh2 / H) * T + n2 * TC) * (H / R);
+      const int64_t r2k = (t2 + hk2) * TD, r2v = (t2 + hv2) * TD;
+      // strided rows, one 128-byte line per request: 256-byte rows of q, k, v; 512-byte rows of g
+      const int64_t eo = (int64_t)((tid >> 1) & (TC - 1)) * HDi + (tid & 1) * 64;
+      l2_prefetch_line(tid < 256 ? ptrs.q + r2k + eo : ptrs.k + r2k + eo);
+      if (tid < 256) l2_prefetch_line(ptrs.v + r2v + eo);
+      l2_prefetch_line(ptrs.g + r2k + (int64_t)(tid >> 2) * HDi + (tid & 3) * 32);
+      if (tid == 256) l2_prefetch_bulk(ptrs.s + (bh2 * N + n2) * TD * TD, 2 * TD * TD);
+    }
+  }
+
   ok = mbar_wait(smem_u32(bars + 2), 0) && ok;
   tc_fence_after();
   if (ok) {
@@ -812,6 +814,9 @@ struct BwdSmem {
   static constexpr uint32_t QH = P;                        // [64][128] bf16: q of the pass's rows
   static constexpr uint32_t K1 = P + 16384;                // [64][128] bf16: k of rows 64..127
   static constexpr uint32_t K0 = V;                        // [64][128] bf16: k of rows 0..63
+  // TMA landing zones of the chunk's gates and raw q at the start of the block (raw k lands in KH)
+  static constexpr uint32_t G0 = SP;                       // [128][128] float row-major (64 KB over S_prev and dS_next)
+  static constexpr uint32_t Q0 = P;                        // [128][128] bf16 row-major
   // One-scale path (chunks whose gates need no secondary chunking), after the phase-1 products:
   static constexpr uint32_t ST0 = DO;                      // [16][512] u32: every thread's own (k | q << 16) of its rows 0..15
   static constexpr uint32_t ST1 = P;                       // [16][512] u32: ... of its rows 16..31
@@ -919,7 +924,6 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
   const int64_t HD = H * TD;                                          // output row pitch (virtual heads)
   const int64_t HDi = (H / R) * TD;                                   // input row pitch
   const int64_t row0 = ((b * T + n * TC) * H + h_) * TD;              // outputs
-  const int64_t row0k = ((b * T + n * TC) * (H / R) + hk_) * TD;      // g, q, k
   const int64_t chunk_id = bh * N + n;
 
   if (warp == 0) {
@@ -934,42 +938,49 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
     mbar_init(smem_u32(bars + 4), 1);
     mbar_init(smem_u32(bars + 5), 1);
     mbar_init(smem_u32(bars + 6), 1);
+    mbar_init(smem_u32(bars + 7), 1);
     mbar_fence_init();
-    // raw k of the whole chunk (row-major) into the region that k_hat will occupy: every thread reads its 32
-    // values from there before the barrier that precedes the k_hat stores
+    // What the block needs first, the gates and raw q, k of the whole chunk (row-major, 128 KB), comes by TMA into
+    // regions whose operand tiles are not needed until the products: g over the S_prev and dS_next regions, q over
+    // the P region, k into the region that k_hat will occupy.  Every thread copies its 32 rows of one feature from
+    // there into registers; after the barrier that follows, the three late tiles are requested.
+    const int z = (int)(b * T + n * TC), yv = (int)hv_, yk = (int)hk_;
     {
       const uint32_t kb = smem_u32(bars + 6);
-      mbar_arrive_expect_tx(kb, 2 * TILE_BYTES);
-      tma_load_3d(smem_u32(sm + BwdSmem::KH), &maps.k, 0, (int)hk_, (int)(b * T + n * TC), kb);
-      tma_load_3d(smem_u32(sm + BwdSmem::KH + TILE_BYTES), &maps.k, 0, (int)hk_, (int)(b * T + n * TC) + 64, kb);
+      mbar_arrive_expect_tx(kb, 8 * TILE_BYTES);
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        tma_load_3d(smem_u32(sm + BwdSmem::G0 + half * 2 * TILE_BYTES), &maps.g, 0, yk, z + 64 * half, kb);
+        tma_load_3d(smem_u32(sm + BwdSmem::Q0 + half * TILE_BYTES), &maps.q, 0, yk, z + 64 * half, kb);
+        tma_load_3d(smem_u32(sm + BwdSmem::KH + half * TILE_BYTES), &maps.k, 0, yk, z + 64 * half, kb);
+      }
     }
-    // the five operand tiles of the chunk by TMA (160 KB in flight); they are first needed by the products, which
-    // are issued after the gates and k_hat have been computed, so the copies run under that work
+    // dO and v keep their own regions and land while the gates are processed
     const uint32_t lb = smem_u32(bars + 5);
-    const int z = (int)(b * T + n * TC), yv = (int)hv_, cr = (int)(chunk_id * TD);
-    mbar_arrive_expect_tx(lb, 5 * 2 * TILE_BYTES);
+    mbar_arrive_expect_tx(lb, 2 * 2 * TILE_BYTES);
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
       tma_load_3d(smem_u32(sm + BwdSmem::DO + half * TILE_BYTES), &maps.dO, 64 * half, yv, z, lb);
       tma_load_3d(smem_u32(sm + BwdSmem::V + half * TILE_BYTES), &maps.v, 64 * half, yv, z, lb);
-      tma_load_2d(smem_u32(sm + BwdSmem::SP + half * TILE_BYTES), &maps.sp, 64 * half, cr, lb);
-      tma_load_2d(smem_u32(sm + BwdSmem::DS + half * TILE_BYTES), &maps.ds, 64 * half, cr, lb);
-      tma_load_2d(smem_u32(sm + BwdSmem::P + half * TILE_BYTES), &maps.p, 64 * half, cr, lb);
     }
   }
 
   // ---- phase 0: gate products per 16 rows; k_hat (the operand tiles are arriving by TMA) ------------------
   float f32r[32];                                   // gates of rows 32 wq_ + [0, 32), feature d
-  uint32_t qraw[32];                                // q of the same rows (bf16 bits)
+  uint32_t kraw[32];                                // k of the same rows and feature (low half), q above it
+  bool ok = true;
   {
-    float p0 = 1.f, p1 = 1.f;
-    const float* gp = g + row0k + (int64_t)(32 * wq_) * HDi + d;
-    const bf16* qp0 = q + row0k + (int64_t)(32 * wq_) * HDi + d;
+    const bool lok = mbar_wait(smem_u32(bars + 6), 0);
+    ok = lok;
+    const float* gs = reinterpret_cast<const float*>(sm + BwdSmem::G0) + (32 * wq_) * TD + d;
+    const unsigned short* qs = reinterpret_cast<const unsigned short*>(sm + BwdSmem::Q0) + (32 * wq_) * TD + d;
+    const unsigned short* ks = reinterpret_cast<const unsigned short*>(sm + BwdSmem::KH) + (32 * wq_) * TD + d;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) f32r[i] = __ldg(gp + (int64_t)i * HDi);      // all 32 loads in flight
-#pragma unroll
-    for (int i = 0; i < 32; ++i) qraw[i] = ldg_u16(qp0 + (int64_t)i * HDi);   // ... and q of the same rows behind them
-    float ga = 0.f;
+    for (int i = 0; i < 32; ++i) {
+      f32r[i] = lok ? gs[i * TD] : 0.f;
+      kraw[i] = lok ? ((uint32_t)ks[i * TD] | ((uint32_t)qs[i * TD] << 16)) : 0u;
+    }
+    float p0 = 1.f, p1 = 1.f, ga = 0.f;
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
       ga += fabsf(f32r[i]);
@@ -979,13 +990,6 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
     tot[(2 * wq_) * TD + d] = p0;
     tot[(2 * wq_ + 1) * TD + d] = p1;
     gab[wq_ * TD + d] = ga;
-  }
-  uint32_t kraw[32];                                // k of the same rows and feature from the staged tile (low half), q above it
-  {
-    const bool kok = mbar_wait(smem_u32(bars + 6), 0);
-    const unsigned short* ks = reinterpret_cast<const unsigned short*>(sm + BwdSmem::KH) + (32 * wq_) * TD + d;
-#pragma unroll
-    for (int i = 0; i < 32; ++i) kraw[i] = (kok ? (uint32_t)ks[i * TD] : 0u) | (qraw[i] << 16);
   }
   tc_fence_before();
   __syncthreads();
@@ -997,6 +1001,19 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
   {
     const float tsum = (gab[d] + gab[TD + d]) + (gab[2 * TD + d] + gab[3 * TD + d]);
     one_scale = __syncthreads_or(!(tsum <= ONE_SCALE_LIMIT) || all_scales != 0) == 0;
+  }
+  if (tid == 0) {
+    // every thread holds its gates, q and k in registers (two barriers back): the landing zones take the three late
+    // operand tiles, which arrive while k_hat is built
+    const uint32_t lb = smem_u32(bars + 7);
+    const int cr = (int)(chunk_id * TD);
+    mbar_arrive_expect_tx(lb, 3 * 2 * TILE_BYTES);
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      tma_load_2d(smem_u32(sm + BwdSmem::SP + half * TILE_BYTES), &maps.sp, 64 * half, cr, lb);
+      tma_load_2d(smem_u32(sm + BwdSmem::DS + half * TILE_BYTES), &maps.ds, 64 * half, cr, lb);
+      tma_load_2d(smem_u32(sm + BwdSmem::P + half * TILE_BYTES), &maps.p, 64 * half, cr, lb);
+    }
   }
   {
     // k_hat[r][d] = k[r][d] * prod_{t > r} f_t   (rows of this thread: 32 wq_ + i)
@@ -1027,9 +1044,9 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
   // Issued by four threads of four warps on different schedulers (8 to 16 MMAs each instead of 40 from one): the
   // issuing thread's instruction stream is serial, so this shortens the wait of everybody else.  The two halves of
   // dV come from the same thread, in order.
-  bool ok = true;
   if (lane == 0 && (warp == 3 || warp == 6 || warp == 9 || warp == 12)) {
-    ok = mbar_wait(smem_u32(bars + 5), 0);          // operand tiles landed
+    ok = mbar_wait(smem_u32(bars + 5), 0) && ok;    // operand tiles landed
+    ok = mbar_wait(smem_u32(bars + 7), 0) && ok;
     tc_fence_after();
     constexpr uint32_t iKK = idesc_bf16(128, 128, 0, 0), iMM = idesc_bf16(128, 128, 1, 1);
     const uint32_t aDO = smem_u32(sm + BwdSmem::DO), aV = smem_u32(sm + BwdSmem::V);
@@ -1085,6 +1102,7 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
   }
   ok = mbar_wait(smem_u32(bars + 0), 0) && ok;
   ok = mbar_wait(smem_u32(bars + 5), 0) && ok;      // every thread observes the tiles' arrival itself before reading them
+  ok = mbar_wait(smem_u32(bars + 7), 0) && ok;
   tc_fence_after();
   // dO, v and P have been consumed by the products: their regions take g, q, k of rows 64..127 and k of rows
   // 0..63 by TMA while phase 1.5 runs, so that the W64 build and the first pass read them from shared memory.
@@ -1110,8 +1128,12 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
 
   // ---- phase 1.5: dV out, dP diagonal, the two dG sums ---------------------------------------------------
   {
-    uint32_t r[32];
-    tmem_ld32(tmem + ((uint32_t)(q4 * 32) << 16) + TM_DV + 32 * wq_, r);     // row j = d here (row layout)
+    // three accumulator slices per thread; the first two loads are in flight together, the third (dP) follows
+    // while their values are being used
+    uint32_t r[32], r2[32];
+    const uint32_t lane_base = tmem + ((uint32_t)(q4 * 32) << 16);
+    tmem_ld32(lane_base + TM_DV + 32 * wq_, r);       // row j = d here (row layout)
+    tmem_ld32(lane_base + TM_DKH + 32 * wq_, r2);     // feature d, rows 32 wq_ + m (column layout)
     tmem_ld_wait();
     if (ok) {
       bf16* o = dv_out + row0 + (int64_t)d * HD + 32 * wq_;
@@ -1125,9 +1147,26 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
         st_global_v8(o + 16 * c8, u);
       }
     }
+    // the thread's slice of dP (row i = d, columns 32 wq_ + [0, 32)): the single-anchor path masks all of it into an
+    // operand tile; every path needs the diagonal entries, which lie in the slices with wq_ == q4
+    const bool need_dp = one_scale || wq_ == q4;
+    if (need_dp) tmem_ld32(lane_base + TM_DP + 32 * wq_, r);
+    // dG1[d] = sum_r dKh^T[d][r] k_hat[r][d]   (this thread: rows 32 wq_ + m)
+    {
+      float s1 = 0.f;
+      const uint8_t* tile = sm + BwdSmem::KH + (wq_ >> 1) * TILE_BYTES;
+#pragma unroll
+      for (int c4 = 0; c4 < 4; ++c4) {
+        const uint4 a = *reinterpret_cast<const uint4*>(tile + sw128_chunk(d, (wq_ & 1) * 4 + c4));
+        s1 = fmaf(__uint_as_float(r2[8 * c4 + 0]), bf16_lo(a.x), s1); s1 = fmaf(__uint_as_float(r2[8 * c4 + 1]), bf16_hi(a.x), s1);
+        s1 = fmaf(__uint_as_float(r2[8 * c4 + 2]), bf16_lo(a.y), s1); s1 = fmaf(__uint_as_float(r2[8 * c4 + 3]), bf16_hi(a.y), s1);
+        s1 = fmaf(__uint_as_float(r2[8 * c4 + 4]), bf16_lo(a.z), s1); s1 = fmaf(__uint_as_float(r2[8 * c4 + 5]), bf16_hi(a.z), s1);
+        s1 = fmaf(__uint_as_float(r2[8 * c4 + 6]), bf16_lo(a.w), s1); s1 = fmaf(__uint_as_float(r2[8 * c4 + 7]), bf16_hi(a.w), s1);
+      }
+      dG1[wq_ * TD + d] = s1;
+    }
+    if (need_dp) tmem_ld_wait();
     if (wq_ == q4) {          // the 32 x 32 diagonal block of dP: pick dP[i][i]
-      tmem_ld32(tmem + ((uint32_t)(q4 * 32) << 16) + TM_DP + 32 * q4, r);
-      tmem_ld_wait();
       float dv_ = 0.f;
 #pragma unroll
       for (int m = 0; m < 32; ++m)
@@ -1147,8 +1186,6 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
     if (one_scale) {
       // dP restricted to j < i as a bf16 operand tile (row i = d here, columns 32 wq_ + [0, 32)); the v tile it
       // overwrites was last read by the phase-1 products
-      tmem_ld32(tmem + ((uint32_t)(q4 * 32) << 16) + TM_DP + 32 * wq_, r);
-      tmem_ld_wait();
       uint8_t* tile = sm + BwdSmem::DPM + (wq_ >> 1) * TILE_BYTES;
 #pragma unroll
       for (int c4 = 0; c4 < 4; ++c4) {
@@ -1161,20 +1198,6 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
         *reinterpret_cast<uint4*>(tile + sw128_chunk(d, (wq_ & 1) * 4 + c4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
       }
     }
-    // dG1[d] = sum_r dKh^T[d][r] k_hat[r][d]   (this thread: rows 32 wq_ + m)
-    tmem_ld32(tmem + ((uint32_t)(q4 * 32) << 16) + TM_DKH + 32 * wq_, r);
-    tmem_ld_wait();
-    float s1 = 0.f;
-    const uint8_t* tile = sm + BwdSmem::KH + (wq_ >> 1) * TILE_BYTES;
-#pragma unroll
-    for (int c4 = 0; c4 < 4; ++c4) {
-      const uint4 a = *reinterpret_cast<const uint4*>(tile + sw128_chunk(d, (wq_ & 1) * 4 + c4));
-      s1 = fmaf(__uint_as_float(r[8 * c4 + 0]), bf16_lo(a.x), s1); s1 = fmaf(__uint_as_float(r[8 * c4 + 1]), bf16_hi(a.x), s1);
-      s1 = fmaf(__uint_as_float(r[8 * c4 + 2]), bf16_lo(a.y), s1); s1 = fmaf(__uint_as_float(r[8 * c4 + 3]), bf16_hi(a.y), s1);
-      s1 = fmaf(__uint_as_float(r[8 * c4 + 4]), bf16_lo(a.z), s1); s1 = fmaf(__uint_as_float(r[8 * c4 + 5]), bf16_hi(a.z), s1);
-      s1 = fmaf(__uint_as_float(r[8 * c4 + 6]), bf16_lo(a.w), s1); s1 = fmaf(__uint_as_float(r[8 * c4 + 7]), bf16_hi(a.w), s1);
-    }
-    dG1[wq_ * TD + d] = s1;
     // dG2[d] = sum_v S_prev[d][v] dS_next[d][v]    (this thread: v in 32 wq_ + [0, 32))
     float s2 = 0.f;
     const uint8_t* ts = sm + BwdSmem::SP + (wq_ >> 1) * TILE_BYTES;
@@ -1248,8 +1271,8 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
       constexpr uint32_t iM = idesc_bf16(128, 128, 0, 1);
       const uint64_t kA = desc_kmajor(smem_u32(sm + BwdSmem::QT), TILE_BYTES, 0), mB = desc_mnmajor(smem_u32(sm + BwdSmem::DPM), TILE_BYTES, 0);
 #pragma unroll
-      for (int ks = 0; ks < 8; ++ks)     // dk~^T[d][j] = sum_i q~^T[d][i] dPm[i][j]
-        umma_bf16(tmem + TM_DP, kslice_kmajor(kA, TILE_BYTES, ks), kslice_mnmajor(mB, ks), iM, ks > 0);
+      for (int ks = 0; ks < 8; ++ks)     // dk~^T[d][j] = sum_i q~^T[d][i] dPm[i][j], on top of the inter-chunk term:
+        umma_bf16(tmem + TM_DKH, kslice_kmajor(kA, TILE_BYTES, ks), kslice_mnmajor(mB, ks), iM, 1);   // same weight exp(G - lam_j)
       umma_commit(smem_u32(bars + 2));
     }
     ok = mbar_wait(smem_u32(bars + 1), 0) && ok;
@@ -1282,12 +1305,11 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
         dqt[(rb + i) * TD + d] = __bfloat16_as_ushort(__float2bfloat16_rn(dqv));
       }
       tmem_ld16(lane_base + TM_DKH + rb, a);
-      tmem_ld16(lane_base + TM_DP + rb, c);
       tmem_ld_wait();
       run = hh ? Ck : Ck * t1;
 #pragma unroll
       for (int i = 15; i >= 0; --i) {      // run = exp(G - lam_r)
-        const float dkv = run * (__uint_as_float(a[i]) + __uint_as_float(c[i])) + diag[rb + i] * bf16_hi(qk[i]);
+        const float dkv = run * __uint_as_float(a[i]) + diag[rb + i] * bf16_hi(qk[i]);
         run *= f32r[16 * hh + i];
         dl[i] -= bf16_lo(qk[i]) * dkv;
         dkt[(rb + i) * TD + d] = __bfloat16_as_ushort(__float2bfloat16_rn(dkv));
