@@ -802,7 +802,7 @@ struct BwdSmem {
   static constexpr uint32_t DG1 = DIAG + TC * 4;           // [4][128] float: partial sums of the two dG terms, one slot per
   static constexpr uint32_t DG2 = DG1 + 4 * TD * 4;        // [4][128] float  quarter of the rows (summed in a fixed order)
   static constexpr uint32_t GAB = DG2 + 4 * TD * 4;        // [4][128] float: sums of |g| per 32 rows
-  static constexpr uint32_t BAR = GAB + 4 * TD * 4;        // 7 mbarriers + tmem slot
+  static constexpr uint32_t BAR = GAB + 4 * TD * 4;        // 8 mbarriers + tmem slot
   static constexpr uint32_t END = BAR + 96;
   // After the phase-1 products have completed, dO, v and P are dead; after phase 1.5 the rest is.  Reuse:
   static constexpr uint32_t W64 = KH;                      // 32 KB: k~ / q~ at the h = 64 anchor, all 128 rows
@@ -907,8 +907,12 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
   float* dG1 = reinterpret_cast<float*>(sm + BwdSmem::DG1);
   float* dG2 = reinterpret_cast<float*>(sm + BwdSmem::DG2);
   float* gab = reinterpret_cast<float*>(sm + BwdSmem::GAB);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + BwdSmem::BAR);   // [0]: phase 1, [1],[2]: level buffers, [3],[4]: pass loads, [5]: tiles, [6]: raw k
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
+  // mbarriers [0]: phase-1 products, [1],[2]: level buffers / the two closing products, [3],[4]: pass loads,
+  // [5]: dO and v tiles, [6]: gates and raw q, k, [7]: the three late tiles; the TMEM address slot lies behind them
+  constexpr int BWD_NBARS = 8;
+  static_assert(BWD_NBARS * 8 + 8 <= 96, "barriers and the TMEM slot must fit the space reserved at BwdSmem::BAR");
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + BwdSmem::BAR);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + BWD_NBARS);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int q4 = warp & 3, wq_ = warp >> 2;        // TMEM lane quadrant, and which quarter of the columns
@@ -932,13 +936,8 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
   }
   if (tid == 0) {
     mbar_init(smem_u32(bars + 0), 4);        // four issuing threads commit the phase-1 products
-    mbar_init(smem_u32(bars + 1), 1);
-    mbar_init(smem_u32(bars + 2), 1);
-    mbar_init(smem_u32(bars + 3), 1);
-    mbar_init(smem_u32(bars + 4), 1);
-    mbar_init(smem_u32(bars + 5), 1);
-    mbar_init(smem_u32(bars + 6), 1);
-    mbar_init(smem_u32(bars + 7), 1);
+#pragma unroll
+    for (int i = 1; i < BWD_NBARS; ++i) mbar_init(smem_u32(bars + i), 1);
     mbar_fence_init();
     // What the block needs first, the gates and raw q, k of the whole chunk (row-major, 128 KB), comes by TMA into
     // regions whose operand tiles are not needed until the products: g over the S_prev and dS_next regions, q over
