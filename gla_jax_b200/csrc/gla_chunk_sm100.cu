@@ -964,6 +964,12 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
     }
   }
 
+  // The barriers must be initialised before any other thread waits on one (the first wait follows at once now that
+  // the gates come through shared memory), and the TMEM address must be visible.
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+
   // ---- phase 0: gate products per 16 rows; k_hat (the operand tiles are arriving by TMA) ------------------
   float f32r[32];                                   // gates of rows 32 wq_ + [0, 32), feature d
   uint32_t kraw[32];                                // k of the same rows and feature (low half), q above it
