@@ -732,12 +732,15 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdPtrs ptrs, in
       const int64_t HDi = (H / R) * TD;                                  // input row pitch
       const int64_t t2 = ((bh2 / H) * T + n2 * TC) * (H / R);
       const int64_t r2k = (t2 + hk2) * TD, r2v = (t2 + hv2) * TD;
-      // strided rows, one 128-byte line per request: 256-byte rows of q, k, v; 512-byte rows of g
-      const int64_t eo = (int64_t)((tid >> 1) & (TC - 1)) * HDi + (tid & 1) * 64;
-      l2_prefetch_line(tid < 256 ? ptrs.q + r2k + eo : ptrs.k + r2k + eo);
-      if (tid < 256) l2_prefetch_line(ptrs.v + r2v + eo);
-      l2_prefetch_line(ptrs.g + r2k + (int64_t)(tid >> 2) * HDi + (tid & 3) * 32);
-      if (tid == 256) l2_prefetch_bulk(ptrs.s + (bh2 * N + n2) * TD * TD, 2 * TD * TD);
+      // one bulk request per row and array (a thread issues exactly one): the 128 rows of g (512 bytes each), q, k, v
+      // (256 bytes each); per-line prefetch instructions would put 1536 requests through the load/store path
+      const int64_t ro = (int64_t)(tid & (TC - 1)) * HDi;
+      const int which = tid >> 7;
+      if (which == 0) l2_prefetch_bulk(ptrs.g + r2k + ro, 4 * TD);
+      else if (which == 1) l2_prefetch_bulk(ptrs.q + r2k + ro, 2 * TD);
+      else if (which == 2) l2_prefetch_bulk(ptrs.k + r2k + ro, 2 * TD);
+      else l2_prefetch_bulk(ptrs.v + r2v + ro, 2 * TD);
+      if (tid == 0) l2_prefetch_bulk(ptrs.s + (bh2 * N + n2) * TD * TD, 2 * TD * TD);
     }
   }
 
@@ -1094,11 +1097,16 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
       const int64_t t2 = ((bh2 / H) * T + n2 * TC) * (H / R);
       const int64_t r2k = (t2 + hk2) * TD, r2v = (t2 + hv2) * TD;
       const int64_t c2 = (bh2 * N + n2) * TD * TD;
-      // strided rows: one 128-byte line per request (256-byte rows of dO, v, k, q; 512-byte rows of g)
-      const int64_t eo = (int64_t)((tid >> 1) & (TC - 1)) * HDi + (tid & 1) * 64;
-      l2_prefetch_line(tid < 256 ? dO + r2v + eo : v + r2v + eo);
-      l2_prefetch_line(tid < 256 ? k + r2k + eo : q + r2k + eo);
-      l2_prefetch_line(g + r2k + (int64_t)(tid >> 2) * HDi + (tid & 3) * 32);
+      // strided rows, one bulk request per row and array: 512-byte rows of g, 256-byte rows of q, k, v, dO
+      {
+        const int64_t ro = (int64_t)(tid & (TC - 1)) * HDi;
+        const int which = tid >> 7;
+        if (which == 0) l2_prefetch_bulk(g + r2k + ro, 4 * TD);
+        else if (which == 1) l2_prefetch_bulk(q + r2k + ro, 2 * TD);
+        else if (which == 2) l2_prefetch_bulk(k + r2k + ro, 2 * TD);
+        else l2_prefetch_bulk(v + r2v + ro, 2 * TD);
+        if (tid < TC) l2_prefetch_bulk(dO + r2v + ro, 2 * TD);
+      }
       // contiguous 32 KB tiles: one bulk request each
       if (tid == 0) l2_prefetch_bulk(S_prev + c2, 2 * TD * TD);
       else if (tid == 32) l2_prefetch_bulk(dS_next + c2, 2 * TD * TD);
