@@ -257,9 +257,7 @@ constexpr uint32_t KC_TILE = 64 * 128;    // one SW128 tile of 64 rows
 
 // TMA descriptors of one launch (built on the host per call, passed by value).
 struct FwdMaps { CUtensorMap g, q, k, v, s; };
-// The same arrays as plain pointers, for the L2 prefetch of the chunk that follows on this SM (pf_dist blocks ahead;
-// 0 = no prefetch).
-struct FwdPtrs { const float* g; const bf16 *q, *k, *v, *s; int pf_dist; };
+
 
 // Operands of level slot S (half size 2^S) for the thread's 16 rows x 2 columns, with the decay
 // weights formed on the fly as running products of the gates f (no weight arrays are kept):
@@ -346,9 +344,9 @@ __device__ __noinline__ bool fwd_load_state_late(const unsigned int* state_done,
 }
 
 __global__ void __launch_bounds__(TTHREADS, 1)
-tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdPtrs ptrs, int64_t T, int64_t H, int R, int64_t N,
-                    bf16* __restrict__ out, bf16* __restrict__ P_saved, const unsigned int* __restrict__ state_done,
-                    unsigned int state_target, int all_scales) {
+tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, int R, int64_t N, bf16* __restrict__ out,
+                    bf16* __restrict__ P_saved, const unsigned int* __restrict__ state_done, unsigned int state_target,
+                    int all_scales) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = align1024(smem_raw);
   float* tot = reinterpret_cast<float*>(sm + FwdSmem::TOT);
@@ -719,31 +717,6 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdPtrs ptrs, in
       *reinterpret_cast<uint4*>(pg + row * TC + ch * 8) = u;
     }
   }
-  // While the output product runs: ask L2 for the inputs of the chunk that the block scheduler will start on this SM
-  // when this block retires, so that its load phase streams from L2 instead of waiting for DRAM.  (Issued here
-  // and not earlier because the requests occupy the load/store path, which the earlier phases need for shared
-  // memory.  A state tile that the state kernel has not written yet is simply fetched again later: L2 is the point
-  // of coherence.)
-  {
-    const int64_t nb = (int64_t)blockIdx.x + ptrs.pf_dist;
-    if (ptrs.pf_dist > 0 && nb < (int64_t)gridDim.x) {
-      const int64_t n2 = N - 1 - nb / BHn, bh2 = nb % BHn, h2 = bh2 % H;
-      const int64_t hk2 = (h2 / (R * R)) * R + (h2 % (R * R)) / R, hv2 = (h2 / (R * R)) * R + h2 % R;
-      const int64_t HDi = (H / R) * TD;                                  // input row pitch
-      const int64_t t2 = ((bh2 / H) * T + n2 * TC) * (H / R);
-      const int64_t r2k = (t2 + hk2) * TD, r2v = (t2 + hv2) * TD;
-      // one bulk request per row and array (a thread issues exactly one): the 128 rows of g (512 bytes each), q, k, v
-      // (256 bytes each); per-line prefetch instructions would put 1536 requests through the load/store path
-      const int64_t ro = (int64_t)(tid & (TC - 1)) * HDi;
-      const int which = tid >> 7;
-      if (which == 0) l2_prefetch_bulk(ptrs.g + r2k + ro, 4 * TD);
-      else if (which == 1) l2_prefetch_bulk(ptrs.q + r2k + ro, 2 * TD);
-      else if (which == 2) l2_prefetch_bulk(ptrs.k + r2k + ro, 2 * TD);
-      else l2_prefetch_bulk(ptrs.v + r2v + ro, 2 * TD);
-      if (tid == 0) l2_prefetch_bulk(ptrs.s + (bh2 * N + n2) * TD * TD, 2 * TD * TD);
-    }
-  }
-
   ok = mbar_wait(smem_u32(bars + 2), 0) && ok;
   tc_fence_after();
   if (ok) {
@@ -1097,16 +1070,12 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
       const int64_t t2 = ((bh2 / H) * T + n2 * TC) * (H / R);
       const int64_t r2k = (t2 + hk2) * TD, r2v = (t2 + hv2) * TD;
       const int64_t c2 = (bh2 * N + n2) * TD * TD;
-      // strided rows, one bulk request per row and array: 512-byte rows of g, 256-byte rows of q, k, v, dO
-      {
-        const int64_t ro = (int64_t)(tid & (TC - 1)) * HDi;
-        const int which = tid >> 7;
-        if (which == 0) l2_prefetch_bulk(g + r2k + ro, 4 * TD);
-        else if (which == 1) l2_prefetch_bulk(q + r2k + ro, 2 * TD);
-        else if (which == 2) l2_prefetch_bulk(k + r2k + ro, 2 * TD);
-        else l2_prefetch_bulk(v + r2v + ro, 2 * TD);
-        if (tid < TC) l2_prefetch_bulk(dO + r2v + ro, 2 * TD);
-      }
+      // strided rows: one 128-byte line per request (256-byte rows of dO, v, k, q; 512-byte rows of g).  Bulk
+      // prefetches of whole rows were measured and are slower to issue than these.
+      const int64_t eo = (int64_t)((tid >> 1) & (TC - 1)) * HDi + (tid & 1) * 64;
+      l2_prefetch_line(tid < 256 ? dO + r2v + eo : v + r2v + eo);
+      l2_prefetch_line(tid < 256 ? k + r2k + eo : q + r2k + eo);
+      l2_prefetch_line(g + r2k + (int64_t)(tid >> 2) * HDi + (tid & 3) * 32);
       // contiguous 32 KB tiles: one bulk request each
       if (tid == 0) l2_prefetch_bulk(S_prev + c2, 2 * TD * TD);
       else if (tid == 32) l2_prefetch_bulk(dS_next + c2, 2 * TD * TD);
@@ -1879,7 +1848,6 @@ int tc_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
   GLA_TRY(make_map_bthd(&maps.k, k, 0, B, T, HK, 64, 1));
   GLA_TRY(make_map_bthd(&maps.v, v, 0, B, T, HK, 64, 1));
   GLA_TRY(make_map_rows(&maps.s, S_prev, BHV * N * TD, 64, 128));
-  const FwdPtrs ptrs{g, (const bf16*)q, (const bf16*)k, (const bf16*)v, S_prev, (opts & GLA_OPT_NO_L2_PREFETCH) ? 0 : prefetch_distance(1)};
   {
     ProfScope ps("tc_chunk_fwd_kernel", st);
     bf16* out_p = R > 1 ? out_v : (bf16*)out;
@@ -1895,11 +1863,11 @@ int tc_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
       attr[0].val.programmaticStreamSerializationAllowed = 1;
       cfg.attrs = attr;
       cfg.numAttrs = 1;
-      e = cudaLaunchKernelEx(&cfg, tc_chunk_fwd_kernel, maps, ptrs, T, HV, R, N, out_p, P, (const unsigned int*)early_flag,
+      e = cudaLaunchKernelEx(&cfg, tc_chunk_fwd_kernel, maps, T, HV, R, N, out_p, P, (const unsigned int*)early_flag,
                              early_target, all_scales);
       if (e != cudaSuccess) return record_cuda_error(e);
     } else {
-      tc_chunk_fwd_kernel<<<(unsigned)(BHV * N), TTHREADS, FWD_SMEM, st>>>(maps, ptrs, T, HV, R, N, out_p, P, nullptr, 0u, all_scales);
+      tc_chunk_fwd_kernel<<<(unsigned)(BHV * N), TTHREADS, FWD_SMEM, st>>>(maps, T, HV, R, N, out_p, P, nullptr, 0u, all_scales);
     }
   }
   GLA_CHECK_LAUNCH();
