@@ -5,8 +5,8 @@ there is no fallback if the library is absent."""
 from .gla import chunk_gla, recurrent_gla, recurrent_gla_naive, auto_block_size, decode_step, chunk_gla_packed
 from .layer import GLALayer, log_forget_gate, headnorm_gate
 from ._lib import check_device
-from .ops import cumsum_recursive, cumsum_pallas, rnn_recursive, rnn_pallas, binary_operator, triton_scan
+from .ops import cumsum_recursive, cumsum_pallas, rnn_recursive, rnn_pallas, binary_operator, triton_scan, scan
 
 __all__ = ["chunk_gla", "recurrent_gla", "recurrent_gla_naive", "auto_block_size", "decode_step", "chunk_gla_packed", "cumsum_recursive",
-           "cumsum_pallas", "rnn_recursive", "rnn_pallas", "binary_operator", "triton_scan",
+           "cumsum_pallas", "rnn_recursive", "rnn_pallas", "binary_operator", "triton_scan", "scan",
            "GLALayer", "log_forget_gate", "headnorm_gate", "check_device"]

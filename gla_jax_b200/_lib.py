@@ -48,6 +48,7 @@ SIGNATURES = {
     "gla_profile_enable": (None, [c_int]),
     "gla_profile_report": (c_size_t, [c_char_p, c_size_t]),
     "gla_cumsum": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int]),
+    "gla_scan": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int]),
     "gla_rnn_scan": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
                              c_void_p, c_void_p, c_int, c_int, c_int]),
     "gla_recurrent_fwd": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p,

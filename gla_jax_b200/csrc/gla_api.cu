@@ -128,6 +128,17 @@ int gla_cumsum(void* stream, int64_t N, int64_t T, int64_t D, const void* src, c
                        out_dtype == GLA_BF16);
 }
 
+int gla_scan(void* stream, int op, int64_t N, int64_t T, int64_t D, const void* src, const void* init, void* dst,
+             int reverse, int in_dtype, int out_dtype) {
+  if (!src || !dst) return GLA_ERR_NULL_POINTER;
+  if (N <= 0 || T <= 0 || D <= 0) return GLA_ERR_BAD_DIMS;
+  if (op < GLA_SCAN_ADD || op > GLA_SCAN_LOGADDEXP) return GLA_ERR_UNSUPPORTED;
+  GLA_TRY(check_dtype(in_dtype));
+  GLA_TRY(check_dtype(out_dtype));
+  return launch_cumsum((cudaStream_t)stream, N, T, D, src, init, dst, reverse, in_dtype == GLA_BF16,
+                       out_dtype == GLA_BF16, nullptr, nullptr, op);
+}
+
 int gla_rnn_scan(void* stream, int64_t batch, int64_t T, int64_t K, int64_t V, const float* log_fgate,
                  const void* kv, const float* init_log_fgate, const void* init_kv, float* out_log,
                  void* out_state, int reverse, int last_only, int kv_dtype) {

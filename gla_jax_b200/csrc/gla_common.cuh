@@ -66,7 +66,7 @@ static inline bool aligned32(const void* p) { return (((uintptr_t)p) & 31) == 0;
 // (segment sums first, then the scans), which fills the device when N * D alone is small.
 int launch_cumsum(cudaStream_t st, int64_t N, int64_t T, int64_t D, const void* src, const void* init,
                   void* dst, int reverse, int in_bf16, int out_bf16, const void* sub = nullptr,
-                  float* scratch = nullptr);
+                  float* scratch = nullptr, int op = GLA_SCAN_ADD);
 size_t cumsum_scratch_bytes(int64_t N, int64_t T, int64_t D);
 
 // Exclusive state scan over chunks: for every (bh): S <- init; for n in order:

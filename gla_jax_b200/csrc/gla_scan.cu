@@ -18,11 +18,30 @@ namespace gla {
 constexpr int CS_RPT = 8;    // rows per thread
 constexpr int CS_RL = 8;     // row lanes
 
+// The combine rules of the scan library (gla_scan_op): each is associative with an identity element, which is what
+// the tiled scan needs (padding, carries, segment totals).  ops.py:82-104 scans with an arbitrary traced function;
+// here the function is one of these, picked by the caller.
+struct OpAdd { static __device__ __forceinline__ float id() { return 0.f; }
+               static __device__ __forceinline__ float f(float a, float b) { return a + b; } };
+struct OpMul { static __device__ __forceinline__ float id() { return 1.f; }
+               static __device__ __forceinline__ float f(float a, float b) { return a * b; } };
+struct OpMax { static __device__ __forceinline__ float id() { return -INFINITY; }
+               static __device__ __forceinline__ float f(float a, float b) { return fmaxf(a, b); } };
+struct OpMin { static __device__ __forceinline__ float id() { return INFINITY; }
+               static __device__ __forceinline__ float f(float a, float b) { return fminf(a, b); } };
+struct OpLogAddExp {      // log(exp(a) + exp(b)), evaluated around the larger argument
+  static __device__ __forceinline__ float id() { return -INFINITY; }
+  static __device__ __forceinline__ float f(float a, float b) {
+    const float m = fmaxf(a, b), n = fminf(a, b);
+    return m == -INFINITY ? m : m + log1pf(__expf(n - m));
+  }
+};
+
 // The scan axis may be cut into `nseg` segments of `seg_len` positions (in scan order) that run
 // as separate blocks: a first launch with TOTALS = true leaves every segment's column sums in
 // `totals` (N, nseg, D); the second adds the sums of the segments before its own to its carry.
 // nseg = 1 with totals = nullptr is the plain one-pass scan.
-template <typename TI, typename TO, bool TOTALS>
+template <typename TI, typename TO, bool TOTALS, typename OP>
 __global__ void __launch_bounds__(256) cumsum_kernel(const TI* __restrict__ src, const TI* __restrict__ sub,
                                                      const TI* __restrict__ init, TO* __restrict__ dst, int64_t T,
                                                      int64_t D, int reverse, int nseg, int64_t seg_len,
@@ -33,9 +52,9 @@ __global__ void __launch_bounds__(256) cumsum_kernel(const TI* __restrict__ src,
   const int tx = threadIdx.x, rl = threadIdx.y;
   const int64_t c = (int64_t)blockIdx.y * 32 + tx;
   const bool cvalid = c < D;
-  float carry = (!TOTALS && init != nullptr && cvalid) ? ld_f(init, n * D + c) : 0.f;
+  float carry = (!TOTALS && init != nullptr && cvalid) ? ld_f(init, n * D + c) : OP::id();
   if (!TOTALS && totals != nullptr && cvalid)
-    for (int s2 = 0; s2 < seg; ++s2) carry += totals[(n * nseg + s2) * D + c];
+    for (int s2 = 0; s2 < seg; ++s2) carry = OP::f(carry, totals[(n * nseg + s2) * D + c]);
   const TI* s = src + n * T * D;
   const TI* s2 = sub ? sub + n * T * D : nullptr;   // optional second source, subtracted element-wise
   TO* o = dst + n * T * D;
@@ -47,40 +66,42 @@ __global__ void __launch_bounds__(256) cumsum_kernel(const TI* __restrict__ src,
     for (int r = 0; r < CS_RPT; ++r) {
       int64_t tt = t0 + rl * CS_RPT + r;
       int64_t tp = reverse ? (T - 1 - tt) : tt;
-      x[r] = (cvalid && tt < tend) ? ld_f(s, tp * D + c) : 0.f;
+      x[r] = (cvalid && tt < tend) ? ld_f(s, tp * D + c) : OP::id();
       if (s2 && cvalid && tt < tend) x[r] -= ld_f(s2, tp * D + c);
     }
 #pragma unroll
-    for (int r = 1; r < CS_RPT; ++r) x[r] += x[r - 1];
+    for (int r = 1; r < CS_RPT; ++r) x[r] = OP::f(x[r - 1], x[r]);
     if (TOTALS) {
-      carry += x[CS_RPT - 1];
+      // the row lanes hold consecutive pieces of the tile: combined in order after the loop (each lane keeps the
+      // running combination of ITS pieces, which is only order-safe for commutative rules; all rules here are)
+      carry = OP::f(carry, x[CS_RPT - 1]);
       continue;
     }
     tot[rl][tx] = x[CS_RPT - 1];
     __syncthreads();
-    float off = carry, total = 0.f;
+    float off = carry, total = OP::id();
 #pragma unroll
     for (int r2 = 0; r2 < CS_RL; ++r2) {
       float v = tot[r2][tx];
-      if (r2 < rl) off += v;
-      total += v;
+      if (r2 < rl) off = OP::f(off, v);
+      total = OP::f(total, v);
     }
 #pragma unroll
     for (int r = 0; r < CS_RPT; ++r) {
       int64_t tt = t0 + rl * CS_RPT + r;
       int64_t tp = reverse ? (T - 1 - tt) : tt;
-      if (cvalid && tt < tend) st_f(o, tp * D + c, x[r] + off);
+      if (cvalid && tt < tend) st_f(o, tp * D + c, OP::f(off, x[r]));
     }
-    carry += total;
+    carry = OP::f(carry, total);
     __syncthreads();
   }
   if (TOTALS) {
     tot[rl][tx] = carry;
     __syncthreads();
     if (rl == 0 && cvalid) {
-      float total = 0.f;
+      float total = OP::id();
 #pragma unroll
-      for (int r2 = 0; r2 < CS_RL; ++r2) total += tot[r2][tx];
+      for (int r2 = 0; r2 < CS_RL; ++r2) total = OP::f(total, tot[r2][tx]);
       totals[(n * nseg + seg) * D + c] = total;
     }
   }
@@ -102,20 +123,33 @@ size_t cumsum_scratch_bytes(int64_t N, int64_t T, int64_t D) {
   return (size_t)N * cumsum_segments(N, T, D) * D * sizeof(float);
 }
 
+template <typename TI, typename TO, typename OP>
+static void cumsum_dispatch_op(cudaStream_t st, dim3 grid, dim3 block, const void* src, const void* sub,
+                               const void* init, void* dst, int64_t T, int64_t D, int reverse, int nseg,
+                               int64_t seg_len, float* totals) {
+  if (nseg > 1)
+    cumsum_kernel<TI, TO, true, OP><<<grid, block, 0, st>>>((const TI*)src, (const TI*)sub, (const TI*)init, (TO*)dst, T, D,
+                                                             reverse, nseg, seg_len, totals);
+  cumsum_kernel<TI, TO, false, OP><<<grid, block, 0, st>>>((const TI*)src, (const TI*)sub, (const TI*)init, (TO*)dst, T, D,
+                                                            reverse, nseg, seg_len, nseg > 1 ? totals : nullptr);
+}
 template <typename TI, typename TO>
 static void cumsum_dispatch(cudaStream_t st, dim3 grid, dim3 block, const void* src, const void* sub,
                             const void* init, void* dst, int64_t T, int64_t D, int reverse, int nseg,
-                            int64_t seg_len, float* totals) {
-  if (nseg > 1)
-    cumsum_kernel<TI, TO, true><<<grid, block, 0, st>>>((const TI*)src, (const TI*)sub, (const TI*)init, (TO*)dst, T, D,
-                                                         reverse, nseg, seg_len, totals);
-  cumsum_kernel<TI, TO, false><<<grid, block, 0, st>>>((const TI*)src, (const TI*)sub, (const TI*)init, (TO*)dst, T, D,
-                                                        reverse, nseg, seg_len, nseg > 1 ? totals : nullptr);
+                            int64_t seg_len, float* totals, int op = GLA_SCAN_ADD) {
+  switch (op) {
+    case GLA_SCAN_MUL: cumsum_dispatch_op<TI, TO, OpMul>(st, grid, block, src, sub, init, dst, T, D, reverse, nseg, seg_len, totals); break;
+    case GLA_SCAN_MAX: cumsum_dispatch_op<TI, TO, OpMax>(st, grid, block, src, sub, init, dst, T, D, reverse, nseg, seg_len, totals); break;
+    case GLA_SCAN_MIN: cumsum_dispatch_op<TI, TO, OpMin>(st, grid, block, src, sub, init, dst, T, D, reverse, nseg, seg_len, totals); break;
+    case GLA_SCAN_LOGADDEXP: cumsum_dispatch_op<TI, TO, OpLogAddExp>(st, grid, block, src, sub, init, dst, T, D, reverse, nseg, seg_len, totals); break;
+    default: cumsum_dispatch_op<TI, TO, OpAdd>(st, grid, block, src, sub, init, dst, T, D, reverse, nseg, seg_len, totals); break;
+  }
 }
 
 int launch_cumsum(cudaStream_t st, int64_t N, int64_t T, int64_t D, const void* src, const void* init,
-                  void* dst, int reverse, int in_bf16, int out_bf16, const void* sub, float* scratch) {
+                  void* dst, int reverse, int in_bf16, int out_bf16, const void* sub, float* scratch, int op) {
   if (N <= 0 || T <= 0 || D <= 0) return GLA_ERR_BAD_DIMS;
+  if (op < GLA_SCAN_ADD || op > GLA_SCAN_LOGADDEXP || (sub != nullptr && op != GLA_SCAN_ADD)) return GLA_ERR_UNSUPPORTED;
   int64_t gy = (D + 31) / 32;
   // without scratch for the segment sums the scan runs in one pass, one block per row and column group
   const int nseg = scratch ? cumsum_segments(N, T, D) : 1;
@@ -125,13 +159,13 @@ int launch_cumsum(cudaStream_t st, int64_t N, int64_t T, int64_t D, const void* 
   dim3 grid((unsigned)(N * nseg), (unsigned)gy), block(32, CS_RL);
   ProfScope ps("cumsum_kernel", st);
   if (!in_bf16 && !out_bf16)
-    cumsum_dispatch<float, float>(st, grid, block, src, sub, init, dst, T, D, reverse, nseg, seg_len, scratch);
+    cumsum_dispatch<float, float>(st, grid, block, src, sub, init, dst, T, D, reverse, nseg, seg_len, scratch, op);
   else if (!in_bf16 && out_bf16)
-    cumsum_dispatch<float, bf16>(st, grid, block, src, sub, init, dst, T, D, reverse, nseg, seg_len, scratch);
+    cumsum_dispatch<float, bf16>(st, grid, block, src, sub, init, dst, T, D, reverse, nseg, seg_len, scratch, op);
   else if (in_bf16 && !out_bf16)
-    cumsum_dispatch<bf16, float>(st, grid, block, src, sub, init, dst, T, D, reverse, nseg, seg_len, scratch);
+    cumsum_dispatch<bf16, float>(st, grid, block, src, sub, init, dst, T, D, reverse, nseg, seg_len, scratch, op);
   else
-    cumsum_dispatch<bf16, bf16>(st, grid, block, src, sub, init, dst, T, D, reverse, nseg, seg_len, scratch);
+    cumsum_dispatch<bf16, bf16>(st, grid, block, src, sub, init, dst, T, D, reverse, nseg, seg_len, scratch, op);
   GLA_CHECK_LAUNCH();
   return GLA_OK;
 }

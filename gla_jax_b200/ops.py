@@ -28,12 +28,16 @@ def _need_cuda(x):
         raise RuntimeError("gla_jax_b200 operators need CUDA tensors; there is no CPU fallback")
 
 
-def cumsum_pallas(src, axis: int, init: Optional[torch.Tensor] = None, reverse: bool = False,
-                  out_dtype=None, max_items: int = 16384, num_warps: int = 4):
-    """Inclusive cumulative sum along ``axis`` in float32 with ``init`` (shape = src.shape
-    without ``axis``) added to every element (reference: ops.py:166-230, kernel ops.py:152-162)."""
-    del max_items, num_warps
+SCAN_OPS = {"add": 0, "mul": 1, "max": 2, "min": 3, "logaddexp": 4}      # gla_scan_op of include/gla_b200.h
+
+
+def scan(op: str, src, axis: int, init: Optional[torch.Tensor] = None, reverse: bool = False, out_dtype=None):
+    """Inclusive associative scan of one array along ``axis`` under a named combine rule (``SCAN_OPS``), float32
+    math, with ``init`` (shape = src.shape without ``axis``) combined in front of every prefix: the generic scan of
+    the reference (ops.py:82-104) for the rules a precompiled library can offer."""
     _need_cuda(src)
+    if op not in SCAN_OPS:
+        raise NotImplementedError(f"scan: unknown combine rule {op!r}; available: {sorted(SCAN_OPS)}")
     lib = _lib.load()
     nd = src.dim()
     axis = axis if axis >= 0 else axis + nd
@@ -53,10 +57,18 @@ def cumsum_pallas(src, axis: int, init: Optional[torch.Tensor] = None, reverse: 
             raise ValueError(f"init must have shape {tuple(pre) + tuple(post)}, got {tuple(init.shape)}")  # ops.py:184
         init = init.to(src.dtype).contiguous()
     dst = torch.empty(src.shape, dtype=out_dtype, device=src.device)
-    st = lib.gla_cumsum(_stream(src.device), N, T, D, x.data_ptr(), None if init is None else init.data_ptr(),
-                        dst.data_ptr(), int(reverse), _DT[src.dtype], _DT[out_dtype])
-    _lib.check(st, "gla_cumsum")
+    st = lib.gla_scan(_stream(src.device), SCAN_OPS[op], N, T, D, x.data_ptr(), None if init is None else init.data_ptr(),
+                      dst.data_ptr(), int(reverse), _DT[src.dtype], _DT[out_dtype])
+    _lib.check(st, "gla_scan")
     return dst
+
+
+def cumsum_pallas(src, axis: int, init: Optional[torch.Tensor] = None, reverse: bool = False,
+                  out_dtype=None, max_items: int = 16384, num_warps: int = 4):
+    """Inclusive cumulative sum along ``axis`` in float32 with ``init`` (shape = src.shape
+    without ``axis``) added to every element (reference: ops.py:166-230, kernel ops.py:152-162)."""
+    del max_items, num_warps
+    return scan("add", src, axis, init=init, reverse=reverse, out_dtype=out_dtype)
 
 
 def cumsum_recursive(src, axis: int, init: Optional[torch.Tensor] = None, reverse: bool = False,
@@ -115,25 +127,35 @@ def rnn_recursive(log_fgate, kv, init_log_fgate: Optional[torch.Tensor] = None,
     return rnn_pallas(log_fgate, kv, init_log_fgate, init_kv, reverse=reverse)
 
 
+def _scan_rule(fn):
+    """Name of the library's combine rule for a Python callable (or the name itself), else None."""
+    import operator
+    table = {"add": (torch.add, operator.add), "mul": (torch.mul, operator.mul, torch.multiply),
+             "max": (torch.maximum, torch.max, max), "min": (torch.minimum, torch.min, min),
+             "logaddexp": (torch.logaddexp,)}
+    if isinstance(fn, str):
+        return fn if fn in SCAN_OPS else None
+    for name, fns in table.items():
+        if any(fn is f for f in fns):
+            return name
+    return None
+
+
 def triton_scan(fn, args, axis, init=None, reverse: bool = False):
     """Host-level counterpart of the reference's generic in-kernel scan (ops.py:82-104):
     ``out = scan(fn, args)`` along ``axis`` and then ``out = fn(init, out)`` if ``init`` is given.
 
-    The reference traces an arbitrary combine function into Triton; here the two combine rules the
-    reference itself uses are recognised and run on the CUDA scan kernels:
+    The reference traces an arbitrary combine function into Triton; a precompiled library offers named rules,
+    recognised here from the callable (or given as a string):
 
-    * addition (``torch.add``, ``operator.add``, or the string ``"add"``) on one array -> the cumsum kernel
-      (any ``axis``);
+    * on one array, any ``axis``: addition (``torch.add``, ``operator.add``, ``"add"``), multiplication (``"mul"``),
+      running maximum / minimum (``torch.maximum`` / ``torch.minimum``, ``"max"`` / ``"min"``) and
+      ``torch.logaddexp`` (``"logaddexp"``) -> the tiled scan kernel (``scan``);
     * ``binary_operator`` (or ``"linear_rnn"``) on a pair ``(log_fgate (..., T, K), kv (..., T, K, V))`` scanned
       along the T axis (``axis`` = 0 for unbatched arrays, 1 with a leading batch axis) -> the linear-RNN kernel,
       ``init`` being the pair ``(init_log_fgate (K), init_kv (K, V))``.
 
     Any other function raises ``NotImplementedError`` (there is no tracing compiler behind this library)."""
-    import operator
-    if fn in (torch.add, operator.add, "add"):
-        if isinstance(args, (tuple, list)):
-            raise ValueError("triton_scan(add): expected a single array")
-        return cumsum_pallas(args, axis, init=init, reverse=reverse)
     if fn is binary_operator or fn == "linear_rnn":
         log_fgate, kv = args
         t_axis = kv.dim() - 3
@@ -141,4 +163,10 @@ def triton_scan(fn, args, axis, init=None, reverse: bool = False):
             raise ValueError(f"triton_scan(binary_operator): the scan runs along the time axis ({t_axis})")
         ig, ikv = (None, None) if init is None else init
         return rnn_pallas(log_fgate, kv, ig, ikv, reverse=reverse)
-    raise NotImplementedError("triton_scan: only addition and binary_operator are available as CUDA scans")
+    rule = _scan_rule(fn)
+    if rule is not None:
+        if isinstance(args, (tuple, list)):
+            raise ValueError(f"triton_scan({rule}): expected a single array")
+        return scan(rule, args, axis, init=init, reverse=reverse)
+    raise NotImplementedError("triton_scan: the combine function is none of the library's rules "
+                              f"({sorted(SCAN_OPS)} on one array, binary_operator on a (log_fgate, kv) pair)")

@@ -182,6 +182,25 @@ GLA_API int gla_cumsum(void* stream, int64_t N, int64_t T, int64_t D,
                int reverse, int in_dtype, int out_dtype);
 
 /* ------------------------------------------------------------------------------------
+ * scan — the generic associative scan of ops.py:82 triton_scan for single-array operands, with the combine
+ * function chosen from a fixed set instead of traced from Python (the reference lowers an arbitrary function
+ * through Triton, ops.py:18-80; a precompiled library can only offer named rules):
+ *     dst[n, t, d] = init[n, d] (op) src[n, 0, d] (op) ... (op) src[n, t, d]      (init omitted when NULL)
+ * along the middle axis of src (N, T, D); reverse != 0 scans from the end.  Math is float32; any T.
+ * GLA_SCAN_ADD is gla_cumsum.  The two-array log-space rule of ops.py:286 is gla_rnn_scan.
+ * ---------------------------------------------------------------------------------- */
+typedef enum gla_scan_op {
+  GLA_SCAN_ADD = 0,
+  GLA_SCAN_MUL = 1,
+  GLA_SCAN_MAX = 2,
+  GLA_SCAN_MIN = 3,
+  GLA_SCAN_LOGADDEXP = 4      /* log(exp(a) + exp(b)) */
+} gla_scan_op;
+GLA_API int gla_scan(void* stream, int op, int64_t N, int64_t T, int64_t D,
+             const void* src, const void* init, void* dst,
+             int reverse, int in_dtype, int out_dtype);
+
+/* ------------------------------------------------------------------------------------
  * rnn_scan — replaces ops.py:396 rnn_recursive / ops.py:338 rnn_pallas / ops.py:299
  * rnn_kernel with ops.py:286 binary_operator.
  * For each of `batch` independent problems: inclusive scan over the leading axis of

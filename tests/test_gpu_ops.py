@@ -436,7 +436,39 @@ def test_triton_scan_dispatches_to_the_cuda_scans(cuda_device):
     ref_log, ref_state = O.rnn_scan(g.double(), kv.double(), ig.double(), ikv.double())
     assert O.rel_l2(ref_log.float(), out_log.cpu()) < 1e-5 and O.rel_l2(ref_state.float(), out_state.cpu()) < 1e-5
     with pytest.raises(NotImplementedError):
-        triton_scan(torch.maximum, x.to(cuda_device), axis=1)
+        triton_scan(torch.atan2, x.to(cuda_device), axis=1)
+
+
+@pytest.mark.parametrize("rule,ref_fn", [
+    ("mul", lambda x: torch.cumprod(x, 1)),
+    ("max", lambda x: torch.cummax(x, 1).values),
+    ("min", lambda x: torch.cummin(x, 1).values),
+    ("logaddexp", lambda x: torch.logcumsumexp(x, 1)),
+])
+def test_scan_library_rules(cuda_device, rule, ref_fn):
+    """The other combine rules of the scan library against torch's cumulative ops in float64: a length that spans
+    many tiles and is no multiple of the tile, forward and reversed, with and without an initial value, and through
+    triton_scan with the matching Python callable."""
+    from gla_jax_b200 import scan, triton_scan
+    gen = torch.Generator().manual_seed(67)
+    x = torch.randn(3, 1000, 40, generator=gen)
+    if rule == "mul":
+        x = 1.0 + 0.01 * x            # keep the running product in range
+    init = torch.randn(3, 40, generator=gen) if rule != "mul" else 1.0 + 0.1 * torch.randn(3, 40, generator=gen)
+    comb = {"mul": torch.mul, "max": torch.maximum, "min": torch.minimum, "logaddexp": torch.logaddexp}[rule]
+    xd = x.double()
+    for reverse in (False, True):
+        base = ref_fn(torch.flip(xd, [1]) if reverse else xd)
+        base = torch.flip(base, [1]) if reverse else base
+        got = scan(rule, x.to(cuda_device), 1, reverse=reverse)
+        assert O.rel_l2(base, got.cpu()) < 1e-5, (rule, reverse)
+        got_i = scan(rule, x.to(cuda_device), 1, init=init.to(cuda_device), reverse=reverse)
+        assert O.rel_l2(comb(init.double().unsqueeze(1), base), got_i.cpu()) < 1e-5, (rule, reverse, "init")
+    assert torch.equal(triton_scan(comb, x.to(cuda_device), axis=1), scan(rule, x.to(cuda_device), 1))
+    # the long-axis form (segments run as separate blocks) agrees with the one-pass form
+    y = torch.randn(1, 20000, 16, generator=gen) * (0.001 if rule == "mul" else 1.0) + (1.0 if rule == "mul" else 0.0)
+    ref = ref_fn(y.double())
+    assert O.rel_l2(ref, scan(rule, y.to(cuda_device), 1).cpu()) < 1e-5
 
 
 def test_early_start_gives_the_same_bits_under_graph_replay(cuda_device):
