@@ -1629,27 +1629,34 @@ __global__ void __launch_bounds__(256) tc_gsum_kernel(int64_t BH, int64_t N, con
 // The state recurrence is linear: with S0[n] the state entering chunk n when the slice starts from zero, the state
 // entering it when the slice starts from H_in is S0[n] + exp(sum_{m<n} G_m) (.) H_in (decay along the key axis;
 // ops.py:286-297 applied to the slice's prefix).  The gradient states mirror it with the chunks after n.
-// E[bh][n][d] = exp(sum of Gc over the chunks before n (reverse == 0) or after n (reverse != 0)).
-__global__ void __launch_bounds__(128) sp_cum_gate_kernel(int64_t BH, int64_t N, const float* __restrict__ Gc,
-                                                          float* __restrict__ E, int reverse) {
-  const int64_t e = (int64_t)blockIdx.x * 128 + threadIdx.x;
-  if (e >= BH * TD) return;
-  const int64_t bh = e / TD, dd = e % TD;
+// E[bh][n][d] = exp(sum of Gc over the chunks before n (reverse == 0) or after n (reverse != 0)); one block per
+// (batch, head), one thread per feature.  live[bh][n] = 1 while any feature's factor is non-zero: once the
+// accumulated log decay has underflowed for all 128 features, the incoming state contributes exactly nothing to
+// the chunk and the correction pass skips it (a long slice with ordinary gates needs its first few dozen chunks).
+__global__ void __launch_bounds__(TD) sp_cum_gate_kernel(int64_t N, const float* __restrict__ Gc, float* __restrict__ E,
+                                                         int* __restrict__ live, int reverse) {
+  const int64_t bh = blockIdx.x;
+  const int dd = threadIdx.x;
   float acc = 0.f;
   for (int64_t i = 0; i < N; ++i) {
     const int64_t n = reverse ? N - 1 - i : i;
-    E[(bh * N + n) * TD + dd] = __expf(acc);
+    const float w = __expf(acc);
+    E[(bh * N + n) * TD + dd] = w;
+    const int any = __syncthreads_or(w != 0.f);
+    if (dd == 0) live[bh * N + n] = any;
     acc += Gc[(bh * N + n) * TD + dd];
   }
 }
 // states[bh][n][dk][dv] += E[bh][n][dk] * Hin[bh][dk][dv]; one thread per 8 consecutive dv (16 bytes of bf16).
 __global__ void __launch_bounds__(256) sp_fix_states_kernel(int64_t BH, int64_t N, const float* __restrict__ E,
-                                                            const float* __restrict__ Hin, bf16* __restrict__ states) {
+                                                            const int* __restrict__ live, const float* __restrict__ Hin,
+                                                            bf16* __restrict__ states) {
   const int64_t e = (int64_t)blockIdx.x * 256 + threadIdx.x;
   if (e >= BH * N * TD * (TD / 8)) return;
   const int j = (int)(e % (TD / 8));
   const int dk = (int)((e / (TD / 8)) % TD);
   const int64_t bhn = e / (TD / 8) / TD, bh = bhn / N;
+  if (live[bhn] == 0) return;          // 8 blocks share a chunk-head: the whole block leaves together
   const float w = E[bhn * TD + dk];
   const float4* hp = reinterpret_cast<const float4*>(Hin + (bh * TD + dk) * TD + j * 8);
   const float4 h0 = __ldg(hp), h1 = __ldg(hp + 1);
@@ -1662,17 +1669,19 @@ __global__ void __launch_bounds__(256) sp_fix_states_kernel(int64_t BH, int64_t 
   u.w = pack_bf16x2(fmaf(w, h1.z, d2.x), fmaf(w, h1.w, d2.y));
   *sp = u;
 }
+// E: BH * N * 128 floats followed by BH * N ints (the live flags); both fit the float32 product area of the workspace.
 static int launch_sp_fix(cudaStream_t st, int64_t BH, int64_t N, const float* Gc, float* E, const float* Hin, bf16* states,
                          int reverse) {
+  int* live = reinterpret_cast<int*>(E + BH * N * TD);
   {
     ProfScope ps("sp_cum_gate_kernel", st);
-    sp_cum_gate_kernel<<<(unsigned)((BH * TD + 127) / 128), 128, 0, st>>>(BH, N, Gc, E, reverse);
+    sp_cum_gate_kernel<<<(unsigned)BH, TD, 0, st>>>(N, Gc, E, live, reverse);
     GLA_CHECK_LAUNCH();
   }
   const int64_t n = BH * N * TD * (TD / 8);
   if ((n + 255) / 256 > 2147483647LL) return GLA_ERR_TOO_LARGE;
   ProfScope ps("sp_fix_states_kernel", st);
-  sp_fix_states_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(BH, N, E, Hin, states);
+  sp_fix_states_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(BH, N, E, live, Hin, states);
   GLA_CHECK_LAUNCH();
   return GLA_OK;
 }

@@ -171,10 +171,85 @@ int launch_cumsum(cudaStream_t st, int64_t N, int64_t T, int64_t D, const void* 
 }
 
 // ---------------------------------------------------------------------------------------
-// rnn_scan: one thread per (k, v) element of the state, v fastest (coalesced), sequential
-// over T.  exp() of the gate is recomputed per element: the kernel is bound by the kv
-// stream (4 or 2 bytes in, the same out, per element and step).
+// rnn_scan: sequential over T, parallel over the elements of the state.  A thread owns FOUR consecutive value
+// columns of one key row (one 16- or 8-byte access per step instead of four scalar ones, and one exp() of the
+// gate per step for the four), and keeps the loads of the next UNR steps in flight while it combines the
+// current ones: the recurrence is a chain, so what the kernel can overlap is the memory latency of later steps.
+// The scalar form below serves value widths that are not multiples of four.
 // ---------------------------------------------------------------------------------------
+__device__ __forceinline__ float4 ld4_f(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
+__device__ __forceinline__ float4 ld4_f(const bf16* p) {
+  const uint2 u = __ldg(reinterpret_cast<const uint2*>(p));
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x), b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+  const float2 fa = __bfloat1622float2(a), fb = __bfloat1622float2(b);
+  return make_float4(fa.x, fa.y, fb.x, fb.y);
+}
+__device__ __forceinline__ void st4_f(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void st4_f(bf16* p, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 u;
+  u.x = *reinterpret_cast<uint32_t*>(&a); u.y = *reinterpret_cast<uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+
+template <typename TKV>
+__global__ void __launch_bounds__(128) rnn_scan_vec4_kernel(int64_t T, int64_t K, int64_t V, int64_t nblk,
+                                                            const float* __restrict__ g, const TKV* __restrict__ kv,
+                                                            const float* __restrict__ ig, const TKV* __restrict__ ikv,
+                                                            float* __restrict__ out_log, TKV* __restrict__ out_state,
+                                                            int reverse, int last_only) {
+  constexpr int UNR = 4;
+  const int64_t prob = blockIdx.x / nblk;
+  const int64_t e4 = (blockIdx.x % nblk) * 128 + threadIdx.x;      // group of four value columns
+  const int64_t KV = K * V, V4 = V / 4;
+  if (e4 >= K * V4) return;
+  const int64_t kk = e4 / V4, e = e4 * 4;
+  const bool writes_log = (e4 % V4) == 0;
+  float A = ig ? ig[prob * K + kk] : 0.f;
+  float4 b = ikv ? ld4_f(ikv + prob * KV + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+  const float* gp = g + prob * T * K + kk;
+  const TKV* xp = kv + prob * T * KV + e;
+  TKV* op = out_state + prob * T * KV + e;
+  float* lp = out_log + prob * T * K + kk;
+  auto tix = [&](int64_t s) { return reverse ? (T - 1 - s) : s; };
+  float gn[UNR];
+  float4 xn[UNR];
+#pragma unroll
+  for (int u = 0; u < UNR; ++u) {
+    const int64_t t = tix(u < T ? u : T - 1);
+    gn[u] = gp[t * K];
+    xn[u] = ld4_f(xp + t * KV);
+  }
+  for (int64_t s0 = 0; s0 < T; s0 += UNR) {
+    float gc[UNR];
+    float4 xc[UNR];
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) { gc[u] = gn[u]; xc[u] = xn[u]; }
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {           // the next group's loads, issued before this group is combined
+      const int64_t sn = s0 + UNR + u;
+      const int64_t t = tix(sn < T ? sn : T - 1);
+      gn[u] = gp[t * K];
+      xn[u] = ld4_f(xp + t * KV);
+    }
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      const int64_t sc = s0 + u;
+      if (sc < T) {
+        const float f = expf(gc[u]);
+        b.x = fmaf(f, b.x, xc[u].x); b.y = fmaf(f, b.y, xc[u].y);
+        b.z = fmaf(f, b.z, xc[u].z); b.w = fmaf(f, b.w, xc[u].w);
+        A += gc[u];
+        if (!last_only || sc == T - 1) {
+          const int64_t t = tix(sc);
+          st4_f(op + t * KV, b);
+          if (writes_log) lp[t * K] = A;
+        }
+      }
+    }
+  }
+}
+
 template <typename TKV>
 __global__ void __launch_bounds__(256) rnn_scan_kernel(int64_t T, int64_t K, int64_t V, int64_t nblk,
                                                        const float* __restrict__ g, const TKV* __restrict__ kv,
@@ -208,10 +283,24 @@ __global__ void __launch_bounds__(256) rnn_scan_kernel(int64_t T, int64_t K, int
 int launch_rnn_scan(cudaStream_t st, int64_t batch, int64_t T, int64_t K, int64_t V, const float* g,
                     const void* kv, const float* ig, const void* ikv, float* out_log, void* out_state,
                     int reverse, int last_only, int kv_bf16) {
+  ProfScope ps("rnn_scan_kernel", st);
+  const bool al = (((uintptr_t)kv | (uintptr_t)out_state | (uintptr_t)ikv) & 15) == 0;
+  if (V % 4 == 0 && al) {
+    int64_t nblk = (K * (V / 4) + 127) / 128;
+    if (nblk * batch > 2147483647LL) return GLA_ERR_TOO_LARGE;
+    dim3 grid((unsigned)(nblk * batch)), block(128);
+    if (kv_bf16)
+      rnn_scan_vec4_kernel<bf16><<<grid, block, 0, st>>>(T, K, V, nblk, g, (const bf16*)kv, ig, (const bf16*)ikv,
+                                                         out_log, (bf16*)out_state, reverse, last_only);
+    else
+      rnn_scan_vec4_kernel<float><<<grid, block, 0, st>>>(T, K, V, nblk, g, (const float*)kv, ig, (const float*)ikv,
+                                                          out_log, (float*)out_state, reverse, last_only);
+    GLA_CHECK_LAUNCH();
+    return GLA_OK;
+  }
   int64_t nblk = (K * V + 255) / 256;
   if (nblk * batch > 2147483647LL) return GLA_ERR_TOO_LARGE;
   dim3 grid((unsigned)(nblk * batch)), block(256);
-  ProfScope ps("rnn_scan_kernel", st);
   if (kv_bf16)
     rnn_scan_kernel<bf16><<<grid, block, 0, st>>>(T, K, V, nblk, g, (const bf16*)kv, ig, (const bf16*)ikv,
                                                   out_log, (bf16*)out_state, reverse, last_only);

@@ -1,5 +1,6 @@
 """GPU tests of sequence parallelism: the schedule of gla_jax_b200/parallel.py on the CUDA
-primitives (gla_chunk_local_state, gla_chunk_local_dstate, gla_sp_combine, chunk fwd/bwd).
+primitives (gla_chunk_sp_{fwd,bwd}_{local,finish} where the shape has them, else gla_chunk_local_state /
+gla_chunk_local_dstate with the ordinary forward / backward; gla_sp_combine in both cases).
 On one GPU the ranks run one after another in one process (no kernel waits on another rank,
 the gathers are host-side stacks); with two or more GPUs a real NCCL run is added."""
 import os
@@ -14,15 +15,19 @@ pytestmark = pytest.mark.gpu
 NAMES = ("dhidden_init", "dlog_fgate", "dvalue", "dkey", "dquery")
 
 
-@pytest.mark.parametrize("dtype,D,C,R,impl", [
-    (torch.bfloat16, 128, 128, 4, "auto"),      # tensor-core kernels, 4 ranks x 256 tokens
-    (torch.float32, 64, 32, 2, "fp32"),
+@pytest.mark.parametrize("dtype,D,C,R,impl,T,shift", [
+    (torch.bfloat16, 128, 128, 4, "auto", 1024, 2.0),      # tensor-core kernels, 4 ranks x 256 tokens
+    (torch.bfloat16, 128, 128, 2, "auto+two_kernels", 1024, 2.0),   # ... with the product + scan form of the states
+    # sharp gates and 8 chunks per rank: the accumulated decay underflows after the first chunk or two, so the
+    # correction of the kept states skips the rest (and every chunk takes all levels of the secondary chunking)
+    (torch.bfloat16, 128, 128, 2, "auto", 2048, 0.0),
+    (torch.float32, 64, 32, 2, "fp32", 1024, 2.0),
 ])
-def test_emulated_sequence_parallel_on_one_gpu(cuda_device, dtype, D, C, R, impl):
+def test_emulated_sequence_parallel_on_one_gpu(cuda_device, dtype, D, C, R, impl, T, shift):
     from gla_jax_b200 import parallel as P
     from gla_jax_b200 import chunk_gla
-    B, T, H = 1, 1024, 2
-    h, g, v, k, q = O.make_inputs(B, T, H, D, dtype, seed=5, shift=2.0)
+    B, H = 1, 2
+    h, g, v, k, q = O.make_inputs(B, T, H, D, dtype, seed=5, shift=shift)
     gen = torch.Generator().manual_seed(6)
     dhf = torch.randn(B, H, D, D, generator=gen).to(dtype)
     do = torch.randn(B, T, H, D, generator=gen).to(dtype)
