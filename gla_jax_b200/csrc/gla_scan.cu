@@ -60,15 +60,24 @@ __global__ void __launch_bounds__(256) cumsum_kernel(const TI* __restrict__ src,
   TO* o = dst + n * T * D;
   const int64_t tbeg = (int64_t)seg * seg_len;
   const int64_t tend = tbeg + seg_len < T ? tbeg + seg_len : T;
-  for (int64_t t0 = tbeg; t0 < tend; t0 += CS_RPT * CS_RL) {
-    float x[CS_RPT];
+  // The loads of the NEXT tile are issued before the current one is combined: a block walks its rows in order, so
+  // without this every tile would wait out a full memory latency with nothing in flight.
+  auto fetch = [&](int64_t t0, float (&y)[CS_RPT]) {
 #pragma unroll
     for (int r = 0; r < CS_RPT; ++r) {
       int64_t tt = t0 + rl * CS_RPT + r;
       int64_t tp = reverse ? (T - 1 - tt) : tt;
-      x[r] = (cvalid && tt < tend) ? ld_f(s, tp * D + c) : OP::id();
-      if (s2 && cvalid && tt < tend) x[r] -= ld_f(s2, tp * D + c);
+      y[r] = (cvalid && tt < tend) ? ld_f(s, tp * D + c) : OP::id();
+      if (s2 && cvalid && tt < tend) y[r] -= ld_f(s2, tp * D + c);
     }
+  };
+  float xn[CS_RPT];
+  fetch(tbeg, xn);
+  for (int64_t t0 = tbeg; t0 < tend; t0 += CS_RPT * CS_RL) {
+    float x[CS_RPT];
+#pragma unroll
+    for (int r = 0; r < CS_RPT; ++r) x[r] = xn[r];
+    if (t0 + CS_RPT * CS_RL < tend) fetch(t0 + CS_RPT * CS_RL, xn);
 #pragma unroll
     for (int r = 1; r < CS_RPT; ++r) x[r] = OP::f(x[r - 1], x[r]);
     if (TOTALS) {
