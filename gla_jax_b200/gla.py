@@ -257,11 +257,18 @@ def chunk_gla_packed(hidden_init, log_fgate, value, key, query, cu_seqlens, chun
     """``chunk_gla`` for variable-length sequences packed end to end on one time axis.
 
     ``value/key/query/log_fgate`` are (T, H, D) holding ``nseq`` sequences back to back; ``cu_seqlens`` holds the
-    ``nseq + 1`` token offsets (0 first, T last, every offset a multiple of 128; a list or CPU tensor is validated,
-    a CUDA int32 tensor is used as is without a host round trip); ``hidden_init`` is
-    (nseq, H, D, D).  Returns ``(hidden_final (nseq, H, D, D), out (T, H, D))``, equal to calling ``chunk_gla`` on
-    each sequence; differentiable.  The reference has one length per call (gla.py:499-500, 674); this runs on the
-    tensor-core kernels only (bf16, D = 128)."""
+    ``nseq + 1`` token offsets (0 first, T last); ``hidden_init`` is (nseq, H, D, D).  Returns
+    ``(hidden_final (nseq, H, D, D), out (T, H, D))``, equal to calling ``chunk_gla`` on each sequence;
+    differentiable.  The reference has one length per call and asserts T % chunk == 0 (gla.py:499-500, 674); this
+    runs on the tensor-core kernels only (bf16, D = 128).
+
+    Offsets given as a list or CPU tensor may be ANY rising sequence: the kernels work on chunks of 128 rows that
+    must not straddle two sequences, so sequences whose lengths are not multiples of 128 are first laid out with
+    their tails padded to the next multiple (padding tokens have log_fgate = 0 and key = value = query = 0: no decay,
+    no update, so states and gradients are those of the unpadded sequence) and the outputs are gathered back; the
+    two copies are differentiable torch index operations.  Offsets given as a CUDA int32 tensor are used as they
+    are, without a host round trip, and must be multiples of 128 (the kernels clamp anything else and count it in
+    ``gla_device_bad_offsets``)."""
     if value.dim() != 3 or hidden_init.dim() != 4:
         raise ValueError("chunk_gla_packed: expected value (T, H, D) and hidden_init (nseq, H, D, D)")
     T, H, D = value.shape
@@ -269,17 +276,30 @@ def chunk_gla_packed(hidden_init, log_fgate, value, key, query, cu_seqlens, chun
     nseq = cu.numel() - 1
     if nseq < 1 or tuple(hidden_init.shape) != (nseq, H, D, D):
         raise ValueError("chunk_gla_packed: cu_seqlens must have nseq + 1 entries for hidden_init (nseq, H, D, D)")
-    if not cu.is_cuda:
-        # offsets given on the host are checked here; a CUDA tensor is taken as is (checking it would synchronise)
-        if int(cu[0]) != 0 or int(cu[-1]) != T or bool(((cu[1:] - cu[:-1]) <= 0).any()) or bool((cu % 128 != 0).any()):
-            raise ValueError("chunk_gla_packed: cu_seqlens must rise from 0 to T in multiples of 128")
     if key.shape != value.shape or query.shape != value.shape or log_fgate.shape != value.shape:
         raise ValueError("chunk_gla_packed: log_fgate, value, key, query must all be (T, H, D)")
     if not value.is_cuda:
         raise TypeError("chunk_gla_packed: CUDA tensors required (there is no CPU path)")
+    idx = None
+    if not cu.is_cuda:
+        # offsets given on the host are checked here; a CUDA tensor is taken as is (checking it would synchronise)
+        if int(cu[0]) != 0 or int(cu[-1]) != T or bool(((cu[1:] - cu[:-1]) <= 0).any()):
+            raise ValueError("chunk_gla_packed: cu_seqlens must rise from 0 to T")
+        if bool((cu % 128 != 0).any()):
+            # ragged lengths: positions of the tokens on a time axis where every sequence starts at a multiple of 128
+            lens = (cu[1:] - cu[:-1]).to(torch.int64)
+            plen = (lens + 127) // 128 * 128
+            pcu = torch.zeros(nseq + 1, dtype=torch.int64)
+            pcu[1:] = torch.cumsum(plen, 0)
+            idx = torch.cat([torch.arange(int(lens[s_]), dtype=torch.int64) + int(pcu[s_]) for s_ in range(nseq)]).to(value.device)
+            Tp = int(pcu[-1])
+            pad = lambda x: x.new_zeros((Tp,) + tuple(x.shape[1:])).index_copy(0, idx, x)
+            log_fgate, value, key, query = pad(log_fgate), pad(value), pad(key), pad(query)
+            cu = pcu.to(torch.int32)
     cu = cu.to(value.device).contiguous()
-    return _ChunkGLAPacked.apply(hidden_init.contiguous(), log_fgate.contiguous(), value.contiguous(), key.contiguous(),
-                                 query.contiguous(), cu, int(chunk_size))
+    hf, out = _ChunkGLAPacked.apply(hidden_init.contiguous(), log_fgate.contiguous(), value.contiguous(), key.contiguous(),
+                                    query.contiguous(), cu, int(chunk_size))
+    return (hf, out) if idx is None else (hf, out.index_select(0, idx))
 
 
 def decode_step(state, log_fgate, value, key, query, out_dtype=None):

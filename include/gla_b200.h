@@ -8,7 +8,12 @@
  * Conventions (all entry points)
  *   - plain pointers and sizes only; every pointer is a DEVICE pointer unless stated;
  *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream); all
- *     work is enqueued on it, nothing synchronises, nothing allocates, no global state;
+ *     work is enqueued on it, on the CURRENT device; nothing synchronises and nothing allocates
+ *     device memory.  What the library keeps between calls: on the host, a per-thread cache of
+ *     TMA descriptors keyed by address and shape (a few KB), one "attribute set" bit per kernel
+ *     and device, the launch counter and the optional per-thread kernel timer below; on each
+ *     device, two error counters (gla_device_wait_timeouts, gla_device_bad_offsets) and the fixed
+ *     scratch array of gla_chunk_fwd_static.  No call's result depends on any of it;
  *   - the caller owns every buffer, including the workspace whose size the matching
  *     *_workspace_bytes() function reports;
  *   - arrays are dense row-major with the reference's axis order and an optional leading
@@ -23,7 +28,9 @@
  *     Dimension and alignment problems are reported before anything is launched (the
  *     reference raises Python asserts at trace time instead: gla.py:120-127, 499-500,
  *     975-977; ops.py:195-207, 348-364).
- *   - every function is thread-safe and reentrant (stream-ordered, no shared host state).
+ *   - every function is thread-safe and reentrant: the cached state above is per thread or
+ *     idempotent, and work is ordered by the stream the caller passes (the one exception, the shared
+ *     scratch of gla_chunk_fwd_static, is documented there).
  */
 #ifndef GLA_B200_H_
 #define GLA_B200_H_

@@ -413,9 +413,38 @@ def test_chunk_gla_packed_rejects_bad_offsets(cuda_device):
     x = torch.zeros(256, H, D, device=cuda_device, dtype=torch.bfloat16)
     g = torch.zeros(256, H, D, device=cuda_device)
     h = torch.zeros(2, H, D, D, device=cuda_device, dtype=torch.bfloat16)
-    for cu in ([0, 100, 256], [0, 128, 384], [128, 256, 256], [0, 256]):
+    for cu in ([0, 128, 384], [128, 256, 256], [0, 256], [0, 200, 100, 256]):
         with pytest.raises(ValueError):
             chunk_gla_packed(h, g, x, x, x, cu)
+
+
+def test_chunk_gla_packed_ragged_lengths_vs_oracle(cuda_device):
+    """Sequence lengths that are no multiples of the chunk length (the reference asserts T % chunk == 0,
+    gla.py:499-500): tails are padded with neutral tokens inside the operator.  Forward and all five gradients of
+    every sequence against the float64 oracle on the unpadded sequence."""
+    from gla_jax_b200 import chunk_gla_packed
+    lengths, H, D = [100, 257, 128, 31], 2, 128
+    T, nseq = sum(lengths), len(lengths)
+    cu = [0]
+    for L in lengths:
+        cu.append(cu[-1] + L)
+    _, g, v, k, q = O.make_inputs(1, T, H, D, torch.bfloat16, seed=81, shift=3.0)
+    gen = torch.Generator().manual_seed(82)
+    h = torch.randn(nseq, H, D, D, generator=gen).to(torch.bfloat16)
+    dhf = torch.randn(nseq, H, D, D, generator=gen).to(torch.bfloat16)
+    do = torch.randn(T, H, D, generator=gen).to(torch.bfloat16)
+    dev = cuda_device
+    leaves = [x.to(dev).requires_grad_(True) for x in (h, g[0], v[0], k[0], q[0])]
+    hf, out = chunk_gla_packed(*leaves, cu, chunk_size=128)
+    assert tuple(out.shape) == (T, H, D)
+    grads = torch.autograd.grad((hf.float() * dhf.to(dev).float()).sum() + (out.float() * do.to(dev).float()).sum(), leaves)
+    torch.cuda.synchronize()
+    for s_ in range(nseq):
+        sl = slice(cu[s_], cu[s_ + 1])
+        case = (h[s_:s_ + 1], g[:, sl], v[:, sl], k[:, sl], q[:, sl], dhf[s_:s_ + 1], do[sl].unsqueeze(0))
+        got = (hf[s_:s_ + 1].cpu(), out[sl].unsqueeze(0).cpu(),
+               [grads[0][s_:s_ + 1].cpu()] + [grads[i][sl].unsqueeze(0).cpu() for i in range(1, 5)])
+        _compare(_oracle(*case), got, torch.bfloat16, f"ragged packed sequence {s_} (length {lengths[s_]})")
 
 
 def test_triton_scan_dispatches_to_the_cuda_scans(cuda_device):
