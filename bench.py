@@ -515,6 +515,11 @@ def bench_scans(args, lib, dev, rank, world, local_rank, W, K):
         y = torch.empty_like(x)
         run("cumsum_kernel", lambda: _lib.check(lib.gla_cumsum(stream, N, T, D, x.data_ptr(), None, y.data_ptr(), 0, 0, 0), "gla_cumsum"),
             2 * 4 * N * T * D, f"cumsum (N={N}, T={T}, D={D}) float32: 4 B in + 4 B out per element")
+        N2, T2, D2 = 512, 128, 768                   # the chunk path's layout: (batch x chunks, chunk, heads x D)
+        x2 = x.view(N2, T2, D2)
+        y2 = y.view(N2, T2, D2)
+        run("cumsum_kernel_chunk_layout", lambda: _lib.check(lib.gla_cumsum(stream, N2, T2, D2, x2.data_ptr(), None, y2.data_ptr(), 0, 0, 0), "gla_cumsum"),
+            2 * 4 * N2 * T2 * D2, f"cumsum (N={N2}, T={T2}, D={D2}) float32: 4 B in + 4 B out per element")
     if args.op in ("rnn_scan", "scans"):
         batch, T, Kf, V = 24, 64, 128, 128           # 24 heads x 64 chunks of (128,128) float32 states: 100 MB in, 100 MB out
         g = -torch.rand(batch, T, Kf, device=dev) * 0.1

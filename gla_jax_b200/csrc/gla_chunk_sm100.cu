@@ -346,7 +346,7 @@ __device__ __noinline__ bool fwd_load_state_late(const unsigned int* state_done,
 __global__ void __launch_bounds__(TTHREADS, 1)
 tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, int R, int64_t N, bf16* __restrict__ out,
                     bf16* __restrict__ P_saved, const unsigned int* __restrict__ state_done, unsigned int state_target,
-                    int all_scales) {
+                    int all_scales, int pf_dist) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = align1024(smem_raw);
   float* tot = reinterpret_cast<float*>(sm + FwdSmem::TOT);
@@ -402,6 +402,22 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, 
     for (int half = 0; half < 2; ++half) {
       tma_load_3d(smem_u32(sm + FwdSmem::V + half * TILE_BYTES), &maps.v, 64 * half, yv, z, lb2);
       if (!s_pending) tma_load_2d(smem_u32(sm + FwdSmem::S + half * TILE_BYTES), &maps.s, 64 * half, (int)(chunk_id * TD), lb2);
+    }
+    // The same boxes of the block that the scheduler starts on this SM when this one retires (pf_dist blocks
+    // ahead), requested into L2 only: seven instructions of this one thread, so that the next block's load phase
+    // is served from L2.
+    const int64_t nb = (int64_t)blockIdx.x + pf_dist;
+    if (pf_dist > 0 && nb < (int64_t)gridDim.x) {
+      const int64_t n2 = N - 1 - nb / BHn, bh2 = nb % BHn, h2 = bh2 % H;
+      const int y2 = (int)((h2 / (R * R)) * R + (h2 % (R * R)) / R), yv2 = (int)((h2 / (R * R)) * R + h2 % R);
+      const int z2 = (int)((bh2 / H) * T + n2 * TC);
+      tma_prefetch_l2_3d(&maps.g, 0, y2, z2);
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        tma_prefetch_l2_3d(&maps.q, 64 * half, y2, z2);
+        tma_prefetch_l2_3d(&maps.k, 64 * half, y2, z2);
+        tma_prefetch_l2_3d(&maps.v, 64 * half, yv2, z2);
+      }
     }
   }
   if (warp == 1) {
@@ -902,7 +918,6 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
   const int64_t n = (int64_t)blockIdx.x / BHn, bh = (int64_t)blockIdx.x % BHn, b = bh / H, h_ = bh % H;
   const int64_t hk_ = (h_ / (R * R)) * R + (h_ % (R * R)) / R, hv_ = (h_ / (R * R)) * R + h_ % R;
   const int64_t HD = H * TD;                                          // output row pitch (virtual heads)
-  const int64_t HDi = (H / R) * TD;                                   // input row pitch
   const int64_t row0 = ((b * T + n * TC) * H + h_) * TD;              // outputs
   const int64_t chunk_id = bh * N + n;
 
@@ -1062,24 +1077,27 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
   // This chunk's operands have landed: ask L2 for those of the chunk that the block scheduler will
   // start on this SM when this block retires (pf_dist blocks ahead), so that its load phase streams
   // from L2 while DRAM is busy during everybody's compute phases instead of everybody's load phases.
+  // One thread requests the same boxes the next block will load (tensor prefetches: one instruction per
+  // box, where per-line prefetches cost every thread three instructions and measured 1 us slower).
   {
     const int64_t nb = (int64_t)blockIdx.x + pf_dist;
-    if (pf_dist > 0 && nb < (int64_t)gridDim.x) {
+    if (pf_dist > 0 && nb < (int64_t)gridDim.x && tid == 0) {
       const int64_t n2 = nb / BHn, bh2 = nb % BHn, h2 = bh2 % H;
-      const int64_t hk2 = (h2 / (R * R)) * R + (h2 % (R * R)) / R, hv2 = (h2 / (R * R)) * R + h2 % R;
-      const int64_t t2 = ((bh2 / H) * T + n2 * TC) * (H / R);
-      const int64_t r2k = (t2 + hk2) * TD, r2v = (t2 + hv2) * TD;
+      const int y2 = (int)((h2 / (R * R)) * R + (h2 % (R * R)) / R), yv2 = (int)((h2 / (R * R)) * R + h2 % R);
+      const int z2 = (int)((bh2 / H) * T + n2 * TC);
       const int64_t c2 = (bh2 * N + n2) * TD * TD;
-      // strided rows: one 128-byte line per request (256-byte rows of dO, v, k, q; 512-byte rows of g).  Bulk
-      // prefetches of whole rows were measured and are slower to issue than these.
-      const int64_t eo = (int64_t)((tid >> 1) & (TC - 1)) * HDi + (tid & 1) * 64;
-      l2_prefetch_line(tid < 256 ? dO + r2v + eo : v + r2v + eo);
-      l2_prefetch_line(tid < 256 ? k + r2k + eo : q + r2k + eo);
-      l2_prefetch_line(g + r2k + (int64_t)(tid >> 2) * HDi + (tid & 3) * 32);
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        tma_prefetch_l2_3d(&maps.g, 0, y2, z2 + 64 * half);
+        tma_prefetch_l2_3d(&maps.q, 0, y2, z2 + 64 * half);
+        tma_prefetch_l2_3d(&maps.k, 0, y2, z2 + 64 * half);
+        tma_prefetch_l2_3d(&maps.dO, 64 * half, yv2, z2);
+        tma_prefetch_l2_3d(&maps.v, 64 * half, yv2, z2);
+      }
       // contiguous 32 KB tiles: one bulk request each
-      if (tid == 0) l2_prefetch_bulk(S_prev + c2, 2 * TD * TD);
-      else if (tid == 32) l2_prefetch_bulk(dS_next + c2, 2 * TD * TD);
-      else if (tid == 64) l2_prefetch_bulk(P_saved + (bh2 * N + n2) * TC * TC, 2 * TC * TC);
+      l2_prefetch_bulk(S_prev + c2, 2 * TD * TD);
+      l2_prefetch_bulk(dS_next + c2, 2 * TD * TD);
+      l2_prefetch_bulk(P_saved + (bh2 * N + n2) * TC * TC, 2 * TC * TC);
     }
   }
   ok = mbar_wait(smem_u32(bars + 0), 0) && ok;
@@ -1719,24 +1737,43 @@ __global__ void __launch_bounds__(256) state_block_kernel(const bf16* __restrict
 }
 // Per-virtual-head results (rows, H R R, 128) summed into (rows, H, 128 R): key-side arrays (dq, dk, dg) keep the
 // key block a and sum over the value blocks c; value-side arrays (out, dv) keep c and sum over a.  Float32 sums.
+// Eight consecutive features of one array as floats, through 16-byte accesses.
+__device__ __forceinline__ void ld8_f32(const bf16* p, float (&x)[8]) {
+  const uint4 u = __ldg(reinterpret_cast<const uint4*>(p));
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 f = unpack_bf16x2(w[i]); x[2 * i] = f.x; x[2 * i + 1] = f.y; }
+}
+__device__ __forceinline__ void ld8_f32(const float* p, float (&x)[8]) {
+  const float4 a = __ldg(reinterpret_cast<const float4*>(p)), b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+  x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+}
+__device__ __forceinline__ void st8_f32(bf16* p, const float (&x)[8]) {
+  uint4 u;
+  u.x = pack_bf16x2(x[0], x[1]); u.y = pack_bf16x2(x[2], x[3]); u.z = pack_bf16x2(x[4], x[5]); u.w = pack_bf16x2(x[6], x[7]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+__device__ __forceinline__ void st8_f32(float* p, const float (&x)[8]) {
+  reinterpret_cast<float4*>(p)[0] = make_float4(x[0], x[1], x[2], x[3]);
+  reinterpret_cast<float4*>(p)[1] = make_float4(x[4], x[5], x[6], x[7]);
+}
 template <typename T, int KEYSIDE>
 __global__ void __launch_bounds__(256) sum_blocks_kernel(const T* __restrict__ in, T* __restrict__ out, int64_t rows,
                                                          int64_t H, int R) {
-  const int64_t e = (int64_t)blockIdx.x * 256 + threadIdx.x;      // four consecutive features
-  if (e >= rows * H * R * (TD / 4)) return;
-  const int j = (int)(e % (TD / 4));
-  const int keep = (int)((e / (TD / 4)) % R);
-  const int64_t h = (e / (TD / 4) / R) % H, row = e / (TD / 4) / R / H;
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  const int64_t e = (int64_t)blockIdx.x * 256 + threadIdx.x;      // eight consecutive features
+  if (e >= rows * H * R * (TD / 8)) return;
+  const int j = (int)(e % (TD / 8));
+  const int keep = (int)((e / (TD / 8)) % R);
+  const int64_t h = (e / (TD / 8) / R) % H, row = e / (TD / 8) / R / H;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   for (int s2 = 0; s2 < R; ++s2) {
     const int a = KEYSIDE ? keep : s2, c = KEYSIDE ? s2 : keep;
-    const T* p = in + ((row * H * R * R + (h * R + a) * R + c) * (int64_t)TD + j * 4);
+    float x[8];
+    ld8_f32(in + ((row * H * R * R + (h * R + a) * R + c) * (int64_t)TD + j * 8), x);
 #pragma unroll
-    for (int u = 0; u < 4; ++u) acc[u] += (float)p[u];
+    for (int u = 0; u < 8; ++u) acc[u] += x[u];
   }
-  T* o = out + ((row * H + h) * (int64_t)(TD * R) + keep * TD + j * 4);
-#pragma unroll
-  for (int u = 0; u < 4; ++u) o[u] = (T)acc[u];
+  st8_f32(out + ((row * H + h) * (int64_t)(TD * R) + keep * TD + j * 8), acc);
 }
 static int launch_state_block(cudaStream_t st, const void* in, void* out, int64_t BH, int R, int to_blocked) {
   const int64_t n = BH * R * R * TD * (TD / 8);
@@ -1747,7 +1784,7 @@ static int launch_state_block(cudaStream_t st, const void* in, void* out, int64_
 }
 template <typename T, int KEYSIDE>
 static int launch_sum_blocks(cudaStream_t st, const T* in, T* out, int64_t rows, int64_t H, int R) {
-  const int64_t n = rows * H * R * (TD / 4);
+  const int64_t n = rows * H * R * (TD / 8);
   ProfScope ps("sum_blocks_kernel", st);
   sum_blocks_kernel<T, KEYSIDE><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(in, out, rows, H, R);
   GLA_CHECK_LAUNCH();
@@ -1860,6 +1897,7 @@ int tc_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
   {
     ProfScope ps("tc_chunk_fwd_kernel", st);
     bf16* out_p = R > 1 ? out_v : (bf16*)out;
+    const int pf_dist = (opts & GLA_OPT_NO_L2_PREFETCH) ? 0 : prefetch_distance(1);
     if (early_flag != nullptr) {
       // programmatic dependent of the state kernel launched just before: may start while that one runs
       cudaLaunchConfig_t cfg = {};
@@ -1873,10 +1911,10 @@ int tc_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
       cfg.attrs = attr;
       cfg.numAttrs = 1;
       e = cudaLaunchKernelEx(&cfg, tc_chunk_fwd_kernel, maps, T, HV, R, N, out_p, P, (const unsigned int*)early_flag,
-                             early_target, all_scales);
+                             early_target, all_scales, pf_dist);
       if (e != cudaSuccess) return record_cuda_error(e);
     } else {
-      tc_chunk_fwd_kernel<<<(unsigned)(BHV * N), TTHREADS, FWD_SMEM, st>>>(maps, T, HV, R, N, out_p, P, nullptr, 0u, all_scales);
+      tc_chunk_fwd_kernel<<<(unsigned)(BHV * N), TTHREADS, FWD_SMEM, st>>>(maps, T, HV, R, N, out_p, P, nullptr, 0u, all_scales, pf_dist);
     }
   }
   GLA_CHECK_LAUNCH();

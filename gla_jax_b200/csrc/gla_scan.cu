@@ -116,11 +116,129 @@ __global__ void __launch_bounds__(256) cumsum_kernel(const TI* __restrict__ src,
   }
 }
 
+__device__ __forceinline__ float4 ld4_f(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
+__device__ __forceinline__ float4 ld4_f(const bf16* p) {
+  const uint2 u = __ldg(reinterpret_cast<const uint2*>(p));
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x), b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+  const float2 fa = __bfloat1622float2(a), fb = __bfloat1622float2(b);
+  return make_float4(fa.x, fa.y, fb.x, fb.y);
+}
+__device__ __forceinline__ void st4_f(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void st4_f(bf16* p, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 u;
+  u.x = *reinterpret_cast<uint32_t*>(&a); u.y = *reinterpret_cast<uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+
+
+// The same scan with FOUR consecutive columns per thread (16-byte accesses: a warp reads 512 contiguous bytes of a
+// row) and 16 row lanes: a block covers 128 columns and walks the axis in tiles of 128 rows, 64 KB of float32 per
+// tile with the next tile's loads already in flight.  Rows this wide keep the memory system busy from few blocks,
+// which is what a long scan axis with few rows offers.  Serves D % 4 == 0 with suitably aligned pointers.
+constexpr int C4_RL = 16;    // row lanes
+template <typename OP> __device__ __forceinline__ float4 op4(float4 a, float4 b) {
+  return make_float4(OP::f(a.x, b.x), OP::f(a.y, b.y), OP::f(a.z, b.z), OP::f(a.w, b.w));
+}
+template <typename TI, typename TO, bool TOTALS, typename OP>
+__global__ void __launch_bounds__(32 * C4_RL) cumsum_v4_kernel(const TI* __restrict__ src, const TI* __restrict__ sub,
+                                                               const TI* __restrict__ init, TO* __restrict__ dst,
+                                                               int64_t T, int64_t D, int reverse, int nseg,
+                                                               int64_t seg_len, float* __restrict__ totals) {
+  // both arrays are double-buffered by tile parity, which is what lets a tile get by with ONE block barrier: a
+  // buffer is rewritten two tiles later, after a barrier that every reader of it has passed
+  __shared__ float4 tot[2][C4_RL][32];
+  __shared__ float4 car[2][32];
+  const int64_t n = blockIdx.x / nseg;
+  const int seg = (int)(blockIdx.x % nseg);
+  const int tx = threadIdx.x, rl = threadIdx.y;
+  const int64_t c = ((int64_t)blockIdx.y * 32 + tx) * 4;
+  const bool cvalid = c < D;
+  const float4 ident = make_float4(OP::id(), OP::id(), OP::id(), OP::id());
+  float4 carry = (!TOTALS && init != nullptr && cvalid) ? ld4_f(init + n * D + c) : ident;
+  if (!TOTALS && totals != nullptr && cvalid)
+    for (int s2 = 0; s2 < seg; ++s2)
+      carry = op4<OP>(carry, *reinterpret_cast<const float4*>(totals + (n * nseg + s2) * D + c));
+  const int64_t tbeg = (int64_t)seg * seg_len;
+  const int64_t tend = tbeg + seg_len < T ? tbeg + seg_len : T;
+  // a thread's rows of a tile are `rs` elements apart (backwards in memory for a reversed scan) and its first row
+  // moves by a whole tile per iteration: no multiplication and no 64-bit compare inside the loop
+  const int64_t rs = reverse ? -D : D;
+  const int64_t row0 = tbeg + rl * CS_RPT;
+  const int64_t off0 = n * T * D + c + (reverse ? (T - 1 - row0) : row0) * D;
+  const TI* ps = src + off0;
+  const TI* ps2 = sub ? sub + off0 : nullptr;
+  TO* po = dst + off0;
+  const int64_t step = (int64_t)CS_RPT * C4_RL * rs;
+  // rows of this thread that lie inside the segment, for the tile being fetched / stored (<= 0: none)
+  auto rows_in = [&](int64_t t0) -> int {
+    const int64_t left = tend - (t0 + rl * CS_RPT);
+    return !cvalid ? 0 : left >= CS_RPT ? CS_RPT : left < 0 ? 0 : (int)left;
+  };
+  auto fetch = [&](int nr, float4 (&y)[CS_RPT]) {
+#pragma unroll
+    for (int r = 0; r < CS_RPT; ++r) {
+      y[r] = r < nr ? ld4_f(ps + r * rs) : ident;
+      if (ps2 && r < nr) {
+        const float4 z = ld4_f(ps2 + r * rs);
+        y[r].x -= z.x; y[r].y -= z.y; y[r].z -= z.z; y[r].w -= z.w;
+      }
+    }
+    ps += step;
+    if (ps2) ps2 += step;
+  };
+  float4 xn[CS_RPT];
+  fetch(rows_in(tbeg), xn);
+  if (!TOTALS) {
+    if (rl == C4_RL - 1) car[0][tx] = carry;
+  }
+  int par = 0;
+  for (int64_t t0 = tbeg; t0 < tend; t0 += CS_RPT * C4_RL, par ^= 1) {
+    float4 x[CS_RPT];
+#pragma unroll
+    for (int r = 0; r < CS_RPT; ++r) x[r] = xn[r];
+    const int nr = rows_in(t0);
+    if (t0 + CS_RPT * C4_RL < tend) fetch(rows_in(t0 + CS_RPT * C4_RL), xn);
+#pragma unroll
+    for (int r = 1; r < CS_RPT; ++r) x[r] = op4<OP>(x[r - 1], x[r]);
+    if (TOTALS) {
+      carry = op4<OP>(carry, x[CS_RPT - 1]);    // commutative rules only, as in the scalar form
+      continue;
+    }
+    tot[par][rl][tx] = x[CS_RPT - 1];
+    __syncthreads();
+    // the carry into this tile (left by the last row lane at the end of the tile before) combined with the row
+    // lanes before this one: the trip count is the same for the whole warp
+    float4 off = car[par][tx];
+    for (int r2 = 0; r2 < rl; ++r2) off = op4<OP>(off, tot[par][r2][tx]);
+    if (rl == C4_RL - 1) car[par ^ 1][tx] = op4<OP>(off, x[CS_RPT - 1]);
+#pragma unroll
+    for (int r = 0; r < CS_RPT; ++r)
+      if (r < nr) st4_f(po + r * rs, op4<OP>(off, x[r]));
+    po += step;
+  }
+  if (TOTALS) {
+    tot[0][rl][tx] = carry;
+    __syncthreads();
+    if (rl == 0 && cvalid) {
+      float4 total = ident;
+#pragma unroll
+      for (int r2 = 0; r2 < C4_RL; ++r2) total = op4<OP>(total, tot[0][r2][tx]);
+      *reinterpret_cast<float4*>(totals + (n * nseg + seg) * D + c) = total;
+    }
+  }
+}
+
+// Column width of a block: the four-columns-per-thread kernel serves rows of at least 128 columns that are a
+// multiple of four (and, checked at launch, 16-byte aligned pointers); the scalar kernel everything else.
+static bool cumsum_wide(int64_t D) { return D >= 128 && D % 4 == 0; }
+
 // Segments for a scan of N rows of length T: enough blocks to fill the device when N alone
 // gives too few, but never segments shorter than 256 positions.
 static int cumsum_segments(int64_t N, int64_t T, int64_t D) {
-  const int64_t blocks = N * ((D + 31) / 32);
-  const int64_t want = (4 * 148 + blocks - 1) / blocks;
+  const int64_t blocks = cumsum_wide(D) ? N * ((D + 127) / 128) : N * ((D + 31) / 32);
+  const int64_t target = cumsum_wide(D) ? 2 * 148 : 4 * 148;
+  const int64_t want = (target + blocks - 1) / blocks;
   int64_t nseg = want < 1 ? 1 : want;
   if (nseg > T / 256) nseg = T / 256;
   if (nseg < 1) nseg = 1;
@@ -136,6 +254,14 @@ template <typename TI, typename TO, typename OP>
 static void cumsum_dispatch_op(cudaStream_t st, dim3 grid, dim3 block, const void* src, const void* sub,
                                const void* init, void* dst, int64_t T, int64_t D, int reverse, int nseg,
                                int64_t seg_len, float* totals) {
+  if (block.y == C4_RL) {
+    if (nseg > 1)
+      cumsum_v4_kernel<TI, TO, true, OP><<<grid, block, 0, st>>>((const TI*)src, (const TI*)sub, (const TI*)init, (TO*)dst, T,
+                                                                  D, reverse, nseg, seg_len, totals);
+    cumsum_v4_kernel<TI, TO, false, OP><<<grid, block, 0, st>>>((const TI*)src, (const TI*)sub, (const TI*)init, (TO*)dst, T,
+                                                                 D, reverse, nseg, seg_len, nseg > 1 ? totals : nullptr);
+    return;
+  }
   if (nseg > 1)
     cumsum_kernel<TI, TO, true, OP><<<grid, block, 0, st>>>((const TI*)src, (const TI*)sub, (const TI*)init, (TO*)dst, T, D,
                                                              reverse, nseg, seg_len, totals);
@@ -159,13 +285,20 @@ int launch_cumsum(cudaStream_t st, int64_t N, int64_t T, int64_t D, const void* 
                   void* dst, int reverse, int in_bf16, int out_bf16, const void* sub, float* scratch, int op) {
   if (N <= 0 || T <= 0 || D <= 0) return GLA_ERR_BAD_DIMS;
   if (op < GLA_SCAN_ADD || op > GLA_SCAN_LOGADDEXP || (sub != nullptr && op != GLA_SCAN_ADD)) return GLA_ERR_UNSUPPORTED;
-  int64_t gy = (D + 31) / 32;
+  // 16-byte accesses need every row start on that boundary in each array: D % 4 == 0 makes the row pitch a
+  // multiple of 16 bytes (8 for bf16), so the base pointers decide
+  auto aligned = [](const void* p, int is_bf16) { return p == nullptr || ((uintptr_t)p % (is_bf16 ? 8 : 16)) == 0; };
+  const bool wide = cumsum_wide(D) && aligned(src, in_bf16) && aligned(sub, in_bf16) && aligned(init, in_bf16) &&
+                    aligned(dst, out_bf16) && aligned(scratch, 0);
+  const int64_t gy = wide ? (D + 127) / 128 : (D + 31) / 32;
   // without scratch for the segment sums the scan runs in one pass, one block per row and column group
   const int nseg = scratch ? cumsum_segments(N, T, D) : 1;
+  const int64_t tile = CS_RPT * C4_RL;      // rows of the wide kernel's tile, a multiple of the scalar kernel's
+  static_assert((CS_RPT * C4_RL) % (CS_RPT * CS_RL) == 0, "segment lengths must be whole tiles of both kernels");
   int64_t seg_len = (T + nseg - 1) / nseg;
-  seg_len = (seg_len + CS_RPT * CS_RL - 1) / (CS_RPT * CS_RL) * (CS_RPT * CS_RL);
+  seg_len = (seg_len + tile - 1) / tile * tile;
   if (gy > 65535 || N * nseg > 2147483647LL) return GLA_ERR_TOO_LARGE;
-  dim3 grid((unsigned)(N * nseg), (unsigned)gy), block(32, CS_RL);
+  dim3 grid((unsigned)(N * nseg), (unsigned)gy), block(32, wide ? C4_RL : CS_RL);
   ProfScope ps("cumsum_kernel", st);
   if (!in_bf16 && !out_bf16)
     cumsum_dispatch<float, float>(st, grid, block, src, sub, init, dst, T, D, reverse, nseg, seg_len, scratch, op);
@@ -186,21 +319,6 @@ int launch_cumsum(cudaStream_t st, int64_t N, int64_t T, int64_t D, const void* 
 // current ones: the recurrence is a chain, so what the kernel can overlap is the memory latency of later steps.
 // The scalar form below serves value widths that are not multiples of four.
 // ---------------------------------------------------------------------------------------
-__device__ __forceinline__ float4 ld4_f(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
-__device__ __forceinline__ float4 ld4_f(const bf16* p) {
-  const uint2 u = __ldg(reinterpret_cast<const uint2*>(p));
-  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x), b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
-  const float2 fa = __bfloat1622float2(a), fb = __bfloat1622float2(b);
-  return make_float4(fa.x, fa.y, fb.x, fb.y);
-}
-__device__ __forceinline__ void st4_f(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
-__device__ __forceinline__ void st4_f(bf16* p, float4 v) {
-  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
-  uint2 u;
-  u.x = *reinterpret_cast<uint32_t*>(&a); u.y = *reinterpret_cast<uint32_t*>(&b);
-  *reinterpret_cast<uint2*>(p) = u;
-}
-
 template <typename TKV>
 __global__ void __launch_bounds__(128) rnn_scan_vec4_kernel(int64_t T, int64_t K, int64_t V, int64_t nblk,
                                                             const float* __restrict__ g, const TKV* __restrict__ kv,

@@ -72,11 +72,6 @@ __device__ __forceinline__ void l2_prefetch_bulk(const void* p, uint32_t bytes) 
   asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
 
-// One 128-byte line into L2 (an ordinary load-store-unit request, no data returned).
-__device__ __forceinline__ void l2_prefetch_line(const void* p) {
-  asm volatile("prefetch.global.L2 [%0];" ::"l"(p) : "memory");
-}
-
 // ---- MMA issue / completion -------------------------------------------------------------
 // D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread.
 __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
@@ -136,6 +131,11 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const void* tmap,
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       :: "r"(smem_dst), "l"((uint64_t)tmap), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+// The same box as tma_load_3d would copy, requested into L2 only (no shared-memory destination, no barrier).
+__device__ __forceinline__ void tma_prefetch_l2_3d(const void* tmap, int x, int y, int z) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];"
+               :: "l"((uint64_t)tmap), "r"(x), "r"(y), "r"(z) : "memory");
 }
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" :: "l"((uint64_t)tmap) : "memory");

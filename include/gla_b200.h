@@ -86,7 +86,7 @@ typedef enum gla_chunk_impl {
  *       chunk whose total |log decay| is at most 60 for every feature uses a single anchor, because all its decay
  *       weights then lie within exp(+-60); sharper chunks take all levels.  The choice is made per chunk on the
  *       device from the gates themselves.
- *   NO_L2_PREFETCH   no L2 prefetch of the next chunk's operands in the backward chunk kernel. */
+ *   NO_L2_PREFETCH   no L2 prefetch of the next chunk's operands in the chunk kernels. */
 typedef enum gla_chunk_option {
   GLA_OPT_STATE_TWO_KERNELS = 0x100,
   GLA_OPT_STATE_ONE_PASS = 0x200,

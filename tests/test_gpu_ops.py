@@ -264,6 +264,10 @@ def test_golden_fixtures_on_gpu(cuda_device):
 @pytest.mark.parametrize("N,T,D,reverse,with_init,dtype", [
     (3, 50, 7, False, True, torch.float32), (2, 4096, 96, True, True, torch.float32),
     (1, 1, 33, False, False, torch.float32), (4, 300, 64, True, False, torch.bfloat16),
+    # rows of 128 columns and more take the four-columns-per-thread kernel: whole and partial column blocks,
+    # lengths that are no multiple of its 128-row tile, both directions, both element types
+    (2, 1000, 128, False, True, torch.float32), (3, 333, 160, True, True, torch.float32),
+    (2, 515, 256, True, True, torch.bfloat16), (1, 128, 768, False, False, torch.bfloat16),
 ])
 def test_cumsum_vs_oracle(cuda_device, N, T, D, reverse, with_init, dtype):
     from gla_jax_b200 import cumsum_recursive, cumsum_pallas
@@ -279,6 +283,22 @@ def test_cumsum_vs_oracle(cuda_device, N, T, D, reverse, with_init, dtype):
     y2 = cumsum_pallas(x.to(dev), axis=-2, init=None if init is None else init.to(dev), reverse=reverse,
                        out_dtype=torch.float32)
     assert y2.dtype == torch.float32 and O.rel_l2(ref, y2.cpu()) < (1e-5 if dtype == torch.float32 else 1e-2)
+
+
+def test_cumsum_wide_rows_from_an_unaligned_base(cuda_device):
+    """Rows of 128+ columns whose base address is not 16-byte aligned fall back to the scalar kernel: same result
+    as the aligned call (which takes the four-columns-per-thread kernel), bit for bit in float32 addition order
+    per column."""
+    from gla_jax_b200 import cumsum_recursive
+    gen = torch.Generator().manual_seed(11)
+    x = torch.randn(2, 700, 128, generator=gen)
+    buf = torch.empty(x.numel() + 1, device=cuda_device)
+    xu = buf[1:].view(2, 700, 128)
+    xu.copy_(x)
+    assert xu.data_ptr() % 16 != 0 and xu.is_contiguous()
+    ya, yu = cumsum_recursive(x.to(cuda_device), axis=1), cumsum_recursive(xu, axis=1)
+    assert O.rel_l2(torch.cumsum(x.double(), 1), ya.cpu()) < 1e-5
+    assert O.rel_l2(ya.cpu().double(), yu.cpu()) < 1e-6
 
 
 def test_cumsum_inner_axis_layout(cuda_device):
@@ -498,6 +518,9 @@ def test_scan_library_rules(cuda_device, rule, ref_fn):
     y = torch.randn(1, 20000, 16, generator=gen) * (0.001 if rule == "mul" else 1.0) + (1.0 if rule == "mul" else 0.0)
     ref = ref_fn(y.double())
     assert O.rel_l2(ref, scan(rule, y.to(cuda_device), 1).cpu()) < 1e-5
+    # rows wide enough for the four-columns-per-thread kernel
+    w = torch.randn(2, 300, 256, generator=gen) * (0.01 if rule == "mul" else 1.0) + (1.0 if rule == "mul" else 0.0)
+    assert O.rel_l2(ref_fn(w.double()), scan(rule, w.to(cuda_device), 1).cpu()) < 1e-5
 
 
 def test_early_start_gives_the_same_bits_under_graph_replay(cuda_device):
