@@ -17,7 +17,7 @@ IMPL_AUTO, IMPL_FP32_SIMT, IMPL_TCGEN05 = 0, 1, 2
 _FAMILY = {"auto": IMPL_AUTO, "fp32": IMPL_FP32_SIMT, "simt": IMPL_FP32_SIMT, "tcgen05": IMPL_TCGEN05}
 # gla_chunk_option bits of include/gla_b200.h, by the names accepted after a "+" in an impl string
 OPTIONS = {"two_kernels": 0x100, "one_pass": 0x200, "no_early_start": 0x400, "all_scales": 0x800,
-           "no_l2_prefetch": 0x1000}
+           "no_l2_prefetch": 0x1000, "segments": 0x2000}
 
 
 class _ImplNames(dict):

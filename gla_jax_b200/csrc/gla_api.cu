@@ -50,7 +50,7 @@ static int check_chunk_dims(int64_t B, int64_t T, int64_t H, int64_t D, int64_t 
 // Resolve GLA_IMPL_AUTO; returns a negative status (as -status) if the request is invalid.  The option bits
 // above the low byte are passed on to the tensor-core path as they are.
 constexpr int OPT_BITS = GLA_OPT_STATE_TWO_KERNELS | GLA_OPT_STATE_ONE_PASS | GLA_OPT_NO_EARLY_START | GLA_OPT_ALL_SCALES |
-                         GLA_OPT_NO_L2_PREFETCH;
+                         GLA_OPT_NO_L2_PREFETCH | GLA_OPT_STATE_SEGMENTS;
 static int resolve_impl(int impl_and_opts, int64_t D, int64_t C, int dtype) {
   if (impl_and_opts < 0 || (impl_and_opts & ~(0xff | OPT_BITS)) != 0) return -GLA_ERR_UNSUPPORTED;
   const int impl = impl_and_opts & 0xff;

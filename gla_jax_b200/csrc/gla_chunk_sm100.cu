@@ -1643,40 +1643,47 @@ __global__ void __launch_bounds__(256) tc_gsum_kernel(int64_t BH, int64_t N, con
   Gt[e] = s;
 }
 
-// ---- sequence parallelism: chunk states computed from a zero state, corrected once the true one is known --------
-// The state recurrence is linear: with S0[n] the state entering chunk n when the slice starts from zero, the state
-// entering it when the slice starts from H_in is S0[n] + exp(sum_{m<n} G_m) (.) H_in (decay along the key axis;
-// ops.py:286-297 applied to the slice's prefix).  The gradient states mirror it with the chunks after n.
-// E[bh][n][d] = exp(sum of Gc over the chunks before n (reverse == 0) or after n (reverse != 0)); one block per
-// (batch, head), one thread per feature.  live[bh][n] = 1 while any feature's factor is non-zero: once the
-// accumulated log decay has underflowed for all 128 features, the incoming state contributes exactly nothing to
-// the chunk and the correction pass skips it (a long slice with ordinary gates needs its first few dozen chunks).
-__global__ void __launch_bounds__(TD) sp_cum_gate_kernel(int64_t N, const float* __restrict__ Gc, float* __restrict__ E,
-                                                         int* __restrict__ live, int reverse) {
-  const int64_t bh = blockIdx.x;
+// ---- chunk states computed from a zero state, corrected once the true incoming state is known -------------------
+// The state recurrence is linear: with S0[n] the state entering chunk n when a run of chunks starts from zero, the
+// state entering it when the run starts from H_in is S0[n] + exp(sum_{m<n} G_m) (.) H_in (decay along the key axis;
+// ops.py:286-297 applied to the run's prefix).  The gradient states mirror it with the chunks after n.  Two callers:
+// sequence parallelism (the run is a rank's slice, H_in arrives from the other ranks) and the segmented one-pass
+// state kernel (the runs are `nsegs` pieces of every head's chunks, `Ns` chunks each, H_in of a run follows from
+// the runs before it).  nsegs = 1, Ns = N is the single-run form.
+//
+// E[bh][n][d] = exp(sum of Gc over the chunks of n's run before n (reverse == 0) or after n (reverse != 0)); one
+// block per (batch, head, run), one thread per feature.  live[bh][n] = 1 while any feature's factor is non-zero: once
+// the accumulated log decay has underflowed for all 128 features, the incoming state contributes exactly nothing to
+// the chunk and the correction pass skips it (a long run with ordinary gates needs its first few dozen chunks).
+__global__ void __launch_bounds__(TD) sp_cum_gate_kernel(int64_t N, int nsegs, int64_t Ns, const float* __restrict__ Gc,
+                                                         float* __restrict__ E, int* __restrict__ live,
+                                                         float* __restrict__ Gs, int reverse) {
+  const int64_t bh = blockIdx.x / nsegs, n0 = (blockIdx.x % nsegs) * Ns, n1 = n0 + Ns < N ? n0 + Ns : N;
   const int dd = threadIdx.x;
   float acc = 0.f;
-  for (int64_t i = 0; i < N; ++i) {
-    const int64_t n = reverse ? N - 1 - i : i;
+  for (int64_t i = 0; i < n1 - n0; ++i) {
+    const int64_t n = reverse ? n1 - 1 - i : n0 + i;
     const float w = __expf(acc);
     E[(bh * N + n) * TD + dd] = w;
     const int any = __syncthreads_or(w != 0.f);
     if (dd == 0) live[bh * N + n] = any;
     acc += Gc[(bh * N + n) * TD + dd];
   }
+  if (Gs != nullptr) Gs[(int64_t)blockIdx.x * TD + dd] = acc;       // the run's total log decay, (bh, run, feature)
 }
-// states[bh][n][dk][dv] += E[bh][n][dk] * Hin[bh][dk][dv]; one thread per 8 consecutive dv (16 bytes of bf16).
-__global__ void __launch_bounds__(256) sp_fix_states_kernel(int64_t BH, int64_t N, const float* __restrict__ E,
-                                                            const int* __restrict__ live, const float* __restrict__ Hin,
-                                                            bf16* __restrict__ states) {
+// states[bh][n][dk][dv] += E[bh][n][dk] * Hin[bh][run of n][dk][dv]; one thread per 8 consecutive dv (16 bytes of
+// bf16).  skip_seg: a run whose incoming correction is known to be zero (it started from the true state), or -1.
+__global__ void __launch_bounds__(256) sp_fix_states_kernel(int64_t BH, int64_t N, int nsegs, int64_t Ns, int skip_seg,
+                                                            const float* __restrict__ E, const int* __restrict__ live,
+                                                            const float* __restrict__ Hin, bf16* __restrict__ states) {
   const int64_t e = (int64_t)blockIdx.x * 256 + threadIdx.x;
   if (e >= BH * N * TD * (TD / 8)) return;
   const int j = (int)(e % (TD / 8));
   const int dk = (int)((e / (TD / 8)) % TD);
-  const int64_t bhn = e / (TD / 8) / TD, bh = bhn / N;
-  if (live[bhn] == 0) return;          // 8 blocks share a chunk-head: the whole block leaves together
+  const int64_t bhn = e / (TD / 8) / TD, bh = bhn / N, seg = (bhn % N) / Ns;
+  if (live[bhn] == 0 || seg == skip_seg) return;          // 8 blocks share a chunk-head: the whole block leaves together
   const float w = E[bhn * TD + dk];
-  const float4* hp = reinterpret_cast<const float4*>(Hin + (bh * TD + dk) * TD + j * 8);
+  const float4* hp = reinterpret_cast<const float4*>(Hin + ((bh * nsegs + seg) * TD + dk) * TD + j * 8);
   const float4 h0 = __ldg(hp), h1 = __ldg(hp + 1);
   uint4* sp = reinterpret_cast<uint4*>(states + (bhn * TD + dk) * TD + j * 8);
   uint4 u = *sp;
@@ -1687,19 +1694,96 @@ __global__ void __launch_bounds__(256) sp_fix_states_kernel(int64_t BH, int64_t 
   u.w = pack_bf16x2(fmaf(w, h1.z, d2.x), fmaf(w, h1.w, d2.y));
   *sp = u;
 }
-// E: BH * N * 128 floats followed by BH * N ints (the live flags); both fit the float32 product area of the workspace.
-static int launch_sp_fix(cudaStream_t st, int64_t BH, int64_t N, const float* Gc, float* E, const float* Hin, bf16* states,
-                         int reverse) {
-  int* live = reinterpret_cast<int*>(E + BH * N * TD);
-  {
-    ProfScope ps("sp_cum_gate_kernel", st);
-    sp_cum_gate_kernel<<<(unsigned)BH, TD, 0, st>>>(N, Gc, E, live, reverse);
-    GLA_CHECK_LAUNCH();
+// The scan over the runs of one head, in walk order (time order, or its reverse for the gradient states):
+//   Cin[first run] = init32 (or 0),  Cin[next run] = F[run] + exp(sum of the run's Gc) (.) Cin[run],
+// F[run] being the run's final state computed from its own start and Cin[run] the correction its stored states
+// need, i.e. the part of the true incoming state that its start did not contain.  What leaves the last run is the
+// final state of the whole walk (fin32 float32 and / or fin16 bf16).  One thread per four consecutive dv.
+__global__ void __launch_bounds__(256) seg_scan_kernel(int64_t BH, int nsegs, const float* __restrict__ Gs,
+                                                       const float* __restrict__ F, const float* __restrict__ init32,
+                                                       float* __restrict__ Cin, bf16* __restrict__ fin16,
+                                                       float* __restrict__ fin32, int reverse) {
+  const int64_t e = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (e >= BH * TD * (TD / 4)) return;
+  const int j = (int)(e % (TD / 4));
+  const int dk = (int)((e / (TD / 4)) % TD);
+  const int64_t bh = e / (TD / 4) / TD;
+  const int64_t el = (bh * TD + dk) * TD + j * 4;
+  float4 c = init32 ? *reinterpret_cast<const float4*>(init32 + el) : make_float4(0.f, 0.f, 0.f, 0.f);
+  // the chain is only the multiply-add: the loads of the runs ahead do not depend on it and are kept in flight
+  constexpr int AHEAD = 4;
+  float4 f[AHEAD];
+  float gs[AHEAD];
+  auto run_of = [&](int w) { return (int64_t)(reverse ? nsegs - 1 - w : w); };
+#pragma unroll
+  for (int a = 0; a < AHEAD; ++a)
+    if (a < nsegs) {
+      f[a] = __ldg(reinterpret_cast<const float4*>(F + ((bh * nsegs + run_of(a)) * TD + dk) * TD + j * 4));
+      gs[a] = __ldg(Gs + (bh * nsegs + run_of(a)) * TD + dk);
+    }
+  for (int w0 = 0; w0 < nsegs; w0 += AHEAD) {
+#pragma unroll
+    for (int a = 0; a < AHEAD; ++a) {
+      const int w = w0 + a;
+      if (w < nsegs) {
+        const float4 fw = f[a];
+        const float dec = __expf(gs[a]);
+        if (w + AHEAD < nsegs) {
+          f[a] = __ldg(reinterpret_cast<const float4*>(F + ((bh * nsegs + run_of(w + AHEAD)) * TD + dk) * TD + j * 4));
+          gs[a] = __ldg(Gs + (bh * nsegs + run_of(w + AHEAD)) * TD + dk);
+        }
+        *reinterpret_cast<float4*>(Cin + ((bh * nsegs + run_of(w)) * TD + dk) * TD + j * 4) = c;
+        c = make_float4(fmaf(dec, c.x, fw.x), fmaf(dec, c.y, fw.y), fmaf(dec, c.z, fw.z), fmaf(dec, c.w, fw.w));
+      }
+    }
   }
+  if (fin32) *reinterpret_cast<float4*>(fin32 + el) = c;
+  if (fin16) {
+    uint2 u;
+    u.x = pack_bf16x2(c.x, c.y); u.y = pack_bf16x2(c.z, c.w);
+    *reinterpret_cast<uint2*>(fin16 + el) = u;
+  }
+}
+// Scratch of a correction, carved from the float32 product area of the workspace (BH * N * 128 * 128 floats, unused
+// whenever the one-pass state kernel runs): with runs, F and Cin, BH * nsegs * 128 * 128 floats each (nsegs <= N / 4,
+// so they take at most half of the area); then E, BH * N * 128 floats, the runs' total log decays Gs, BH * nsegs * 128
+// floats, and the live flags, BH * N ints.
+struct FixScratch {
+  float *F, *Cin, *E, *Gs;
+  int* live;
+  FixScratch(float* area, int64_t BH, int64_t N, int nsegs) {
+    const int64_t per = nsegs > 1 ? BH * nsegs * TD * TD : 0;
+    F = area;
+    Cin = F + per;
+    E = Cin + per;
+    Gs = E + BH * N * TD;
+    live = reinterpret_cast<int*>(Gs + (nsegs > 1 ? BH * nsegs * TD : 0));
+  }
+};
+// E, live and the runs' totals Gs from the chunks' log decays (they depend on nothing else).
+static int launch_cum_gate(cudaStream_t st, int64_t BH, int64_t N, int nsegs, const float* Gc, const FixScratch& fx, int reverse) {
+  const int64_t Ns = (N + nsegs - 1) / nsegs;
+  ProfScope ps("sp_cum_gate_kernel", st);
+  sp_cum_gate_kernel<<<(unsigned)(BH * nsegs), TD, 0, st>>>(N, nsegs, Ns, Gc, fx.E, fx.live, nsegs > 1 ? fx.Gs : nullptr, reverse);
+  GLA_CHECK_LAUNCH();
+  return GLA_OK;
+}
+static int launch_seg_scan(cudaStream_t st, int64_t BH, int nsegs, const FixScratch& fx, const float* init32, void* fin16,
+                           float* fin32, int reverse) {
+  const int64_t n = BH * TD * (TD / 4);
+  ProfScope ps("seg_scan_kernel", st);
+  seg_scan_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(BH, nsegs, fx.Gs, fx.F, init32, fx.Cin, (bf16*)fin16, fin32, reverse);
+  GLA_CHECK_LAUNCH();
+  return GLA_OK;
+}
+// Hin: (BH, nsegs, 128, 128) float32, the correction entering every run; E and live from launch_cum_gate.
+static int launch_fix_states(cudaStream_t st, int64_t BH, int64_t N, int nsegs, int skip_seg, const FixScratch& fx,
+                             const float* Hin, bf16* states) {
+  const int64_t Ns = (N + nsegs - 1) / nsegs;
   const int64_t n = BH * N * TD * (TD / 8);
   if ((n + 255) / 256 > 2147483647LL) return GLA_ERR_TOO_LARGE;
   ProfScope ps("sp_fix_states_kernel", st);
-  sp_fix_states_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(BH, N, E, live, Hin, states);
+  sp_fix_states_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(BH, N, nsegs, Ns, skip_seg, fx.E, fx.live, Hin, states);
   GLA_CHECK_LAUNCH();
   return GLA_OK;
 }
@@ -1852,8 +1936,17 @@ int tc_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
     init_v = hib; fin_v = hfb;
   }
   const bool fused_states = !state_only && (R > 1 || cu != nullptr || tc_state_fused_preferred(BHV, N, opts));
+  // runs of chunks walked by separate blocks and corrected afterwards (plain head size, dense batches)
+  const int nsegs = (fused_states && R == 1 && cu == nullptr) ? tc_state_segments(BHV, N, opts) : 1;
+  const FixScratch fx(kv, BHV, N, nsegs);
   if (sp_phase == 1) {
-    if (fused_states) {
+    if (nsegs > 1) {
+      // every run from zero; the scan over the runs gives the slice's final state (its corrections are recomputed
+      // in the finish phase, which knows the state entering the slice; the runs' final states stay in the workspace)
+      GLA_TRY(tc_state_fused(st, 0, B, T, HV, R, g, k, v, nullptr, S_prev, nullptr, Gc, 0, nullptr, nullptr, nullptr, fx.F, nsegs));
+      GLA_TRY(launch_cum_gate(st, BHV, N, nsegs, Gc, fx, 0));          // stays in the workspace for the finish phase
+      GLA_TRY(launch_seg_scan(st, BHV, nsegs, fx, nullptr, nullptr, S_local, 0));
+    } else if (fused_states) {
       GLA_TRY(tc_state_fused(st, 0, B, T, HV, R, g, k, v, nullptr, S_prev, nullptr, Gc, 0, nullptr, nullptr, nullptr, S_local));
     } else {
       GLA_TRY((launch_tc_kv<0>(st, B, T, H, g, k, v, kv, Gc)));
@@ -1866,11 +1959,22 @@ int tc_chunk_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
   }
   // The chunk kernel may start beside the one-pass state kernel (which fills only 4 x batch x heads SMs) when it
   // is the very next launch: plain head size, and the kv area of the workspace, unused then, holds the counter.
-  unsigned int* early_flag = (sp_phase == 0 && fused_states && R == 1 && !(opts & GLA_OPT_NO_EARLY_START)) ? (unsigned int*)kv : nullptr;
+  unsigned int* early_flag = (sp_phase == 0 && fused_states && R == 1 && nsegs == 1 && !(opts & GLA_OPT_NO_EARLY_START)) ? (unsigned int*)kv : nullptr;
   unsigned int early_target = 0;
-  if (sp_phase == 2) {
+  if (sp_phase == 2 && nsegs > 1) {
+    // the corrections of all runs, now from the state that enters the slice, in one pass over the stored states
+    GLA_TRY(launch_seg_scan(st, BHV, nsegs, fx, H_in, nullptr, nullptr, 0));
+    GLA_TRY(launch_fix_states(st, BHV, N, nsegs, -1, fx, fx.Cin, S_prev));
+  } else if (sp_phase == 2) {
     // the product area of the workspace is dead by now: it takes the cumulative decays
-    GLA_TRY(launch_sp_fix(st, BHV, N, Gc, kv, H_in, S_prev, 0));
+    GLA_TRY(launch_cum_gate(st, BHV, N, 1, Gc, fx, 0));
+    GLA_TRY(launch_fix_states(st, BHV, N, 1, -1, fx, H_in, S_prev));
+  } else if (nsegs > 1) {
+    // the first run starts from hidden_init and needs no correction; the others get theirs from the scan over runs
+    GLA_TRY(tc_state_fused(st, 0, B, T, HV, R, g, k, v, init_v, S_prev, nullptr, Gc, 0, nullptr, nullptr, nullptr, fx.F, nsegs));
+    GLA_TRY(launch_cum_gate(st, BHV, N, nsegs, Gc, fx, 0));
+    GLA_TRY(launch_seg_scan(st, BHV, nsegs, fx, nullptr, fin_v, nullptr, 0));
+    GLA_TRY(launch_fix_states(st, BHV, N, nsegs, 0, fx, fx.Cin, S_prev));
   } else if (fused_states) {
     GLA_TRY(tc_state_fused(st, 0, B, T, HV, R, g, k, v, init_v, S_prev, fin_v, Gc, nseq, cu, early_flag, &early_target));
   } else {
@@ -1974,8 +2078,15 @@ int tc_chunk_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
     GLA_TRY(launch_state_block(st, dhidden_final, dhfb, B * H, R, 1));
     dfin_v = dhfb; dinit_v = dhib;
   }
+  const bool fused_states = R > 1 || cu != nullptr || tc_state_fused_preferred(BHV, N, opts);
+  const int nsegs = (fused_states && R == 1 && cu == nullptr) ? tc_state_segments(BHV, N, opts) : 1;
+  const FixScratch fx(dstate, BHV, N, nsegs);
   if (sp_phase == 1) {
-    if (tc_state_fused_preferred(BHV, N, opts)) {
+    if (nsegs > 1) {
+      GLA_TRY(tc_state_fused(st, 1, B, T, HV, R, g, q, dout, nullptr, dS_next, nullptr, nullptr, 0, nullptr, nullptr, nullptr, fx.F, nsegs));
+      GLA_TRY(launch_cum_gate(st, BHV, N, nsegs, Gc, fx, 1));
+      GLA_TRY(launch_seg_scan(st, BHV, nsegs, fx, nullptr, nullptr, A_local, 1));
+    } else if (fused_states) {
       GLA_TRY(tc_state_fused(st, 1, B, T, HV, R, g, q, dout, nullptr, dS_next, nullptr, nullptr, 0, nullptr, nullptr, nullptr, A_local));
     } else {
       GLA_TRY((launch_tc_kv<1>(st, B, T, H, g, q, dout, dstate, nullptr)));
@@ -1983,9 +2094,19 @@ int tc_chunk_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
     }
     return GLA_OK;
   }
-  if (sp_phase == 2) {
-    GLA_TRY(launch_sp_fix(st, BHV, N, Gc, dstate, dH_out, dS_next, 1));
-  } else if (R > 1 || cu != nullptr || tc_state_fused_preferred(BHV, N, opts)) {
+  if (sp_phase == 2 && nsegs > 1) {
+    GLA_TRY(launch_seg_scan(st, BHV, nsegs, fx, dH_out, nullptr, nullptr, 1));
+    GLA_TRY(launch_fix_states(st, BHV, N, nsegs, -1, fx, fx.Cin, dS_next));
+  } else if (sp_phase == 2) {
+    GLA_TRY(launch_cum_gate(st, BHV, N, 1, Gc, fx, 1));
+    GLA_TRY(launch_fix_states(st, BHV, N, 1, -1, fx, dH_out, dS_next));
+  } else if (nsegs > 1) {
+    // the run that is walked first (the last in time) starts from dhidden_final and needs no correction
+    GLA_TRY(tc_state_fused(st, 1, B, T, HV, R, g, q, dout, dfin_v, dS_next, nullptr, nullptr, 0, nullptr, nullptr, nullptr, fx.F, nsegs));
+    GLA_TRY(launch_cum_gate(st, BHV, N, nsegs, Gc, fx, 1));
+    GLA_TRY(launch_seg_scan(st, BHV, nsegs, fx, nullptr, dinit_v, nullptr, 1));
+    GLA_TRY(launch_fix_states(st, BHV, N, nsegs, nsegs - 1, fx, fx.Cin, dS_next));
+  } else if (fused_states) {
     GLA_TRY(tc_state_fused(st, 1, B, T, HV, R, g, q, dout, dfin_v, dS_next, dinit_v, nullptr, nseq, cu));
   } else {
     GLA_TRY((launch_tc_kv<1>(st, B, T, H, g, q, dout, dstate, nullptr)));

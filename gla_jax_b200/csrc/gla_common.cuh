@@ -126,7 +126,8 @@ bool tc_state_fused_preferred(int64_t BH, int64_t N, int opts);
 int tc_state_fused(cudaStream_t st, int mode, int64_t B, int64_t T, int64_t H, int R, const float* g, const void* x,
                    const void* y, const void* init, void* states, void* fin, float* Gc, int64_t nseq = 0,
                    const int* cu = nullptr, unsigned int* done = nullptr, unsigned int* done_target = nullptr,
-                   float* fin32 = nullptr);
+                   float* fin32 = nullptr, int nsegs = 1);
+int tc_state_segments(int64_t BH, int64_t N, int opts);
 unsigned int tc_state_read_wait_timeouts();
 unsigned int tc_state_read_bad_offsets();
 int tc_chunk_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, int64_t C,

@@ -79,7 +79,7 @@ template <int MODE>
 __global__ void __launch_bounds__(STHREADS, 1)
 tc_state_kernel(const __grid_constant__ StMaps maps, int64_t T, int64_t H, int R, int Nall, const int* __restrict__ cu,
                 const bf16* __restrict__ init, bf16* __restrict__ states, bf16* __restrict__ fin, float* __restrict__ fin32,
-                float* __restrict__ Gc, unsigned int* __restrict__ done) {
+                float* __restrict__ Gc, unsigned int* __restrict__ done, int nsegs) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* sm = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   float* tot = reinterpret_cast<float*>(sm + StSmem::TOT);
@@ -100,7 +100,13 @@ tc_state_kernel(const __grid_constant__ StMaps maps, int64_t T, int64_t H, int R
   // Packed sequences (cu != null): the arrays hold ONE time axis (B = 1) with sequences laid end to end, cu[s] the
   // token offset of sequence s (a multiple of 128); blockIdx then ranges over (sequence, head, slice), the block
   // walks only its sequence's chunks, and init / fin are per (sequence, head).
-  const int64_t bh = blockIdx.x >> 2, hh = bh % H;
+  // Segments (nsegs > 1, dense batches only): the chunks of every (batch, head) are cut into nsegs runs of equal
+  // length that are walked by separate blocks, each from a zero state except the first in walk order, which starts
+  // from init; every run leaves its final state, unrounded, in fin32[(bh, segment)].  The recurrence is linear in
+  // its starting state, so the caller corrects the stored states afterwards (seg_fix_states in the chunk file);
+  // what this buys is nsegs times as many blocks for shapes with few heads and many chunks.
+  const int seg = nsegs > 1 ? (int)((blockIdx.x >> 2) % nsegs) : 0;
+  const int64_t bh = nsegs > 1 ? (blockIdx.x >> 2) / nsegs : blockIdx.x >> 2, hh = bh % H;
   const int64_t b = cu ? 0 : bh / H;
   // Offsets come from device memory nobody has validated: whatever they hold, this block only touches chunks
   // [base, base + N) inside [0, Nall).  Offsets that are not rising multiples of the chunk length inside the
@@ -112,8 +118,15 @@ tc_state_kernel(const __grid_constant__ StMaps maps, int64_t T, int64_t H, int R
     N = min(max((hi - lo) / SC, 0), Nall - base);
     const bool bad = lo < 0 || hi < lo || lo % SC != 0 || hi % SC != 0 || hi / SC > Nall;
     if (bad && tid == 0 && slice == 0) atomicAdd(&g_state_bad_offsets, 1u);
+  } else if (nsegs > 1) {
+    const int Ns = (Nall + nsegs - 1) / nsegs;
+    base = min(seg * Ns, Nall);
+    N = min(Ns, Nall - base);
+    if (seg != (MODE == 0 ? 0 : nsegs - 1)) init = nullptr;
+    fin = nullptr;                                                // the caller combines the runs' final states
+    fin32 += ((bh * nsegs + seg) - bh) * (int64_t)SD * SD;        // the element offsets below start at bh * SD * SD
   }
-  const int64_t rowbase = cu ? hh * (int64_t)Nall + base : bh * (int64_t)Nall;   // row of chunk 0 in states / Gc
+  const int64_t rowbase = cu ? hh * (int64_t)Nall + base : bh * (int64_t)Nall + base;   // row of chunk 0 in states / Gc
   const int64_t hk = (hh / (R * R)) * R + (hh % (R * R)) / R, hv = (hh / (R * R)) * R + hh % R;
   auto chunk_of = [&](int i) { return MODE == 0 ? i : N - 1 - i; };
 
@@ -358,10 +371,40 @@ bool tc_state_fused_preferred(int64_t BH, int64_t N, int opts) {
   if (opts & GLA_OPT_STATE_ONE_PASS) return true;
   if (opts & GLA_OPT_STATE_TWO_KERNELS) return false;
   const int sms = sm_count();
+  if (tc_state_segments(BH, N, opts) > 1) return true;          // runs make the one-pass form the better one
   const double waves = (double)((4 * BH + sms - 1) / sms);
   const double t_fused = waves * (double)N * 1.0 + 8.0;          // us
   const double t_pair = (double)(BH * N) * 0.1 + 10.0;           // us
   return t_fused < t_pair;
+}
+
+// How many runs to cut every head's chunks into for the one-pass kernel (1: none).  A run costs its chunks in
+// sequence, the grid costs its waves over the SMs, and cutting adds a correction pass over the stored states
+// (read + write, 64 KB per chunk-head) plus three small launches; runs shorter than four chunks are not worth it.
+// The option bit GLA_OPT_STATE_SEGMENTS forces runs (four, or two below 16 chunks, none below 8) for any shape.
+int tc_state_segments(int64_t BH, int64_t N, int opts) {
+  // the runs must all be non-empty: with ns chunks per run, ceil(N / ns) runs cover the axis
+  auto whole_runs = [&](int64_t c) { const int64_t ns = (N + c - 1) / c; return (int)((N + ns - 1) / ns); };
+  if (opts & GLA_OPT_STATE_TWO_KERNELS) return 1;
+  if (opts & GLA_OPT_STATE_SEGMENTS) return N >= 16 ? whole_runs(4) : N >= 8 ? 2 : 1;    // at most N / 4 runs
+  if (opts & GLA_OPT_STATE_ONE_PASS) return 1;
+  const int sms = sm_count();
+  auto cost = [&](int64_t nsegs) {
+    const int64_t waves = (4 * BH * nsegs + sms - 1) / sms, ns = (N + nsegs - 1) / nsegs;
+    double t = (double)waves * ((double)ns * 1.25 + 3.0) + 8.0;       // a block: its steps plus start-up
+    // correction pass over the stored states, three small launches, the sequential walks over a run's chunks and over
+    // the runs (whose final states, 64 KB per head and run, are written, read and turned into corrections)
+    if (nsegs > 1) t += (double)(BH * N) * 0.015 + 30.0 + (double)ns * 0.2 + (double)nsegs * ((double)BH * 0.03 + 0.5);
+    return t;
+  };
+  int64_t best = 1;
+  double tb = cost(1);
+  for (int64_t c = 2; c <= N / 4 && c <= 512; ++c) {
+    const double t = cost(c);
+    if (t < tb) { tb = t; best = c; }
+  }
+  best = whole_runs(best);
+  return cost(best) < 0.8 * cost(1) ? (int)best : 1;
 }
 
 // H counts virtual heads of size 128 (real heads x R x R for head size 128 R; init/states/fin are laid out per
@@ -370,7 +413,8 @@ bool tc_state_fused_preferred(int64_t BH, int64_t N, int opts) {
 // mode 1: states[n] = gradient state after chunk n (from init = dhidden_final), fin = dhidden_init.
 int tc_state_fused(cudaStream_t st, int mode, int64_t B, int64_t T, int64_t H, int R, const float* g, const void* x,
                    const void* y, const void* init, void* states, void* fin, float* Gc, int64_t nseq, const int* cu,
-                   unsigned int* done, unsigned int* done_target, float* fin32) {
+                   unsigned int* done, unsigned int* done_target, float* fin32, int nsegs) {
+  if (nsegs < 1 || (nsegs > 1 && (cu != nullptr || fin32 == nullptr || done != nullptr || nsegs > T / SC))) return GLA_ERR_UNSUPPORTED;
   // packed sequences: B == 1, cu (device, nseq + 1 token offsets) non-null, init / fin are (nseq, H, 128, 128)
   const int64_t N = T / SC, BH = (cu ? nseq : B) * H;          // H: virtual heads (real heads x R x R)
   const int64_t HK = H / R;                      // heads of the (B, T, HK, 128) view of the arrays
@@ -389,8 +433,9 @@ int tc_state_fused(cudaStream_t st, int mode, int64_t B, int64_t T, int64_t H, i
   }
   {
     ProfScope ps(mode == 0 ? "tc_state_kernel" : "tc_dstate_scan_kernel", st);
-    kern<<<(unsigned)(BH * 4), STHREADS, ST_SMEM, st>>>(maps, T, H, R, (int)N, cu, (const bf16*)init, (bf16*)states, (bf16*)fin, fin32,
-                                                        Gc, done);
+    if (BH * 4 * nsegs > 2147483647LL) return GLA_ERR_TOO_LARGE;
+    kern<<<(unsigned)(BH * 4 * nsegs), STHREADS, ST_SMEM, st>>>(maps, T, H, R, (int)N, cu, (const bf16*)init, (bf16*)states,
+                                                                (bf16*)fin, fin32, Gc, done, nsegs);
   }
   GLA_CHECK_LAUNCH();
   return GLA_OK;

@@ -86,13 +86,18 @@ typedef enum gla_chunk_impl {
  *       chunk whose total |log decay| is at most 60 for every feature uses a single anchor, because all its decay
  *       weights then lie within exp(+-60); sharper chunks take all levels.  The choice is made per chunk on the
  *       device from the gates themselves.
- *   NO_L2_PREFETCH   no L2 prefetch of the next chunk's operands in the chunk kernels. */
+ *   NO_L2_PREFETCH   no L2 prefetch of the next chunk's operands in the chunk kernels.
+ *   STATE_SEGMENTS   cut every head's chunks into runs that separate thread blocks walk from a zero state, then
+ *       correct the stored states with the state that really enters each run (the recurrence is linear in it).
+ *       Default: done when (batch x heads) alone gives the one-pass state kernel too few blocks for the device
+ *       and the sequence is long; this bit forces it for any shape. */
 typedef enum gla_chunk_option {
   GLA_OPT_STATE_TWO_KERNELS = 0x100,
   GLA_OPT_STATE_ONE_PASS = 0x200,
   GLA_OPT_NO_EARLY_START = 0x400,
   GLA_OPT_ALL_SCALES = 0x800,
-  GLA_OPT_NO_L2_PREFETCH = 0x1000
+  GLA_OPT_NO_L2_PREFETCH = 0x1000,
+  GLA_OPT_STATE_SEGMENTS = 0x2000
 } gla_chunk_option;
 
 /* Human-readable text for a status code. Never NULL. (Reference: Python assert messages.) */

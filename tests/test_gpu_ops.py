@@ -170,6 +170,34 @@ def test_chunk_states_one_pass_vs_product_and_scan(cuda_device, B, T, H):
         _compare(_oracle(*case), got["1"], torch.bfloat16, f"chunk_gla one-pass states {B,T,H}")
 
 
+@pytest.mark.parametrize("B,T,H,shift", [
+    (1, 2048, 2, 2.0),      # 16 chunks: four runs of four
+    (2, 2176, 1, 2.0),      # 17 chunks: runs of 5, 5, 5, 2
+    (1, 1152, 3, 2.0),      # 9 chunks: two runs (5 + 4)
+    (1, 2048, 1, 0.0),      # sharp gates: the corrections underflow inside a run and are skipped
+])
+def test_chunk_states_in_runs_vs_one_walk(cuda_device, B, T, H, shift):
+    """The one-pass state kernel over runs of chunks (every run from zero, corrected afterwards with the state that
+    really enters it; chosen by itself for few heads and long sequences, forced here) against the single walk and
+    the oracle: forward, backward, both final states."""
+    import ctypes
+    from gla_jax_b200 import chunk_gla, _lib
+    lib = _lib.load()
+    case = _case(B, T, H, 128, torch.bfloat16, 41, shift, False)
+    one = _run_gpu(chunk_gla, cuda_device, *case, chunk_size=128, impl="tcgen05+one_pass")
+    lib.gla_profile_enable(1)
+    runs = _run_gpu(chunk_gla, cuda_device, *case, chunk_size=128, impl="tcgen05+segments")
+    lib.gla_profile_enable(0)
+    buf = ctypes.create_string_buffer(1 << 14)
+    lib.gla_profile_report(buf, len(buf))
+    assert b"seg_scan_kernel" in buf.value and b"sp_fix_states_kernel" in buf.value, buf.value
+    assert lib.gla_device_wait_timeouts() == 0
+    for name, a, b in zip(["hidden_final", "out", *NAMES], [one[0], one[1], *one[2]], [runs[0], runs[1], *runs[2]]):
+        err = O.rel_l2(a, b)
+        assert err <= 4e-3, f"{name}: runs vs one walk {err:.3e}"      # stored states are rounded to bf16 twice
+    _compare(_oracle(*case), runs, torch.bfloat16, f"chunk_gla states in runs {B,T,H}")
+
+
 def test_auto_picks_tcgen05_for_readme_shape(cuda_device):
     """impl='auto' must run the tensor-core kernels at D = chunk = 128 in bf16 (checked through
     the library's own launch profile) and the fp32 kernels elsewhere."""

@@ -21,6 +21,8 @@ NAMES = ("dhidden_init", "dlog_fgate", "dvalue", "dkey", "dquery")
     # sharp gates and 8 chunks per rank: the accumulated decay underflows after the first chunk or two, so the
     # correction of the kept states skips the rest (and every chunk takes all levels of the secondary chunking)
     (torch.bfloat16, 128, 128, 2, "auto", 2048, 0.0),
+    # each rank's 16 chunks in four runs: local runs from zero, one correction pass per direction in the finish phase
+    (torch.bfloat16, 128, 128, 2, "auto+segments", 4096, 2.0),
     (torch.float32, 64, 32, 2, "fp32", 1024, 2.0),
 ])
 def test_emulated_sequence_parallel_on_one_gpu(cuda_device, dtype, D, C, R, impl, T, shift):
