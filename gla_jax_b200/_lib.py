@@ -98,6 +98,8 @@ SIGNATURES = {
                                         c_void_p, c_void_p, c_size_t]),
     "gla_sp_combine": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int,
                                c_void_p, c_int, c_int]),
+    "gla_sp_combine2": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64,
+                                c_void_p, c_int, c_void_p, c_void_p, c_int, c_int]),
 }
 
 

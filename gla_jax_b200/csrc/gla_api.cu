@@ -87,7 +87,7 @@ int gla_last_cuda_error(void) { return g_last_cuda_error; }
 
 long long gla_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
-unsigned int gla_device_wait_timeouts(void) { return tc_read_wait_timeouts() + tc_state_read_wait_timeouts(); }
+unsigned int gla_device_wait_timeouts(void) { return tc_read_wait_timeouts() + tc_state_read_wait_timeouts() + scan_read_wait_timeouts(); }
 
 unsigned int gla_device_bad_offsets(void) { return tc_state_read_bad_offsets(); }
 
@@ -457,6 +457,18 @@ int gla_sp_combine(void* stream, int64_t R, int64_t rank, int64_t BH, int64_t D,
   GLA_TRY(check_dtype(result_dtype));
   return launch_sp_combine((cudaStream_t)stream, R, rank, BH, D, all_G, all_S, init, init_dtype == GLA_BF16, result,
                            result_dtype == GLA_BF16, reverse);
+}
+
+int gla_sp_combine2(void* stream, int64_t R, int64_t rank, int64_t BH, int64_t D, const float* all_G, int64_t g_rank_stride,
+                    const float* all_S, int64_t s_rank_stride, const void* init, int init_dtype, float* entering,
+                    void* total, int total_dtype, int reverse) {
+  if (!all_G || !all_S || (!entering && !total)) return GLA_ERR_NULL_POINTER;
+  if (R <= 0 || rank < 0 || rank >= R || BH <= 0 || D <= 0 || g_rank_stride < BH * D || s_rank_stride < BH * D * D)
+    return GLA_ERR_BAD_DIMS;
+  GLA_TRY(check_dtype(init_dtype));
+  GLA_TRY(check_dtype(total_dtype));
+  return launch_sp_combine2((cudaStream_t)stream, R, rank, BH, D, all_G, g_rank_stride, all_S, s_rank_stride, init,
+                            init_dtype == GLA_BF16, entering, total, total_dtype == GLA_BF16, reverse);
 }
 
 }  // extern "C"

@@ -129,6 +129,7 @@ int tc_state_fused(cudaStream_t st, int mode, int64_t B, int64_t T, int64_t H, i
                    float* fin32 = nullptr, int nsegs = 1);
 int tc_state_segments(int64_t BH, int64_t N, int opts);
 unsigned int tc_state_read_wait_timeouts();
+unsigned int scan_read_wait_timeouts();
 unsigned int tc_state_read_bad_offsets();
 int tc_chunk_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, int64_t C,
                  const float* g, const void* v, const void* k, const void* q, const void* saved,
@@ -145,6 +146,9 @@ int launch_rnn_scan(cudaStream_t st, int64_t batch, int64_t T, int64_t K, int64_
 int launch_sp_combine(cudaStream_t st, int64_t R, int64_t rank, int64_t BH, int64_t D, const float* all_G,
                       const float* all_S, const void* init, int init_bf16, void* result, int result_bf16,
                       int reverse);
+int launch_sp_combine2(cudaStream_t st, int64_t R, int64_t rank, int64_t BH, int64_t D, const float* all_G, int64_t gstride,
+                       const float* all_S, int64_t sstride, const void* init, int init_bf16, float* entering, void* total,
+                       int total_bf16, int reverse);
 int recurrent_fwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, int bf, const void* hidden_init,
                   const float* g, const void* v, const void* k, const void* q, void* hidden_final, void* out,
                   int out_bf, int reverse);

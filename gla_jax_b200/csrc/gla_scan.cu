@@ -7,6 +7,8 @@
 // tiles, scanning within a tile in registers and carrying the running total, so any length
 // is one launch with fully coalesced 128-byte row segments.
 #include "gla_common.cuh"
+#include "tc_ptx.cuh"
+#include "tma_maps.cuh"
 
 namespace gla {
 
@@ -229,6 +231,181 @@ __global__ void __launch_bounds__(32 * C4_RL) cumsum_v4_kernel(const TI* __restr
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// The float32 scan of wide rows as a TMA pipeline.  What limits the kernels above on a long axis is how many bytes
+// a thread block can keep in flight with ordinary loads; here a 64-row x 128-column tile travels as ONE tensor copy
+// (cp.async.bulk.tensor over a 3-d map (column, row, n): rows past the end of the axis and columns past D are
+// zero-filled on the way in and skipped on the way out) into a ring of NST shared-memory stages, the threads scan
+// a landed tile out of shared memory, write the result into one of two staging tiles, and a tensor store takes it
+// back.  Up to NST tiles (32 KB each) are in flight per block at no register cost.  (One bulk copy per ROW was
+// measured first: 128 copy instructions per tile made the kernel twice as slow as the load/store one.)
+//   thread 0       issues the copy of tile i + NST once tile i has been read
+//   thread 32      issues the store of tile i and waits for the store of tile i - 2 to have read its stage
+//   all 8 warps    thread = four columns x eight consecutive scan positions; row lanes combine as in the kernel above
+// A reversed scan walks the tiles from the end of the axis; its tiles are laid out so that every one but the FIRST
+// in scan order starts on a multiple of 64 rows from the end (no store ever starts at a negative row), and a
+// thread's scan position p sits in stage row nr - 1 - p.
+// Every mbarrier wait is bounded; a block whose wait expires stops, waits (bounded) for the copies it still has
+// in flight and counts itself in g_scan_wait_timeouts.
+// ---------------------------------------------------------------------------------------
+namespace {
+using namespace tc;
+__device__ unsigned int g_scan_wait_timeouts = 0;
+constexpr int BK_RL = 8;                       // row lanes
+constexpr int BK_ROWS = CS_RPT * BK_RL;        // rows of a tile (64)
+constexpr int BK_NST = 4;                      // input stages
+constexpr int BK_TILE = BK_ROWS * 128 * 4;     // bytes of a tile (32 KB)
+constexpr int BK_SMEM = (BK_NST + 2) * BK_TILE + 1024;
+
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int PENDING> __device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" :: "n"(PENDING) : "memory");
+}
+template <int PENDING> __device__ __forceinline__ void bulk_wait_all() {
+  asm volatile("cp.async.bulk.wait_group %0;" :: "n"(PENDING) : "memory");
+}
+
+struct ScanMaps { CUtensorMap in, out; };
+
+template <typename OP, bool MULTI>
+__global__ void __launch_bounds__(32 * BK_RL, 1) cumsum_tma_kernel(const __grid_constant__ ScanMaps maps, const float* __restrict__ init,
+                                                                   int64_t N, int64_t T, int64_t D, int reverse) {
+  extern __shared__ uint8_t bk_raw[];
+  uint8_t* sm = (uint8_t*)(((uintptr_t)bk_raw + 1023) & ~(uintptr_t)1023);
+  __shared__ float4 tot[2][BK_RL][32];
+  __shared__ float4 car[2][32];
+  __shared__ uint64_t full[BK_NST];
+  const int tx = threadIdx.x, rl = threadIdx.y, tid = rl * 32 + tx;
+  // Work items are (row n, block of 128 columns); a block takes items blockIdx.x, + gridDim.x, ... and streams their
+  // tiles back to back through the same ring, so that short axes (a chunk of 128 positions is two tiles) do not pay
+  // a block start-up each.
+  const int64_t gy = (D + 127) / 128, items = N * gy;
+  // MULTI == false is the same kernel for grids with one item per block: the walk over items folds away
+  const int64_t my_items = MULTI ? (items - blockIdx.x + gridDim.x - 1) / gridDim.x : 1;
+  // tiles of an item in scan order: forward tile i starts at row 64 i; reversed, tile 0 holds the last `rem` rows of
+  // the axis and tile i >= 1 the 64 rows before those of tile i - 1
+  const int rem = (int)(T % BK_ROWS ? T % BK_ROWS : BK_ROWS);
+  const int64_t ntiles = (T + BK_ROWS - 1) / BK_ROWS, total = my_items * ntiles;
+  const int Ti = (int)T;
+  auto rows_of = [&](int i) {
+    if (reverse) return i == 0 ? rem : BK_ROWS;
+    const int left = Ti - i * BK_ROWS;
+    return left < BK_ROWS ? left : BK_ROWS;
+  };
+  auto start_of = [&](int i) { return reverse ? Ti - rem - i * BK_ROWS : i * BK_ROWS; };
+  const uint32_t in0 = smem_u32(sm), out0 = in0 + BK_NST * BK_TILE, full0 = smem_u32(full);
+  const float4 ident = make_float4(OP::id(), OP::id(), OP::id(), OP::id());
+
+  if (tid == 0) {
+    for (int s2 = 0; s2 < BK_NST; ++s2) mbar_init(full0 + 8 * s2, 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  static_assert((BK_NST & (BK_NST - 1)) == 0, "the ring index is kept with a mask");
+  // the producer's own walk over (item, tile), NST tiles ahead of the consumers'; all walks keep their place with
+  // counters (no division per tile)
+  int64_t p_item = blockIdx.x, p_g = 0;
+  int p_i = 0, p_n = (int)(p_item / gy), p_c0 = (int)(p_item % gy) * 128;
+  auto issue_load = [&]() {                   // one thread
+    const uint32_t sidx = (uint32_t)p_g & (BK_NST - 1), bar = full0 + 8 * sidx;
+    mbar_arrive_expect_tx(bar, BK_TILE);      // the box counts in full, zero-filled parts included
+    tma_load_3d(in0 + sidx * BK_TILE, &maps.in, p_c0, start_of(p_i), p_n, bar);
+    ++p_g;
+    ++p_i;
+    if (MULTI && p_i == (int)ntiles) {
+      p_i = 0; p_item += gridDim.x;
+      p_n = (int)(p_item / gy); p_c0 = (int)(p_item % gy) * 128;
+    }
+  };
+  if (tid == 0)
+    for (int a = 0; a < BK_NST && p_g < total; ++a) issue_load();
+  auto init_of = [&](int nn, int cc) {
+    const int64_t c = (int64_t)cc + tx * 4;
+    return (init != nullptr && c < D) ? ld4_f(init + (int64_t)nn * D + c) : ident;
+  };
+  int64_t item = blockIdx.x, g = 0;
+  int i = 0, n = (int)(item / gy), c0 = (int)(item % gy) * 128;
+  if (rl == BK_RL - 1 && total > 0) car[0][tx] = init_of(n, c0);
+  bool ok = true;
+  int par = 0, st = 0;
+  uint32_t phase = 0;
+  for (; g < total; ++g, par ^= 1) {
+    const bool cvalid = (int64_t)c0 + tx * 4 < D;
+    ok = mbar_wait(full0 + 8 * st, phase);       // on expiry the tile is garbage: voted on below
+    const int nrt = rows_of(i);
+    const int nr = nrt - rl * CS_RPT;                 // this thread's scan positions inside the tile (<= 0: none)
+    // scan position p = 8 rl + r of the tile sits in stage row p (forward) or nrt - 1 - p (reversed)
+    const int row0 = reverse ? nrt - 1 - rl * CS_RPT : rl * CS_RPT, rstep = reverse ? -32 : 32;
+    const float4* in = reinterpret_cast<const float4*>(sm + st * BK_TILE) + row0 * 32 + tx;
+    float4 x[CS_RPT];
+#pragma unroll
+    for (int r = 0; r < CS_RPT; ++r) x[r] = (cvalid && r < nr) ? in[r * rstep] : ident;
+#pragma unroll
+    for (int r = 1; r < CS_RPT; ++r) x[r] = op4<OP>(x[r - 1], x[r]);
+    tot[par][rl][tx] = x[CS_RPT - 1];
+    // the staging tile that this tile is about to write was last read by the store of two tiles ago: all but the
+    // newest store group must have read their stage
+    if (tid == 32) bulk_wait_read<1>();
+    // stage st has been read by everyone and the totals are visible; the same barrier takes the vote on the waits,
+    // so that the whole block leaves together if any thread's wait expired
+    if (!__syncthreads_and(ok)) { ok = false; break; }
+    if (tid == 0 && p_g < total) issue_load();
+    float4 off = car[par][tx];
+    for (int r2 = 0; r2 < rl; ++r2) off = op4<OP>(off, tot[par][r2][tx]);
+    const bool last_tile = MULTI && i + 1 == (int)ntiles;
+    int n2 = n, c2 = c0;
+    if (last_tile) { const int64_t nx = item + gridDim.x; n2 = (int)(nx / gy); c2 = (int)(nx % gy) * 128; }
+    // the carry into the next tile: this item's running value, or the next item's initial value
+    if (rl == BK_RL - 1)
+      car[par ^ 1][tx] = !last_tile ? op4<OP>(off, x[CS_RPT - 1]) : item + gridDim.x < items ? init_of(n2, c2) : ident;
+    float4* o = reinterpret_cast<float4*>(sm + (BK_NST + par) * BK_TILE) + row0 * 32 + tx;
+#pragma unroll
+    for (int r = 0; r < CS_RPT; ++r)
+      if (r < nr) o[r * rstep] = op4<OP>(off, x[r]);
+    fence_async_smem();                                // the staging tile is read by the async proxy
+    __syncthreads();
+    if (tid == 32) {
+      tma_store_3d(&maps.out, c0, start_of(i), n, out0 + (uint32_t)par * BK_TILE);
+      bulk_commit();
+    }
+    if (last_tile) { i = 0; item += gridDim.x; n = n2; c0 = c2; } else ++i;
+    if (++st == BK_NST) { st = 0; phase ^= 1u; }
+  }
+  if (tid == 32) bulk_wait_all<0>();                    // the block's stores have completed before it leaves
+  if (!ok) {
+    // copies already requested land in this block's shared memory: give them their (bounded) time before leaving
+    if (tid == 0)
+      for (int64_t j = g; j < p_g; ++j) mbar_wait(full0 + 8 * ((uint32_t)j & (BK_NST - 1)), (uint32_t)((j / BK_NST) & 1));
+    if (tid == 0) atomicAdd(&g_scan_wait_timeouts, 1u);
+  }
+}
+}  // namespace
+
+unsigned int scan_read_wait_timeouts() {
+  unsigned int v = 0;
+  cudaMemcpyFromSymbol(&v, g_scan_wait_timeouts, sizeof(v));
+  return v;
+}
+
+template <typename OP>
+static int launch_cumsum_tma_op(cudaStream_t st, int64_t N, int64_t T, int64_t D, const float* src, const float* init, float* dst,
+                                int reverse) {
+  static SmemAttrOnce attr[2];
+  GLA_TRY(attr[0].ensure(cumsum_tma_kernel<OP, false>, BK_SMEM));
+  GLA_TRY(attr[1].ensure(cumsum_tma_kernel<OP, true>, BK_SMEM));
+  ScanMaps maps;
+  GLA_TRY(make_map_ntd_f32(&maps.in, src, N, T, D, BK_ROWS));
+  GLA_TRY(make_map_ntd_f32(&maps.out, dst, N, T, D, BK_ROWS));
+  // one block per SM (the ring takes most of its shared memory), fewer when there are fewer (row, column block) items
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int64_t items = N * ((D + 127) / 128);
+  dim3 block(32, BK_RL);
+  if (items <= sms) cumsum_tma_kernel<OP, false><<<dim3((unsigned)items), block, BK_SMEM, st>>>(maps, init, N, T, D, reverse);
+  else              cumsum_tma_kernel<OP, true><<<dim3((unsigned)sms), block, BK_SMEM, st>>>(maps, init, N, T, D, reverse);
+  return GLA_OK;
+}
+
 // Column width of a block: the four-columns-per-thread kernel serves rows of at least 128 columns that are a
 // multiple of four (and, checked at launch, 16-byte aligned pointers); the scalar kernel everything else.
 static bool cumsum_wide(int64_t D) { return D >= 128 && D % 4 == 0; }
@@ -290,6 +467,22 @@ int launch_cumsum(cudaStream_t st, int64_t N, int64_t T, int64_t D, const void* 
   auto aligned = [](const void* p, int is_bf16) { return p == nullptr || ((uintptr_t)p % (is_bf16 ? 8 : 16)) == 0; };
   const bool wide = cumsum_wide(D) && aligned(src, in_bf16) && aligned(sub, in_bf16) && aligned(init, in_bf16) &&
                     aligned(dst, out_bf16) && aligned(scratch, 0);
+  // float32 in and out, no second source, one pass: the bulk-copy pipeline
+  if (wide && !in_bf16 && !out_bf16 && sub == nullptr && scratch == nullptr && T >= 2 * BK_ROWS) {
+    if ((D + 127) / 128 > 65535 || N > 2147483647LL) return GLA_ERR_TOO_LARGE;
+    ProfScope ps("cumsum_kernel", st);
+    int rc;
+    switch (op) {
+      case GLA_SCAN_MUL: rc = launch_cumsum_tma_op<OpMul>(st, N, T, D, (const float*)src, (const float*)init, (float*)dst, reverse); break;
+      case GLA_SCAN_MAX: rc = launch_cumsum_tma_op<OpMax>(st, N, T, D, (const float*)src, (const float*)init, (float*)dst, reverse); break;
+      case GLA_SCAN_MIN: rc = launch_cumsum_tma_op<OpMin>(st, N, T, D, (const float*)src, (const float*)init, (float*)dst, reverse); break;
+      case GLA_SCAN_LOGADDEXP: rc = launch_cumsum_tma_op<OpLogAddExp>(st, N, T, D, (const float*)src, (const float*)init, (float*)dst, reverse); break;
+      default: rc = launch_cumsum_tma_op<OpAdd>(st, N, T, D, (const float*)src, (const float*)init, (float*)dst, reverse); break;
+    }
+    if (rc != GLA_OK) return rc;
+    GLA_CHECK_LAUNCH();
+    return GLA_OK;
+  }
   const int64_t gy = wide ? (D + 127) / 128 : (D + 31) / 32;
   // without scratch for the segment sums the scan runs in one pass, one block per row and column group
   const int nseg = scratch ? cumsum_segments(N, T, D) : 1;
@@ -533,6 +726,47 @@ __global__ void __launch_bounds__(256) sp_combine_kernel(int64_t R, int64_t rank
       acc = expf(all_G[(s * BH + bh) * D + dk]) * acc + all_S[s * BH * DD + e];
   }
   st_f(result, e, acc);
+}
+
+// Both results a rank needs from the gathered pairs in one launch: the state entering its slice (float32, for the
+// correction of its stored states) and the state leaving the last slice in scan order (the whole sequence's
+// hidden_final, or dhidden_init in the reverse direction).  The pairs may sit in one packed record per rank (what
+// a single all-gather of [G | S] gives): gstride / sstride are the distances between ranks in floats.
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256) sp_combine2_kernel(int64_t R, int64_t rank, int64_t BH, int64_t D,
+                                                          const float* __restrict__ all_G, int64_t gstride,
+                                                          const float* __restrict__ all_S, int64_t sstride,
+                                                          const TI* __restrict__ init, float* __restrict__ entering,
+                                                          TO* __restrict__ total, int reverse) {
+  const int64_t DD = D * D;
+  const int64_t e = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (e >= BH * DD) return;
+  const int64_t bh = e / DD, dk = (e % DD) / D;
+  float acc = init ? ld_f(init, e) : 0.f;
+  for (int64_t i = 0; i < R; ++i) {
+    const int64_t s = reverse ? R - 1 - i : i;
+    if (s == rank && entering != nullptr) entering[e] = acc;
+    acc = expf(all_G[s * gstride + bh * D + dk]) * acc + all_S[s * sstride + e];
+  }
+  if (total != nullptr) st_f(total, e, acc);
+}
+
+int launch_sp_combine2(cudaStream_t st, int64_t R, int64_t rank, int64_t BH, int64_t D, const float* all_G, int64_t gstride,
+                       const float* all_S, int64_t sstride, const void* init, int init_bf16, float* entering, void* total,
+                       int total_bf16, int reverse) {
+  const int64_t n = BH * D * D;
+  dim3 grid((unsigned)((n + 255) / 256));
+  ProfScope ps("sp_combine_kernel", st);
+  if (init_bf16 && total_bf16)
+    sp_combine2_kernel<bf16, bf16><<<grid, 256, 0, st>>>(R, rank, BH, D, all_G, gstride, all_S, sstride, (const bf16*)init, entering, (bf16*)total, reverse);
+  else if (init_bf16 && !total_bf16)
+    sp_combine2_kernel<bf16, float><<<grid, 256, 0, st>>>(R, rank, BH, D, all_G, gstride, all_S, sstride, (const bf16*)init, entering, (float*)total, reverse);
+  else if (!init_bf16 && total_bf16)
+    sp_combine2_kernel<float, bf16><<<grid, 256, 0, st>>>(R, rank, BH, D, all_G, gstride, all_S, sstride, (const float*)init, entering, (bf16*)total, reverse);
+  else
+    sp_combine2_kernel<float, float><<<grid, 256, 0, st>>>(R, rank, BH, D, all_G, gstride, all_S, sstride, (const float*)init, entering, (float*)total, reverse);
+  GLA_CHECK_LAUNCH();
+  return GLA_OK;
 }
 
 int launch_sp_combine(cudaStream_t st, int64_t R, int64_t rank, int64_t BH, int64_t D, const float* all_G,

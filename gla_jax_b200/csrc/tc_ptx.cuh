@@ -137,6 +137,11 @@ __device__ __forceinline__ void tma_prefetch_l2_3d(const void* tmap, int x, int 
   asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];"
                :: "l"((uint64_t)tmap), "r"(x), "r"(y), "r"(z) : "memory");
 }
+// Bulk tensor store shared -> global of one box (bulk-group completion); never start one at a negative coordinate.
+__device__ __forceinline__ void tma_store_3d(const void* tmap, int x, int y, int z, uint32_t smem_src) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];"
+               :: "l"((uint64_t)tmap), "r"(x), "r"(y), "r"(z), "r"(smem_src) : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" :: "l"((uint64_t)tmap) : "memory");
 }

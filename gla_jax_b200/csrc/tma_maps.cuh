@@ -83,6 +83,26 @@ inline int make_map_rows(CUtensorMap* m, const void* ptr, int64_t rows, int box_
   return GLA_OK;
 }
 
+// float32 array (N, T, D) seen as 3-d (d, t, n); box = (128, box_rows, 1), no swizzle: the box's rows lie 512 bytes
+// apart in shared memory.  Rows past T and columns past D are zero-filled by loads and skipped by stores, so a box
+// never touches the next n.  D must be a multiple of 4 (strides in multiples of 16 bytes).
+inline int make_map_ntd_f32(CUtensorMap* m, const void* ptr, int64_t N, int64_t T, int64_t D, int box_rows) {
+  if (T > 0x7fffffffLL || D > 0x7fffffffLL || N > 0x7fffffffLL) return GLA_ERR_TOO_LARGE;
+  const MapKey key{ptr, N, T, 3, (int)D, box_rows, 0};
+  if (const CUtensorMap* hit = map_cache().find(key)) { *m = *hit; return GLA_OK; }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return GLA_ERR_NO_DEVICE;
+  cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)T, (cuuint64_t)N};
+  cuuint64_t strides[2] = {(cuuint64_t)D * 4, (cuuint64_t)T * D * 4};
+  cuuint32_t box[3] = {128, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return GLA_ERR_LAUNCH;
+  map_cache().put(key, *m);
+  return GLA_OK;
+}
+
 // cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (kernel, device) instead of on every call.
 struct SmemAttrOnce {
   unsigned long long done = 0;       // bit per device; a lost update only repeats an idempotent call

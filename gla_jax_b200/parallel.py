@@ -110,6 +110,21 @@ class CudaOps:
         _lib.check(st, "gla_sp_combine")
         return res
 
+    def combine_both(self, all_G, all_S, rank, init, total_dtype, reverse):
+        """-> (state entering the slice of `rank`, float32; state leaving the last slice in scan order, `total_dtype`)
+        in one launch.  all_G (R,B,H,D) / all_S (R,B,H,D,D) may be views into one packed gather: only the rank axis
+        may be strided."""
+        R, B, H, D = all_G.shape
+        assert all_G[0].is_contiguous() and all_S[0].is_contiguous()
+        entering = torch.empty(B, H, D, D, dtype=torch.float32, device=all_G.device)
+        total = torch.empty(B, H, D, D, dtype=total_dtype, device=all_G.device)
+        init = init.contiguous()
+        st = self.lib.gla_sp_combine2(self._stream(all_G.device), R, rank, B * H, D, all_G.data_ptr(), all_G.stride(0),
+                                      all_S.data_ptr(), all_S.stride(0), init.data_ptr(), self._DT[init.dtype],
+                                      entering.data_ptr(), total.data_ptr(), self._DT[total_dtype], int(reverse))
+        _lib.check(st, "gla_sp_combine2")
+        return entering, total
+
     def chunk_fwd(self, h, g, v, k, q, chunk):
         """-> (hidden_final, out, residuals)"""
         from .gla import _chunk_fwd_raw
@@ -200,6 +215,10 @@ def sp_forward(ops, rank: int, all_G, all_S, hidden_init, ctx, g, v, k, q, chunk
     """Phases 3-4 of the forward for one rank, given the gathered (G, S) of all ranks and the rank's local context.
     Returns (hidden_final_of_whole_sequence, out_slice, residuals)."""
     R = all_G.shape[0]
+    if hasattr(ops, "combine_both"):
+        H_in, hidden_final = ops.combine_both(all_G, all_S, rank, hidden_init, hidden_init.dtype, False)
+        out, res = ops.fwd_finish(ctx, H_in, g, v, k, q, chunk)
+        return hidden_final, out, res
     H_in = ops.combine(all_G, all_S, rank, hidden_init, getattr(ops, "exchange_dtype", torch.float32), False)
     out, res = ops.fwd_finish(ctx, H_in, g, v, k, q, chunk)
     hidden_final = ops.combine(all_G, all_S, R, hidden_init, hidden_init.dtype, False)
@@ -209,6 +228,10 @@ def sp_forward(ops, rank: int, all_G, all_S, hidden_init, ctx, g, v, k, q, chunk
 def sp_backward(ops, rank: int, all_G, all_A, dhidden_final, ctx, g, v, k, q, residuals, dout, chunk):
     """Phases 3-4 of the backward for one rank.  Returns (dhidden_init of the whole sequence,
     dg, dv, dk, dq of the slice)."""
+    if hasattr(ops, "combine_both"):
+        dH_out, dhidden_init = ops.combine_both(all_G, all_A, rank, dhidden_final, dhidden_final.dtype, True)
+        dg, dv, dk, dq = ops.bwd_finish(ctx, dH_out, g, v, k, q, residuals, dout, chunk)
+        return dhidden_init, dg, dv, dk, dq
     dH_out = ops.combine(all_G, all_A, rank, dhidden_final, getattr(ops, "exchange_dtype", torch.float32), True)
     dg, dv, dk, dq = ops.bwd_finish(ctx, dH_out, g, v, k, q, residuals, dout, chunk)
     dhidden_init = ops.combine(all_G, all_A, -1, dhidden_final, dhidden_final.dtype, True)
@@ -264,7 +287,11 @@ class _SeqParallelChunkGLA(torch.autograd.Function):
         _validate_ranks(hidden_init, v, chunk, group)
         g32 = g.float().contiguous()
         G, S, lctx = ops.fwd_local(g32, v, k, chunk)
-        all_G, all_S = _all_gather(G, group), _all_gather(S, group)
+        # one all-gather of a packed [G | S] record per rank; all_G / all_S are views into the gathered records
+        nG = G.numel()
+        packed = _all_gather(torch.cat([G.reshape(-1), S.reshape(-1).to(G.dtype)]), group)
+        all_G = packed[:, :nG].unflatten(1, tuple(G.shape))
+        all_S = packed[:, nG:].unflatten(1, tuple(S.shape))
         hf, out, res = sp_forward(ops, rank, all_G, all_S, hidden_init, lctx, g32, v, k, q, chunk)
         ctx.save_for_backward(g32, v, k, q, all_G, *res)
         ctx.chunk, ctx.group, ctx.ops, ctx.rank, ctx.g_dtype = chunk, group, ops, rank, g.dtype

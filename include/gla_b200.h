@@ -429,6 +429,16 @@ GLA_API int gla_sp_combine(void* stream, int64_t R, int64_t rank, int64_t BH, in
                    const void* init, int init_dtype,
                    void* result, int result_dtype, int reverse);
 
+/* The two results a rank needs from the gathered pairs, in one launch: `entering` (BH, D, D) float32, the state that
+ * enters the slice of `rank` (0 <= rank < R; what gla_chunk_sp_fwd_finish / _bwd_finish take), and `total`, the state
+ * that leaves the last slice in scan order (hidden_final of the whole sequence; with reverse != 0 dhidden_init).
+ * Either may be NULL.  all_G / all_S need not be separate arrays: g_rank_stride / s_rank_stride are the distances
+ * between consecutive ranks in floats, so one all-gather of a packed [G | S] record per rank serves
+ * (all_S = all_G + BH * D, both strides BH * D * (D + 1)).  No counterpart in the reference (single device). */
+GLA_API int gla_sp_combine2(void* stream, int64_t R, int64_t rank, int64_t BH, int64_t D,
+                    const float* all_G, int64_t g_rank_stride, const float* all_S, int64_t s_rank_stride,
+                    const void* init, int init_dtype, float* entering, void* total, int total_dtype, int reverse);
+
 #ifdef __cplusplus
 }
 #endif
