@@ -600,6 +600,36 @@ def run_cfg4(lib, dev, rank, world, barrier, steps=5, warmup=2):
         sp_step()
     ms = timed(sp_step, steps, barrier)
     hf_sp, out_sp, _ = sp_step()
+    # The same step as ONE CUDA graph per rank (operator calls, NCCL all-gathers and the backward captured together):
+    # at 4 and 8 ranks a rank's kernels take less time than Python needs to enqueue them, so the eager number above
+    # measures the host; the replay measures the GPUs.  Every rank captures (collectives must be captured by all);
+    # a rank whose capture fails tells the others, and nobody replays.
+    graph_ms = graph_err = None
+    try:
+        leaves_g = [h.detach().requires_grad_(True)] + [x.detach().requires_grad_(True) for x in mine]
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        gph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            # thread-local capture mode: the process group's watchdog thread may query events meanwhile
+            with torch.cuda.graph(gph, stream=side, capture_error_mode="thread_local"):
+                hf_g, out_g = P.sequence_parallel_chunk_gla(*leaves_g, chunk_size=C)
+                grads_g = torch.autograd.grad(hf_g.float().sum() + out_g.float().sum(), leaves_g)
+        torch.cuda.synchronize()
+        okflag = torch.ones(1, device=dev)
+    except Exception as e:           # noqa: BLE001 - reported in the JSON line, the eager number stands
+        graph_err = f"{type(e).__name__}: {e}"[:200]
+        try:
+            torch.cuda.synchronize()
+        except Exception:            # noqa: BLE001
+            pass
+        okflag = torch.zeros(1, device=dev)
+    dist.all_reduce(okflag, op=dist.ReduceOp.MIN)
+    if float(okflag) > 0:
+        for _ in range(warmup):
+            gph.replay()
+        graph_ms = timed(lambda i: gph.replay(), steps, barrier)
+        graph_parity = O.rel_l2(out_sp.cpu(), out_g.cpu())
     # the exchange alone: two all-gathers of (G, S) and the four combines of a step, on tensors of the same size
     B, H, D = cfg["B"], cfg["H"], cfg["D"]
     Gl = torch.zeros(B, H, D, device=dev)
@@ -628,12 +658,18 @@ def run_cfg4(lib, dev, rank, world, barrier, steps=5, warmup=2):
     barrier()
     wt = int(lib.gla_device_wait_timeouts())
     ms, ms_ex = reduce_max([ms, ms_ex], dev, world)
+    if graph_ms is not None:
+        (graph_ms,) = reduce_max([graph_ms], dev, world)
     per = ms / steps
     return {"workload": cfg["what"], "parallelism": f"sequence split over {world} ranks ({L} tokens each), one all-gather of "
             f"(G, S) per direction over NCCL + local combine", "scaling": "strong",
             "tokens_per_s": cfg["B"] * T / (per * 1e-3), "ms_per_step": per, "steps": steps,
             "exchange_ms_per_step": ms_ex / steps, "single_gpu_whole_sequence_ms": single,
             "speedup_vs_single_gpu": None if single is None else single / per,
+            "graph_replay_ms_per_step": None if graph_ms is None else graph_ms / steps,
+            "graph_replay_speedup_vs_single_gpu": None if (single is None or graph_ms is None) else single / (graph_ms / steps),
+            "graph_replay_out_rel_l2_vs_eager": None if graph_ms is None else graph_parity,
+            "graph_capture_error": graph_err,
             "parity_vs_single_gpu": parity, "device_wait_timeouts": wt}
 
 
