@@ -253,6 +253,15 @@ struct FwdSmem {
 // one anchor for the whole chunk every decay weight stays within exp(+-limit), far inside the range of bf16 and
 // float32, so the dyadic levels (which exist to keep exponents non-positive, gla.py:986-993) collapse into one.
 constexpr float ONE_SCALE_LIMIT = 60.f;
+// Between the two limits the single anchor still serves if it is put in the MIDDLE of the chunk's decay instead of
+// at an end: every feature d gets the anchor value m_d = -(sum_rows |g|) / 2, q~ = q exp(lam - m) and
+// k~ = k exp(m - lam) then stay within exp(+-limit / 2), and the one operand per side that must be anchored at the
+// chunk's end for the inter-chunk products (q_hat in the forward, k_hat in the backward) is replaced by the
+// balanced one with the factor exp(-m_d) moved onto the rows of the state tile (S_prev, resp. dS_next), which are
+// rescaled in shared memory.  Sharp gates (log_sigmoid(N(0,1)): about -103 per chunk) run this way; chunks beyond
+// the second limit take all levels.  In the backward the transposed accumulators then hold values up to
+// exp(limit / 2) |k| |dP| 128, which is what bounds the limit (float32 overflows at exp(88.7)).
+constexpr float BALANCED_LIMIT = 140.f;
 constexpr uint32_t KC_TILE = 64 * 128;    // one SW128 tile of 64 rows
 
 // TMA descriptors of one launch (built on the host per call, passed by value).
@@ -454,7 +463,8 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, 
   }
   __syncthreads();          // raw g, q, k have been consumed (their regions become operand buffers); tot and gab are visible
   // One scale or all of them: the chunk's total |log decay| per feature decides, the same way for every thread.
-  bool one_scale;
+  bool one_scale, balanced;
+  float2 anchor = make_float2(1.f, 1.f);
   {
     float2 tsum = make_float2(0.f, 0.f);
 #pragma unroll
@@ -462,9 +472,17 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, 
       const float2 t = *reinterpret_cast<const float2*>(gab + r2 * TD + 2 * cp);
       tsum.x += t.x; tsum.y += t.y;
     }
-    // (a NaN gate fails the comparison and takes the general path)
-    const int over = !(tsum.x <= ONE_SCALE_LIMIT && tsum.y <= ONE_SCALE_LIMIT) || all_scales != 0;
-    one_scale = __syncthreads_or(over) == 0;
+    // (a NaN gate fails the comparisons and takes the general path)
+    // (mild chunks, the common case, pay one block-wide vote; only a chunk that fails it takes the second)
+    one_scale = __syncthreads_or(!(tsum.x <= ONE_SCALE_LIMIT && tsum.y <= ONE_SCALE_LIMIT) || all_scales != 0) == 0;
+    balanced = false;
+    if (!one_scale) balanced = one_scale = __syncthreads_or(!(tsum.x <= BALANCED_LIMIT && tsum.y <= BALANCED_LIMIT) || all_scales != 0) == 0;
+    if (balanced) {
+      // exp(-m_d) = exp(sum |g| / 2) for the thread's two features; row group 0 leaves exp(m_d) for the rescaling of
+      // the state tile (the |g| sums have been read by everybody: two barriers back)
+      anchor = make_float2(__expf(0.5f * tsum.x), __expf(0.5f * tsum.y));
+      if (rg == 0) *reinterpret_cast<float2*>(gab + 2 * cp) = make_float2(1.f / anchor.x, 1.f / anchor.y);
+    }
   }
   const uint32_t sQ0 = smem_u32(sm + FwdSmem::Q), sK0 = smem_u32(sm + FwdSmem::K);
   uint8_t* sQb[2] = {sm + FwdSmem::Q, sm + FwdSmem::Q + 2 * TILE_BYTES};
@@ -477,7 +495,7 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, 
     // (1 / prod of the gates up to the end of the thread's run) x (running product back from that end),
     // so it costs two reciprocals per thread.
     {
-      float2 crossq = make_float2(1.f, 1.f);
+      float2 crossq = anchor;                           // 1, or exp(-m_d) with the balanced anchor
       for (int r2 = 0; r2 < rg; ++r2) {
         const float2 t = *reinterpret_cast<const float2*>(tot + r2 * TD + 2 * cp);
         crossq.x *= t.x; crossq.y *= t.y;
@@ -702,6 +720,30 @@ tc_chunk_fwd_kernel(const __grid_constant__ FwdMaps maps, int64_t T, int64_t H, 
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
+  if (balanced) {
+    // the q_hat operand carries exp(-m_d): row d of the state tile takes exp(m_d) before the product.  Every thread
+    // waits for the tile itself here (a block that started beside the state kernel requests it first).
+    if (tid == 32 && *s_pending_sm != 0u) {
+      if (!fwd_load_state_late(state_done, state_target, &maps.s, smem_u32(sm + FwdSmem::S), (int)(chunk_id * TD), smem_u32(bars + 4)))
+        atomicAdd(&g_tc_wait_timeouts, 1u);
+      *s_pending_sm = 0u;
+    }
+    __syncwarp();
+    ok = mbar_wait(smem_u32(bars + 4), 0) && ok;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int id = tid + TTHREADS * j, row = id >> 4, ch = id & 15;
+      const float w = gab[row];
+      uint4* p4 = reinterpret_cast<uint4*>(sm + FwdSmem::S + (ch >> 3) * TILE_BYTES + sw128_chunk(row, ch & 7));
+      uint4 u = *p4;
+      float2 a = unpack_bf16x2(u.x), b2 = unpack_bf16x2(u.y), c2 = unpack_bf16x2(u.z), d2 = unpack_bf16x2(u.w);
+      u.x = pack_bf16x2(a.x * w, a.y * w); u.y = pack_bf16x2(b2.x * w, b2.y * w);
+      u.z = pack_bf16x2(c2.x * w, c2.y * w); u.w = pack_bf16x2(d2.x * w, d2.y * w);
+      *p4 = u;
+    }
+    fence_async_smem();
+    __syncthreads();
+  }
   if (tid == 0) {
     ok = mbar_wait(smem_u32(bars + 4), 0) && ok;       // v and S_prev have landed (long ago, as a rule)
     tc_fence_after();
@@ -885,6 +927,23 @@ __device__ __forceinline__ float bf16_lo(uint32_t u) { return __uint_as_float(u 
 __device__ __forceinline__ float bf16_hi(uint32_t u) { return __uint_as_float(u & 0xffff0000u); }
 __device__ __forceinline__ void st_bf16(uint8_t* p, float v) { *reinterpret_cast<bf16*>(p) = __float2bfloat16_rn(v); }
 
+// Out of line on purpose (inlined, even skipped, it cost the common path 5 us per launch): the balanced anchor's
+// rescaling of the dS_next tile.  Row d of the tile takes w = 1 / A (this thread: its columns 32 wq + [0, 32)), so that
+// k_hat dS_next and dS_next V^T come out as with the end anchor, the latter divided by A like the dk~ term that joins
+// it.  Waits (bounded) for the tile to have landed first and leaves it alone if it has not.
+__device__ __noinline__ void bwd_rescale_ds(uint8_t* ds, uint32_t bar, float w, int d, int wq) {
+  if (!mbar_wait(bar, 0)) return;
+  uint8_t* td = ds + (wq >> 1) * TILE_BYTES;
+#pragma unroll
+  for (int c4 = 0; c4 < 4; ++c4) {
+    uint4* p4 = reinterpret_cast<uint4*>(td + sw128_chunk(d, (wq & 1) * 4 + c4));
+    uint4 u = *p4;
+    u.x = pack_bf16x2(bf16_lo(u.x) * w, bf16_hi(u.x) * w); u.y = pack_bf16x2(bf16_lo(u.y) * w, bf16_hi(u.y) * w);
+    u.z = pack_bf16x2(bf16_lo(u.z) * w, bf16_hi(u.z) * w); u.w = pack_bf16x2(bf16_lo(u.w) * w, bf16_hi(u.w) * w);
+    *p4 = u;
+  }
+}
+
 __global__ void __launch_bounds__(TTHREADS, 1)
 tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, int R, int64_t N, int pf_dist, const float* __restrict__ g, const bf16* __restrict__ v,
                     const bf16* __restrict__ k, const bf16* __restrict__ q, const bf16* __restrict__ dO,
@@ -993,10 +1052,16 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
   const uint32_t tmem = *tmem_slot;
   // One scale or all of them (see ONE_SCALE_LIMIT): decided from the chunk's total |log decay| per feature, the
   // same way for every thread of the block.
-  bool one_scale;
+  bool one_scale, balanced;
+  float A = 1.f;
   {
     const float tsum = (gab[d] + gab[TD + d]) + (gab[2 * TD + d] + gab[3 * TD + d]);
     one_scale = __syncthreads_or(!(tsum <= ONE_SCALE_LIMIT) || all_scales != 0) == 0;
+    balanced = false;
+    if (!one_scale) balanced = one_scale = __syncthreads_or(!(tsum <= BALANCED_LIMIT) || all_scales != 0) == 0;
+    // balanced anchor (see BALANCED_LIMIT): A = exp(-m_d) = exp(sum |g| / 2) rides on k_hat, its inverse on the rows
+    // of the dS_next tile and on q~
+    if (balanced) A = __expf(0.5f * tsum);
   }
   if (tid == 0) {
     // every thread holds its gates, q and k in registers (two barriers back): the landing zones take the three late
@@ -1012,8 +1077,8 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
     }
   }
   {
-    // k_hat[r][d] = k[r][d] * prod_{t > r} f_t   (rows of this thread: 32 wq_ + i)
-    float run = 1.f;
+    // k_hat[r][d] = k[r][d] * prod_{t > r} f_t   (rows of this thread: 32 wq_ + i), times A with the balanced anchor
+    float run = A;
     for (int b2 = 2 * wq_ + 2; b2 < 8; ++b2) run *= tot[b2 * TD + d];
     // stored TRANSPOSED: row = feature dk, columns = chunk rows j, so the thread's 32 values are 64
     // contiguous bytes (four 16-byte stores instead of 32 two-byte ones)
@@ -1035,6 +1100,13 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
+  if (balanced) {
+    // (its wait is not folded into `ok`: measured, that dependency alone cost the common path 3.5 us per launch; a
+    // tile that never lands fails the issuing threads' wait on the same barrier below)
+    bwd_rescale_ds(sm + BwdSmem::DS, smem_u32(bars + 7), 1.f / A, d, wq_);
+    fence_async_smem();
+    __syncthreads();
+  }
 
   // ---- phase 1: the four dense products --------------------------------------------------------------
   // Issued by four threads of four warps on different schedulers (8 to 16 MMAs each instead of 40 from one): the
@@ -1215,7 +1287,7 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
   __syncthreads();      // all readers of the phase-1 tiles are done: the regions can be reused
   tc_fence_after();
 
-  float eG = 1.f;
+  float eG = A;           // exp(G), times A with the balanced anchor (dG2 was formed from the rescaled dS_next tile)
 #pragma unroll
   for (int b2 = 0; b2 < 8; ++b2) eG *= tot[b2 * TD + d];
   // the four partial sums of each dG term in a fixed order: the result does not depend on which warp came first
@@ -1229,8 +1301,11 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
     // two 128 x 128 x 128 products; a thread (feature d, rows 32 wq_ + [0, 32)) then finishes its rows in one pass.
     const uint32_t lane_base = tmem + ((uint32_t)(q4 * 32) << 16);
     const float t0 = tot[(2 * wq_) * TD + d], t1 = tot[(2 * wq_ + 1) * TD + d];
-    float Cq = 1.f, Ck = 1.f;                           // gate products of the rows before / after this thread's 32
-    for (int b2 = 0; b2 < 2 * wq_; ++b2) Cq *= tot[b2 * TD + d];
+    // gate products of the rows before / after this thread's 32; with the balanced anchor Ck and 1 / eG carry A and
+    // 1 / A, which keeps every running product below within exp(+-limit / 2)
+    const float invG = 1.f / eG;
+    float Cq = 1.f, Cqi = invG, Ck = A;       // Cqi: the same product as Cq started from 1 / eG (see the closing pass)
+    for (int b2 = 0; b2 < 2 * wq_; ++b2) { const float t = tot[b2 * TD + d]; Cq *= t; Cqi *= t; }
     for (int b2 = 2 * wq_ + 2; b2 < 8; ++b2) Ck *= tot[b2 * TD + d];
     const uint32_t* st0 = reinterpret_cast<const uint32_t*>(sm + BwdSmem::ST0) + tid;     // this thread's parked (k | q << 16)
     const uint32_t* st1 = reinterpret_cast<const uint32_t*>(sm + BwdSmem::ST1) + tid;
@@ -1281,7 +1356,6 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
     // The operands of the two products are consumed: their regions stage the chunk's dq, dk (bf16) and the dlam suffix
     // sums (float32) row-major, so that they leave for global memory as whole rows instead of two or four bytes per
     // thread and row.
-    const float invG = 1.f / eG;
     float* dlb = reinterpret_cast<float*>(sm + BwdSmem::DLB);
     unsigned short* dqt = reinterpret_cast<unsigned short*>(sm + BwdSmem::DQT);
     unsigned short* dkt = reinterpret_cast<unsigned short*>(sm + BwdSmem::DKT);
@@ -1296,11 +1370,14 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
       tmem_ld16(lane_base + TM_DQH + rb, a);
       tmem_ld16(lane_base + TM_DV + rb, c);
       tmem_ld_wait();
-      float run = hh ? Cq * t0 : Cq;
+      // run = exp(lam_r) for the inter-chunk term (may underflow to zero in a sharp chunk, as the term itself does);
+      // runi = exp(lam_r) / eG for the intra-chunk term, kept as a product of its own so that it never leaves the range
+      float run = hh ? Cq * t0 : Cq, runi = hh ? Cqi * t0 : Cqi;
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
-        run *= f32r[16 * hh + i];          // exp(lam_r)
-        const float dqv = run * fmaf(invG, __uint_as_float(c[i]), __uint_as_float(a[i])) + diag[rb + i] * bf16_lo(qk[i]);
+        run *= f32r[16 * hh + i];
+        runi *= f32r[16 * hh + i];
+        const float dqv = fmaf(runi, __uint_as_float(c[i]), run * __uint_as_float(a[i])) + diag[rb + i] * bf16_lo(qk[i]);
         dl[i] = bf16_hi(qk[i]) * dqv;
         dqt[(rb + i) * TD + d] = __bfloat16_as_ushort(__float2bfloat16_rn(dqv));
       }

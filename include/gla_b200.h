@@ -84,8 +84,9 @@ typedef enum gla_chunk_impl {
  *       a programmatic dependent and its first blocks start on the SMs the state kernel leaves idle).
  *   ALL_SCALES       always run every level of the secondary chunking (gla.py:843-852, 985-1027).  Default: a
  *       chunk whose total |log decay| is at most 60 for every feature uses a single anchor, because all its decay
- *       weights then lie within exp(+-60); sharper chunks take all levels.  The choice is made per chunk on the
- *       device from the gates themselves.
+ *       weights then lie within exp(+-60); up to 140 a single anchor in the middle of the decay (weights within
+ *       exp(+-70), the state tile rescaled to match); sharper chunks take all levels.  The choice is made per chunk
+ *       on the device from the gates themselves.
  *   NO_L2_PREFETCH   no L2 prefetch of the next chunk's operands in the chunk kernels.
  *   STATE_SEGMENTS   cut every head's chunks into runs that separate thread blocks walk from a zero state, then
  *       correct the stored states with the state that really enters each run (the recurrence is linear in it).

@@ -127,20 +127,27 @@ def test_chunk_gla_tcgen05_vs_oracle(cuda_device, B, T, H, shift, zero_init, sca
 
 
 def test_one_scale_limit_is_decided_per_chunk(cuda_device):
-    """A sequence whose chunks alternate between mild gates and gates far too sharp for a single anchor (total log
-    decay of a chunk about -250, where exp() of it underflows): every chunk must take the path its own gates
-    allow, and the result must match the oracle and the all-levels path."""
+    """A sequence whose chunks fall into all three regimes of the secondary chunking: mild gates (one anchor at the
+    chunk's end), total log decay of a chunk between -60 and -140 (one anchor in the middle of the decay, state tile
+    rescaled) and gates far too sharp for a single anchor (about -250 per chunk, where exp() of it underflows).
+    Every chunk must take the path its own gates allow; the result must match the oracle and the all-levels path."""
     from gla_jax_b200 import chunk_gla, _lib
-    B, T, H = 1, 768, 2
+    B, T, H = 1, 1024, 2
     h, g, v, k, q, dhf, do = _case(B, T, H, 128, torch.bfloat16, 29, 5.0)
     g = g.clone()
-    g[:, 128:256] = -2.0 + 0.5 * torch.randn(B, 128, H, 128, generator=torch.Generator().manual_seed(3)).clamp(-2, 2)
-    g[:, 512:640, 1, :64] = -1.9          # only some features of one head cross the limit
+    gen = torch.Generator().manual_seed(3)
+    g[:, 128:256] = -2.0 + 0.5 * torch.randn(B, 128, H, 128, generator=gen).clamp(-2, 2)      # all levels
+    g[:, 256:384] = -0.8 + 0.2 * torch.randn(B, 128, H, 128, generator=gen).clamp(-2, 2)      # about -102: middle anchor
+    g[:, 512:640, 1, :64] = -1.9          # only some features of one head cross the second limit
+    g[:, 640:768, 0, 64:] = -1.05         # -134 for half of the features of one head: middle anchor, close to its limit
+    g[:, 768:896] = -0.45                 # -57.6: still the end anchor
     case = (h, g, v, k, q, dhf, do)
     ref = _oracle(*case)
     got = _run_gpu(chunk_gla, cuda_device, *case, chunk_size=128, impl="tcgen05")
     full = _run_gpu(chunk_gla, cuda_device, *case, chunk_size=128, impl="tcgen05+all_scales")
     assert _lib.load().gla_device_wait_timeouts() == 0
+    for t in (got[0], got[1], *got[2]):
+        assert torch.isfinite(t.float()).all()
     _compare(ref, got, torch.bfloat16, "mixed chunks, per-chunk choice")
     _compare(ref, full, torch.bfloat16, "mixed chunks, all levels")
 
