@@ -51,6 +51,9 @@ SIGNATURES = {
     "gla_scan": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int]),
     "gla_rnn_scan": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
                              c_void_p, c_void_p, c_int, c_int, c_int]),
+    "gla_rnn_scan_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int64]),
+    "gla_rnn_scan_ws": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
+                                c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_size_t]),
     "gla_recurrent_fwd": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p,
                                   c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int]),
     "gla_decode_step": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p,

@@ -150,6 +150,22 @@ int gla_rnn_scan(void* stream, int64_t batch, int64_t T, int64_t K, int64_t V, c
                          out_state, reverse, last_only, kv_dtype == GLA_BF16);
 }
 
+size_t gla_rnn_scan_workspace_bytes(int64_t batch, int64_t T, int64_t K, int64_t V) {
+  if (batch <= 0 || T <= 0 || K <= 0 || V <= 0) return 0;
+  return rnn_scan_ws_bytes(batch, T, K, V);
+}
+
+int gla_rnn_scan_ws(void* stream, int64_t batch, int64_t T, int64_t K, int64_t V, const float* log_fgate,
+                    const void* kv, const float* init_log_fgate, const void* init_kv, float* out_log,
+                    void* out_state, int reverse, int last_only, int kv_dtype, void* workspace, size_t workspace_bytes) {
+  if (!log_fgate || !kv || !out_log || !out_state) return GLA_ERR_NULL_POINTER;
+  if ((init_log_fgate == nullptr) != (init_kv == nullptr)) return GLA_ERR_NULL_POINTER;
+  if (batch <= 0 || T <= 0 || K <= 0 || V <= 0) return GLA_ERR_BAD_DIMS;
+  GLA_TRY(check_dtype(kv_dtype));
+  return launch_rnn_scan((cudaStream_t)stream, batch, T, K, V, log_fgate, kv, init_log_fgate, init_kv, out_log,
+                         out_state, reverse, last_only, kv_dtype == GLA_BF16, (float*)workspace, workspace_bytes);
+}
+
 int gla_recurrent_fwd(void* stream, int64_t B, int64_t T, int64_t H, int64_t D, int dtype, const void* hidden_init,
                       const float* log_fgate, const void* value, const void* key, const void* query,
                       void* hidden_final, void* out, int out_dtype, int reverse) {

@@ -1287,7 +1287,9 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
   __syncthreads();      // all readers of the phase-1 tiles are done: the regions can be reused
   tc_fence_after();
 
-  float eG = A;           // exp(G), times A with the balanced anchor (dG2 was formed from the rescaled dS_next tile)
+  // (A is formed again from the |g| sums here rather than kept in a register across the products and phase 1.5)
+  const float A2 = balanced ? __expf(0.5f * ((gab[d] + gab[TD + d]) + (gab[2 * TD + d] + gab[3 * TD + d]))) : 1.f;
+  float eG = A2;          // exp(G), times A with the balanced anchor (dG2 was formed from the rescaled dS_next tile)
 #pragma unroll
   for (int b2 = 0; b2 < 8; ++b2) eG *= tot[b2 * TD + d];
   // the four partial sums of each dG term in a fixed order: the result does not depend on which warp came first
@@ -1304,7 +1306,7 @@ tc_chunk_bwd_kernel(const __grid_constant__ BwdMaps maps, int64_t T, int64_t H, 
     // gate products of the rows before / after this thread's 32; with the balanced anchor Ck and 1 / eG carry A and
     // 1 / A, which keeps every running product below within exp(+-limit / 2)
     const float invG = 1.f / eG;
-    float Cq = 1.f, Cqi = invG, Ck = A;       // Cqi: the same product as Cq started from 1 / eG (see the closing pass)
+    float Cq = 1.f, Cqi = invG, Ck = A2;      // Cqi: the same product as Cq started from 1 / eG (see the closing pass)
     for (int b2 = 0; b2 < 2 * wq_; ++b2) { const float t = tot[b2 * TD + d]; Cq *= t; Cqi *= t; }
     for (int b2 = 2 * wq_ + 2; b2 < 8; ++b2) Ck *= tot[b2 * TD + d];
     const uint32_t* st0 = reinterpret_cast<const uint32_t*>(sm + BwdSmem::ST0) + tid;     // this thread's parked (k | q << 16)
@@ -1737,14 +1739,29 @@ __global__ void __launch_bounds__(TD) sp_cum_gate_kernel(int64_t N, int nsegs, i
                                                          float* __restrict__ Gs, int reverse) {
   const int64_t bh = blockIdx.x / nsegs, n0 = (blockIdx.x % nsegs) * Ns, n1 = n0 + Ns < N ? n0 + Ns : N;
   const int dd = threadIdx.x;
+  // the flags start at zero and every thread with a non-zero factor raises its chunk's: one barrier for the whole
+  // walk instead of a block-wide vote per chunk (the walk is a chain of additions; the loads do not depend on it)
+  for (int64_t n = n0 + dd; n < n1; n += TD) live[bh * N + n] = 0;
+  __syncthreads();
   float acc = 0.f;
-  for (int64_t i = 0; i < n1 - n0; ++i) {
-    const int64_t n = reverse ? n1 - 1 - i : n0 + i;
-    const float w = __expf(acc);
-    E[(bh * N + n) * TD + dd] = w;
-    const int any = __syncthreads_or(w != 0.f);
-    if (dd == 0) live[bh * N + n] = any;
-    acc += Gc[(bh * N + n) * TD + dd];
+  for (int64_t i0 = 0; i0 < n1 - n0; i0 += 8) {
+    float gq[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {          // eight loads in flight; the chain below is additions only
+      const int64_t i = i0 + u < n1 - n0 ? i0 + u : n1 - n0 - 1;
+      gq[u] = __ldg(Gc + (bh * N + (reverse ? n1 - 1 - i : n0 + i)) * TD + dd);
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int64_t i = i0 + u;
+      if (i < n1 - n0) {
+        const int64_t n = reverse ? n1 - 1 - i : n0 + i;
+        const float w = __expf(acc);
+        E[(bh * N + n) * TD + dd] = w;
+        if (w != 0.f) live[bh * N + n] = 1;
+        acc += gq[u];
+      }
+    }
   }
   if (Gs != nullptr) Gs[(int64_t)blockIdx.x * TD + dd] = acc;       // the run's total log decay, (bh, run, feature)
 }

@@ -142,7 +142,8 @@ int tc_chunk_bwd(cudaStream_t st, int64_t B, int64_t T, int64_t H, int64_t D, in
 namespace gla {
 int launch_rnn_scan(cudaStream_t st, int64_t batch, int64_t T, int64_t K, int64_t V, const float* g,
                     const void* kv, const float* ig, const void* ikv, float* out_log, void* out_state,
-                    int reverse, int last_only, int kv_bf16);
+                    int reverse, int last_only, int kv_bf16, float* ws = nullptr, size_t ws_bytes = 0);
+size_t rnn_scan_ws_bytes(int64_t batch, int64_t T, int64_t K, int64_t V);
 int launch_sp_combine(cudaStream_t st, int64_t R, int64_t rank, int64_t BH, int64_t D, const float* all_G,
                       const float* all_S, const void* init, int init_bf16, void* result, int result_bf16,
                       int reverse);

@@ -512,26 +512,32 @@ int launch_cumsum(cudaStream_t st, int64_t N, int64_t T, int64_t D, const void* 
 // current ones: the recurrence is a chain, so what the kernel can overlap is the memory latency of later steps.
 // The scalar form below serves value widths that are not multiples of four.
 // ---------------------------------------------------------------------------------------
-template <typename TKV>
+template <typename TKV, bool RUNS>
 __global__ void __launch_bounds__(128) rnn_scan_vec4_kernel(int64_t T, int64_t K, int64_t V, int64_t nblk,
                                                             const float* __restrict__ g, const TKV* __restrict__ kv,
                                                             const float* __restrict__ ig, const TKV* __restrict__ ikv,
                                                             float* __restrict__ out_log, TKV* __restrict__ out_state,
-                                                            int reverse, int last_only) {
+                                                            int reverse, int last_only, int nseg, int64_t L) {
   constexpr int UNR = 4;
-  const int64_t prob = blockIdx.x / nblk;
+  // nseg > 1: the axis is cut into runs of L scan positions that separate blocks scan, every run but the first from
+  // the identity; rnn_carry_kernel / rnn_fix_kernel below then put the runs together (long axes with few rows)
+  // (RUNS == false is the plain scan: the run arithmetic folds away)
+  const int64_t prob2 = blockIdx.x / nblk, prob = RUNS ? prob2 / nseg : prob2, seg = RUNS ? prob2 % nseg : 0;
   const int64_t e4 = (blockIdx.x % nblk) * 128 + threadIdx.x;      // group of four value columns
   const int64_t KV = K * V, V4 = V / 4;
   if (e4 >= K * V4) return;
   const int64_t kk = e4 / V4, e = e4 * 4;
   const bool writes_log = (e4 % V4) == 0;
-  float A = ig ? ig[prob * K + kk] : 0.f;
-  float4 b = ikv ? ld4_f(ikv + prob * KV + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+  float A = (ig && seg == 0) ? ig[prob * K + kk] : 0.f;
+  float4 b = (ikv && seg == 0) ? ld4_f(ikv + prob * KV + e) : make_float4(0.f, 0.f, 0.f, 0.f);
   const float* gp = g + prob * T * K + kk;
   const TKV* xp = kv + prob * T * KV + e;
   TKV* op = out_state + prob * T * KV + e;
   float* lp = out_log + prob * T * K + kk;
-  auto tix = [&](int64_t s) { return reverse ? (T - 1 - s) : s; };
+  const int64_t s_beg = RUNS ? seg * L : 0;
+  const int64_t Tfull = T;
+  if (RUNS) T = Tfull - s_beg < L ? Tfull - s_beg : L;             // scan positions of this run (T below: the run's)
+  auto tix = [&](int64_t s) { return reverse ? (Tfull - 1 - (s_beg + s)) : s_beg + s; };
   float gn[UNR];
   float4 xn[UNR];
 #pragma unroll
@@ -570,6 +576,66 @@ __global__ void __launch_bounds__(128) rnn_scan_vec4_kernel(int64_t T, int64_t K
   }
 }
 
+// The runs of a segmented scan put together.  carry (one thread per four value columns, sequential over the runs):
+// the true pair at the end of run s - 1, C_s = (CL_s, CS_s), from the runs' local last rows
+//   C_1 = local last row of run 0 (which started from the caller's initial pair),
+//   CL_{s+1} = CL_s + l_s,   CS_{s+1} = exp(l_s) CS_s + x_s        (l_s, x_s: local last row of run s),
+// into wsL (batch, nseg, K) and wsS (batch, nseg, K, V), float32.
+template <typename TKV>
+__global__ void __launch_bounds__(128) rnn_carry_kernel(int64_t T, int64_t K, int64_t V, int64_t nblk, int nseg, int64_t L,
+                                                        const float* __restrict__ out_log, const TKV* __restrict__ out_state,
+                                                        float* __restrict__ wsL, float* __restrict__ wsS, int reverse) {
+  const int64_t prob = blockIdx.x / nblk;
+  const int64_t e4 = (blockIdx.x % nblk) * 128 + threadIdx.x;
+  const int64_t KV = K * V, V4 = V / 4;
+  if (e4 >= K * V4) return;
+  const int64_t kk = e4 / V4, e = e4 * 4;
+  const bool writes_log = (e4 % V4) == 0;
+  float CL = 0.f;
+  float4 CS = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int sg = 0; sg < nseg; ++sg) {
+    if (sg > 0) {
+      if (writes_log) wsL[(prob * nseg + sg) * K + kk] = CL;
+      *reinterpret_cast<float4*>(wsS + (prob * nseg + sg) * KV + e) = CS;
+    }
+    const int64_t last = (sg + 1) * L < T ? (sg + 1) * L - 1 : T - 1;      // scan position of the run's last row
+    const int64_t row = reverse ? T - 1 - last : last;
+    const float l = out_log[(prob * T + row) * K + kk];
+    const float4 x = ld4_f(out_state + (prob * T + row) * KV + e);
+    const float f = expf(l);
+    CS = make_float4(fmaf(f, CS.x, x.x), fmaf(f, CS.y, x.y), fmaf(f, CS.z, x.z), fmaf(f, CS.w, x.w));
+    CL += l;
+  }
+}
+// fix (one thread per row and four value columns, rows of the runs after the first): state = exp(local log) C_S + local
+// state.  The logs are corrected by rnn_fix_log_kernel afterwards (this kernel reads the local ones).
+template <typename TKV>
+__global__ void __launch_bounds__(256) rnn_fix_kernel(int64_t batch, int64_t T, int64_t K, int64_t V, int nseg, int64_t L,
+                                                      const float* __restrict__ out_log, TKV* __restrict__ out_state,
+                                                      const float* __restrict__ wsS, int reverse) {
+  const int64_t KV4 = K * (V / 4), rows = T - L;
+  const int64_t id = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (id >= batch * rows * KV4) return;
+  const int64_t e4 = id % KV4, pos = L + (id / KV4) % rows, prob = id / KV4 / rows;
+  const int64_t kk = e4 / (V / 4), e = e4 * 4, sg = pos / L;
+  const int64_t row = reverse ? T - 1 - pos : pos;
+  const float f = expf(out_log[(prob * T + row) * K + kk]);
+  const float4 c = *reinterpret_cast<const float4*>(wsS + (prob * nseg + sg) * K * V + e);
+  TKV* p = out_state + (prob * T + row) * K * V + e;
+  const float4 x = ld4_f(p);
+  st4_f(p, make_float4(fmaf(f, c.x, x.x), fmaf(f, c.y, x.y), fmaf(f, c.z, x.z), fmaf(f, c.w, x.w)));
+}
+__global__ void __launch_bounds__(256) rnn_fix_log_kernel(int64_t batch, int64_t T, int64_t K, int nseg, int64_t L,
+                                                          float* __restrict__ out_log, const float* __restrict__ wsL,
+                                                          int reverse) {
+  const int64_t rows = T - L;
+  const int64_t id = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (id >= batch * rows * K) return;
+  const int64_t kk = id % K, pos = L + (id / K) % rows, prob = id / K / rows;
+  const int64_t row = reverse ? T - 1 - pos : pos;
+  out_log[(prob * T + row) * K + kk] += wsL[(prob * nseg + pos / L) * K + kk];
+}
+
 template <typename TKV>
 __global__ void __launch_bounds__(256) rnn_scan_kernel(int64_t T, int64_t K, int64_t V, int64_t nblk,
                                                        const float* __restrict__ g, const TKV* __restrict__ kv,
@@ -600,22 +666,67 @@ __global__ void __launch_bounds__(256) rnn_scan_kernel(int64_t T, int64_t K, int
   }
 }
 
+// Runs for a long axis with few rows: enough blocks for the device, runs of at least 128 positions.
+static void rnn_scan_runs(int64_t batch, int64_t T, int64_t K, int64_t V, int* nseg, int64_t* L) {
+  *nseg = 1; *L = T;
+  if (V % 4 != 0 || T < 512) return;
+  const int64_t blocks = batch * ((K * (V / 4) + 127) / 128);
+  if (blocks >= 2 * 148) return;
+  int64_t want = (4 * 148 + blocks - 1) / blocks;
+  if (want > T / 128) want = T / 128;
+  if (want < 2) return;
+  *L = (T + want - 1) / want;
+  *nseg = (int)((T + *L - 1) / *L);
+}
+size_t rnn_scan_ws_bytes(int64_t batch, int64_t T, int64_t K, int64_t V) {
+  int nseg; int64_t L;
+  rnn_scan_runs(batch, T, K, V, &nseg, &L);
+  return nseg > 1 ? (size_t)(batch * nseg * (K + K * V)) * sizeof(float) + 16 : 0;
+}
+
 int launch_rnn_scan(cudaStream_t st, int64_t batch, int64_t T, int64_t K, int64_t V, const float* g,
                     const void* kv, const float* ig, const void* ikv, float* out_log, void* out_state,
-                    int reverse, int last_only, int kv_bf16) {
+                    int reverse, int last_only, int kv_bf16, float* ws, size_t ws_bytes) {
   ProfScope ps("rnn_scan_kernel", st);
   const bool al = (((uintptr_t)kv | (uintptr_t)out_state | (uintptr_t)ikv) & 15) == 0;
   if (V % 4 == 0 && al) {
     int64_t nblk = (K * (V / 4) + 127) / 128;
-    if (nblk * batch > 2147483647LL) return GLA_ERR_TOO_LARGE;
-    dim3 grid((unsigned)(nblk * batch)), block(128);
-    if (kv_bf16)
-      rnn_scan_vec4_kernel<bf16><<<grid, block, 0, st>>>(T, K, V, nblk, g, (const bf16*)kv, ig, (const bf16*)ikv,
-                                                         out_log, (bf16*)out_state, reverse, last_only);
+    int nseg = 1; int64_t L = T;
+    if (ws != nullptr && !last_only && ((uintptr_t)ws & 15) == 0) {
+      rnn_scan_runs(batch, T, K, V, &nseg, &L);
+      if (ws_bytes < (size_t)(batch * nseg * (K + K * V)) * sizeof(float) + 16) { nseg = 1; L = T; }
+    }
+    if (nblk * batch * nseg > 2147483647LL) return GLA_ERR_TOO_LARGE;
+    dim3 grid((unsigned)(nblk * batch * nseg)), block(128);
+    if (kv_bf16 && nseg > 1)
+      rnn_scan_vec4_kernel<bf16, true><<<grid, block, 0, st>>>(T, K, V, nblk, g, (const bf16*)kv, ig, (const bf16*)ikv,
+                                                               out_log, (bf16*)out_state, reverse, last_only, nseg, L);
+    else if (kv_bf16)
+      rnn_scan_vec4_kernel<bf16, false><<<grid, block, 0, st>>>(T, K, V, nblk, g, (const bf16*)kv, ig, (const bf16*)ikv,
+                                                                out_log, (bf16*)out_state, reverse, last_only, 1, T);
+    else if (nseg > 1)
+      rnn_scan_vec4_kernel<float, true><<<grid, block, 0, st>>>(T, K, V, nblk, g, (const float*)kv, ig, (const float*)ikv,
+                                                                out_log, (float*)out_state, reverse, last_only, nseg, L);
     else
-      rnn_scan_vec4_kernel<float><<<grid, block, 0, st>>>(T, K, V, nblk, g, (const float*)kv, ig, (const float*)ikv,
-                                                          out_log, (float*)out_state, reverse, last_only);
+      rnn_scan_vec4_kernel<float, false><<<grid, block, 0, st>>>(T, K, V, nblk, g, (const float*)kv, ig, (const float*)ikv,
+                                                                 out_log, (float*)out_state, reverse, last_only, 1, T);
     GLA_CHECK_LAUNCH();
+    if (nseg > 1) {
+      float* wsL = ws;
+      float* wsS = ws + batch * nseg * K;      // batch * nseg * K floats: a multiple of 16 bytes when K % 4 == 0
+      if ((batch * nseg * K) % 4 != 0) wsS += 4 - (batch * nseg * K) % 4;
+      const int64_t nfix = batch * (T - L) * K * (V / 4), nlog = batch * (T - L) * K;
+      if ((nfix + 255) / 256 > 2147483647LL) return GLA_ERR_TOO_LARGE;
+      if (kv_bf16) {
+        rnn_carry_kernel<bf16><<<(unsigned)(nblk * batch), 128, 0, st>>>(T, K, V, nblk, nseg, L, out_log, (const bf16*)out_state, wsL, wsS, reverse);
+        rnn_fix_kernel<bf16><<<(unsigned)((nfix + 255) / 256), 256, 0, st>>>(batch, T, K, V, nseg, L, out_log, (bf16*)out_state, wsS, reverse);
+      } else {
+        rnn_carry_kernel<float><<<(unsigned)(nblk * batch), 128, 0, st>>>(T, K, V, nblk, nseg, L, out_log, (const float*)out_state, wsL, wsS, reverse);
+        rnn_fix_kernel<float><<<(unsigned)((nfix + 255) / 256), 256, 0, st>>>(batch, T, K, V, nseg, L, out_log, (float*)out_state, wsS, reverse);
+      }
+      rnn_fix_log_kernel<<<(unsigned)((nlog + 255) / 256), 256, 0, st>>>(batch, T, K, nseg, L, out_log, wsL, reverse);
+      GLA_CHECK_LAUNCH();
+    }
     return GLA_OK;
   }
   int64_t nblk = (K * V + 255) / 256;

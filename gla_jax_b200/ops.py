@@ -112,10 +112,14 @@ def rnn_pallas(log_fgate, kv, init_log_fgate: Optional[torch.Tensor] = None,
     ikv = None if init_kv is None else init_kv.to(kv.dtype).contiguous()
     out_log = torch.zeros(Bn, T, K, dtype=torch.float32, device=kv.device)
     out_state = torch.zeros_like(x)
-    st = lib.gla_rnn_scan(_stream(kv.device), Bn, T, K, V, g.data_ptr(), x.data_ptr(),
-                          None if ig is None else ig.data_ptr(), None if ikv is None else ikv.data_ptr(),
-                          out_log.data_ptr(), out_state.data_ptr(), int(reverse), int(last_only), _DT[kv.dtype])
-    _lib.check(st, "gla_rnn_scan")
+    # scratch for long axes with few rows (0 bytes when the plain scan serves)
+    nws = 0 if last_only else lib.gla_rnn_scan_workspace_bytes(Bn, T, K, V)
+    ws = torch.empty(nws, dtype=torch.uint8, device=kv.device) if nws else None
+    st = lib.gla_rnn_scan_ws(_stream(kv.device), Bn, T, K, V, g.data_ptr(), x.data_ptr(),
+                             None if ig is None else ig.data_ptr(), None if ikv is None else ikv.data_ptr(),
+                             out_log.data_ptr(), out_state.data_ptr(), int(reverse), int(last_only), _DT[kv.dtype],
+                             None if ws is None else ws.data_ptr(), nws)
+    _lib.check(st, "gla_rnn_scan_ws")
     out_log = out_log.to(log_fgate.dtype)
     return (out_log, out_state) if batched else (out_log[0], out_state[0])
 

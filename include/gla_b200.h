@@ -231,6 +231,19 @@ GLA_API int gla_rnn_scan(void* stream, int64_t batch, int64_t T, int64_t K, int6
                  float* out_log, void* out_state,
                  int reverse, int last_only, int kv_dtype);
 
+/* The same scan with scratch for long axes with few rows (the case ops.py:396-456 rnn_recursive serves by
+ * recursion): when batch x K x V alone gives the device too few threads and T >= 512, the axis is cut into runs
+ * that separate thread blocks scan from the identity, a small kernel scans the runs' last rows and one pass adds
+ * exp(local log decay) x (state entering the run) to every row after the first run.  workspace:
+ * gla_rnn_scan_workspace_bytes (0 when the plain scan is used anyway; a NULL or short workspace also selects it).
+ * Results agree with gla_rnn_scan to rounding (the order of the additions differs). */
+GLA_API size_t gla_rnn_scan_workspace_bytes(int64_t batch, int64_t T, int64_t K, int64_t V);
+GLA_API int gla_rnn_scan_ws(void* stream, int64_t batch, int64_t T, int64_t K, int64_t V,
+                 const float* log_fgate, const void* kv,
+                 const float* init_log_fgate, const void* init_kv,
+                 float* out_log, void* out_state,
+                 int reverse, int last_only, int kv_dtype, void* workspace, size_t workspace_bytes);
+
 /* ------------------------------------------------------------------------------------
  * recurrent_gla — replaces gla.py:405 recurrent_gla (forward: gla.py:99, kernel gla.py:50)
  * and, with out_dtype = GLA_F32, gla.py:26 recurrent_gla_naive.

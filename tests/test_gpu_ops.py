@@ -347,6 +347,10 @@ def test_cumsum_inner_axis_layout(cuda_device):
 @pytest.mark.parametrize("T,K,V,reverse,with_init,dtype", [
     (20, 5, 4, False, True, torch.float32), (32, 128, 128, True, True, torch.float32),
     (300, 16, 24, False, False, torch.float32), (64, 64, 64, False, True, torch.bfloat16),
+    # long axes with few rows: cut into runs scanned by separate blocks and put together afterwards (7 runs of 143
+    # and 142 positions; 5 runs with a short last one)
+    (1000, 32, 32, False, True, torch.float32), (1000, 32, 32, True, True, torch.float32),
+    (641, 16, 64, True, False, torch.float32), (1000, 32, 32, False, True, torch.bfloat16),
 ])
 def test_rnn_scan_vs_oracle(cuda_device, T, K, V, reverse, with_init, dtype):
     from gla_jax_b200 import rnn_recursive, rnn_pallas
@@ -367,6 +371,27 @@ def test_rnn_scan_vs_oracle(cuda_device, T, K, V, reverse, with_init, dtype):
     A2, S2 = rnn_pallas(mv(g), mv(kv), mv(ig), mv(ikv), reverse=reverse, last_only=True)
     last = 0 if reverse else T - 1
     assert O.rel_l2(A0[last], A2[last].cpu()) < 1e-5 and O.rel_l2(S0[last], S2[last].cpu().float()) < tol
+
+
+def test_rnn_scan_long_axis_in_runs_matches_the_single_walk(cuda_device):
+    """The segmented form of the linear-RNN scan (chosen for long axes with few rows) against the single sequential
+    walk of the same library (gla_rnn_scan, no scratch), batched, both directions."""
+    from gla_jax_b200 import rnn_pallas, _lib
+    lib = _lib.load()
+    Bn, T, K, V = 2, 2048, 16, 32
+    assert lib.gla_rnn_scan_workspace_bytes(Bn, T, K, V) > 0 and lib.gla_rnn_scan_workspace_bytes(64, T, 128, 128) == 0
+    gen = torch.Generator().manual_seed(12)
+    g = (-0.1 * torch.rand(Bn, T, K, generator=gen)).to(cuda_device)
+    kv = torch.randn(Bn, T, K, V, generator=gen).to(cuda_device)
+    ig = (-torch.rand(Bn, K, generator=gen)).to(cuda_device)
+    ikv = torch.randn(Bn, K, V, generator=gen).to(cuda_device)
+    stream = torch.cuda.current_stream(cuda_device).cuda_stream
+    for reverse in (False, True):
+        A1, S1 = rnn_pallas(g, kv, ig, ikv, reverse=reverse)
+        A0, S0 = torch.zeros_like(g), torch.zeros_like(kv)
+        _lib.check(lib.gla_rnn_scan(stream, Bn, T, K, V, g.data_ptr(), kv.data_ptr(), ig.data_ptr(), ikv.data_ptr(),
+                                    A0.data_ptr(), S0.data_ptr(), int(reverse), 0, _lib.GLA_F32), "gla_rnn_scan")
+        assert O.rel_l2(A0.cpu(), A1.cpu()) < 1e-6 and O.rel_l2(S0.cpu(), S1.cpu()) < 1e-5, reverse
 
 
 def test_chunk_equals_recurrent_on_gpu_full_size_slice(cuda_device):
