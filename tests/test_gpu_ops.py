@@ -303,6 +303,10 @@ def test_golden_fixtures_on_gpu(cuda_device):
     # lengths that are no multiple of its 128-row tile, both directions, both element types
     (2, 1000, 128, False, True, torch.float32), (3, 333, 160, True, True, torch.float32),
     (2, 515, 256, True, True, torch.bfloat16), (1, 128, 768, False, False, torch.bfloat16),
+    # the float32 pipeline at its edges: exactly two tiles, one position more (reversed: a first tile of one row),
+    # a last column block of four columns, more (row, column block) items than SMs
+    (4, 128, 256, False, True, torch.float32), (2, 129, 128, True, False, torch.float32),
+    (2, 200, 132, False, True, torch.float32), (40, 192, 512, True, True, torch.float32),
 ])
 def test_cumsum_vs_oracle(cuda_device, N, T, D, reverse, with_init, dtype):
     from gla_jax_b200 import cumsum_recursive, cumsum_pallas
@@ -371,6 +375,36 @@ def test_rnn_scan_vs_oracle(cuda_device, T, K, V, reverse, with_init, dtype):
     A2, S2 = rnn_pallas(mv(g), mv(kv), mv(ig), mv(ikv), reverse=reverse, last_only=True)
     last = 0 if reverse else T - 1
     assert O.rel_l2(A0[last], A2[last].cpu()) < 1e-5 and O.rel_l2(S0[last], S2[last].cpu().float()) < tol
+
+
+def test_sp_combine2_matches_two_calls_of_sp_combine(cuda_device):
+    """The one-launch combine (state entering a rank's slice + state leaving the last slice, from packed [G | S]
+    records addressed through rank strides) against two calls of gla_sp_combine on separate arrays."""
+    from gla_jax_b200 import _lib
+    lib = _lib.load()
+    R, BH, D = 5, 3, 128
+    gen = torch.Generator().manual_seed(21)
+    nG, nS = BH * D, BH * D * D
+    packed = torch.randn(R, nG + nS, generator=gen)
+    packed[:, :nG] = -packed[:, :nG].abs()
+    packed = packed.to(cuda_device)
+    init = torch.randn(BH, D, D, generator=gen).bfloat16().to(cuda_device)
+    all_G, all_S = packed[:, :nG].contiguous(), packed[:, nG:].contiguous()
+    stream = torch.cuda.current_stream(cuda_device).cuda_stream
+    for reverse in (0, 1):
+        for rank in range(R):
+            ent = torch.empty(BH, D, D, device=cuda_device)
+            tot = torch.empty(BH, D, D, dtype=torch.bfloat16, device=cuda_device)
+            _lib.check(lib.gla_sp_combine2(stream, R, rank, BH, D, packed.data_ptr(), nG + nS, packed.data_ptr() + 4 * nG, nG + nS,
+                                           init.data_ptr(), _lib.GLA_BF16, ent.data_ptr(), tot.data_ptr(), _lib.GLA_BF16, reverse),
+                       "gla_sp_combine2")
+            ent0 = torch.empty_like(ent)
+            tot0 = torch.empty_like(tot)
+            _lib.check(lib.gla_sp_combine(stream, R, rank, BH, D, all_G.data_ptr(), all_S.data_ptr(), init.data_ptr(), _lib.GLA_BF16,
+                                          ent0.data_ptr(), _lib.GLA_F32, reverse), "gla_sp_combine")
+            _lib.check(lib.gla_sp_combine(stream, R, -1 if reverse else R, BH, D, all_G.data_ptr(), all_S.data_ptr(), init.data_ptr(),
+                                          _lib.GLA_BF16, tot0.data_ptr(), _lib.GLA_BF16, reverse), "gla_sp_combine")
+            assert torch.equal(ent, ent0) and torch.equal(tot, tot0), (reverse, rank)
 
 
 def test_rnn_scan_long_axis_in_runs_matches_the_single_walk(cuda_device):
