@@ -643,17 +643,21 @@ def run_cfg4(lib, dev, rank, world, barrier, steps=5, warmup=2):
             gph.replay()
         graph_ms = timed(lambda i: gph.replay(), steps, barrier)
         graph_parity = O.rel_l2(out_sp.cpu(), out_g.cpu())
-    # the exchange alone: two all-gathers of (G, S) and the four combines of a step, on tensors of the same size
+    # the exchange alone: the all-gathers and combine launches of a step, on tensors of the same size
     B, H, D = cfg["B"], cfg["H"], cfg["D"]
     Gl = torch.zeros(B, H, D, device=dev)
     Sl = torch.zeros(B, H, D, D, device=dev)
     ops = P.CudaOps()
 
     def exch(_i=0):
-        for rev in (False, True):
-            aG, aS = P._all_gather(Gl, None), P._all_gather(Sl, None)
-            ops.combine(aG, aS, rank, h, h.dtype, rev)
-            ops.combine(aG, aS, -1 if rev else world, h, h.dtype, rev)
+        # forward: one all-gather of the packed [G | S] record and one combine launch; backward: one all-gather of A
+        # (G is kept from the forward) and one combine launch
+        nG = Gl.numel()
+        packed = P._all_gather(torch.cat([Gl.reshape(-1), Sl.reshape(-1)]), None)
+        aG, aS = packed[:, :nG].unflatten(1, tuple(Gl.shape)), packed[:, nG:].unflatten(1, tuple(Sl.shape))
+        ops.combine_both(aG, aS, rank, h, h.dtype, False)
+        aA = P._all_gather(Sl, None)
+        ops.combine_both(aG, aA, rank, h, h.dtype, True)
 
     exch()
     ms_ex = timed(exch, steps, barrier)
