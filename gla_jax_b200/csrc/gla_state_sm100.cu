@@ -283,10 +283,12 @@ tc_state_kernel(const __grid_constant__ StMaps maps, int64_t T, int64_t H, int R
       *reinterpret_cast<uint4*>(bop + sw128_chunk(lane, 2 * (w & 3))) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
       *reinterpret_cast<uint4*>(bop + sw128_chunk(lane, 2 * (w & 3) + 1)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
       fence_async_smem();
-      // on behalf of the issuer (these have long completed as a rule; the builders have the slack to check):
-      // accumulator g read out by the updaters (step i-2), and the v / dO tile of step i landed
-      if (i >= 2 && ok) ok = mbar_wait(smem_u32(accfree + g), (uint32_t)(((i - 2) >> 1) & 1));
-      if (ok) ok = mbar_wait(smem_u32(fully + (i % NY)), (uint32_t)((i / NY) & 1));
+      // on behalf of the issuer (these have long completed as a rule): accumulator g read out by the updaters
+      // (step i-2), and the v / dO tile of step i landed.  The issuer goes once ALL warps of the group have arrived,
+      // so one warp checking each condition before its own arrival is enough; even a completed mbarrier costs a
+      // wait some 300 cycles, and the builders' serial path is what paces the kernel (measured with clock stamps).
+      if (w == 0 && i >= 2 && ok) ok = mbar_wait(smem_u32(accfree + g), (uint32_t)(((i - 2) >> 1) & 1));
+      if (w == 1 && ok) ok = mbar_wait(smem_u32(fully + (i % NY)), (uint32_t)((i / NY) & 1));
       bar_arrive(3 + g, READY_COUNT);
     }
     if (!ok && lane == 0) atomicAdd(&g_state_wait_timeouts, 1u);
