@@ -63,8 +63,8 @@ struct StSmem {
   static constexpr uint32_t TOT = BOP + 2 * 8192;           // [2 groups][2][8][32] float: gate products per 16 rows
   static constexpr uint32_t GSUM = TOT + 4 * 8 * SL * 4;    // [2 groups][2][8][32] float: gate sums per 16 rows
   static constexpr uint32_t EG = GSUM + 4 * 8 * SL * 4;     // [4][32] float: e^G of the chunk, by step & 3
-  static constexpr uint32_t BAR = EG + 4 * SL * 4;          // fully[NY], fullgx[NGX], mma[2], accfree[2], egbar[4], tmem slot
-  static constexpr uint32_t END = BAR + 128;
+  static constexpr uint32_t BAR = EG + 4 * SL * 4;          // fully[NY], fullgx[NGX], mma[2], accfree[2], egbar[4], yfree[NY], tmem slot
+  static constexpr uint32_t END = BAR + 192;
 };
 static_assert(StSmem::BOP % 1024 == 0, "operand buffers need 1024-byte alignment");
 constexpr size_t ST_SMEM = 1024 + StSmem::END;
@@ -90,7 +90,9 @@ tc_state_kernel(const __grid_constant__ StMaps maps, int64_t T, int64_t H, int R
   uint64_t* mma = fullgx + NGX;
   uint64_t* accfree = mma + 2;
   uint64_t* egbar = accfree + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(egbar + 4);
+  uint64_t* yfree = egbar + 4;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(yfree + NY);
+  static_assert((NY + NGX + 2 + 2 + 4 + NY) * 8 + 8 <= 192, "barriers and the TMEM slot must fit the space reserved at StSmem::BAR");
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int slice = blockIdx.x & 3;
@@ -137,6 +139,7 @@ tc_state_kernel(const __grid_constant__ StMaps maps, int64_t T, int64_t H, int R
   if (done != nullptr && tid == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (tid == NBUILD + NUPD) {
     for (int s = 0; s < NY; ++s) mbar_init(smem_u32(fully + s), 1);
+    for (int s = 0; s < NY; ++s) mbar_init(smem_u32(yfree + s), 1);
     for (int s = 0; s < NGX; ++s) mbar_init(smem_u32(fullgx + s), 1);
     mbar_init(smem_u32(mma + 0), 1);
     mbar_init(smem_u32(mma + 1), 1);
@@ -184,9 +187,12 @@ tc_state_kernel(const __grid_constant__ StMaps maps, int64_t T, int64_t H, int R
       bar_sync(3 + g, READY_COUNT);          // operand of step j written: its g / k slices are consumed
       if (lane == 0) {
         if (j + NGX < N) load_gx(zgx, sgx);
-        // the product of step j-1 has completed (or is about to): its tile stage takes step j-1+NY
+        // the product of step j-1 has completed (or is about to): its tile stage takes step j-1+NY.  The wait is on
+        // the STAGE's own barrier (the issuer commits every product to it as well): its next completion needs the
+        // tile this thread is about to request, so the phase waited for cannot be overtaken.  (mma[g] also completes
+        // for step j+1 without this thread's help; a parity wait on it that wakes late would miss a phase.)
         if (j >= 1 && j - 1 + NY < N) {
-          if (ok) ok = mbar_wait(smem_u32(mma + (g ^ 1)), (uint32_t)(((j - 1) >> 1) & 1));
+          if (ok) ok = mbar_wait(smem_u32(yfree + sy), (uint32_t)(((j - 1) / NY) & 1));
           load_y(zy, sy);
         }
       }
@@ -215,6 +221,7 @@ tc_state_kernel(const __grid_constant__ StMaps maps, int64_t T, int64_t H, int R
         for (int ks = 0; ks < 8; ++ks)       // D[dv][dk] = sum_c y[c][dv] x_hat[c][dk]
           umma_bf16(acc, desc_advance(a0, ks * 2048), desc_advance(b0, (ks >> 2) * 4096 + (ks & 3) * 32), idesc, ks > 0);
         umma_commit(smem_u32(mma + g));
+        umma_commit(smem_u32(yfree + ys));      // the tile stage of this step may be refilled
       }
       ys = ys == NY - 1 ? 0 : ys + 1;
       __syncwarp();
