@@ -314,7 +314,10 @@ tc_state_kernel(const __grid_constant__ StMaps maps, int64_t T, int64_t H, int R
       if (ok) ok = mbar_wait(smem_u32(egbar + (i & 3)), (uint32_t)((i >> 2) & 1));     // e^G of step i written
       float e[16];
 #pragma unroll
-      for (int j = 0; j < 16; ++j) e[j] = eG[(i & 3) * SL + 16 * cg + j];
+      for (int j4 = 0; j4 < 4; ++j4) {          // 16 consecutive floats, 64-byte aligned: four 16-byte loads
+        const float4 t = *reinterpret_cast<const float4*>(eG + (i & 3) * SL + 16 * cg + 4 * j4);
+        e[4 * j4] = t.x; e[4 * j4 + 1] = t.y; e[4 * j4 + 2] = t.z; e[4 * j4 + 3] = t.w;
+      }
       if (ok) ok = mbar_wait(smem_u32(mma + g), (uint32_t)((i >> 1) & 1));
       tc_fence_after();
       uint32_t r[16];
